@@ -1,0 +1,30 @@
+import importlib
+import pathlib
+import sys
+
+import pytest
+
+ROOT = pathlib.Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+@pytest.fixture(scope="session")
+def golden_dir():
+    return ROOT / "tests" / "golden"
+
+
+@pytest.fixture(scope="session")
+def orc():
+    """The CPU checker (test infrastructure)."""
+    return importlib.import_module("oracle.lkb_oracle")
+
+
+@pytest.fixture(scope="session")
+def lkb():
+    """The product package (directory name carries a hyphen, hence import_module)."""
+    return importlib.import_module("lfm2-ampere_b200")

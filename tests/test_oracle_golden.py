@@ -1,0 +1,92 @@
+"""Pins the CPU checker against the reference's own golden vectors (CPU only)."""
+import numpy as np
+
+
+def _f16(u16):
+    return np.asarray(u16, np.uint16).view(np.float16).astype(np.float32)
+
+
+def test_quant_fixture_known_answers(orc, golden_dir):
+    """ref/quant_fixture.bin: four Q4_0 cases on real weight blocks.
+
+    The stored expected_exact uses fp32 (unrounded) d8 and sum
+    (tests/make_quant_fixture.py:27-40,73-81), so it pins the formula and the
+    integer block sums; the reference's own gate is 5e-3 relative
+    (tests/test_quant.cu:162).  Feeding the checker's integer sums into that
+    fp32-scale formula must reproduce the stored value to float32 resolution.
+    """
+    g = np.load(golden_dir / "quant_q4_cases.npz")
+    assert int(g["ncases"]) == 4
+    for k in range(4):
+        qs, d, x = g[f"c{k}_qs"], g[f"c{k}_d"], g[f"c{k}_x"]
+        nblk = d.size
+        q, d16, s16 = orc.quantize_q8_1(x)
+        # quants: C roundf vs numpy round differ only on exact .5 ties
+        ref_q = g[f"c{k}_ref_q"]
+        diff = np.nonzero(q != ref_q)[0]
+        for i in diff:
+            dd = np.float32(np.max(np.abs(x[i // 32 * 32:i // 32 * 32 + 32]))) / np.float32(127.0)
+            r = np.float32(x[i]) / dd
+            assert abs(abs(float(r)) % 1.0 - 0.5) < 1e-6, "quant mismatch that is not a rounding tie"
+        sumi = orc.block_sumi(qs, q, 1, nblk)[0] if nblk <= 64 else None
+        if diff.size == 0:
+            assert np.array_equal(sumi, g[f"c{k}_ref_sumi"]), "integer block sums differ from the reference recipe"
+        # fp32-scale convention of the fixture, float64 combine
+        d4 = _f16(d).astype(np.float64)
+        d8 = g[f"c{k}_ref_d8"].astype(np.float64)
+        rs = g[f"c{k}_ref_rawsum"].astype(np.float64)
+        val = float(np.sum(d4 * (d8 * sumi.astype(np.float64) - 8.0 * rs)))
+        exp = float(g[f"c{k}_expected_exact"])
+        assert abs(val - exp) <= 2e-7 * max(1.0, abs(exp)), (k, val, exp)
+        # engine convention (fp16-rounded d8 / sum) through the checker's GEMV:
+        y = orc.gemv_q4_0(qs, d, (q, d16, s16), 1, nblk)[0]
+        y64, mag = orc.gemv_q4_0_f64(qs, d, (q, d16, s16), 1, nblk)
+        assert abs(y - y64[0]) <= 1e-5 * mag[0]
+        assert abs(y - exp) <= 5e-3 * abs(exp)          # the reference's own gate
+        assert abs(y - float(g[f"c{k}_expected_fp32"])) <= 5e-2 * abs(exp) + 5e-2
+    # the single-block case: known integer sum
+    q, _, _ = orc.quantize_q8_1(g["c3_x"])
+    assert int(orc.block_sumi(g["c3_qs"], q, 1, 1)[0, 0]) == -1720
+
+
+def test_router_on_real_gate_matrix(orc, golden_dir):
+    """ref/kernel_fixture.bin router: ids exact, weights 1e-5 (tests/test_kernels.cu:212-219)."""
+    g = np.load(golden_dir / "router_fixture.npz")
+    logits = orc.router_dot(g["h"], g["gate"])
+    l64 = g["gate"].astype(np.float64) @ g["h"].astype(np.float64)
+    assert np.max(np.abs(logits - l64)) < 1e-5
+    sel, sig = orc.router_gate(logits, g["bias"])
+    idx, w = orc.router_select(sel, sig)
+    assert idx.tolist() == g["expected_idx"].tolist() == [59, 45, 58, 40]
+    assert np.max(np.abs(w.astype(np.float64) - g["expected_w"])) < 1e-5
+    assert abs(float(w.sum()) - 1.0) < 1e-6
+    assert orc.router_margin(sel) > 1e-3                 # not a near-tie
+
+
+def test_against_reference_numpy_helpers(orc, golden_dir):
+    """tools/ref_forward.py q8_1() and q4_mv_q8() executed from the reference."""
+    g = np.load(golden_dir / "ref_numpy_vectors.npz")
+    for tag, rows, K in (("a", 96, 2048), ("b", 64, 1536), ("c", 32, 256)):
+        bpr = K // 32
+        x = g[f"{tag}_x"]
+        q, d16, s16 = orc.quantize_q8_1(x)
+        assert np.array_equal(_f16(d16), g[f"{tag}_ref_d8"])
+        # the raw sum is order-dependent in fp32: ours is the GPU's butterfly, numpy's is pairwise
+        assert np.all(np.abs(_f16(s16) - g[f"{tag}_ref_sum"]) <= np.maximum(np.abs(g[f"{tag}_ref_sum"]) * 2.0 ** -10, 1e-6))
+        mism = np.nonzero(q != g[f"{tag}_ref_q"].reshape(-1))[0]
+        assert mism.size <= 2                              # only rounding ties may differ
+        y = orc.gemv_q4_0(g[f"{tag}_qs"], g[f"{tag}_d"], (q, d16, s16), rows, bpr)
+        y64, mag = orc.gemv_q4_0_f64(g[f"{tag}_qs"], g[f"{tag}_d"], (q, d16, s16), rows, bpr)
+        assert np.all(np.abs(y - y64) <= 1e-5 * mag)
+        # numpy's answer used its own sum rounding: allow the fp16 step of 8*sum per block
+        slack = 8.0 * np.sum(np.abs(_f16(s16)) * 2.0 ** -10) * np.max(_f16(g[f"{tag}_d"]))
+        assert np.all(np.abs(y - g[f"{tag}_ref_y"]) <= 1e-5 * mag + slack)
+
+
+def test_zero_and_subnormal_blocks(orc):
+    x = np.zeros(64, np.float32)
+    x[32:] = np.linspace(-3e-4, 3e-4, 32, dtype=np.float32)
+    q, d16, s16 = orc.quantize_q8_1(x)
+    assert np.all(q[:32] == 0) and d16[0] == 0 and s16[0] == 0
+    assert np.max(np.abs(q[32:])) == 127 and q.min() >= -127
+    assert 0 < d16[1] < 0x0400                               # fp16 subnormal scale kept, not flushed
