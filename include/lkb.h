@@ -1,0 +1,216 @@
+/*
+ * lkb.h - C ABI of the B200 (sm_100a) Q4_0 x Q8_1 MoE hot path.
+ *
+ * One entry point per kernel (or host launcher) of the reference engine's hot
+ * path.  Each takes the reference kernel's own parameter list -- same order,
+ * same meaning -- followed by the CUDA stream to launch on, and returns an int
+ * status (LKB_OK, or a negative LKB_ERR_* / -cudaError_t) instead of exiting the
+ * process.  Grid and block shapes are chosen inside.  All pointers are DEVICE
+ * pointers owned by the caller; nothing here allocates device memory, blocks the
+ * host or synchronises the stream, so every call may be captured into a CUDA
+ * graph (after lkb_init() has run once for the device).
+ *
+ * "ref:" comments give the reference interface an entry point replaces, as
+ * <file>:<line> relative to the reference repository (Nathan-T-Ray/lfm2-ampere).
+ *
+ * Data formats (identical to the reference's planar pack):
+ *   Q4_0 weights   qs plane: 16 bytes per 32-element block, byte j = element j
+ *                  (low nibble) | element j+16 (high nibble), nibbles unsigned;
+ *                  d plane: one fp16 scale per block.  Row-major [row][bpr];
+ *                  the experts of one tensor are stacked: row = e*rows_per_expert + r.
+ *                  ref: src/quant.cuh:4-9,124-130
+ *   block_q8_1     36 bytes: {fp16 d = amax/127, fp16 s = raw sum, int8 qs[32]}.
+ *                  ref: src/quant.cuh:27-31
+ *   planar Q8_1    lkb_pf_act: qs int8 [rows][kb*32], sc float2 [rows][kb] with
+ *                  .x = float(fp16 d), .y = 8*float(fp16 sum).  ref: src/prefill.cuh:27-36
+ */
+#ifndef LKB_H
+#define LKB_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)   /* the entry points below are the library's whole export list */
+#endif
+
+#define LKB_OK               0
+#define LKB_ERR_SHAPE       -10001   /* a documented shape precondition is violated */
+#define LKB_ERR_NULL        -10002   /* a required pointer is null */
+#define LKB_ERR_UNSUPPORTED -10003   /* a mode of the reference that this build leaves out */
+#define LKB_ERR_NOT_INIT    -10004   /* lkb_init() has not run for the current device */
+#define LKB_ERR_DEVICE      -10005   /* not an sm_100 device */
+#define LKB_ERR_TIMEOUT     -10006   /* a bounded device-side wait gave up (status word set) */
+
+/* Model constants of the path.  ref: src/kernels.cuh:11-24 */
+#define LKB_HIDDEN      2048
+#define LKB_N_EXPERTS   64
+#define LKB_TOP_K       4
+#define LKB_MOE_INTER   1536
+#define LKB_EPS         1e-5f
+#define LKB_TOPK_GUARD  6.103515625e-5f
+#define LKB_MOE_BN      64           /* token tile of the MoE plan.  ref: src/prefill.cuh:72 */
+
+typedef struct CUstream_st * lkb_stream_t;          /* == cudaStream_t */
+
+typedef struct { uint16_t d, s; int8_t qs[32]; } lkb_block_q8_1;   /* 36 bytes */
+
+/* ref: src/kernels.cuh:413-418 (LKNormProd) */
+typedef struct {
+    const float *    w;      /* norm weights to apply, or null: no producer step */
+    float *          h32;    /* raw x*w in fp32 (router input), or null */
+    lkb_block_q8_1 * yq8;    /* quantised RAW activation x*w */
+    float *          ssq;    /* [64] per-block sums of squares of x */
+} lkb_norm_prod_t;
+
+/* ref: src/prefill.cuh:33-36 (PfAct) */
+typedef struct {
+    int8_t * qs;
+    float *  sc;             /* float2 per block */
+} lkb_pf_act;
+
+/* ref: src/prefill.cuh:45-66 (PfGemm); tiles entries are int4 {expert, start, count, 0} */
+typedef struct {
+    const void *   qs[3];        /* uint4 per block */
+    const void *   d[3];         /* fp16 per block */
+    int            seg_end[3];   /* cumulative row ends, multiples of 128 */
+    int            N;            /* output rows (features): multiple of 128 (64 for the SwiGLU form) */
+    int            bpr;          /* 32-element blocks per row, multiple of 8 */
+    long long      exp_stride;   /* blocks per expert, 0 if dense */
+    const int8_t * aqs;          /* activations, row pitch bpr*32 */
+    const float *  asc;          /* float2 [rows][bpr] */
+    int            ntok;         /* dense: token rows */
+    const int *    perm;         /* MoE: slot ids grouped by expert, or null */
+    const int *    tiles;        /* MoE: int4 {expert, start in perm, count, 0} */
+    const int *    ntiles;       /* MoE: device-side tile count */
+    int            a_shift;      /* activation row = slot >> a_shift */
+    const float *  scale;        /* per activation row, or null */
+    float *        out;
+    int            out_ld;
+    int            add;          /* 1: out += result */
+    int8_t *       oqs;          /* SwiGLU form only: planar Q8_1 output */
+    float *        osc;
+    int            okb;
+} lkb_pf_gemm;
+
+/* ------------------------------------------------------------------ set-up */
+/* One-time per device: checks for sm_100, records the SM count, sets the
+ * dynamic shared-memory limits of the kernels.  Not part of the reference
+ * (its launchers do this lazily behind function-local statics,
+ * ref: src/prefill.cu:705-709); call it before any stream capture. */
+int lkb_init(int device);
+const char * lkb_error_string(int status);
+int lkb_sm_count(void);
+/* 1: launch the decode kernels with programmatic dependent launch so that a
+ * kernel's weight prefetch overlaps its predecessor's tail.  Default 0. */
+int lkb_set_pdl(int enable);
+
+/* ------------------------------------------------- activation quantisers */
+/* ref: src/kernels.cuh:73-74  k_quantize_q8_1<<<nblocks,32>>> */
+int lkb_quantize_q8_1(const float * x, lkb_block_q8_1 * y, int nblocks, lkb_stream_t st);
+/* ref: src/kernels.cuh:66-68  k_rmsnorm_q8_1<<<1,256>>>; n must be 2048; y16 is fp16 */
+int lkb_rmsnorm_q8_1(const float * x, const float * w, int n, float eps, float * y32,
+                     void * y16, lkb_block_q8_1 * yq8, lkb_stream_t st);
+/* The stand-alone producer of the scale-carrying norm split: quantise x*w, emit
+ * ssq[64] (and h32).  ref: src/kernels.cuh:421-431 (lk_norm_prod_warp, called by
+ * k_moe_accum4 with a zero contribution); n must be a multiple of 32. */
+int lkb_norm_produce(const float * x, int n, const lkb_norm_prod_t * np, lkb_stream_t st);
+
+/* ------------------------------------------------------------ decode GEMVs */
+/* ref: src/kernels.cuh:449-452  k_gemv_q4_0 */
+int lkb_gemv_q4_0(const void * qs, const void * d, const lkb_block_q8_1 * xq, int out_rows, int bpr,
+                  float * y, int add_residual, const float * ssq, float eps, lkb_stream_t st);
+/* ref: src/kernels.cuh:457-460  k_gemv_q4_0_prod; out_rows % 32 == 0 */
+int lkb_gemv_q4_0_prod(const void * qs, const void * d, const lkb_block_q8_1 * xq, int out_rows, int bpr,
+                       float * y, int add_residual, const lkb_norm_prod_t * np, lkb_stream_t st);
+/* ref: src/kernels.cuh:704-711  k_gemv_q4_0_3 */
+int lkb_gemv_q4_0_3(const void * qs0, const void * d0, int rows0, float * y0,
+                    const void * qs1, const void * d1, int rows1, float * y1,
+                    const void * qs2, const void * d2, int rows2, float * y2,
+                    const lkb_block_q8_1 * xq, int bpr, const float * ssq, float eps, lkb_stream_t st);
+/* ref: src/kernels.cuh:713-722  k_gemv_q4_0_exp2.  The router-in-prologue group
+ * (sel, sig, idx_out, w_out; off by default in the reference) must be null. */
+int lkb_gemv_q4_0_exp2(const void * qs_a, const void * d_a, const void * qs_b, const void * d_b,
+                       const lkb_block_q8_1 * xq, int out_rows, int bpr, int rows_per_expert, int xq_stride,
+                       const int * d_idx, const float * sel, const float * sig, int * idx_out, float * w_out,
+                       float * y_a, float * y_b, const float * ssq, float eps, lkb_stream_t st);
+/* ref: src/kernels.cuh:724-731  k_gemv_q4_0_exp */
+int lkb_gemv_q4_0_exp(const void * qs, const void * d, const lkb_block_q8_1 * xq, int out_rows, int bpr,
+                      int rows_per_expert, int xq_stride, const int * d_idx, float * y, lkb_stream_t st);
+/* ref: src/kernels.cuh:476-481  k_swiglu (n % 32 == 0).  pf_* describe the
+ * down-projection weights to pull towards L2 while the activation is built. */
+int lkb_swiglu(const float * gate, const float * up, int n, float * out, lkb_block_q8_1 * yq8,
+               const void * pf_qs, const int * pf_idx, int pf_rows_per_expert, int pf_bpr, long pf_bytes,
+               lkb_stream_t st);
+/* ref: src/kernels.cuh:733-734  k_moe_accum4 */
+int lkb_moe_accum4(float * dst, const float * down4, const float * d_w, int n, const lkb_norm_prod_t * np,
+                   lkb_stream_t st);
+/* ref: src/kernels.cuh:735-739  k_moe_down_accum; out_rows % 32 == 0 */
+int lkb_moe_down_accum(const void * qs, const void * d, const lkb_block_q8_1 * xq, int out_rows, int bpr,
+                       int rows_per_expert, int xq_stride, const int * d_idx, const float * d_w,
+                       float * dst, const lkb_norm_prod_t * np, lkb_stream_t st);
+
+/* ------------------------------------------------------------------ router */
+/* ref: src/kernels.cuh:543-547  k_router_dot<<<64,32>>> (sel/sig may be null) */
+int lkb_router_dot(const float * h, const float * gate_inp, float * logits, const float * bias,
+                   float * sel, float * sig, const float * ssq, float eps, lkb_stream_t st);
+/* ref: src/kernels.cuh:548-550  k_router_top4<<<1,64>>> */
+int lkb_router_top4(const float * logits, const float * bias, int * idx_out, float * w_out, lkb_stream_t st);
+/* Softmax gate of the synthetic configurations: p = softmax(logits), ranking by
+ * p + bias (bias may be null), weights p renormalised over the top four.  No
+ * counterpart in the reference (its gate is the sigmoid above). */
+int lkb_router_top4_softmax(const float * logits, const float * bias, int * idx_out, float * w_out,
+                            lkb_stream_t st);
+
+/* ------------------------------------------------------------ debug taps */
+/* Integer block sums S[row][blk] = sum_i nibble_i * q_i of one activation row
+ * against a [rows][bpr] matrix.  No counterpart in the reference; it exposes the
+ * int32 value inside dot_q4_0_q8_1 (ref: src/quant.cuh:141-151) for parity tests. */
+int lkb_block_sumi(const void * qs, const lkb_block_q8_1 * xq, int rows, int bpr, int32_t * out,
+                   lkb_stream_t st);
+
+/* ----------------------------------------------------------------- prefill */
+/* ref: src/prefill.cuh:81-82  k_pf_norm<<<m,256>>> */
+int lkb_pf_norm(const float * X, const float * w, int plain, lkb_pf_act a, float * inv_out, float * h32,
+                int m, lkb_stream_t st);
+/* ref: src/prefill.cuh:107  k_pf_quant_rows */
+int lkb_pf_quant_rows(const float * X, int ld, int kb, lkb_pf_act a, int rows, lkb_stream_t st);
+/* ref: src/prefill.cuh:108  k_pf_swiglu */
+int lkb_pf_swiglu(const float * Y, int ld, int up_off, int kb, lkb_pf_act a, int rows, lkb_stream_t st);
+/* ref: src/prefill.cuh:109-114  k_pf_router / k_pf_router_small.  The engine
+ * picks the small form for m <= 256 (ref: src/engine.cu:1170-1176); so does this. */
+int lkb_pf_router(const float * H, int m, const float * Wr, const float * bias, const float * inv,
+                  float * sel, float * sig, lkb_stream_t st);
+int lkb_pf_router_small(const float * H, int m, const float * Wr, const float * bias, const float * inv,
+                        float * sel, float * sig, lkb_stream_t st);
+/* ref: src/prefill.cuh:115-116  k_pf_select */
+int lkb_pf_select(const float * sel, const float * sig, int m, int * idx, float * w, lkb_stream_t st);
+/* ref: src/prefill.cuh:117-122  k_pf_moe_count / _plan / _scatter.  cnt must be
+ * zero on entry to count (the engine memsets it, ref: src/engine.cu:1182). */
+int lkb_pf_moe_count(const int * idx, int n, int * cnt, lkb_stream_t st);
+int lkb_pf_moe_plan(const int * cnt, int * off, int * tiles, int * ntiles, lkb_stream_t st);
+int lkb_pf_moe_scatter(const int * idx, int n, const int * off, int * perm, lkb_stream_t st);
+/* ref: src/prefill.cuh:69-71  pf_gemm_dense / pf_gemm_moe / pf_gemm_swiglu */
+int lkb_pf_gemm_dense(const lkb_pf_gemm * g, lkb_stream_t st);
+int lkb_pf_gemm_moe(const lkb_pf_gemm * g, int max_tiles, lkb_stream_t st);
+int lkb_pf_gemm_swiglu(const lkb_pf_gemm * g, int max_tiles, lkb_stream_t st);
+/* Kernel-configuration selector of the three launchers above: -1 (default) the
+ * tensor-core form wherever it covers the shape, 0 the CUDA-core form, 1 the
+ * tensor-core form or an error.  Also read once from the environment variable
+ * LKB_PF_CFG by lkb_init().  ref: src/prefill.cu:813-848 (LK_PF_CFG_DENSE/MOE/SWIGLU) */
+int lkb_pf_gemm_config(int cfg);
+/* ref: src/prefill.cuh:123-127  k_pf_moe_combine / k_pf_moe_combine_norm / k_pf_pack_q8_1 */
+int lkb_pf_moe_combine(float * X, const float * D, const float * w, int m, lkb_stream_t st);
+int lkb_pf_moe_combine_norm(float * X, const float * D, const float * w, const float * nw, lkb_pf_act a,
+                            float * inv_out, int m, lkb_stream_t st);
+int lkb_pf_pack_q8_1(lkb_pf_act a, int t, lkb_block_q8_1 * y, lkb_stream_t st);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* LKB_H */

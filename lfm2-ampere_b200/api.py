@@ -1,0 +1,213 @@
+"""Thin torch-tensor wrappers over the C ABI, named after the reference's kernels.
+
+Each function takes the reference kernel's arguments (device tensors instead of
+raw pointers), launches on torch's current CUDA stream through the C entry point
+and raises LkbError on a non-zero status.  Nothing here computes anything.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import NormProd, PfAct, PfGemm, check, lib
+
+__all__ = [
+    "ptr", "stream", "norm_prod", "pf_act", "make_pf_gemm",
+    "k_quantize_q8_1", "k_rmsnorm_q8_1", "norm_produce", "k_gemv_q4_0", "k_gemv_q4_0_prod", "k_gemv_q4_0_3",
+    "k_gemv_q4_0_exp2", "k_gemv_q4_0_exp", "k_swiglu", "k_moe_accum4", "k_moe_down_accum", "k_router_dot",
+    "k_router_top4", "router_top4_softmax", "block_sumi", "k_pf_norm", "k_pf_quant_rows", "k_pf_swiglu",
+    "k_pf_router", "k_pf_router_small", "k_pf_select", "k_pf_moe_count", "k_pf_moe_plan", "k_pf_moe_scatter",
+    "pf_gemm_dense", "pf_gemm_moe", "pf_gemm_swiglu", "k_pf_moe_combine", "k_pf_moe_combine_norm",
+    "k_pf_pack_q8_1", "set_pdl", "pf_gemm_config", "sm_count",
+]
+
+
+def ptr(t):
+    if t is None:
+        return None
+    assert t.is_cuda and t.is_contiguous(), "device-resident contiguous tensors only"
+    return t.data_ptr()
+
+
+def stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def norm_prod(w=None, h32=None, yq8=None, ssq=None):
+    """lkb_norm_prod_t from tensors (ref: LKNormProd)."""
+    return NormProd(ptr(w), ptr(h32), ptr(yq8), ptr(ssq))
+
+
+def pf_act(qs, sc):
+    return PfAct(ptr(qs), ptr(sc))
+
+
+def _np(np_):
+    return None if np_ is None else C.byref(np_)
+
+
+def set_pdl(on):
+    check(lib.lkb_set_pdl(1 if on else 0))
+
+
+def pf_gemm_config(cfg):
+    check(lib.lkb_pf_gemm_config(int(cfg)))
+
+
+def sm_count():
+    return lib.lkb_sm_count()
+
+
+# ------------------------------------------------------------------ decode --
+def k_quantize_q8_1(x, y, nblocks):
+    check(lib.lkb_quantize_q8_1(ptr(x), ptr(y), nblocks, stream()), "k_quantize_q8_1")
+
+
+def k_rmsnorm_q8_1(x, w, n, eps, y32, y16, yq8):
+    check(lib.lkb_rmsnorm_q8_1(ptr(x), ptr(w), n, eps, ptr(y32), ptr(y16), ptr(yq8), stream()), "k_rmsnorm_q8_1")
+
+
+def norm_produce(x, n, np_):
+    check(lib.lkb_norm_produce(ptr(x), n, C.byref(np_), stream()), "norm_produce")
+
+
+def k_gemv_q4_0(qs, d, xq, out_rows, bpr, y, add_residual=0, ssq=None, eps=1e-5):
+    check(lib.lkb_gemv_q4_0(ptr(qs), ptr(d), ptr(xq), out_rows, bpr, ptr(y), add_residual, ptr(ssq), eps, stream()),
+          "k_gemv_q4_0")
+
+
+def k_gemv_q4_0_prod(qs, d, xq, out_rows, bpr, y, add_residual, np_):
+    check(lib.lkb_gemv_q4_0_prod(ptr(qs), ptr(d), ptr(xq), out_rows, bpr, ptr(y), add_residual, _np(np_), stream()),
+          "k_gemv_q4_0_prod")
+
+
+def k_gemv_q4_0_3(qs0, d0, rows0, y0, qs1, d1, rows1, y1, qs2, d2, rows2, y2, xq, bpr, ssq=None, eps=1e-5):
+    check(lib.lkb_gemv_q4_0_3(ptr(qs0), ptr(d0), rows0, ptr(y0), ptr(qs1), ptr(d1), rows1, ptr(y1),
+                              ptr(qs2), ptr(d2), rows2, ptr(y2), ptr(xq), bpr, ptr(ssq), eps, stream()),
+          "k_gemv_q4_0_3")
+
+
+def k_gemv_q4_0_exp2(qs_a, d_a, qs_b, d_b, xq, out_rows, bpr, rows_per_expert, xq_stride, d_idx, y_a, y_b,
+                     ssq=None, eps=1e-5, sel=None, sig=None, idx_out=None, w_out=None):
+    check(lib.lkb_gemv_q4_0_exp2(ptr(qs_a), ptr(d_a), ptr(qs_b), ptr(d_b), ptr(xq), out_rows, bpr, rows_per_expert,
+                                 xq_stride, ptr(d_idx), ptr(sel), ptr(sig), ptr(idx_out), ptr(w_out),
+                                 ptr(y_a), ptr(y_b), ptr(ssq), eps, stream()), "k_gemv_q4_0_exp2")
+
+
+def k_gemv_q4_0_exp(qs, d, xq, out_rows, bpr, rows_per_expert, xq_stride, d_idx, y):
+    check(lib.lkb_gemv_q4_0_exp(ptr(qs), ptr(d), ptr(xq), out_rows, bpr, rows_per_expert, xq_stride, ptr(d_idx),
+                                ptr(y), stream()), "k_gemv_q4_0_exp")
+
+
+def k_swiglu(gate, up, n, out, yq8, pf_qs=None, pf_idx=None, pf_rows_per_expert=0, pf_bpr=0, pf_bytes=0):
+    check(lib.lkb_swiglu(ptr(gate), ptr(up), n, ptr(out), ptr(yq8), ptr(pf_qs), ptr(pf_idx), pf_rows_per_expert,
+                         pf_bpr, pf_bytes, stream()), "k_swiglu")
+
+
+def k_moe_accum4(dst, down4, d_w, n, np_=None):
+    check(lib.lkb_moe_accum4(ptr(dst), ptr(down4), ptr(d_w), n, _np(np_), stream()), "k_moe_accum4")
+
+
+def k_moe_down_accum(qs, d, xq, out_rows, bpr, rows_per_expert, xq_stride, d_idx, d_w, dst, np_=None):
+    check(lib.lkb_moe_down_accum(ptr(qs), ptr(d), ptr(xq), out_rows, bpr, rows_per_expert, xq_stride, ptr(d_idx),
+                                 ptr(d_w), ptr(dst), _np(np_), stream()), "k_moe_down_accum")
+
+
+def k_router_dot(h, gate_inp, logits, bias=None, sel=None, sig=None, ssq=None, eps=1e-5):
+    check(lib.lkb_router_dot(ptr(h), ptr(gate_inp), ptr(logits), ptr(bias), ptr(sel), ptr(sig), ptr(ssq), eps,
+                             stream()), "k_router_dot")
+
+
+def k_router_top4(logits, bias, idx_out, w_out):
+    check(lib.lkb_router_top4(ptr(logits), ptr(bias), ptr(idx_out), ptr(w_out), stream()), "k_router_top4")
+
+
+def router_top4_softmax(logits, bias, idx_out, w_out):
+    check(lib.lkb_router_top4_softmax(ptr(logits), ptr(bias), ptr(idx_out), ptr(w_out), stream()),
+          "router_top4_softmax")
+
+
+def block_sumi(qs, xq, rows, bpr, out):
+    check(lib.lkb_block_sumi(ptr(qs), ptr(xq), rows, bpr, ptr(out), stream()), "block_sumi")
+
+
+# ----------------------------------------------------------------- prefill --
+def k_pf_norm(X, w, plain, a, inv_out, h32, m):
+    check(lib.lkb_pf_norm(ptr(X), ptr(w), plain, a, ptr(inv_out), ptr(h32), m, stream()), "k_pf_norm")
+
+
+def k_pf_quant_rows(X, ld, kb, a, rows):
+    check(lib.lkb_pf_quant_rows(ptr(X), ld, kb, a, rows, stream()), "k_pf_quant_rows")
+
+
+def k_pf_swiglu(Y, ld, up_off, kb, a, rows):
+    check(lib.lkb_pf_swiglu(ptr(Y), ld, up_off, kb, a, rows, stream()), "k_pf_swiglu")
+
+
+def k_pf_router(H, m, Wr, bias, inv, sel, sig):
+    check(lib.lkb_pf_router(ptr(H), m, ptr(Wr), ptr(bias), ptr(inv), ptr(sel), ptr(sig), stream()), "k_pf_router")
+
+
+def k_pf_router_small(H, m, Wr, bias, inv, sel, sig):
+    check(lib.lkb_pf_router_small(ptr(H), m, ptr(Wr), ptr(bias), ptr(inv), ptr(sel), ptr(sig), stream()),
+          "k_pf_router_small")
+
+
+def k_pf_select(sel, sig, m, idx, w):
+    check(lib.lkb_pf_select(ptr(sel), ptr(sig), m, ptr(idx), ptr(w), stream()), "k_pf_select")
+
+
+def k_pf_moe_count(idx, n, cnt):
+    check(lib.lkb_pf_moe_count(ptr(idx), n, ptr(cnt), stream()), "k_pf_moe_count")
+
+
+def k_pf_moe_plan(cnt, off, tiles, ntiles):
+    check(lib.lkb_pf_moe_plan(ptr(cnt), ptr(off), ptr(tiles), ptr(ntiles), stream()), "k_pf_moe_plan")
+
+
+def k_pf_moe_scatter(idx, n, off, perm):
+    check(lib.lkb_pf_moe_scatter(ptr(idx), n, ptr(off), ptr(perm), stream()), "k_pf_moe_scatter")
+
+
+def make_pf_gemm(segs, seg_end, N, bpr, aqs, asc, *, ntok=0, exp_stride=0, perm=None, tiles=None, ntiles=None,
+                 a_shift=0, scale=None, out=None, out_ld=0, add=0, oqs=None, osc=None, okb=0):
+    """lkb_pf_gemm from tensors; segs = [(qs, d), ...] (1 to 3 stacked weight tensors)."""
+    g = PfGemm()
+    for i in range(3):
+        q, d = segs[min(i, len(segs) - 1)]
+        g.qs[i] = ptr(q)
+        g.d[i] = ptr(d)
+        g.seg_end[i] = seg_end[min(i, len(seg_end) - 1)]
+    g.N, g.bpr, g.exp_stride = N, bpr, exp_stride
+    g.aqs, g.asc, g.ntok = ptr(aqs), ptr(asc), ntok
+    g.perm, g.tiles, g.ntiles = ptr(perm), ptr(tiles), ptr(ntiles)
+    g.a_shift, g.scale = a_shift, ptr(scale)
+    g.out, g.out_ld, g.add = ptr(out), out_ld, add
+    g.oqs, g.osc, g.okb = ptr(oqs), ptr(osc), okb
+    return g
+
+
+def pf_gemm_dense(g):
+    check(lib.lkb_pf_gemm_dense(C.byref(g), stream()), "pf_gemm_dense")
+
+
+def pf_gemm_moe(g, max_tiles):
+    check(lib.lkb_pf_gemm_moe(C.byref(g), max_tiles, stream()), "pf_gemm_moe")
+
+
+def pf_gemm_swiglu(g, max_tiles):
+    check(lib.lkb_pf_gemm_swiglu(C.byref(g), max_tiles, stream()), "pf_gemm_swiglu")
+
+
+def k_pf_moe_combine(X, D, w, m):
+    check(lib.lkb_pf_moe_combine(ptr(X), ptr(D), ptr(w), m, stream()), "k_pf_moe_combine")
+
+
+def k_pf_moe_combine_norm(X, D, w, nw, a, inv_out, m):
+    check(lib.lkb_pf_moe_combine_norm(ptr(X), ptr(D), ptr(w), ptr(nw), a, ptr(inv_out), m, stream()),
+          "k_pf_moe_combine_norm")
+
+
+def k_pf_pack_q8_1(a, t, y):
+    check(lib.lkb_pf_pack_q8_1(a, t, ptr(y), stream()), "k_pf_pack_q8_1")

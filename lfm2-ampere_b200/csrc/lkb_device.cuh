@@ -1,0 +1,158 @@
+// lkb_device.cuh - device primitives shared by the decode and prefill kernels.
+//
+// Arithmetic contract.  Every fused multiply-add is spelled fmaf() and every
+// unfused product / sum uses __fmul_rn / __fadd_rn, so the rounding sequence is
+// the one written here whatever the compiler's contraction setting.  The
+// sequences are the ones the reference engine evaluates (file:line cited per
+// function, relative to the reference repository), so integer results, fp16
+// scale fields and -- wherever no approximate intrinsic is involved -- the fp32
+// results are bit-identical to the reference's kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include "../../include/lkb.h"
+
+#define LKB_FULL 0xffffffffu
+
+struct __align__(4) lkb_q8blk {            // == lkb_block_q8_1, device view
+    __half2 ds;                            // .x = d, .y = raw sum
+    int8_t  qs[32];
+};
+static_assert(sizeof(lkb_q8blk) == 36, "block_q8_1 is 36 bytes");
+static_assert(sizeof(lkb_block_q8_1) == 36, "block_q8_1 is 36 bytes");
+
+// xor-butterfly sum; every lane ends with the same value.  ref: src/kernels.cuh:28-32
+__device__ __forceinline__ float lkb_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(LKB_FULL, v, o));
+    return v;
+}
+
+// silu with the fast exponential, as the reference.  ref: src/kernels.cuh:33
+// (fast __expf, IEEE add and divide).
+__device__ __forceinline__ float lkb_silu(float v) { return __fdiv_rn(v, __fadd_rn(1.0f, __expf(-v))); }
+
+// Q8_1 quantiser, one warp per 32-element block, one element per lane.
+// ref: src/quant.cuh:106-121.  Returns q for this lane; lane 0 gets (d, sum).
+__device__ __forceinline__ int lkb_quant_lane(float xi, float & d_out, float & sum_out) {
+    const unsigned am = __reduce_max_sync(LKB_FULL, __float_as_uint(fabsf(xi)));
+    sum_out = lkb_warp_sum(xi);
+    const float d = __fdiv_rn(__uint_as_float(am), 127.0f);
+    d_out = d;
+    return (am == 0u) ? 0 : (int) roundf(__fdiv_rn(xi, d));
+}
+
+__device__ __forceinline__ void lkb_quant_store(float xi, lkb_q8blk * __restrict__ y, int lane) {
+    float d, s;
+    const int q = lkb_quant_lane(xi, d, s);
+    y->qs[lane] = (int8_t) q;
+    if (lane == 0) y->ds = __floats2half2_rn(d, s);
+}
+
+// Planar twin.  ref: src/prefill.cu:90-103
+__device__ __forceinline__ void lkb_quant_store_planar(float xi, int8_t * __restrict__ qs,
+                                                       float2 * __restrict__ sc, int lane) {
+    float d, s;
+    const int q = lkb_quant_lane(xi, d, s);
+    qs[lane] = (int8_t) q;
+    if (lane == 0) {
+        const __half2 ds = __floats2half2_rn(d, s);
+        *sc = make_float2(__low2float(ds), __fmul_rn(8.0f, __high2float(ds)));
+    }
+}
+
+// Producer of the scale-carrying norm split: quantise RAW u = x*w, emit the
+// block's sum of squares of x.  ref: src/kernels.cuh:421-431
+__device__ __forceinline__ void lkb_norm_prod_warp(float xv, float uv, int lane,
+                                                   lkb_q8blk * __restrict__ yq8,
+                                                   float * __restrict__ ssq, int b) {
+    lkb_quant_store(uv, yq8 + b, lane);
+    const float sq = lkb_warp_sum(__fmul_rn(xv, xv));
+    if (lane == 0) ssq[b] = sq;
+}
+
+// Consumer: inv = rsqrt(sum(ssq)/2048 + eps) from 64 partials.  ref: src/kernels.cuh:441-447
+__device__ __forceinline__ float lkb_norm_inv(const float * __restrict__ ssq, int lane, float eps) {
+    const float s = lkb_warp_sum(__fadd_rn(ssq[lane], ssq[lane + 32]));
+    return rsqrtf(fmaf(s, 1.0f / (float) LKB_HIDDEN, eps));
+}
+
+// Integer block sum: 16 weight bytes (unsigned nibbles) against 32 int8.
+// ref: src/quant.cuh:141-151
+__device__ __forceinline__ int lkb_sumi(const uint4 q, const int (&x)[8]) {
+    int s = 0;
+    s = __dp4a((int) (q.x & 0x0F0F0F0Fu), x[0], s);  s = __dp4a((int) ((q.x >> 4) & 0x0F0F0F0Fu), x[4], s);
+    s = __dp4a((int) (q.y & 0x0F0F0F0Fu), x[1], s);  s = __dp4a((int) ((q.y >> 4) & 0x0F0F0F0Fu), x[5], s);
+    s = __dp4a((int) (q.z & 0x0F0F0F0Fu), x[2], s);  s = __dp4a((int) ((q.z >> 4) & 0x0F0F0F0Fu), x[6], s);
+    s = __dp4a((int) (q.w & 0x0F0F0F0Fu), x[3], s);  s = __dp4a((int) ((q.w >> 4) & 0x0F0F0F0Fu), x[7], s);
+    return s;
+}
+
+// acc + d4*(d8*sumi - 8*sum): inner = fma(d8, float(sumi), -8sum), acc' = fma(d4, inner, acc).
+// ref: src/quant.cuh:154-157; src/prefill.cu:391-399
+__device__ __forceinline__ float lkb_block_acc(float d4, float d8, int sumi, float sum8, float acc) {
+    return fmaf(d4, fmaf(d8, (float) sumi, -sum8), acc);
+}
+
+// Streaming 128-bit load that does not allocate in L1 (weights are read once).
+__device__ __forceinline__ uint4 lkb_ldg_stream(const uint4 * p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ unsigned short lkb_ldg_stream_u16(const __half * p) {
+    unsigned short v;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float lkb_h2f(unsigned short bits) {
+    return __half2float(__ushort_as_half(bits));
+}
+
+// Programmatic dependent launch hooks (no-ops when the launch carries no
+// programmatic dependency).
+__device__ __forceinline__ void lkb_pdl_wait()    { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void lkb_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Top-4 of 64 with the reference's tie rule (greater value wins, equal value ->
+// lower index), then w_k = sig[idx_k] / max(sum_k, guard).  One warp; every lane
+// ends with the full result.  ref: src/kernels.cuh:515-541
+__device__ __forceinline__ void lkb_router_select(const float * __restrict__ sel,
+                                                  const float * __restrict__ sig,
+                                                  int lane, int * ord, float * wv) {
+    float v0 = sel[lane], v1 = sel[lane + 32];
+    const int i0 = lane, i1 = lane + 32;
+#pragma unroll
+    for (int r = 0; r < LKB_TOP_K; ++r) {
+        float mv = (v0 >= v1) ? v0 : v1;
+        int   mi = (v0 >= v1) ? i0 : i1;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(LKB_FULL, mv, o);
+            const int   oi = __shfl_xor_sync(LKB_FULL, mi, o);
+            if (ov > mv || (ov == mv && oi < mi)) { mv = ov; mi = oi; }
+        }
+        ord[r] = mi;
+        if (i0 == mi) v0 = -1e30f;
+        if (i1 == mi) v1 = -1e30f;
+    }
+    float wsum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < LKB_TOP_K; ++k) { wv[k] = sig[ord[k]]; wsum = __fadd_rn(wsum, wv[k]); }
+    if (wsum < LKB_TOPK_GUARD) wsum = LKB_TOPK_GUARD;
+#pragma unroll
+    for (int k = 0; k < LKB_TOP_K; ++k) wv[k] = __fdiv_rn(wv[k], wsum);
+}
+
+// ---- host-side plumbing shared by the translation units ---------------------
+struct lkb_ctx {
+    int  inited;
+    int  device;
+    int  sm_count;
+    int  pdl;
+};
+lkb_ctx & lkb_context();
+int lkb_check_launch();        // cudaGetLastError -> status
+int lkb_prefill_init();        // per-device attributes of the prefill kernels

@@ -1,0 +1,610 @@
+// lkb_prefill.cu - batched-prefill kernels around the grouped GEMM (sm_100a):
+// per-token RMSNorm -> planar Q8_1, row quantiser, SwiGLU quantiser, the batched
+// router, top-4 selection, the deterministic expert count / tile plan / scatter,
+// the rank-order combine, and a CUDA-core (dp4a) form of the Q4_0 x Q8_1 GEMM that
+// serves as the always-available configuration (the tensor-core form lives in
+// lkb_gemm_tc.cu).  Each kernel evaluates the per-token formula of its decode
+// twin, so per-token results are bit-identical to the decode kernels.
+#include "lkb_device.cuh"
+
+#define LKB_REQUIRE_INIT() do { if (!lkb_context().inited) return LKB_ERR_NOT_INIT; } while (0)
+
+// ---------------------------------------------------------------------------
+// Per-token norm.  grid m x 256.  ref: src/prefill.cu:871-932
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_pf_norm(const float * __restrict__ X, const float * __restrict__ w, int plain,
+                                                 int8_t * __restrict__ aqs, float2 * __restrict__ asc,
+                                                 float * __restrict__ inv_out, float * __restrict__ h32) {
+    const int t = blockIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const float * x = X + (size_t) t * LKB_HIDDEN;
+    int8_t * q = aqs + (size_t) t * LKB_HIDDEN;
+    float2 * s = asc + (size_t) t * (LKB_HIDDEN / 32);
+    __shared__ float s_sq[256];
+    if (plain) {
+        float xv[8], wv[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { xv[j] = x[tid + j * 256]; wv[j] = w[tid + j * 256]; }
+        float sq = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sq = fmaf(xv[j], xv[j], sq);
+        s_sq[tid] = sq;
+        __syncthreads();
+#pragma unroll
+        for (int o = 128; o > 16; o >>= 1) {
+            if (tid < o) s_sq[tid] = __fadd_rn(s_sq[tid], s_sq[tid + o]);
+            __syncthreads();
+        }
+        if (tid < 32) {
+            const float v = lkb_warp_sum(s_sq[tid]);
+            if (tid == 0) s_sq[0] = v;
+        }
+        __syncthreads();
+        const float inv = rsqrtf(fmaf(s_sq[0], 1.0f / 2048.0f, LKB_EPS));
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float tv = __fmul_rn(__fmul_rn(xv[j], inv), wv[j]);
+            const int b = warp + 8 * j;
+            lkb_quant_store_planar(tv, q + b * 32, s + b, lane);
+        }
+        if (tid == 0) inv_out[t] = 1.0f;
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int b = warp + 8 * j;
+        const int i = b * 32 + lane;
+        const float xv = x[i];
+        const float uv = __fmul_rn(xv, w[i]);
+        if (h32) h32[(size_t) t * LKB_HIDDEN + i] = uv;
+        lkb_quant_store_planar(uv, q + b * 32, s + b, lane);
+        const float sq = lkb_warp_sum(__fmul_rn(xv, xv));
+        if (lane == 0) s_sq[b] = sq;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const float sv = lkb_warp_sum(__fadd_rn(s_sq[lane], s_sq[lane + 32]));
+        if (lane == 0) inv_out[t] = rsqrtf(fmaf(sv, 1.0f / (float) LKB_HIDDEN, LKB_EPS));
+    }
+}
+
+// grid (rows, ceil(kb/8)) x 256.  ref: src/prefill.cu:1574-1581
+__global__ void __launch_bounds__(256) k_pf_quant_rows(const float * __restrict__ X, int ld, int kb,
+                                                       int8_t * __restrict__ aqs, float2 * __restrict__ asc) {
+    const int r = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.y * 8 + warp;
+    if (b >= kb) return;
+    const float v = X[(size_t) r * ld + b * 32 + lane];
+    lkb_quant_store_planar(v, aqs + (size_t) r * kb * 32 + b * 32, asc + (size_t) r * kb + b, lane);
+}
+
+// ref: src/prefill.cu:1584-1594
+__global__ void __launch_bounds__(256) k_pf_swiglu(const float * __restrict__ Y, int ld, int up_off, int kb,
+                                                   int8_t * __restrict__ aqs, float2 * __restrict__ asc) {
+    const int r = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.y * 8 + warp;
+    if (b >= kb) return;
+    const int i = b * 32 + lane;
+    const float * y = Y + (size_t) r * ld;
+    const float v = __fmul_rn(lkb_silu(y[i]), y[up_off + i]);
+    lkb_quant_store_planar(v, aqs + (size_t) r * kb * 32 + b * 32, asc + (size_t) r * kb + b, lane);
+}
+
+// ---------------------------------------------------------------------------
+// Router.  Small form: one warp per (expert, token), the decode router's
+// arithmetic verbatim.  ref: src/prefill.cu:1668-1693
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(32) k_pf_router_small(const float * __restrict__ H, const float * __restrict__ Wr,
+                                                        const float * __restrict__ bias, const float * __restrict__ inv,
+                                                        float * __restrict__ sel, float * __restrict__ sig) {
+    const int e = blockIdx.x, t = blockIdx.y, lane = threadIdx.x;
+    const float * h = H + (size_t) t * LKB_HIDDEN;
+    const float * row = Wr + (size_t) e * LKB_HIDDEN;
+    float acc = 0.0f;
+#pragma unroll 16
+    for (int j = 0; j < LKB_HIDDEN / 32; ++j) acc = fmaf(row[j * 32 + lane], h[j * 32 + lane], acc);
+    acc = lkb_warp_sum(acc);
+    if (lane == 0) {
+        const float l = __fmul_rn(acc, inv[t]);
+        const float gv = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-l)));
+        sig[(size_t) t * 64 + e] = gv;
+        sel[(size_t) t * 64 + e] = __fadd_rn(gv, bias[e]);
+    }
+}
+
+// Tiled form: CTA = 32 tokens x 64 experts, thread = 2 tokens x 4 experts, K
+// staged 32 at a time.  Each (token, expert) logit is one FMA chain over
+// k = 0..2047 ascending.  ref: src/prefill.cu:1606-1666 (same per-logit order)
+#define LKB_RT_K 32
+__global__ void __launch_bounds__(256) k_pf_router(const float * __restrict__ H, int m, const float * __restrict__ Wr,
+                                                   const float * __restrict__ bias, const float * __restrict__ inv,
+                                                   float * __restrict__ sel, float * __restrict__ sig) {
+    __shared__ __align__(16) float sH[LKB_RT_K][34];      // [k][token]
+    __shared__ __align__(16) float sW[LKB_RT_K][68];      // [k][expert]
+    const int tid = threadIdx.x;
+    const int te = tid & 15, tt = tid >> 4;               // experts 4te.., tokens 2tt..
+    const int t0 = blockIdx.x * 32;
+    float acc[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    for (int k0 = 0; k0 < LKB_HIDDEN; k0 += LKB_RT_K) {
+#pragma unroll
+        for (int q = 0; q < (32 * LKB_RT_K) / 256; ++q) {
+            const int i = tid + q * 256;
+            const int r = i / LKB_RT_K, c = i % LKB_RT_K;
+            const int tk = t0 + r;
+            sH[c][r] = (tk < m) ? H[(size_t) tk * LKB_HIDDEN + k0 + c] : 0.0f;
+        }
+#pragma unroll
+        for (int q = 0; q < (64 * LKB_RT_K) / 256; ++q) {
+            const int i = tid + q * 256;
+            const int r = i / LKB_RT_K, c = i % LKB_RT_K;
+            sW[c][r] = Wr[(size_t) r * LKB_HIDDEN + k0 + c];
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int c = 0; c < LKB_RT_K; ++c) {
+            const float2 h = *reinterpret_cast<const float2 *>(&sH[c][tt * 2]);
+            const float4 wv = *reinterpret_cast<const float4 *>(&sW[c][te * 4]);
+            acc[0][0] = fmaf(h.x, wv.x, acc[0][0]); acc[0][1] = fmaf(h.x, wv.y, acc[0][1]);
+            acc[0][2] = fmaf(h.x, wv.z, acc[0][2]); acc[0][3] = fmaf(h.x, wv.w, acc[0][3]);
+            acc[1][0] = fmaf(h.y, wv.x, acc[1][0]); acc[1][1] = fmaf(h.y, wv.y, acc[1][1]);
+            acc[1][2] = fmaf(h.y, wv.z, acc[1][2]); acc[1][3] = fmaf(h.y, wv.w, acc[1][3]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int tk = t0 + tt * 2 + i;
+        if (tk >= m) continue;
+        float sg[4], sl[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float l = __fmul_rn(acc[i][j], inv[tk]);
+            const float gv = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-l)));
+            sg[j] = gv;
+            sl[j] = __fadd_rn(gv, bias[te * 4 + j]);
+        }
+        *reinterpret_cast<float4 *>(sig + (size_t) tk * 64 + te * 4) = make_float4(sg[0], sg[1], sg[2], sg[3]);
+        *reinterpret_cast<float4 *>(sel + (size_t) tk * 64 + te * 4) = make_float4(sl[0], sl[1], sl[2], sl[3]);
+    }
+}
+
+// One warp per token.  ref: src/prefill.cu:1696-1708
+__global__ void __launch_bounds__(256) k_pf_select(const float * __restrict__ sel, const float * __restrict__ sig, int m,
+                                                   int * __restrict__ idx, float * __restrict__ w) {
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (t >= m) return;
+    int ord[LKB_TOP_K]; float wv[LKB_TOP_K];
+    lkb_router_select(sel + (size_t) t * 64, sig + (size_t) t * 64, lane, ord, wv);
+    if (lane == 0) {
+        *reinterpret_cast<int4 *>(idx + t * 4) = make_int4(ord[0], ord[1], ord[2], ord[3]);
+        *reinterpret_cast<float4 *>(w + t * 4) = make_float4(wv[0], wv[1], wv[2], wv[3]);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// count / plan / scatter.  ref: src/prefill.cu:1710-1756
+// ---------------------------------------------------------------------------
+// Per-CTA shared histogram, then 64 global atomics per CTA (integer: order-free).
+__global__ void __launch_bounds__(256) k_pf_moe_count(const int * __restrict__ idx, int n, int * __restrict__ cnt) {
+    __shared__ int s_c[LKB_N_EXPERTS];
+    if (threadIdx.x < LKB_N_EXPERTS) s_c[threadIdx.x] = 0;
+    __syncthreads();
+    for (int s = blockIdx.x * blockDim.x + threadIdx.x; s < n; s += gridDim.x * blockDim.x) atomicAdd(&s_c[idx[s]], 1);
+    __syncthreads();
+    if (threadIdx.x < LKB_N_EXPERTS && s_c[threadIdx.x]) atomicAdd(&cnt[threadIdx.x], s_c[threadIdx.x]);
+}
+
+// One warp: exclusive scan over the 64 counts, then tiles in expert order.
+__global__ void __launch_bounds__(32) k_pf_moe_plan(const int * __restrict__ cnt, int * __restrict__ off,
+                                                    int4 * __restrict__ tiles, int * __restrict__ ntiles) {
+    const int lane = threadIdx.x;
+    const int c0 = cnt[lane], c1 = cnt[lane + 32];
+    const int n0 = (c0 + LKB_MOE_BN - 1) / LKB_MOE_BN, n1 = (c1 + LKB_MOE_BN - 1) / LKB_MOE_BN;
+    // inclusive scans over lanes for experts 0..31, then offset experts 32..63
+    int so = c0, st = n0, so1 = c1, st1 = n1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int a = __shfl_up_sync(LKB_FULL, so, o), b = __shfl_up_sync(LKB_FULL, st, o);
+        const int c = __shfl_up_sync(LKB_FULL, so1, o), d = __shfl_up_sync(LKB_FULL, st1, o);
+        if (lane >= o) { so += a; st += b; so1 += c; st1 += d; }
+    }
+    const int tot_o = __shfl_sync(LKB_FULL, so, 31), tot_t = __shfl_sync(LKB_FULL, st, 31);
+    const int off0 = so - c0, off1 = tot_o + so1 - c1;
+    const int tb0 = st - n0, tb1 = tot_t + st1 - n1;
+    off[lane] = off0; off[lane + 32] = off1;
+    for (int i = 0; i < n0; ++i)
+        tiles[tb0 + i] = make_int4(lane, off0 + i * LKB_MOE_BN, min(LKB_MOE_BN, c0 - i * LKB_MOE_BN), 0);
+    for (int i = 0; i < n1; ++i)
+        tiles[tb1 + i] = make_int4(lane + 32, off1 + i * LKB_MOE_BN, min(LKB_MOE_BN, c1 - i * LKB_MOE_BN), 0);
+    if (lane == 31) *ntiles = tot_t + st1;
+}
+
+// Stable scatter.  CTA c owns slots [1024c, 1024c+1024): it histograms every
+// earlier slot (L2-resident reads) to learn how many slots of each expert precede
+// its chunk, ranks its own slots with match_any, and writes perm.  Result:
+// expert-major, slot-ascending within an expert -- identical to the reference's
+// per-expert compaction (ref: src/prefill.cu:1733-1756) without re-reading idx 64x.
+__global__ void __launch_bounds__(1024) k_pf_moe_scatter(const int * __restrict__ idx, int n, const int * __restrict__ off,
+                                                         int * __restrict__ perm) {
+    __shared__ int s_prior[LKB_N_EXPERTS];
+    __shared__ int s_wc[32][LKB_N_EXPERTS];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int c0 = blockIdx.x * 1024;
+    if (tid < LKB_N_EXPERTS) s_prior[tid] = off[tid];
+    for (int i = tid; i < 32 * LKB_N_EXPERTS; i += 1024) (&s_wc[0][0])[i] = 0;
+    __syncthreads();
+    for (int s = tid; s < c0; s += 1024) atomicAdd(&s_prior[idx[s]], 1);
+    const int s = c0 + tid;
+    const bool live = s < n;
+    const int e = live ? idx[s] : -1 - lane;               // dead lanes match nobody
+    const unsigned same = __match_any_sync(LKB_FULL, e);
+    const int rank_w = __popc(same & ((1u << lane) - 1u));
+    if (live && rank_w == 0) s_wc[warp][e] = __popc(same);
+    __syncthreads();
+    // exclusive scan over warps, per expert (64 threads x 32 steps)
+    if (tid < LKB_N_EXPERTS) {
+        int run = s_prior[tid];
+        for (int wv = 0; wv < 32; ++wv) { const int c = s_wc[wv][tid]; s_wc[wv][tid] = run; run += c; }
+    }
+    __syncthreads();
+    if (live) perm[s_wc[warp][e] + rank_w] = s;
+}
+
+// ---------------------------------------------------------------------------
+// combine.  ref: src/prefill.cu:1804-1814 and 1764-1800
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_pf_moe_combine(float * __restrict__ X, const float * __restrict__ D,
+                                                        const float * __restrict__ w) {
+    const int t = blockIdx.x;
+    const int n = blockIdx.y * blockDim.x + threadIdx.x;
+    float a = 0.0f;
+#pragma unroll
+    for (int k = 0; k < LKB_TOP_K; ++k) a = fmaf(w[t * 4 + k], D[(size_t) (t * 4 + k) * LKB_HIDDEN + n], a);
+    float * xp = X + (size_t) t * LKB_HIDDEN + n;
+    *xp = __fadd_rn(*xp, a);
+}
+
+__global__ void __launch_bounds__(256) k_pf_moe_combine_norm(float * __restrict__ X, const float * __restrict__ D,
+                                                             const float * __restrict__ w, const float * __restrict__ nw,
+                                                             int8_t * __restrict__ aqs, float2 * __restrict__ asc,
+                                                             float * __restrict__ inv_out) {
+    const int t = blockIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    __shared__ float s_sq[64];
+    float wk[LKB_TOP_K];
+#pragma unroll
+    for (int k = 0; k < LKB_TOP_K; ++k) wk[k] = w[t * 4 + k];
+    float * x = X + (size_t) t * LKB_HIDDEN;
+    int8_t * q = aqs + (size_t) t * LKB_HIDDEN;
+    float2 * sc = asc + (size_t) t * (LKB_HIDDEN / 32);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = tid + 256 * j;
+        float acc = 0.0f;
+#pragma unroll
+        for (int k = 0; k < LKB_TOP_K; ++k) acc = fmaf(wk[k], D[(size_t) (t * 4 + k) * LKB_HIDDEN + i], acc);
+        const float xv = __fadd_rn(x[i], acc);
+        x[i] = xv;
+        const int b = warp + 8 * j;
+        const float uv = __fmul_rn(xv, nw[i]);
+        lkb_quant_store_planar(uv, q + b * 32, sc + b, lane);
+        const float sq = lkb_warp_sum(__fmul_rn(xv, xv));
+        if (lane == 0) s_sq[b] = sq;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const float sv = lkb_warp_sum(__fadd_rn(s_sq[lane], s_sq[lane + 32]));
+        if (lane == 0) inv_out[t] = rsqrtf(fmaf(sv, 1.0f / (float) LKB_HIDDEN, LKB_EPS));
+    }
+}
+
+// planar row -> 36-byte blocks (exact).  ref: src/prefill.cu:1819-1828
+__global__ void __launch_bounds__(64) k_pf_pack_q8_1(const int8_t * __restrict__ aqs, const float2 * __restrict__ asc, int t,
+                                                     lkb_q8blk * __restrict__ y) {
+    const int b = threadIdx.x;
+    const float2 s = asc[(size_t) t * 64 + b];
+    y[b].ds = __floats2half2_rn(s.x, __fmul_rn(s.y, 0.125f));
+    const int4 * src = reinterpret_cast<const int4 *>(aqs + (size_t) t * LKB_HIDDEN + b * 32);
+    const int4 v0 = src[0], v1 = src[1];
+    int * dq = reinterpret_cast<int *>(y[b].qs);
+    dq[0] = v0.x; dq[1] = v0.y; dq[2] = v0.z; dq[3] = v0.w;
+    dq[4] = v1.x; dq[5] = v1.y; dq[6] = v1.z; dq[7] = v1.w;
+}
+
+// ---------------------------------------------------------------------------
+// CUDA-core form of the Q4_0 x Q8_1 GEMM (dense, grouped, SwiGLU epilogue).
+// CTA = 64 weight rows (EPI 1: 32 gate + the same 32 up rows) x one 64-token
+// tile; thread = rows (lane, lane+32) x 8 tokens, so a warp holds 32 consecutive
+// rows of a token and the SwiGLU epilogue quantises with the standard warp
+// quantiser: fused output == unfused output bit for bit.
+// Per (row, token): acc = fma(d4, fma(d8, float(S_b), -8sum), acc) for b ascending,
+// then * scale, then (+ out).  ref: src/prefill.cu:172-491 (semantics), 391-399
+// ---------------------------------------------------------------------------
+#define SG_KB 8
+#define SG_WP (SG_KB * 16 + 16)        // weight row pitch in smem (bytes), +16 against bank conflicts
+
+template <int EPI>
+__global__ void __launch_bounds__(256) k_pf_gemm_simple(const lkb_pf_gemm g) {
+    __shared__ __align__(16) unsigned char s_w[64 * SG_WP];
+    __shared__ __align__(16) __half        s_d[64 * SG_KB];
+    __shared__ __align__(16) int8_t        s_a[64 * SG_KB * 32];
+    __shared__ __align__(16) float2        s_s[64 * SG_KB];
+    __shared__ int   s_arow[64];
+    __shared__ int   s_orow[64];
+    __shared__ float s_scl[64];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    int rt, tstart, tcnt, expert = 0;
+    if (g.perm) {
+        if ((int) blockIdx.y >= *g.ntiles) return;
+        const int4 tl = reinterpret_cast<const int4 *>(g.tiles)[blockIdx.y];
+        expert = tl.x; tstart = tl.y; tcnt = tl.z; rt = blockIdx.x;
+    } else {
+        rt = blockIdx.x; tstart = blockIdx.y * 64;
+        tcnt = g.ntok - tstart; if (tcnt > 64) tcnt = 64;
+    }
+    if (tid < 64) {
+        int slot = -1;
+        if (tid < tcnt) slot = g.perm ? g.perm[tstart + tid] : tstart + tid;
+        const int ar = (slot >= 0) ? (slot >> g.a_shift) : -1;
+        s_arow[tid] = ar; s_orow[tid] = slot;
+        s_scl[tid] = (ar >= 0 && g.scale) ? g.scale[ar] : 1.0f;
+    }
+    // weight rows of this CTA: local row r in [0,64)
+    const int row0 = EPI ? rt * 32 : rt * 64;
+    const size_t eo = (size_t) expert * g.exp_stride;
+    const uint4 * wq[2]; const __half * wd[2];
+    if (EPI) {
+        wq[0] = (const uint4 *) g.qs[0] + eo + (size_t) row0 * g.bpr; wd[0] = (const __half *) g.d[0] + eo + (size_t) row0 * g.bpr;
+        wq[1] = (const uint4 *) g.qs[1] + eo + (size_t) row0 * g.bpr; wd[1] = (const __half *) g.d[1] + eo + (size_t) row0 * g.bpr;
+    } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = row0 + 32 * h;
+            const int seg = (r < g.seg_end[0]) ? 0 : (r < g.seg_end[1]) ? 1 : 2;
+            const int sbase = seg ? g.seg_end[seg - 1] : 0;
+            wq[h] = (const uint4 *) g.qs[seg] + eo + (size_t) (r - sbase) * g.bpr;
+            wd[h] = (const __half *) g.d[seg] + eo + (size_t) (r - sbase) * g.bpr;
+        }
+    }
+    __syncthreads();
+
+    float acc[2][8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[h][j] = 0.0f;
+
+    for (int kb0 = 0; kb0 < g.bpr; kb0 += SG_KB) {
+        // stage: 64 rows x 8 blocks of weights, 64 tokens x 8 blocks of activations
+        for (int c = tid; c < 64 * SG_KB; c += 256) {
+            const int r = c / SG_KB, kk = c % SG_KB;
+            const int h = r >> 5, rr = r & 31;
+            *reinterpret_cast<uint4 *>(s_w + r * SG_WP + kk * 16) = wq[h][(size_t) rr * g.bpr + kb0 + kk];
+            s_d[r * SG_KB + kk] = wd[h][(size_t) rr * g.bpr + kb0 + kk];
+            const int ar = s_arow[r];
+            s_s[r * SG_KB + kk] = (ar >= 0) ? reinterpret_cast<const float2 *>(g.asc)[(size_t) ar * g.bpr + kb0 + kk]
+                                            : make_float2(0.0f, 0.0f);
+        }
+        for (int c = tid; c < 64 * SG_KB * 2; c += 256) {
+            const int r = c / (SG_KB * 2), kk = c % (SG_KB * 2);
+            const int ar = s_arow[r];
+            int4 v = make_int4(0, 0, 0, 0);
+            if (ar >= 0) v = *reinterpret_cast<const int4 *>(g.aqs + (size_t) ar * g.bpr * 32 + (size_t) kb0 * 32 + kk * 16);
+            *reinterpret_cast<int4 *>(s_a + r * SG_KB * 32 + kk * 16) = v;
+        }
+        __syncthreads();
+#pragma unroll 2
+        for (int kk = 0; kk < SG_KB; ++kk) {
+            uint4 wv[2]; float d4[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                wv[h] = *reinterpret_cast<const uint4 *>(s_w + (lane + 32 * h) * SG_WP + kk * 16);
+                d4[h] = __half2float(s_d[(lane + 32 * h) * SG_KB + kk]);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int tk = warp * 8 + j;
+                const int4 a0 = *reinterpret_cast<const int4 *>(s_a + tk * SG_KB * 32 + kk * 32);
+                const int4 a1 = *reinterpret_cast<const int4 *>(s_a + tk * SG_KB * 32 + kk * 32 + 16);
+                const int xv[8] = { a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w };
+                const float2 sc = s_s[tk * SG_KB + kk];
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    acc[h][j] = lkb_block_acc(d4[h], sc.x, lkb_sumi(wv[h], xv), sc.y, acc[h][j]);
+            }
+        }
+        __syncthreads();
+    }
+
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int tk = warp * 8 + j;
+        const int orow = s_orow[tk];            // warp-uniform
+        if (orow < 0) continue;
+        const float scl = s_scl[tk];
+        if (EPI) {
+            const float gt = __fmul_rn(acc[0][j], scl);
+            const float up = __fmul_rn(acc[1][j], scl);
+            const float v = __fmul_rn(lkb_silu(gt), up);
+            lkb_quant_store_planar(v, g.oqs + (size_t) orow * (g.okb * 32) + row0,
+                                   reinterpret_cast<float2 *>(g.osc) + (size_t) orow * g.okb + row0 / 32, lane);
+        } else {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const float a = __fmul_rn(acc[h][j], scl);
+                float * p = g.out + (size_t) orow * g.out_ld + row0 + 32 * h + lane;
+                *p = g.add ? __fadd_rn(*p, a) : a;
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------
+int lkb_gemm_tc_init();                                      // lkb_gemm_tc.cu
+int lkb_gemm_tc_launch(const lkb_pf_gemm * g, int epi, int max_tiles, cudaStream_t st);   // LKB_ERR_UNSUPPORTED if shape not covered
+
+static int g_gemm_cfg = -1;        // -1: tensor-core form when it covers the shape; 0: CUDA-core form
+
+int lkb_prefill_init() {
+    const char * v = getenv("LKB_PF_CFG");
+    if (v) g_gemm_cfg = atoi(v);
+    return lkb_gemm_tc_init();
+}
+
+static int gemm_check(const lkb_pf_gemm * g, int epi) {
+    if (!g) return LKB_ERR_NULL;
+    if (!g->qs[0] || !g->d[0] || !g->aqs || !g->asc) return LKB_ERR_NULL;
+    if (epi) { if (!g->qs[1] || !g->d[1] || !g->oqs || !g->osc) return LKB_ERR_NULL; }
+    else if (!g->out) return LKB_ERR_NULL;
+    if (g->bpr <= 0 || g->bpr % 8) return LKB_ERR_SHAPE;
+    if (epi ? (g->N % 64) : (g->N % 128)) return LKB_ERR_SHAPE;
+    if (!epi && (g->seg_end[0] % 128 || g->seg_end[1] % 128)) return LKB_ERR_SHAPE;
+    if (g->perm && (!g->tiles || !g->ntiles)) return LKB_ERR_NULL;
+    return LKB_OK;
+}
+
+static int gemm_dispatch(const lkb_pf_gemm * g, int epi, int max_tiles, cudaStream_t st) {
+    LKB_REQUIRE_INIT();
+    const int r = gemm_check(g, epi);
+    if (r != LKB_OK) return r;
+    const int ty = g->perm ? max_tiles : (g->ntok + 63) / 64;
+    if (ty <= 0) return g->perm ? LKB_ERR_SHAPE : LKB_OK;
+    if (g_gemm_cfg != 0) {
+        const int t = lkb_gemm_tc_launch(g, epi, max_tiles, st);
+        if (t != LKB_ERR_UNSUPPORTED) return t;
+        if (g_gemm_cfg > 0) return t;
+    }
+    if (epi) k_pf_gemm_simple<1><<<dim3(g->N / 32, ty), 256, 0, st>>>(*g);
+    else     k_pf_gemm_simple<0><<<dim3(g->N / 64, ty), 256, 0, st>>>(*g);
+    return lkb_check_launch();
+}
+
+extern "C" {
+
+int lkb_pf_gemm_config(int cfg) { g_gemm_cfg = cfg; return LKB_OK; }
+
+int lkb_pf_norm(const float * X, const float * w, int plain, lkb_pf_act a, float * inv_out, float * h32,
+                int m, lkb_stream_t st) {
+    LKB_REQUIRE_INIT();
+    if (!X || !w || !a.qs || !a.sc || !inv_out) return LKB_ERR_NULL;
+    if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
+    k_pf_norm<<<m, 256, 0, (cudaStream_t) st>>>(X, w, plain, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out, h32);
+    return lkb_check_launch();
+}
+
+int lkb_pf_quant_rows(const float * X, int ld, int kb, lkb_pf_act a, int rows, lkb_stream_t st) {
+    LKB_REQUIRE_INIT();
+    if (!X || !a.qs || !a.sc) return LKB_ERR_NULL;
+    if (rows <= 0 || kb <= 0) return (rows == 0) ? LKB_OK : LKB_ERR_SHAPE;
+    k_pf_quant_rows<<<dim3(rows, (kb + 7) / 8), 256, 0, (cudaStream_t) st>>>(X, ld, kb, a.qs, reinterpret_cast<float2 *>(a.sc));
+    return lkb_check_launch();
+}
+
+int lkb_pf_swiglu(const float * Y, int ld, int up_off, int kb, lkb_pf_act a, int rows, lkb_stream_t st) {
+    LKB_REQUIRE_INIT();
+    if (!Y || !a.qs || !a.sc) return LKB_ERR_NULL;
+    if (rows <= 0 || kb <= 0) return (rows == 0) ? LKB_OK : LKB_ERR_SHAPE;
+    k_pf_swiglu<<<dim3(rows, (kb + 7) / 8), 256, 0, (cudaStream_t) st>>>(Y, ld, up_off, kb, a.qs, reinterpret_cast<float2 *>(a.sc));
+    return lkb_check_launch();
+}
+
+int lkb_pf_router_small(const float * H, int m, const float * Wr, const float * bias, const float * inv,
+                        float * sel, float * sig, lkb_stream_t st) {
+    LKB_REQUIRE_INIT();
+    if (!H || !Wr || !bias || !inv || !sel || !sig) return LKB_ERR_NULL;
+    if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
+    if (m > 65535) return LKB_ERR_SHAPE;
+    k_pf_router_small<<<dim3(LKB_N_EXPERTS, m), 32, 0, (cudaStream_t) st>>>(H, Wr, bias, inv, sel, sig);
+    return lkb_check_launch();
+}
+
+int lkb_pf_router(const float * H, int m, const float * Wr, const float * bias, const float * inv,
+                  float * sel, float * sig, lkb_stream_t st) {
+    LKB_REQUIRE_INIT();
+    if (!H || !Wr || !bias || !inv || !sel || !sig) return LKB_ERR_NULL;
+    if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
+    if (m <= 256) return lkb_pf_router_small(H, m, Wr, bias, inv, sel, sig, st);
+    k_pf_router<<<(m + 31) / 32, 256, 0, (cudaStream_t) st>>>(H, m, Wr, bias, inv, sel, sig);
+    return lkb_check_launch();
+}
+
+int lkb_pf_select(const float * sel, const float * sig, int m, int * idx, float * w, lkb_stream_t st) {
+    LKB_REQUIRE_INIT();
+    if (!sel || !sig || !idx || !w) return LKB_ERR_NULL;
+    if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
+    k_pf_select<<<(m + 7) / 8, 256, 0, (cudaStream_t) st>>>(sel, sig, m, idx, w);
+    return lkb_check_launch();
+}
+
+int lkb_pf_moe_count(const int * idx, int n, int * cnt, lkb_stream_t st) {
+    LKB_REQUIRE_INIT();
+    if (!idx || !cnt) return LKB_ERR_NULL;
+    if (n <= 0) return n == 0 ? LKB_OK : LKB_ERR_SHAPE;
+    int grid = (n + 255) / 256; if (grid > 64) grid = 64;
+    k_pf_moe_count<<<grid, 256, 0, (cudaStream_t) st>>>(idx, n, cnt);
+    return lkb_check_launch();
+}
+
+int lkb_pf_moe_plan(const int * cnt, int * off, int * tiles, int * ntiles, lkb_stream_t st) {
+    LKB_REQUIRE_INIT();
+    if (!cnt || !off || !tiles || !ntiles) return LKB_ERR_NULL;
+    k_pf_moe_plan<<<1, 32, 0, (cudaStream_t) st>>>(cnt, off, reinterpret_cast<int4 *>(tiles), ntiles);
+    return lkb_check_launch();
+}
+
+int lkb_pf_moe_scatter(const int * idx, int n, const int * off, int * perm, lkb_stream_t st) {
+    LKB_REQUIRE_INIT();
+    if (!idx || !off || !perm) return LKB_ERR_NULL;
+    if (n <= 0) return n == 0 ? LKB_OK : LKB_ERR_SHAPE;
+    k_pf_moe_scatter<<<(n + 1023) / 1024, 1024, 0, (cudaStream_t) st>>>(idx, n, off, perm);
+    return lkb_check_launch();
+}
+
+int lkb_pf_gemm_dense(const lkb_pf_gemm * g, lkb_stream_t st) {
+    if (g && g->perm) return LKB_ERR_SHAPE;
+    return gemm_dispatch(g, 0, 0, (cudaStream_t) st);
+}
+int lkb_pf_gemm_moe(const lkb_pf_gemm * g, int max_tiles, lkb_stream_t st) {
+    if (g && !g->perm) return LKB_ERR_NULL;
+    return gemm_dispatch(g, 0, max_tiles, (cudaStream_t) st);
+}
+int lkb_pf_gemm_swiglu(const lkb_pf_gemm * g, int max_tiles, lkb_stream_t st) {
+    return gemm_dispatch(g, 1, max_tiles, (cudaStream_t) st);
+}
+
+int lkb_pf_moe_combine(float * X, const float * D, const float * w, int m, lkb_stream_t st) {
+    LKB_REQUIRE_INIT();
+    if (!X || !D || !w) return LKB_ERR_NULL;
+    if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
+    k_pf_moe_combine<<<dim3(m, LKB_HIDDEN / 256), 256, 0, (cudaStream_t) st>>>(X, D, w);
+    return lkb_check_launch();
+}
+
+int lkb_pf_moe_combine_norm(float * X, const float * D, const float * w, const float * nw, lkb_pf_act a,
+                            float * inv_out, int m, lkb_stream_t st) {
+    LKB_REQUIRE_INIT();
+    if (!X || !D || !w || !nw || !a.qs || !a.sc || !inv_out) return LKB_ERR_NULL;
+    if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
+    k_pf_moe_combine_norm<<<m, 256, 0, (cudaStream_t) st>>>(X, D, w, nw, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out);
+    return lkb_check_launch();
+}
+
+int lkb_pf_pack_q8_1(lkb_pf_act a, int t, lkb_block_q8_1 * y, lkb_stream_t st) {
+    LKB_REQUIRE_INIT();
+    if (!a.qs || !a.sc || !y) return LKB_ERR_NULL;
+    if (t < 0) return LKB_ERR_SHAPE;
+    k_pf_pack_q8_1<<<1, 64, 0, (cudaStream_t) st>>>(a.qs, reinterpret_cast<const float2 *>(a.sc), t, reinterpret_cast<lkb_q8blk *>(y));
+    return lkb_check_launch();
+}
+
+}  // extern "C"

@@ -1,0 +1,56 @@
+"""The C-ABI library loads and exports every entry point include/lkb.h declares (no GPU needed)."""
+import ctypes
+import re
+
+import numpy as np
+
+
+def test_every_declared_symbol_is_exported(lkb):
+    names = [n for n, _, _ in lkb.declared_entry_points()]
+    assert len(names) >= 35 and len(set(names)) == len(names)
+    raw = ctypes.CDLL(str(lkb.LIB_PATH))
+    for n in names:
+        assert hasattr(raw, n), f"liblkb.so lacks {n}"
+    # every declaration carries a citation of the reference interface it replaces (or says it has none)
+    text = lkb.HEADER.read_text()
+    for n in names:
+        if n in ("lkb_error_string", "lkb_sm_count", "lkb_set_pdl"):
+            continue
+        pos = re.search(r"\bint\s+%s\(" % n, text).start()
+        assert re.search(r"ref: src/\w+\.cuh?:\d+|[Nn]o\s+counterpart|Not part of the reference",
+                         text[max(0, pos - 1500):pos]), n
+
+
+def test_struct_layouts_match_header(lkb, tmp_path):
+    """ctypes mirrors vs the C compiler's layout of include/lkb.h."""
+    import subprocess
+    src = tmp_path / "layout.c"
+    src.write_text('''#include <stdio.h>
+#include <stddef.h>
+#include "lkb.h"
+int main(void) {
+    printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(lkb_pf_act), sizeof(lkb_norm_prod_t), sizeof(lkb_pf_gemm),
+           offsetof(lkb_pf_gemm, exp_stride), offsetof(lkb_pf_gemm, aqs), offsetof(lkb_pf_gemm, a_shift),
+           offsetof(lkb_pf_gemm, okb), sizeof(lkb_block_q8_1));
+    return 0;
+}''')
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", str(lkb.ROOT / "include"), str(src), "-o", str(exe)], check=True)
+    got = [int(v) for v in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
+    G = lkb.PfGemm
+    assert got == [ctypes.sizeof(lkb.PfAct), ctypes.sizeof(lkb.NormProd), ctypes.sizeof(G), G.exp_stride.offset,
+                   G.aqs.offset, G.a_shift.offset, G.okb.offset, 36]
+
+
+def test_compute_calls_fail_loudly_without_init(lkb):
+    """No CPU fallback: before lkb_init (or without a GPU) every compute entry point refuses."""
+    import torch
+    if torch.cuda.is_available():
+        return                      # on a GPU box another test may already have initialised the library
+    assert lkb.lib.lkb_init(0) != 0
+    buf = np.zeros(64, np.float32)
+    p = buf.ctypes.data
+    assert lkb.lib.lkb_quantize_q8_1(p, p, 1, None) == -10004
+    assert lkb.lib.lkb_router_dot(p, p, p, None, None, None, None, 0.0, None) == -10004
+    assert lkb.lib.lkb_pf_moe_plan(p, p, p, p, None) == -10004
+    assert b"lkb_init" in lkb.lib.lkb_error_string(-10004)
