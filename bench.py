@@ -1,0 +1,396 @@
+#!/usr/bin/env python3
+"""Benchmark of the Q4_0 x Q8_1 MoE hot path on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline (one JSON line on stdout, rank 0):
+  metric  "bs1 decode tok/s": one step = ONE token through the 40-layer MoE-FFN stack of
+          the synthetic model (benchmark configuration 1 repeated over 40 distinct layers:
+          router -> top-4 -> gate|up GEMV of the 4 chosen experts -> SwiGLU/Q8_1 -> down
+          GEMV + weighted sum + residual + next layer's norm quantiser).  13.6 GB of expert
+          weights are resident; a step streams 871 MB of them (which experts depends on the
+          token), so nothing is served from the 126 MB L2 twice.
+  value   tokens/s with inputs resident in HBM (CUDA-event time, max over ranks).
+  e2e     the same steps driven through the public API with the token's hidden state
+          copied host->device from pinned memory and the result copied back every step.
+  roofline  the dominant kernel (MoE gate|up GEMV): algorithmic bytes / its CUDA-event time.
+  prefill   4096-token batched prefill through the same 40 layers (configuration 3, Zipf-
+          skewed routing): tok/s, grouped-GEMM TMAC/s and tensor-pipe roofline; expert-
+          parallel over N GPUs when N > 1.
+Decode does not shard (batch 1): with --gpus N each rank runs an independent replica.
+Data are seeded synthetic tensors with the configurations' shapes and value distributions.
+"""
+import argparse
+import importlib
+import json
+import os
+import pathlib
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+N_LAYERS = 40
+H, E, TOPK, I = 2048, 64, 4, 1536
+LAYER_BYTES = E * H * 4 + 2 * TOPK * I * (H // 32) * 18 + TOPK * H * (I // 32) * 18 + 3 * H * 4   # 21,782,528
+GATEUP_BYTES = 2 * TOPK * I * (H // 32) * 18 + 64 * 36 + 2 * TOPK * I * 4                          # per launch
+METRIC = "bs1 decode tok/s"
+UNIT = "tok/s"
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured", d
+    return 6650.0, "fallback", {}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while a timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.idx}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        self.t.join(timeout=2)
+        mhz, mx, reasons = [], None, set()
+        for ln in self.lines:
+            f = [v.strip() for v in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                mhz.append(float(f[1]))
+                mx = float(f[2])
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(mhz)) if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+# --------------------------------------------------------------------------- CPU baseline
+_HOST_LAYER = {}
+
+
+def host_layer(seed=4321):
+    """One MoE layer on the host with the benchmark's value distributions (numpy, seeded)."""
+    if seed in _HOST_LAYER:
+        return _HOST_LAYER[seed]
+    rng = np.random.default_rng(seed)
+
+    def q4(rows, bpr):
+        qs = rng.integers(0, 256, size=(rows, bpr, 16), dtype=np.uint8)
+        d = np.abs(rng.normal(0, 0.02, size=(rows, bpr))).astype(np.float16).view(np.uint16)
+        return qs, d
+    _HOST_LAYER[seed] = dict(gate=q4(E * I, H // 32), up=q4(E * I, H // 32), down=q4(E * H, I // 32),
+                             router=(0.02 * rng.standard_normal((E, H))).astype(np.float32),
+                             bias=(0.01 * rng.standard_normal(E)).astype(np.float32),
+                             nw=(1 + 0.05 * rng.standard_normal(H)).astype(np.float32))
+    return _HOST_LAYER[seed]
+
+
+def cpu_layer_token(orc, L, x):
+    """The checker's statement of one batch-1 MoE FFN layer (the reference's CPU-side formulas)."""
+    h32, act, ssq = orc.norm_prod(x, L["nw"])
+    inv = orc.norm_inv(ssq)
+    logits = orc.router_dot(h32, L["router"], ninv=inv)
+    sel, sig = orc.router_gate(logits, L["bias"])
+    idx, w = orc.router_select(sel, sig)
+    g = orc.gemv_q4_0_exp(L["gate"][0], L["gate"][1], act, I, H // 32, I, 0, idx, ninv=inv)
+    u = orc.gemv_q4_0_exp(L["up"][0], L["up"][1], act, I, H // 32, I, 0, idx, ninv=inv)
+    act2 = orc.quantize_q8_1(orc.swiglu(g, u))
+    xo, _, _, _ = orc.moe_down_accum(L["down"][0], L["down"][1], act2, H, I // 32, H, I // 32, idx, w, x, None)
+    return xo
+
+
+def cpu_baseline(target_s=12.0, max_tokens=None):
+    orc = importlib.import_module("oracle.lkb_oracle")
+    L = host_layer()
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal(H).astype(np.float32)
+    t0 = time.perf_counter()
+    x1 = cpu_layer_token(orc, L, x)
+    t1 = time.perf_counter() - t0
+    n = max(2, int(target_s / max(t1, 1e-4)))
+    if max_tokens:
+        n = min(n, max_tokens)
+    t0 = time.perf_counter()
+    for i in range(n):
+        x1 = cpu_layer_token(orc, L, x if i % 2 else x1 * 0.5)
+    dt = time.perf_counter() - t0
+    per_layer = dt / n
+    return {"value": 1.0 / (per_layer * N_LAYERS), "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
+            "sample": f"{n} MoE-layer passes of one token on the host (the CPU checker's restatement of the "
+                      f"reference formulas, OpenMP over rows); {per_layer * 1e3:.2f} ms per layer, x{N_LAYERS} layers per token"}, per_layer
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    per = []
+    for _ in range(args.warmup):
+        cpu_baseline(target_s=0.5)
+    t0 = time.perf_counter()
+    for _ in range(max(1, args.steps)):
+        cb, per_layer = cpu_baseline(target_s=min(20.0, 60.0 / max(1, args.steps)))
+        per.append(per_layer)
+    wall = time.perf_counter() - t0
+    per_layer = float(np.mean(per))
+    val = 1.0 / (per_layer * N_LAYERS)
+    cb["value"] = val
+    out = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+           "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_layer * N_LAYERS * 1e3,
+           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8xint4->int32, fp32 accumulate",
+           "data": "synthetic (seeded; shapes and distributions of the benchmark configuration)",
+           "config": {"workload": f"config 1 x {N_LAYERS} layers: batch-1 MoE FFN stack (64 experts, top-4, "
+                                  "hidden 2048, inter 1536, Q4_0 weights x Q8_1 activations); each step here is a "
+                                  "bounded sample of MoE-layer passes on the host cores",
+                      "wall_s": wall},
+           "cpu_baseline": cb,
+           "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+           "gpu_launches": 0}
+    print(json.dumps(out), flush=True)
+
+
+# --------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    lkb = importlib.import_module("lfm2-ampere_b200")
+    synth = importlib.import_module("lfm2-ampere_b200.synth")
+    decode = importlib.import_module("lfm2-ampere_b200.decode")
+    prefill = importlib.import_module("lfm2-ampere_b200.prefill")
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for this path "
+                         "(use --impl reference for the host-side baseline)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lkb.init(local)
+    lkb.set_pdl(not args.no_pdl)
+    hbm_peak, peak_kind, _ = peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    layers = synth.make_model(args.layers, seed=1234 + 1000003 * rank, zipf_s=1.1)
+    stack = decode.DecodeStack(layers)
+    rng = np.random.default_rng(99 + rank)
+    n_in = 64
+    x_host = torch.from_numpy(rng.standard_normal((n_in, H)).astype(np.float32)).pin_memory()
+    y_host = torch.empty(H, dtype=torch.float32).pin_memory()
+    x_pool = x_host.cuda()
+    st = torch.cuda.current_stream()
+
+    # one CUDA graph per step shape: copy-in of a resident input, then the 201 kernels
+    use_graph = not args.no_graph
+    graph = None
+    x_in = torch.zeros(H, device="cuda")
+    if use_graph:
+        stack.x.copy_(x_pool[0])
+        stack.step()                                  # warm the launch path before capture
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            stack.x.copy_(x_in)
+            stack.step()
+
+    def one_step(i, e2e=False):
+        if e2e:
+            x_in.copy_(x_host[i % n_in], non_blocking=True)
+        else:
+            x_in.copy_(x_pool[i % n_in])
+        if graph is not None:
+            graph.replay()
+        else:
+            stack.x.copy_(x_in)
+            stack.step()
+        if e2e:
+            y_host.copy_(stack.x, non_blocking=True)
+            st.synchronize()
+
+    for i in range(max(3, args.warmup)):
+        one_step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(args.steps):
+        one_step(i)
+    ev1.record()
+    barrier()
+    ms = max_over_ranks(ev0.elapsed_time(ev1))
+    clocks = sampler.stop() if rank == 0 else None
+    tok_s = world * args.steps / (ms * 1e-3)
+
+    # end to end: host buffers, copies inside the timed region
+    for i in range(3):
+        one_step(i, e2e=True)
+    barrier()
+    ev0.record()
+    for i in range(args.steps):
+        one_step(i, e2e=True)
+    ev1.record()
+    barrier()
+    ms_e2e = max_over_ranks(ev0.elapsed_time(ev1))
+    e2e_tok_s = world * args.steps / (ms_e2e * 1e-3)
+
+    # dominant kernel: MoE gate|up GEMV, CUDA events around every launch of it while the
+    # same steps run un-graphed (the graph hides individual launches from events)
+    evs = []
+    lkb.set_pdl(False)
+    for i in range(min(args.steps, 10)):
+        stack.x.copy_(x_pool[i % n_in])
+        lkb.norm_produce(stack.x, H, stack._np[0])
+        for li, l in enumerate(layers):
+            lkb.k_router_dot(stack.h32, l.router, stack.logits, l.rbias, None, None, stack.ssq, 1e-5)
+            lkb.k_router_top4(stack.logits, l.rbias, stack.idx, stack.w)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            lkb.k_gemv_q4_0_exp2(l.gate_qs, l.gate_d, l.up_qs, l.up_d, stack.xq, I, H // 32, I, 0, stack.idx,
+                                 stack.gu[:TOPK * I], stack.gu[TOPK * I:], stack.ssq, 1e-5)
+            b.record()
+            evs.append((a, b))
+            lkb.k_swiglu(stack.gu[:TOPK * I], stack.gu[TOPK * I:], TOPK * I, None, stack.xq2, l.down_qs, stack.idx,
+                         H, I // 32, stack.pf_bytes)
+            nxt = stack._np[li + 1] if li + 1 < len(layers) else None
+            lkb.k_moe_down_accum(l.down_qs, l.down_d, stack.xq2, H, I // 32, H, I // 32, stack.idx, stack.w, stack.x, nxt)
+    torch.cuda.synchronize()
+    k_ms = float(np.mean([a.elapsed_time(b) for a, b in evs]))
+    lkb.set_pdl(not args.no_pdl)
+    ach = GATEUP_BYTES / (k_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "k_gemv_multi<2,4> (MoE gate|up GEMV, 8 x 1536 rows x K2048)",
+                "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
+                "peak_kind": f"of {peak_kind}", "traffic": None,
+                "algorithmic_bytes_per_launch": GATEUP_BYTES, "avg_launch_ms": k_ms,
+                "whole_step": {"bytes_per_step": args.layers * LAYER_BYTES,
+                               "achieved_GBs": args.layers * LAYER_BYTES / (ms / args.steps * 1e-3) / 1e9,
+                               "frac": args.layers * LAYER_BYTES / (ms / args.steps * 1e-3) / 1e9 / hbm_peak}}
+
+    # ---------------------------------------------------------------- prefill (configuration 3)
+    pf = None
+    if not args.no_prefill:
+        m = args.pf_tokens
+        del graph
+        ps = prefill.PrefillStack(layers, m)
+        Xh = torch.from_numpy(np.random.default_rng(5).standard_normal((m, H)).astype(np.float32)).pin_memory()
+        Xd = Xh.cuda()
+        Yh = torch.empty(m, H, dtype=torch.float32).pin_memory()
+
+        def pf_step(e2e=False):
+            ps.X.copy_(Xh if e2e else Xd, non_blocking=True)
+            ps.step()
+            if e2e:
+                Yh.copy_(ps.X, non_blocking=True)
+                st.synchronize()
+        pf_step()
+        barrier()
+        ev0.record()
+        for _ in range(args.pf_steps):
+            pf_step()
+        ev1.record()
+        barrier()
+        pms = max_over_ranks(ev0.elapsed_time(ev1)) / args.pf_steps
+        ev0.record()
+        for _ in range(args.pf_steps):
+            pf_step(e2e=True)
+        ev1.record()
+        barrier()
+        pms_e2e = max_over_ranks(ev0.elapsed_time(ev1)) / args.pf_steps
+        cnt = ps.cnt.cpu().numpy()
+        tmacs = ps.macs_per_step() / (pms * 1e-3) / 1e12
+        pf = {"metric": "4k prefill tok/s (40-layer MoE-FFN stack, replicas)" if world > 1 else
+                        "4k prefill tok/s (40-layer MoE-FFN stack)",
+              "tokens": m, "value": world * m / (pms * 1e-3), "unit": UNIT, "ms_per_step": pms,
+              "e2e": {"value": world * m / (pms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": m * H * 4,
+                      "d2h_bytes_per_step": m * H * 4},
+              "gemm_tmacs": tmacs, "last_layer_max_over_mean_slots_per_expert": float(cnt.max() / max(1.0, cnt.mean())),
+              "gpu_launches": args.pf_steps * ps.launches_per_step,
+              "roofline": {"bound": "tensor", "achieved": 2 * tmacs, "unit": "TOP/s (int8)",
+                           "peak": None, "frac": None,
+                           "note": "int8 tensor peak is not in MEASURED_PEAKS.json; nominal dense 4500 TOP/s"}}
+
+    if rank == 0:
+        cb, _ = cpu_baseline() if world == 1 and not args.no_cpu else (None, None)
+        out = {"metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+               "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
+               "scaling": "weak", "vs_baseline": None, "dtype": "int8xint4->int32, fp32 accumulate",
+               "data": "synthetic (seeded; shapes and distributions of the benchmark configurations)",
+               "config": {"workload": f"config 1 x {args.layers} layers: batch-1 MoE FFN stack (64 experts, top-4, hidden "
+                                      "2048, inter 1536, Q4_0 weights x Q8_1 activations, sigmoid+bias router)",
+                          "layers": args.layers, "resident_weight_bytes": args.layers * 339738624,
+                          "bytes_per_token": args.layers * LAYER_BYTES,
+                          "cold_cache": "each step streams 871 MB of a 13.6 GB weight set (inputs larger than L2)",
+                          "parallelism": "replicas" if world > 1 else "single GPU",
+                          "cuda_graph": use_graph, "pdl": not args.no_pdl},
+               "e2e": {"value": e2e_tok_s, "unit": UNIT, "h2d_bytes_per_step": H * 4, "d2h_bytes_per_step": H * 4},
+               "gpu_launches": args.steps * stack.launches_per_step,
+               "roofline": roofline, "cpu_baseline": cb, "clocks": clocks, "prefill": pf}
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=N_LAYERS)
+    ap.add_argument("--pf-tokens", type=int, default=4096)
+    ap.add_argument("--pf-steps", type=int, default=3)
+    ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

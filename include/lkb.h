@@ -190,6 +190,8 @@ int lkb_pf_select(const float * sel, const float * sig, int m, int * idx, float 
 /* ref: src/prefill.cuh:117-122  k_pf_moe_count / _plan / _scatter.  cnt must be
  * zero on entry to count (the engine memsets it, ref: src/engine.cu:1182). */
 int lkb_pf_moe_count(const int * idx, int n, int * cnt, lkb_stream_t st);
+/* ref: src/engine.cu:1182  cudaMemsetAsync(p.cnt, 0, 64*4, st) -- the zeroing that precedes the count */
+int lkb_zero_i32(int * p, int n, lkb_stream_t st);
 int lkb_pf_moe_plan(const int * cnt, int * off, int * tiles, int * ntiles, lkb_stream_t st);
 int lkb_pf_moe_scatter(const int * idx, int n, const int * off, int * perm, lkb_stream_t st);
 /* ref: src/prefill.cuh:69-71  pf_gemm_dense / pf_gemm_moe / pf_gemm_swiglu */

@@ -19,7 +19,7 @@ __all__ = [
     "k_router_top4", "router_top4_softmax", "block_sumi", "k_pf_norm", "k_pf_quant_rows", "k_pf_swiglu",
     "k_pf_router", "k_pf_router_small", "k_pf_select", "k_pf_moe_count", "k_pf_moe_plan", "k_pf_moe_scatter",
     "pf_gemm_dense", "pf_gemm_moe", "pf_gemm_swiglu", "k_pf_moe_combine", "k_pf_moe_combine_norm",
-    "k_pf_pack_q8_1", "set_pdl", "pf_gemm_config", "sm_count",
+    "k_pf_pack_q8_1", "zero_i32", "set_pdl", "pf_gemm_config", "sm_count",
 ]
 
 
@@ -160,6 +160,10 @@ def k_pf_select(sel, sig, m, idx, w):
 
 def k_pf_moe_count(idx, n, cnt):
     check(lib.lkb_pf_moe_count(ptr(idx), n, ptr(cnt), stream()), "k_pf_moe_count")
+
+
+def zero_i32(p, n):
+    check(lib.lkb_zero_i32(ptr(p), n, stream()), "zero_i32")
 
 
 def k_pf_moe_plan(cnt, off, tiles, ntiles):

@@ -555,6 +555,13 @@ int lkb_pf_moe_count(const int * idx, int n, int * cnt, lkb_stream_t st) {
     return lkb_check_launch();
 }
 
+int lkb_zero_i32(int * p, int n, lkb_stream_t st) {
+    if (!p) return LKB_ERR_NULL;
+    if (n < 0) return LKB_ERR_SHAPE;
+    const cudaError_t e = cudaMemsetAsync(p, 0, (size_t) n * 4, (cudaStream_t) st);
+    return e == cudaSuccess ? LKB_OK : -(int) e;
+}
+
 int lkb_pf_moe_plan(const int * cnt, int * off, int * tiles, int * ntiles, lkb_stream_t st) {
     LKB_REQUIRE_INIT();
     if (!cnt || !off || !tiles || !ntiles) return LKB_ERR_NULL;

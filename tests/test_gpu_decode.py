@@ -311,3 +311,34 @@ def test_error_statuses(L):
     assert L.lib.lkb_gemv_q4_0(None, None, None, 1, 1, None, 0, None, 0.0, None) == -10002
     assert L.lib.lkb_rmsnorm_q8_1(x.data_ptr(), x.data_ptr(), 100, 1e-5, None, None, None, None) == -10001
     assert L.lib.lkb_moe_accum4(x.data_ptr(), x.data_ptr(), x.data_ptr(), 33, None, None) == -10001
+
+
+def test_decode_stack_pdl_and_graph_are_bit_identical(L):
+    """Programmatic dependent launch and CUDA-graph replay must not change a single bit."""
+    import importlib
+    synth = importlib.import_module("lfm2-ampere_b200.synth")
+    decode = importlib.import_module("lfm2-ampere_b200.decode")
+    layers = synth.make_model(3, seed=77)
+    st = decode.DecodeStack(layers)
+    x0 = torch.randn(2048, device="cuda", generator=torch.Generator("cuda").manual_seed(5))
+    outs = []
+    for pdl in (False, True, True, False):
+        L.set_pdl(pdl)
+        st.x.copy_(x0)
+        st.step()
+        torch.cuda.synchronize()
+        outs.append(st.x.clone())
+    L.set_pdl(True)
+    g = torch.cuda.CUDAGraph()
+    st.x.copy_(x0)
+    with torch.cuda.graph(g):
+        st.step()
+    for _ in range(3):
+        st.x.copy_(x0)
+        g.replay()
+        torch.cuda.synchronize()
+        outs.append(st.x.clone())
+    L.set_pdl(False)
+    assert torch.isfinite(outs[0]).all()
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
