@@ -152,6 +152,45 @@ int lkb_moe_down_accum(const void * qs, const void * d, const lkb_block_q8_1 * x
                        int rows_per_expert, int xq_stride, const int * d_idx, const float * d_w,
                        float * dst, const lkb_norm_prod_t * np, lkb_stream_t st);
 
+/* ------------------------------------------------ fused MoE FFN (decode) */
+/* One MoE layer's tensors (device pointers into the planar pack). */
+typedef struct {
+    const void *  gate_qs; const void * gate_d;     /* [64*1536][64] blocks */
+    const void *  up_qs;   const void * up_d;
+    const void *  down_qs; const void * down_d;     /* [64*2048][48] blocks */
+    const float * router;                           /* [64][2048] */
+    const float * rbias;                            /* [64] or null */
+    const float * norm_w;                           /* [2048] ffn_norm weights */
+    int           softmax;                          /* 0: sigmoid+bias gate (the reference's); 1: softmax gate */
+} lkb_moe_layer;
+/* Caller-owned global scratch of the fused kernels: 64 floats, 2*4*1536 floats and
+ * two 32-bit words (barrier counter, status; status != 0 after the kernel means a
+ * bounded wait expired: 1000+10*layer+n = grid barrier n, 100/200/300+layer = a copy). */
+#define LKB_MOE_SCRATCH_LOGITS 64
+#define LKB_MOE_SCRATCH_GU     (2 * LKB_TOP_K * LKB_MOE_INTER)
+#define LKB_MOE_SCRATCH_SYNC   2
+typedef struct {
+    float *    logits;
+    float *    gu;
+    unsigned * sync;
+} lkb_moe_scratch;
+/* One launch for one batch-1 MoE FFN layer: x (the residual stream, fp32[2048]) is
+ * normalised-and-quantised with layer->norm_w, routed, pushed through the four chosen
+ * experts and updated in place; idx_out/w_out (optional) receive the selection; `next`
+ * (optional, w != null) receives the quantised raw activation, ssq and h32 of the new x
+ * for the caller's next consumer.  Bit-identical to the sequence lkb_norm_produce ->
+ * lkb_router_dot -> lkb_router_top4 -> lkb_gemv_q4_0_exp2 -> lkb_swiglu ->
+ * lkb_moe_down_accum.  No counterpart in the reference: it fuses the five launches of
+ * ref: src/engine.cu:739-811 into a persistent cooperative kernel (one CTA per SM). */
+int lkb_moe_ffn_decode(const lkb_moe_layer * layer, float * x, int * idx_out, float * w_out,
+                       const lkb_norm_prod_t * next, const lkb_moe_scratch * scratch, lkb_stream_t st);
+/* The same for n_layers consecutive layers in ONE launch; layers_dev is a DEVICE array
+ * of descriptors; idx_out/w_out (optional) are [n_layers][4].  No counterpart in the
+ * reference (its decode step is a 343-node graph, ref: src/engine.cu:1336-1342). */
+int lkb_moe_ffn_decode_stack(const lkb_moe_layer * layers_dev, int n_layers, int softmax, float * x,
+                             int * idx_out, float * w_out, const lkb_norm_prod_t * next,
+                             const lkb_moe_scratch * scratch, lkb_stream_t st);
+
 /* ------------------------------------------------------------------ router */
 /* ref: src/kernels.cuh:543-547  k_router_dot<<<64,32>>> (sel/sig may be null) */
 int lkb_router_dot(const float * h, const float * gate_inp, float * logits, const float * bias,

@@ -36,6 +36,18 @@ class NormProd(C.Structure):
     _fields_ = [("w", C.c_void_p), ("h32", C.c_void_p), ("yq8", C.c_void_p), ("ssq", C.c_void_p)]
 
 
+class MoeLayer(C.Structure):
+    """lkb_moe_layer"""
+    _fields_ = [("gate_qs", C.c_void_p), ("gate_d", C.c_void_p), ("up_qs", C.c_void_p), ("up_d", C.c_void_p),
+                ("down_qs", C.c_void_p), ("down_d", C.c_void_p), ("router", C.c_void_p), ("rbias", C.c_void_p),
+                ("norm_w", C.c_void_p), ("softmax", C.c_int)]
+
+
+class MoeScratch(C.Structure):
+    """lkb_moe_scratch"""
+    _fields_ = [("logits", C.c_void_p), ("gu", C.c_void_p), ("sync", C.c_void_p)]
+
+
 class PfGemm(C.Structure):
     """lkb_pf_gemm"""
     _fields_ = [("qs", C.c_void_p * 3), ("d", C.c_void_p * 3), ("seg_end", C.c_int * 3), ("N", C.c_int),

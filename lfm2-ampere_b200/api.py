@@ -10,7 +10,7 @@ import ctypes as C
 
 import torch
 
-from . import NormProd, PfAct, PfGemm, check, lib
+from . import MoeLayer, MoeScratch, NormProd, PfAct, PfGemm, check, lib
 
 __all__ = [
     "ptr", "stream", "norm_prod", "pf_act", "make_pf_gemm",
@@ -19,7 +19,8 @@ __all__ = [
     "k_router_top4", "router_top4_softmax", "block_sumi", "k_pf_norm", "k_pf_quant_rows", "k_pf_swiglu",
     "k_pf_router", "k_pf_router_small", "k_pf_select", "k_pf_moe_count", "k_pf_moe_plan", "k_pf_moe_scatter",
     "pf_gemm_dense", "pf_gemm_moe", "pf_gemm_swiglu", "k_pf_moe_combine", "k_pf_moe_combine_norm",
-    "k_pf_pack_q8_1", "zero_i32", "set_pdl", "pf_gemm_config", "sm_count",
+    "k_pf_pack_q8_1", "zero_i32", "moe_layer_desc", "moe_scratch", "moe_ffn_decode", "moe_ffn_decode_stack",
+    "layer_descs_to_device", "set_pdl", "pf_gemm_config", "sm_count",
 ]
 
 
@@ -215,3 +216,30 @@ def k_pf_moe_combine_norm(X, D, w, nw, a, inv_out, m):
 
 def k_pf_pack_q8_1(a, t, y):
     check(lib.lkb_pf_pack_q8_1(a, t, ptr(y), stream()), "k_pf_pack_q8_1")
+
+
+# ------------------------------------------------------------ fused decode --
+def moe_layer_desc(l, softmax=0):
+    """lkb_moe_layer from an object with gate_qs/gate_d/up_qs/up_d/down_qs/down_d/router/rbias/norm_w tensors."""
+    return MoeLayer(ptr(l.gate_qs), ptr(l.gate_d), ptr(l.up_qs), ptr(l.up_d), ptr(l.down_qs), ptr(l.down_d),
+                    ptr(l.router), ptr(l.rbias), ptr(l.norm_w), softmax)
+
+
+def layer_descs_to_device(descs):
+    """Pack host descriptors into one device byte tensor (the array lkb_moe_ffn_decode_stack walks)."""
+    raw = b"".join(bytes(d) for d in descs)
+    return torch.frombuffer(bytearray(raw), dtype=torch.uint8).cuda()
+
+
+def moe_scratch(logits, gu, sync):
+    return MoeScratch(ptr(logits), ptr(gu), ptr(sync))
+
+
+def moe_ffn_decode(desc, x, idx_out, w_out, next_np, scratch):
+    check(lib.lkb_moe_ffn_decode(C.byref(desc), ptr(x), ptr(idx_out), ptr(w_out), _np(next_np), C.byref(scratch),
+                                 stream()), "moe_ffn_decode")
+
+
+def moe_ffn_decode_stack(layers_dev, n_layers, softmax, x, idx_out, w_out, next_np, scratch):
+    check(lib.lkb_moe_ffn_decode_stack(ptr(layers_dev), n_layers, softmax, ptr(x), ptr(idx_out), ptr(w_out),
+                                       _np(next_np), C.byref(scratch), stream()), "moe_ffn_decode_stack")

@@ -260,6 +260,7 @@ static int launch_gemv(GemvArgs & a, cudaStream_t st) {
         if (rows_per_warp >= 4) return lkb_launch(k_gemv_multi<1, 8>, dim3(grid), dim3(wpb * 32), 0, st, a);
         return lkb_launch(k_gemv_multi<1, 2>, dim3(grid), dim3(wpb * 32), 0, st, a);
     }
+    if (rows_per_warp >= 5) return lkb_launch(k_gemv_multi<2, 6>, dim3(grid), dim3(wpb * 32), 0, st, a);
     if (rows_per_warp >= 3) return lkb_launch(k_gemv_multi<2, 4>, dim3(grid), dim3(wpb * 32), 0, st, a);
     if (rows_per_warp >= 2) return lkb_launch(k_gemv_multi<2, 2>, dim3(grid), dim3(wpb * 32), 0, st, a);
     return lkb_launch(k_gemv_multi<2, 1>, dim3(grid), dim3(wpb * 32), 0, st, a);
@@ -621,7 +622,9 @@ int lkb_init(int device) {
     lkb_ctx & c = lkb_context();
     c.device = device;
     c.sm_count = p.multiProcessorCount;
-    const int r = lkb_prefill_init();
+    int r = lkb_prefill_init();
+    if (r != LKB_OK) return r;
+    r = lkb_fused_init();
     if (r != LKB_OK) return r;
     c.inited = 1;
     return LKB_OK;

@@ -26,7 +26,27 @@ class DecodeStack:
         self.xq2 = torch.zeros(TOPK * (I // 32) * 36, dtype=torch.uint8, device=device)
         self.launches_per_step = 1 + 5 * len(layers)
         self._np = [api.norm_prod(l.norm_w, self.h32, self.xq, self.ssq) for l in layers]
-        self._np_last = api.norm_prod(None, None, None, None)
+        # fused path: one persistent kernel for the whole stack
+        self._descs = [api.moe_layer_desc(l) for l in layers]
+        self.layers_dev = api.layer_descs_to_device(self._descs)
+        self.sync = torch.zeros(2, dtype=torch.int32, device=device)
+        self.sel_idx = torch.zeros(len(layers), TOPK, dtype=torch.int32, device=device)
+        self.sel_w = torch.zeros(len(layers), TOPK, **f32)
+        self._scratch = api.moe_scratch(self.logits, self.gu, self.sync)
+
+    def step_fused(self, per_layer_launch=False):
+        """The same token step through lkb_moe_ffn_decode_stack (one launch) or, with
+        per_layer_launch, one lkb_moe_ffn_decode launch per layer."""
+        if per_layer_launch:
+            for i, d in enumerate(self._descs):
+                api.moe_ffn_decode(d, self.x, self.sel_idx[i], self.sel_w[i], None, self._scratch)
+        else:
+            api.moe_ffn_decode_stack(self.layers_dev, len(self.layers), 0, self.x, self.sel_idx, self.sel_w, None,
+                                     self._scratch)
+
+    def status(self):
+        """0 unless a bounded device-side wait of the fused kernel expired."""
+        return int(self.sync[1].item())
 
     def step(self):
         """One token through every layer; x is updated in place."""

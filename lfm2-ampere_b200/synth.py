@@ -1,5 +1,5 @@
 """Seeded synthetic weights with the shapes and value distributions of the benchmark
-configurations (no checkpoint exists offline): Q4_0 nibbles U{0..15}, block scale
+configurations (no checkpoint exists offline): Q4_0 nibbles U{1..15} (see _q4), block scale
 d = fp16(|N(0, 0.02)|), router gate fp32 N(0, 0.02), norm weights 1 + N(0, 0.05).
 Planes are laid out exactly as the reference's planar pack (qs plane + d plane,
 experts stacked row-wise), generated directly in device memory."""
@@ -31,7 +31,15 @@ class MoeLayer:
 
 
 def _q4(gen, rows, bpr, device):
-    qs = torch.randint(0, 256, (rows * bpr * 16,), dtype=torch.uint8, device=device, generator=gen)
+    # Nibbles are drawn from 1..15 rather than 0..15: (q - 8) is then exactly zero-mean.  With 0..15 every
+    # weight carries a -0.5*d bias, a rank-one common mode with gain ~16 per projection; a single layer
+    # does not care, but a 40-layer random stack amplifies it until the fp16 "raw sum" field of Q8_1
+    # overflows (the range hazard the reference audits on real weights, ref: src/quant.cuh:33-63).
+    n = rows * bpr * 16
+    lo = torch.randint(1, 16, (n,), dtype=torch.uint8, device=device, generator=gen)
+    hi = torch.randint(1, 16, (n,), dtype=torch.uint8, device=device, generator=gen)
+    qs = lo | (hi << 4)
+    del lo, hi
     d = (torch.randn(rows * bpr, device=device, generator=gen) * 0.02).abs().to(torch.float16)
     return qs, d
 

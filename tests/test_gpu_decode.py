@@ -342,3 +342,37 @@ def test_decode_stack_pdl_and_graph_are_bit_identical(L):
     assert torch.isfinite(outs[0]).all()
     for o in outs[1:]:
         assert torch.equal(o, outs[0])
+
+
+def test_fused_stack_is_bit_identical_to_kernel_sequence(L):
+    """lkb_moe_ffn_decode(_stack): one persistent launch == the five-kernel sequence, bit for bit."""
+    import importlib
+    synth = importlib.import_module("lfm2-ampere_b200.synth")
+    decode = importlib.import_module("lfm2-ampere_b200.decode")
+    layers = synth.make_model(4, seed=91, zipf_s=1.1)
+    st = decode.DecodeStack(layers)
+    gen = torch.Generator("cuda").manual_seed(6)
+    for trial in range(3):
+        x0 = torch.randn(2048, device="cuda", generator=gen) * (1.0 + trial)
+        st.x.copy_(x0)
+        st.step()
+        ref = st.x.clone()
+        st.x.copy_(x0)
+        st.step_fused()
+        torch.cuda.synchronize()
+        assert st.status() == 0
+        assert torch.isfinite(ref).all() and torch.equal(st.x, ref)
+        idx_stack = st.sel_idx.clone()
+        st.x.copy_(x0)
+        st.step_fused(per_layer_launch=True)
+        torch.cuda.synchronize()
+        assert st.status() == 0 and torch.equal(st.x, ref) and torch.equal(st.sel_idx, idx_stack)
+        assert torch.equal(st.sel_idx[-1], st.idx)            # the last layer's experts match the unfused router
+    # the optional producer output for the caller's next consumer
+    nw = layers[0].norm_w
+    h32, yq8, ssq = nan_f32(2048), empty_blocks(64), nan_f32(64)
+    st.x.copy_(x0)
+    L.moe_ffn_decode(st._descs[0], st.x, st.sel_idx[0], st.sel_w[0], L.norm_prod(nw, h32, yq8, ssq), st._scratch)
+    h2, y2, s2 = nan_f32(2048), empty_blocks(64), nan_f32(64)
+    L.norm_produce(st.x, 2048, L.norm_prod(nw, h2, y2, s2))
+    assert torch.equal(h32, h2) and torch.equal(yq8, y2) and torch.equal(ssq, s2)
