@@ -222,7 +222,8 @@ def run_ours(args):
     st = torch.cuda.current_stream()
 
     # one CUDA graph per step shape: copy-in of a resident input, then the 201 kernels
-    use_graph = not args.no_graph
+    fused = args.decode_impl == "fused"
+    use_graph = (not args.no_graph) and not fused
     graph = None
     x_in = torch.zeros(H, device="cuda")
     if use_graph:
@@ -241,6 +242,9 @@ def run_ours(args):
             x_in.copy_(x_pool[i % n_in])
         if graph is not None:
             graph.replay()
+        elif fused:
+            stack.x.copy_(x_in)
+            stack.step_fused()
         else:
             stack.x.copy_(x_in)
             stack.step()
@@ -276,37 +280,51 @@ def run_ours(args):
     ms_e2e = max_over_ranks(ev0.elapsed_time(ev1))
     e2e_tok_s = world * args.steps / (ms_e2e * 1e-3)
 
-    # dominant kernel: MoE gate|up GEMV, CUDA events around every launch of it while the
-    # same steps run un-graphed (the graph hides individual launches from events)
-    evs = []
-    lkb.set_pdl(False)
-    for i in range(min(args.steps, 10)):
-        stack.x.copy_(x_pool[i % n_in])
-        lkb.norm_produce(stack.x, H, stack._np[0])
-        for li, l in enumerate(layers):
-            lkb.k_router_dot(stack.h32, l.router, stack.logits, l.rbias, None, None, stack.ssq, 1e-5)
-            lkb.k_router_top4(stack.logits, l.rbias, stack.idx, stack.w)
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            lkb.k_gemv_q4_0_exp2(l.gate_qs, l.gate_d, l.up_qs, l.up_d, stack.xq, I, H // 32, I, 0, stack.idx,
-                                 stack.gu[:TOPK * I], stack.gu[TOPK * I:], stack.ssq, 1e-5)
-            b.record()
-            evs.append((a, b))
-            lkb.k_swiglu(stack.gu[:TOPK * I], stack.gu[TOPK * I:], TOPK * I, None, stack.xq2, l.down_qs, stack.idx,
-                         H, I // 32, stack.pf_bytes)
-            nxt = stack._np[li + 1] if li + 1 < len(layers) else None
-            lkb.k_moe_down_accum(l.down_qs, l.down_d, stack.xq2, H, I // 32, H, I // 32, stack.idx, stack.w, stack.x, nxt)
-    torch.cuda.synchronize()
-    k_ms = float(np.mean([a.elapsed_time(b) for a, b in evs]))
-    lkb.set_pdl(not args.no_pdl)
-    ach = GATEUP_BYTES / (k_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "k_gemv_multi<2,4> (MoE gate|up GEMV, 8 x 1536 rows x K2048)",
-                "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
-                "peak_kind": f"of {peak_kind}", "traffic": None,
-                "algorithmic_bytes_per_launch": GATEUP_BYTES, "avg_launch_ms": k_ms,
-                "whole_step": {"bytes_per_step": args.layers * LAYER_BYTES,
-                               "achieved_GBs": args.layers * LAYER_BYTES / (ms / args.steps * 1e-3) / 1e9,
-                               "frac": args.layers * LAYER_BYTES / (ms / args.steps * 1e-3) / 1e9 / hbm_peak}}
+    if fused and stack.status() != 0:
+        raise SystemExit(f"fused decode kernel reported status {stack.status()} (a bounded wait expired)")
+    if fused:
+        # the dominant kernel IS the step: one launch of k_moe_ffn_stack per token; its CUDA-event
+        # duration over the timed region is ms / steps
+        k_ms = ms / args.steps
+        ach = args.layers * LAYER_BYTES / (k_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": f"k_moe_ffn_stack (persistent, {args.layers} MoE layers per launch)",
+                    "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
+                    "peak_kind": f"of {peak_kind}", "traffic": None,
+                    "algorithmic_bytes_per_launch": args.layers * LAYER_BYTES, "avg_launch_ms": k_ms}
+        n_launch = args.steps
+    else:
+        # dominant kernel: MoE gate|up GEMV, CUDA events around every launch of it while the
+        # same steps run un-graphed (the graph hides individual launches from events)
+        evs = []
+        lkb.set_pdl(False)
+        for i in range(min(args.steps, 10)):
+            stack.x.copy_(x_pool[i % n_in])
+            lkb.norm_produce(stack.x, H, stack._np[0])
+            for li, l in enumerate(layers):
+                lkb.k_router_dot(stack.h32, l.router, stack.logits, l.rbias, None, None, stack.ssq, 1e-5)
+                lkb.k_router_top4(stack.logits, l.rbias, stack.idx, stack.w)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                lkb.k_gemv_q4_0_exp2(l.gate_qs, l.gate_d, l.up_qs, l.up_d, stack.xq, I, H // 32, I, 0, stack.idx,
+                                     stack.gu[:TOPK * I], stack.gu[TOPK * I:], stack.ssq, 1e-5)
+                b.record()
+                evs.append((a, b))
+                lkb.k_swiglu(stack.gu[:TOPK * I], stack.gu[TOPK * I:], TOPK * I, None, stack.xq2, l.down_qs, stack.idx,
+                             H, I // 32, stack.pf_bytes)
+                nxt = stack._np[li + 1] if li + 1 < len(layers) else None
+                lkb.k_moe_down_accum(l.down_qs, l.down_d, stack.xq2, H, I // 32, H, I // 32, stack.idx, stack.w, stack.x, nxt)
+        torch.cuda.synchronize()
+        k_ms = float(np.mean([a.elapsed_time(b) for a, b in evs]))
+        lkb.set_pdl(not args.no_pdl)
+        ach = GATEUP_BYTES / (k_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "k_gemv_multi<2,6> (MoE gate|up GEMV, 8 x 1536 rows x K2048)",
+                    "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
+                    "peak_kind": f"of {peak_kind}", "traffic": None,
+                    "algorithmic_bytes_per_launch": GATEUP_BYTES, "avg_launch_ms": k_ms,
+                    "whole_step": {"bytes_per_step": args.layers * LAYER_BYTES,
+                                   "achieved_GBs": args.layers * LAYER_BYTES / (ms / args.steps * 1e-3) / 1e9,
+                                   "frac": args.layers * LAYER_BYTES / (ms / args.steps * 1e-3) / 1e9 / hbm_peak}}
+        n_launch = args.steps * stack.launches_per_step
 
     # ---------------------------------------------------------------- prefill (configuration 3)
     pf = None
@@ -363,9 +381,9 @@ def run_ours(args):
                           "bytes_per_token": args.layers * LAYER_BYTES,
                           "cold_cache": "each step streams 871 MB of a 13.6 GB weight set (inputs larger than L2)",
                           "parallelism": "replicas" if world > 1 else "single GPU",
-                          "cuda_graph": use_graph, "pdl": not args.no_pdl},
+                          "decode_impl": args.decode_impl, "cuda_graph": use_graph, "pdl": (not args.no_pdl) and not fused},
                "e2e": {"value": e2e_tok_s, "unit": UNIT, "h2d_bytes_per_step": H * 4, "d2h_bytes_per_step": H * 4},
-               "gpu_launches": args.steps * stack.launches_per_step,
+               "gpu_launches": n_launch,
                "roofline": roofline, "cpu_baseline": cb, "clocks": clocks, "prefill": pf}
         print(json.dumps(out), flush=True)
     if world > 1:
@@ -385,6 +403,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--decode-impl", default="fused", choices=["fused", "kernels"],
+                    help="fused: one persistent launch per token (lkb_moe_ffn_decode_stack); "
+                         "kernels: the reference's five launches per layer, graph + PDL")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -81,12 +81,12 @@ __device__ __forceinline__ float lkb_norm_inv(const float * __restrict__ ssq, in
 // Integer block sum: 16 weight bytes (unsigned nibbles) against 32 int8.
 // ref: src/quant.cuh:141-151
 __device__ __forceinline__ int lkb_sumi(const uint4 q, const int (&x)[8]) {
-    int s = 0;
-    s = __dp4a((int) (q.x & 0x0F0F0F0Fu), x[0], s);  s = __dp4a((int) ((q.x >> 4) & 0x0F0F0F0Fu), x[4], s);
-    s = __dp4a((int) (q.y & 0x0F0F0F0Fu), x[1], s);  s = __dp4a((int) ((q.y >> 4) & 0x0F0F0F0Fu), x[5], s);
-    s = __dp4a((int) (q.z & 0x0F0F0F0Fu), x[2], s);  s = __dp4a((int) ((q.z >> 4) & 0x0F0F0F0Fu), x[6], s);
-    s = __dp4a((int) (q.w & 0x0F0F0F0Fu), x[3], s);  s = __dp4a((int) ((q.w >> 4) & 0x0F0F0F0Fu), x[7], s);
-    return s;
+    // four independent integer chains (integer addition is exact in any order)
+    int s0 = __dp4a((int) (q.x & 0x0F0F0F0Fu), x[0], 0), s1 = __dp4a((int) (q.y & 0x0F0F0F0Fu), x[1], 0);
+    int s2 = __dp4a((int) (q.z & 0x0F0F0F0Fu), x[2], 0), s3 = __dp4a((int) (q.w & 0x0F0F0F0Fu), x[3], 0);
+    s0 = __dp4a((int) ((q.x >> 4) & 0x0F0F0F0Fu), x[4], s0); s1 = __dp4a((int) ((q.y >> 4) & 0x0F0F0F0Fu), x[5], s1);
+    s2 = __dp4a((int) ((q.z >> 4) & 0x0F0F0F0Fu), x[6], s2); s3 = __dp4a((int) ((q.w >> 4) & 0x0F0F0F0Fu), x[7], s3);
+    return (s0 + s1) + (s2 + s3);
 }
 
 // acc + d4*(d8*sumi - 8*sum): inner = fma(d8, float(sumi), -8sum), acc' = fma(d4, inner, acc).
@@ -119,24 +119,28 @@ __device__ __forceinline__ void lkb_pdl_trigger() { asm volatile("griddepcontrol
 // Top-4 of 64 with the reference's tie rule (greater value wins, equal value ->
 // lower index), then w_k = sig[idx_k] / max(sum_k, guard).  One warp; every lane
 // ends with the full result.  ref: src/kernels.cuh:515-541
+__device__ __forceinline__ unsigned lkb_orderable(float f) {       // monotone float -> uint map
+    const unsigned u = __float_as_uint(__fadd_rn(f, 0.0f));       // -0 -> +0: equal floats get equal keys
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
 __device__ __forceinline__ void lkb_router_select(const float * __restrict__ sel,
                                                   const float * __restrict__ sig,
                                                   int lane, int * ord, float * wv) {
-    float v0 = sel[lane], v1 = sel[lane + 32];
-    const int i0 = lane, i1 = lane + 32;
+    // Lane l holds experts l and l+32.  Each round: the maximum over all 64 values by one
+    // hardware reduction on order-preserving keys, then the LOWEST expert index holding it
+    // (ballot over the low half first) -- the same winner as the reference's butterfly with
+    // "greater wins, equal -> lower index", in 3 warp-wide instructions instead of 10 shuffles.
+    unsigned k0 = lkb_orderable(sel[lane]), k1 = lkb_orderable(sel[lane + 32]);
+    const unsigned gone = lkb_orderable(-1e30f);
 #pragma unroll
     for (int r = 0; r < LKB_TOP_K; ++r) {
-        float mv = (v0 >= v1) ? v0 : v1;
-        int   mi = (v0 >= v1) ? i0 : i1;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(LKB_FULL, mv, o);
-            const int   oi = __shfl_xor_sync(LKB_FULL, mi, o);
-            if (ov > mv || (ov == mv && oi < mi)) { mv = ov; mi = oi; }
-        }
+        const unsigned m = __reduce_max_sync(LKB_FULL, k0 > k1 ? k0 : k1);
+        const unsigned lo = __ballot_sync(LKB_FULL, k0 == m);
+        const unsigned hi = __ballot_sync(LKB_FULL, k1 == m);
+        const int mi = lo ? (__ffs(lo) - 1) : (32 + __ffs(hi) - 1);
         ord[r] = mi;
-        if (i0 == mi) v0 = -1e30f;
-        if (i1 == mi) v1 = -1e30f;
+        if (mi == lane) k0 = gone;
+        if (mi == lane + 32) k1 = gone;
     }
     float wsum = 0.0f;
 #pragma unroll

@@ -40,7 +40,8 @@ struct FusedSmem {
     alignas(16)  float  router[LKB_HIDDEN];                               // 8192
     alignas(16)  float  h[LKB_HIDDEN];                                    // 8192 raw u = x*w
     alignas(16)  lkb_q8blk xq[LKB_HIDDEN / 32];                           // 2304
-    alignas(16)  lkb_q8blk xq2[LKB_TOP_K * DN_BPR];                       // 6912
+    alignas(16)  int8_t xq2_q[LKB_TOP_K * DN_BPR * 32];                   // 6144: quants of silu(g)*u, 32 B per block
+    alignas(8)   float2 xq2_s[LKB_TOP_K * DN_BPR];                        // 1536: (float(fp16 d), 8*float(fp16 sum))
     float  ssq[LKB_HIDDEN / 32];
     float  sel[LKB_N_EXPERTS];
     float  sig[LKB_N_EXPERTS];
@@ -49,6 +50,8 @@ struct FusedSmem {
     float  wk[LKB_TOP_K];
     float  inv;
     int    abort;
+    unsigned bar_target;
+    alignas(8) lkb_moe_layer ly;          // this layer's descriptor (staged: a global read costs ~1 us of latency)
     alignas(8) unsigned long long mbar_gu[N_GU_CH];
     alignas(8) unsigned long long mbar_dn[N_DN_CH];
     alignas(8) unsigned long long mbar_rt;
@@ -85,18 +88,24 @@ __device__ __forceinline__ unsigned ld_acquire(const unsigned * p) {
 }
 
 // Grid barrier over gridDim.x CTAs on a monotonically increasing counter (zeroed by
-// the launcher).  Returns false if the wait expired or another CTA reported a fault.
-__device__ __forceinline__ bool grid_barrier(unsigned * bar, unsigned * status, FusedSmem & S, unsigned code) {
-    __syncthreads();
+// the launcher), split into arrive and wait so that independent work can sit between
+// them.  Both are called by every thread; thread 0 does the global traffic.
+// wait returns false if it expired or another CTA reported a fault.
+__device__ __forceinline__ void grid_arrive(unsigned * bar, FusedSmem & S) {
+    __syncthreads();                                   // this CTA's global writes are issued
     if (threadIdx.x == 0) {
         __threadfence();
         const unsigned ticket = atomicAdd(bar, 1u);
-        const unsigned target = (ticket / gridDim.x + 1u) * gridDim.x;
+        S.bar_target = (ticket / gridDim.x + 1u) * gridDim.x;
+    }
+}
+__device__ __forceinline__ bool grid_wait(unsigned * bar, unsigned * status, FusedSmem & S, unsigned code) {
+    if (threadIdx.x == 0) {
+        const unsigned target = S.bar_target;
         bool ok = false;
         for (unsigned i = 0; i < SPIN_LIMIT; ++i) {
             if (ld_acquire(bar) >= target) { ok = true; break; }
             if ((i & 1023u) == 1023u && ld_acquire(status) != 0u) break;
-            __nanosleep(20);
         }
         if (!ok) { atomicCAS(status, 0u, code); S.abort = 1; }
     }
@@ -123,6 +132,23 @@ __device__ __forceinline__ void issue_rows(const SegView & v, int seg_rows, int 
         bulk_g2s(sq, v.q[s] + (size_t) r * bpr, (unsigned) n * bpr * 16u, mb);
         bulk_g2s(sd, v.d[s] + (size_t) r * bpr, (unsigned) n * bpr * 2u, mb);
         sq += (size_t) n * bpr * 16; sd += (size_t) n * bpr; g += n;
+    }
+}
+
+// Gate|up logical rows g = (half*4 + k)*1536 + row; [g_begin, g_end) may straddle one segment boundary.
+__device__ __forceinline__ void issue_gu_rows(const lkb_moe_layer & ly, const int * idx, int g_begin, int g_end,
+                                              unsigned char * sq, __half * sd, unsigned long long * mb) {
+    mbar_expect_tx(mb, (unsigned) (g_end - g_begin) * (unsigned) GU_BPR * 18u);
+    int g = g_begin;
+    while (g < g_end) {
+        const int seg = g / LKB_MOE_INTER, r = g - seg * LKB_MOE_INTER;
+        int n = g_end - g; if (n > LKB_MOE_INTER - r) n = LKB_MOE_INTER - r;
+        const size_t blk = ((size_t) idx[seg & 3] * LKB_MOE_INTER + r) * GU_BPR;
+        const uint4 * q = (const uint4 *) (seg < 4 ? ly.gate_qs : ly.up_qs) + blk;
+        const __half * d = (const __half *) (seg < 4 ? ly.gate_d : ly.up_d) + blk;
+        bulk_g2s(sq, q, (unsigned) n * GU_BPR * 16u, mb);
+        bulk_g2s(sd, d, (unsigned) n * GU_BPR * 2u, mb);
+        sq += (size_t) n * GU_BPR * 16; sd += (size_t) n * GU_BPR; g += n;
     }
 }
 
@@ -162,6 +188,39 @@ __device__ __forceinline__ void load_xregs(const lkb_q8blk * xq, int bpr, int la
     }
 }
 
+// Optional phase timestamps (clock64 of thread 0) for tuning: [cta][layer][16].
+static unsigned long long * g_fused_timing = nullptr;
+#define FUSED_STAMP(slot) do { if (a.timing && tid == 0 && l < 4) a.timing[((size_t) cta * 4 + l) * 16 + (slot)] = clock64(); } while (0)
+
+
+// Four independent 32-element blocks quantised together: the same operations per block
+// as lkb_quant_lane, with the four dependency chains interleaved so their latencies
+// overlap (the idea of the reference's quantize_q8_1_warp2, ref: src/quant.cuh:83-104).
+template <int N>
+__device__ __forceinline__ void quantN(const float (&v)[N], int (&q)[N], float (&d)[N], float (&sum)[N]) {
+    unsigned am[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) { am[j] = __reduce_max_sync(LKB_FULL, __float_as_uint(fabsf(v[j]))); sum[j] = v[j]; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int j = 0; j < N; ++j) sum[j] = __fadd_rn(sum[j], __shfl_xor_sync(LKB_FULL, sum[j], o));
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+        d[j] = __fdiv_rn(__uint_as_float(am[j]), 127.0f);
+        q[j] = (am[j] == 0u) ? 0 : (int) roundf(__fdiv_rn(v[j], d[j]));
+    }
+}
+__device__ __forceinline__ void quant4(const float (&v)[4], int (&q)[4], float (&d)[4], float (&sum)[4]) { quantN<4>(v, q, d, sum); }
+__device__ __forceinline__ void sumsq4(const float (&x)[4], float (&sq)[4]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) sq[j] = __fmul_rn(x[j], x[j]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) sq[j] = __fadd_rn(sq[j], __shfl_xor_sync(LKB_FULL, sq[j], o));
+}
+
 struct FusedArgs {
     lkb_moe_layer         one;         // used when layers == nullptr
     const lkb_moe_layer * layers;      // device array, or null
@@ -177,19 +236,30 @@ struct FusedArgs {
     float *               gu;          // scratch [2*4*1536]
     unsigned *            bar;         // scratch [2]: {barrier counter, status}
     int                   softmax;
+    unsigned long long *  timing;
 };
 
-// Quantise u = x*w for all 2048 elements into S.xq / S.ssq / S.h (every CTA, redundantly).
-__device__ __forceinline__ void fused_norm_prod(FusedSmem & S, const float * __restrict__ x, const float * __restrict__ nw) {
+// Blocks b = warp + 16 j (j = 0..3) of the 2048-vector belong to this warp, element `lane`.
+// Loads x (written by other CTAs -> L2) and forms u = x*w into S.h.
+__device__ __forceinline__ void fused_load_u(FusedSmem & S, const float * __restrict__ x, const float (&nw)[4],
+                                             float (&xv)[4], float (&uv)[4]) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll
-    for (int j = 0; j < (LKB_HIDDEN / 32) / FUSED_WARPS; ++j) {
+    for (int j = 0; j < 4; ++j) xv[j] = __ldcg(x + (warp + FUSED_WARPS * j) * 32 + lane);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { uv[j] = __fmul_rn(xv[j], nw[j]); S.h[(warp + FUSED_WARPS * j) * 32 + lane] = uv[j]; }
+}
+// Q8_1 of u, ssq of x, inv -> S.xq, S.ssq, S.inv (ends with a CTA barrier).
+__device__ __forceinline__ void fused_quant_u(FusedSmem & S, const float (&xv)[4], const float (&uv)[4]) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int q[4]; float d[4], sm[4], sq[4];
+    quant4(uv, q, d, sm);
+    sumsq4(xv, sq);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
         const int b = warp + FUSED_WARPS * j;
-        const int i = b * 32 + lane;
-        const float xv = __ldcg(x + i);                    // written by other CTAs: bypass L1
-        const float uv = __fmul_rn(xv, nw[i]);
-        S.h[i] = uv;
-        lkb_norm_prod_warp(xv, uv, lane, S.xq, S.ssq, b);
+        S.xq[b].qs[lane] = (int8_t) q[j];
+        if (lane == 0) { S.xq[b].ds = __floats2half2_rn(d[j], sm[j]); S.ssq[b] = sq[j]; }
     }
     __syncthreads();
     if (warp == 0) {
@@ -224,45 +294,65 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
     __syncthreads();
 
     const lkb_moe_layer * L = a.layers ? a.layers : &a.one;
-    // first layer's router row
+    // first layer's router row, first layer's norm weights
     if (cta < LKB_N_EXPERTS && tid == 0) {
         mbar_expect_tx(&S.mbar_rt, LKB_HIDDEN * 4);
         bulk_g2s(S.router, L[0].router + (size_t) cta * LKB_HIDDEN, LKB_HIDDEN * 4, &S.mbar_rt);
     }
+    float nw[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) nw[j] = L[0].norm_w[(warp + FUSED_WARPS * j) * 32 + lane];
+
+    if (tid < (int) (sizeof(lkb_moe_layer) / 8))
+        reinterpret_cast<unsigned long long *>(&S.ly)[tid] = reinterpret_cast<const unsigned long long *>(&L[0])[tid];
+    __syncthreads();
 
     for (int l = 0; l < a.n_layers; ++l) {
-        const lkb_moe_layer & ly = L[l];
+        const lkb_moe_layer & ly = S.ly;
         const unsigned par = (unsigned) (l & 1);
 
-        // ---- phase 0: u = x*w, Q8_1, ssq, inv (every CTA) ----------------------
-        fused_norm_prod(S, a.x, ly.norm_w);
-
-        // ---- phase 1: router logit of expert `cta` ------------------------------
-        if (cta < LKB_N_EXPERTS && warp == 0) {
-            if (!mbar_wait(&S.mbar_rt, par)) { if (lane == 0) { atomicCAS(status, 0u, 100u + l); S.abort = 1; } }
-            else {
-                float acc = 0.0f;
+        // ---- A: u = x*w; the 64 router CTAs produce their logit; arrive ----------
+        FUSED_STAMP(0);
+        float xv[4], uv[4];
+        fused_load_u(S, a.x, nw, xv, uv);
+        if (cta < LKB_N_EXPERTS) {
+            __syncthreads();                                        // S.h complete
+            if (warp == 0) {
+                if (!mbar_wait(&S.mbar_rt, par)) { if (lane == 0) { atomicCAS(status, 0u, 100u + l); S.abort = 1; } }
+                else {
+                    float acc = 0.0f;
 #pragma unroll 16
-                for (int j = 0; j < LKB_HIDDEN / 32; ++j) acc = fmaf(S.router[j * 32 + lane], S.h[j * 32 + lane], acc);
-                acc = lkb_warp_sum(acc);
-                if (lane == 0) a.logits[cta] = __fmul_rn(acc, S.inv);
+                    for (int j = 0; j < LKB_HIDDEN / 32; ++j) acc = fmaf(S.router[j * 32 + lane], S.h[j * 32 + lane], acc);
+                    acc = lkb_warp_sum(acc);
+                    if (lane == 0) S.sel[0] = acc;                   // multiplied by inv below, once inv exists
+                }
             }
         }
-        if (!grid_barrier(a.bar, status, S, 1000u + 10u * l + 1u)) return;
+        FUSED_STAMP(1);
+        // ---- B: Q8_1 of u, ssq, inv (needed for the logit scale and for gate|up) --
+        fused_quant_u(S, xv, uv);
+        if (cta < LKB_N_EXPERTS && tid == 0) a.logits[cta] = __fmul_rn(S.sel[0], S.inv);
+        FUSED_STAMP(2);
+        grid_arrive(a.bar, S);
+        if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 1u)) return;
+        FUSED_STAMP(3);
 
-        // ---- phase 2: selection (every CTA), then request every weight row ------
-        if (tid < LKB_N_EXPERTS) {
-            const float lg = __ldcg(a.logits + tid);
-            if (!a.softmax) {
-                const float g = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-lg)));
-                S.sig[tid] = g;
-                S.sel[tid] = __fadd_rn(g, ly.rbias ? ly.rbias[tid] : 0.0f);
-            } else {
-                S.sel[tid] = lg;
+        // ---- C: selection (every CTA, warp 0; the softmax gate takes the 64-thread path) ----
+        if (!a.softmax) {
+            if (warp == 0) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int e = lane + 32 * h;
+                    const float lg = __ldcg(a.logits + e);
+                    const float g = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-lg)));
+                    S.sig[e] = g;
+                    S.sel[e] = __fadd_rn(g, ly.rbias ? ly.rbias[e] : 0.0f);
+                }
+                __syncwarp();
             }
-        }
-        __syncthreads();
-        if (a.softmax) {
+        } else {
+            if (tid < LKB_N_EXPERTS) S.sel[tid] = __ldcg(a.logits + tid);
+            __syncthreads();
             float p = 0.0f;
             if (tid < LKB_N_EXPERTS) {
                 float mx = S.sel[0];
@@ -281,6 +371,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
             if (tid < LKB_N_EXPERTS) { S.sig[tid] = pn; S.sel[tid] = __fadd_rn(pn, ly.rbias ? ly.rbias[tid] : 0.0f); }
             __syncthreads();
         }
+        FUSED_STAMP(8);
         if (warp == 0) {
             int ord[LKB_TOP_K]; float wv[LKB_TOP_K];
             lkb_router_select(S.sel, S.sig, lane, ord, wv);
@@ -297,34 +388,32 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
             }
         }
         __syncthreads();
-        if (tid == 0) {
+        FUSED_STAMP(9);
+        // ---- D: request every weight row of the layer, one issuing lane per chunk ---
+        if (lane == 0) {
             fence_proxy_async();
-            SegView gv, dv;
-#pragma unroll
-            for (int k = 0; k < LKB_TOP_K; ++k) {
-                const size_t eo = (size_t) S.idx[k] * LKB_MOE_INTER * GU_BPR;
-                gv.q[k] = (const uint4 *) ly.gate_qs + eo;     gv.d[k] = (const __half *) ly.gate_d + eo;
-                gv.q[4 + k] = (const uint4 *) ly.up_qs + eo;   gv.d[4 + k] = (const __half *) ly.up_d + eo;
-                const size_t ed = (size_t) S.idx[k] * LKB_HIDDEN * DN_BPR;
-                dv.q[k] = (const uint4 *) ly.down_qs + ed;     dv.d[k] = (const __half *) ly.down_d + ed;
-            }
-            for (int c = 0; c < n_gu_ch; ++c) {
-                const int j0 = c * CH_ROWS, j1 = min(n_gu, j0 + CH_ROWS);
-                issue_rows(gv, LKB_MOE_INTER, GU_BPR, gu0 + j0, gu0 + j1, S.gu_q + (size_t) j0 * GU_BPR * 16,
-                           S.gu_d + (size_t) j0 * GU_BPR, &S.mbar_gu[c]);
-            }
-            for (int k = 0; k < LKB_TOP_K; ++k)
-                for (int c = 0; c < dn_ch_per_k; ++c) {
-                    const int j0 = c * CH_ROWS, j1 = min(n_dn, j0 + CH_ROWS);
-                    // expert k's rows dn0+j0 .. dn0+j1 (one segment: no straddle)
-                    SegView one; one.q[0] = dv.q[k]; one.d[0] = dv.d[k];
-                    issue_rows(one, LKB_HIDDEN, DN_BPR, dn0 + j0, dn0 + j1,
-                               S.dn_q + ((size_t) k * MAX_DN_ROWS + j0) * DN_BPR * 16,
-                               S.dn_d + ((size_t) k * MAX_DN_ROWS + j0) * DN_BPR, &S.mbar_dn[k * dn_ch_per_k + c]);
+            for (int c = warp; c < n_gu_ch + LKB_TOP_K * dn_ch_per_k; c += FUSED_WARPS) {
+                if (c < n_gu_ch) {
+                    const int j0 = c * CH_ROWS, j1 = min(n_gu, j0 + CH_ROWS);
+                    issue_gu_rows(ly, S.idx, gu0 + j0, gu0 + j1, S.gu_q + (size_t) j0 * GU_BPR * 16,
+                                  S.gu_d + (size_t) j0 * GU_BPR, &S.mbar_gu[c]);
+                } else {
+                    const int cc = c - n_gu_ch, k = cc / dn_ch_per_k, ch = cc % dn_ch_per_k;
+                    const int j0 = ch * CH_ROWS, j1 = min(n_dn, j0 + CH_ROWS);
+                    const size_t ed = (size_t) S.idx[k] * LKB_HIDDEN * DN_BPR;
+                    unsigned long long * mb = &S.mbar_dn[k * dn_ch_per_k + ch];
+                    mbar_expect_tx(mb, (unsigned) (j1 - j0) * DN_BPR * 18u);
+                    bulk_g2s(S.dn_q + ((size_t) k * MAX_DN_ROWS + j0) * DN_BPR * 16,
+                             (const uint4 *) ly.down_qs + ed + (size_t) (dn0 + j0) * DN_BPR, (unsigned) (j1 - j0) * DN_BPR * 16u, mb);
+                    bulk_g2s(S.dn_d + ((size_t) k * MAX_DN_ROWS + j0) * DN_BPR,
+                             (const __half *) ly.down_d + ed + (size_t) (dn0 + j0) * DN_BPR, (unsigned) (j1 - j0) * DN_BPR * 2u, mb);
                 }
+            }
         }
+        __syncwarp();
+        FUSED_STAMP(4);
 
-        // ---- phase 3: gate|up rows of this CTA ----------------------------------
+        // ---- E: gate|up rows of this CTA ------------------------------------------
         {
             int xq[2][8]; float d8[2], s8[2];
             load_xregs<2>(S.xq, GU_BPR, lane, xq, d8, s8);
@@ -336,55 +425,107 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
                 }
                 const float acc = lkb_warp_sum(smem_row_partial<2>(S.gu_q + (size_t) j * GU_BPR * 16, S.gu_d + (size_t) j * GU_BPR,
                                                                    GU_BPR, lane, xq, d8, s8));
-                // logical row -> (half, k, row): the stand-alone kernel's y_a / y_b layout, gate first
+                // logical row g = (half*4 + k)*1536 + row: the stand-alone kernel's y_a | y_b layout
                 if (lane == 0) a.gu[gu0 + j] = __fmul_rn(acc, ninv);
             }
         }
-        if (!grid_barrier(a.bar, status, S, 1000u + 10u * l + 2u)) return;
+        FUSED_STAMP(5);
+        grid_arrive(a.bar, S);
+        // between arrive and wait: the next layer's router row and norm weights (static data)
+        if (l + 1 < a.n_layers) {
+            if (cta < LKB_N_EXPERTS && tid == 0) {
+                fence_proxy_async();
+                mbar_expect_tx(&S.mbar_rt, LKB_HIDDEN * 4);
+                bulk_g2s(S.router, L[l + 1].router + (size_t) cta * LKB_HIDDEN, LKB_HIDDEN * 4, &S.mbar_rt);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) nw[j] = L[l + 1].norm_w[(warp + FUSED_WARPS * j) * 32 + lane];
+        }
+        if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 2u)) return;
+        FUSED_STAMP(6);
 
-        // ---- phase 4: SwiGLU + Q8_1 (every CTA), down rows, residual ------------
+        // ---- F: SwiGLU + Q8_1 (every CTA), down rows, residual ---------------------
         {
-            const int GU = LKB_TOP_K * LKB_MOE_INTER;
-            for (int b = warp; b < GU / 32; b += FUSED_WARPS) {
-                const int i = b * 32 + lane;
-                const float g = __ldcg(a.gu + i), u = __ldcg(a.gu + GU + i);
-                const float v = __fmul_rn(lkb_silu(g), u);
-                lkb_quant_store(v, S.xq2 + b, lane);
+            const int GU = LKB_TOP_K * LKB_MOE_INTER;             // 6144 = 192 blocks, 12 per warp
+            float g[12], u[12], v[12], d[12], sm[12]; int q[12];
+#pragma unroll
+            for (int j = 0; j < 12; ++j) {
+                const int i = (warp + FUSED_WARPS * j) * 32 + lane;
+                g[j] = __ldcg(a.gu + i); u[j] = __ldcg(a.gu + GU + i);
+            }
+#pragma unroll
+            for (int j = 0; j < 12; ++j) v[j] = __fmul_rn(lkb_silu(g[j]), u[j]);
+            FUSED_STAMP(10);
+            quantN<12>(v, q, d, sm);
+#pragma unroll
+            for (int j = 0; j < 12; ++j) {
+                const int b = warp + FUSED_WARPS * j;
+                S.xq2_q[b * 32 + lane] = (int8_t) q[j];
+                if (lane == 0) {
+                    const __half2 ds = __floats2half2_rn(d[j], sm[j]);
+                    S.xq2_s[b] = make_float2(__low2float(ds), __fmul_rn(8.0f, __high2float(ds)));
+                }
             }
         }
         __syncthreads();
-        // next layer's router row can start now (S.router is no longer read in this layer)
-        if (l + 1 < a.n_layers && cta < LKB_N_EXPERTS && tid == 0) {
-            fence_proxy_async();
-            mbar_expect_tx(&S.mbar_rt, LKB_HIDDEN * 4);
-            bulk_g2s(S.router, L[l + 1].router + (size_t) cta * LKB_HIDDEN, LKB_HIDDEN * 4, &S.mbar_rt);
-        }
-        for (int t = warp; t < n_dn * LKB_TOP_K; t += FUSED_WARPS) {
-            const int k = t % LKB_TOP_K, j = t / LKB_TOP_K;
-            int xq[2][8]; float d8[2], s8[2];
-            load_xregs<2>(S.xq2 + k * DN_BPR, DN_BPR, lane, xq, d8, s8);
-            if (!mbar_wait(&S.mbar_dn[k * dn_ch_per_k + j / CH_ROWS], par)) {
-                if (lane == 0) { atomicCAS(status, 0u, 300u + l); S.abort = 1; }
-                break;
+        FUSED_STAMP(11);
+        // one output row per warp, its four expert dots interleaved
+        for (int j = warp; j < n_dn; j += FUSED_WARPS) {
+            bool ok = true;
+#pragma unroll
+            for (int k = 0; k < LKB_TOP_K; ++k) ok = ok && mbar_wait(&S.mbar_dn[k * dn_ch_per_k + j / CH_ROWS], par);
+            if (!ok) { if (lane == 0) { atomicCAS(status, 0u, 300u + l); S.abort = 1; } break; }
+            float acc[LKB_TOP_K];
+#pragma unroll
+            for (int k = 0; k < LKB_TOP_K; ++k) {
+                const unsigned char * wq = S.dn_q + ((size_t) k * MAX_DN_ROWS + j) * DN_BPR * 16;
+                const __half * wd = S.dn_d + ((size_t) k * MAX_DN_ROWS + j) * DN_BPR;
+                float acc_k = 0.0f;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int blk = lane + 32 * h;
+                    if (blk < DN_BPR) {
+                        const uint4 w = *reinterpret_cast<const uint4 *>(wq + (size_t) blk * 16);
+                        const int4 x0 = *reinterpret_cast<const int4 *>(S.xq2_q + (k * DN_BPR + blk) * 32);
+                        const int4 x1 = *reinterpret_cast<const int4 *>(S.xq2_q + (k * DN_BPR + blk) * 32 + 16);
+                        const int xv8[8] = { x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w };
+                        const float2 sc = S.xq2_s[k * DN_BPR + blk];
+                        acc_k = lkb_block_acc(__half2float(wd[blk]), sc.x, lkb_sumi(w, xv8), sc.y, acc_k);
+                    }
+                }
+                acc[k] = acc_k;
             }
-            const float acc = lkb_warp_sum(smem_row_partial<2>(S.dn_q + ((size_t) k * MAX_DN_ROWS + j) * DN_BPR * 16,
-                                                               S.dn_d + ((size_t) k * MAX_DN_ROWS + j) * DN_BPR,
-                                                               DN_BPR, lane, xq, d8, s8));
-            if (lane == 0) S.dot[k][j] = acc;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int k = 0; k < LKB_TOP_K; ++k) acc[k] = __fadd_rn(acc[k], __shfl_xor_sync(LKB_FULL, acc[k], o));
+            if (lane == 0) {
+#pragma unroll
+                for (int k = 0; k < LKB_TOP_K; ++k) S.dot[k][j] = acc[k];
+            }
         }
         __syncthreads();
+        FUSED_STAMP(12);
         if (tid < n_dn) {
             float acc = 0.0f;
 #pragma unroll
             for (int k = 0; k < LKB_TOP_K; ++k) acc = fmaf(S.wk[k], S.dot[k][tid], acc);
             a.x[dn0 + tid] = __fadd_rn(__ldcg(a.x + dn0 + tid), acc);
         }
-        if (!grid_barrier(a.bar, status, S, 1000u + 10u * l + 3u)) return;
+        FUSED_STAMP(7);
+        grid_arrive(a.bar, S);
+        if (l + 1 < a.n_layers && tid < (int) (sizeof(lkb_moe_layer) / 8))
+            reinterpret_cast<unsigned long long *>(&S.ly)[tid] = reinterpret_cast<const unsigned long long *>(&L[l + 1])[tid];
+        if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 3u)) return;
     }
 
     // optional: the quantised, un-normalised activation of the final x for the caller's next consumer
     if (a.final_norm_w && cta == 0) {
-        fused_norm_prod(S, a.x, a.final_norm_w);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) nw[j] = a.final_norm_w[(warp + FUSED_WARPS * j) * 32 + lane];
+        float xv[4], uv[4];
+        fused_load_u(S, a.x, nw, xv, uv);
+        fused_quant_u(S, xv, uv);
         for (int i = tid; i < LKB_HIDDEN; i += FUSED_THREADS) if (a.out_h32) a.out_h32[i] = S.h[i];
         for (int i = tid; i < LKB_HIDDEN / 32 * 9; i += FUSED_THREADS)
             reinterpret_cast<int *>(a.out_yq8)[i] = reinterpret_cast<const int *>(S.xq)[i];
@@ -414,6 +555,7 @@ static int fused_launch(FusedArgs & a, cudaStream_t st) {
     if ((GU_TOTAL + grid - 1) / grid > MAX_GU_ROWS || (LKB_HIDDEN + grid - 1) / grid > MAX_DN_ROWS) return LKB_ERR_DEVICE;
     cudaError_t e = cudaMemsetAsync(a.bar, 0, 2 * sizeof(unsigned), st);
     if (e != cudaSuccess) return -(int) e;
+    a.timing = g_fused_timing;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid); cfg.blockDim = dim3(FUSED_THREADS); cfg.dynamicSmemBytes = sizeof(FusedSmem); cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -426,6 +568,9 @@ static int fused_launch(FusedArgs & a, cudaStream_t st) {
 }
 
 extern "C" {
+
+// Tuning hook (not part of the public header): device buffer of [#CTAs][4 layers][16] clock64 stamps, or null.
+__attribute__((visibility("default"))) int lkb_debug_fused_timing(unsigned long long * buf) { g_fused_timing = buf; return LKB_OK; }
 
 int lkb_moe_ffn_decode(const lkb_moe_layer * layer, float * x, int * idx_out, float * w_out,
                        const lkb_norm_prod_t * next, const lkb_moe_scratch * scratch, lkb_stream_t st) {
