@@ -242,6 +242,10 @@ int lkb_pf_gemm_swiglu(const lkb_pf_gemm * g, int max_tiles, lkb_stream_t st);
  * tensor-core form or an error.  Also read once from the environment variable
  * LKB_PF_CFG by lkb_init().  ref: src/prefill.cu:813-848 (LK_PF_CFG_DENSE/MOE/SWIGLU) */
 int lkb_pf_gemm_config(int cfg);
+/* Every device-side wait of the tensor-core form is bounded; this SYNCHRONISES the device and
+ * returns 0, or the code of the first wait that expired since the last call (10 loader,
+ * 20/21 MMA issuer, 30/31 epilogue) and clears it.  No counterpart in the reference. */
+int lkb_pf_gemm_status(void);
 /* ref: src/prefill.cuh:123-127  k_pf_moe_combine / k_pf_moe_combine_norm / k_pf_pack_q8_1 */
 int lkb_pf_moe_combine(float * X, const float * D, const float * w, int m, lkb_stream_t st);
 int lkb_pf_moe_combine_norm(float * X, const float * D, const float * w, const float * nw, lkb_pf_act a,

@@ -1,5 +1,451 @@
-// lkb_gemm_tc.cu - tensor-core (tcgen05) form of the Q4_0 x Q8_1 grouped GEMM.
+// lkb_gemm_tc.cu - tensor-core form of the Q4_0 x Q8_1 grouped GEMM for sm_100a:
+// tcgen05.mma.kind::i8 with accumulators in tensor memory (TMEM).
+//
+//   out[slot][n] (+)= scale[arow] * sum_{b ascending} fma(d4[n][b], fma(d8[arow][b], float(S_b), -8sum[arow][b]), .)
+//   S_b = sum_{i<32} nibble[n][b][i] * q8[arow][b][i]                     (int32, exact)
+//
+// One MMA per 32-element block: K = 32 int8 is exactly one Q4_0/Q8_1 block, and the
+// per-block scales forbid accumulating across blocks inside the tensor core, so every
+// block's 128x128 int32 result is read back from TMEM and folded into fp32 register
+// accumulators by the CUDA cores (2 FMA + 1 convert per value).  That epilogue, not
+// the MMA, bounds the kernel (MMA ~64 clk per block per SM, epilogue >= 256), so the
+// design spends the SM on it:
+//   * M (TMEM lanes) = 128 tokens, N (TMEM columns) = 128 weight rows.  A thread owns one
+//     token: d8 / 8sum are per-thread scalars, the 32 intermediate rows of a Q8_1 output
+//     block sit in 32 registers of one thread, so the SwiGLU epilogue quantises with no
+//     shuffle at all (in the standard butterfly order: bit-identical to the unfused path);
+//   * warps 0-3 load: activations are gathered through `perm` and weights are expanded
+//     nibble -> int8 straight into the canonical K-major core-matrix layout (8 rows x
+//     16 B); warp 12 lane 0 issues the MMAs; warps 4-11 are the epilogue (two per TMEM
+//     lane quadrant, splitting the columns);
+//   * four TMEM buffers of 128 columns: MMAs run up to four blocks ahead of the epilogue;
+//   * persistent: one CTA per SM walks (row tile, 128-token tile) work items built from
+//     the device-side tile list, expert by expert, so an expert's weights stay in L2.
+// Every wait is bounded; on expiry a status word is set and all roles drain and exit,
+// freeing TMEM.
 #include "lkb_device.cuh"
 
-int lkb_gemm_tc_init() { return LKB_OK; }
-int lkb_gemm_tc_launch(const lkb_pf_gemm *, int, int, cudaStream_t) { return LKB_ERR_UNSUPPORTED; }
+#define TC_THREADS   416            // 13 warps: 4 loaders, 8 epilogue, 1 MMA issuer
+#define TC_LOADERS   128
+#define TC_EPI_WARPS 8
+#define TC_KB        4              // blocks per pipeline stage
+#define TC_STAGES    4
+#define TC_TBUF      4              // TMEM buffers (128 columns each)
+#define TC_M         128            // tokens per tile
+#define TC_N         128            // weight rows (columns of D) per MMA
+#define TC_SPIN      (1u << 24)
+#define TC_MAX_TILES 1024           // 64-token plan tiles the work list can hold
+
+struct TcStage {
+    alignas(128) unsigned char A[TC_KB][TC_M * 32];      // activations, canonical layout, 4 KB per block
+    alignas(128) unsigned char B[TC_KB][TC_N * 32];      // weights expanded to int8, 4 KB per block
+    alignas(16)  float  d4[TC_KB][TC_N];                 // weight block scales as fp32
+    alignas(16)  float2 sc[TC_KB][TC_M];                 // (d8, 8*sum) per token
+};
+
+struct TcSmem {
+    TcStage st[TC_STAGES];
+    alignas(8) unsigned long long full[TC_STAGES], empty[TC_STAGES], tfull[TC_TBUF], tempty[TC_TBUF];
+    unsigned tmem_base;
+    int      abort;
+    int      n_mtiles;
+    // work list: M tiles of up to 128 slots: {expert, start in perm, count}
+    int      mt_expert[TC_MAX_TILES], mt_start[TC_MAX_TILES], mt_count[TC_MAX_TILES];
+};
+
+__device__ unsigned g_tc_status;     // 0, or the code of the first bounded wait that expired
+
+// ---- PTX -------------------------------------------------------------------
+__device__ __forceinline__ unsigned tc_smem_u32(const void * p) { return (unsigned) __cvta_generic_to_shared(p); }
+__device__ __forceinline__ void tc_mbar_init(unsigned long long * b, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(tc_smem_u32(b)), "r"(count));
+}
+__device__ __forceinline__ void tc_mbar_arrive(unsigned long long * b) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(tc_smem_u32(b)) : "memory");
+}
+__device__ __forceinline__ bool tc_mbar_try(unsigned long long * b, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(tc_smem_u32(b)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when it expired or another role already aborted.
+__device__ __forceinline__ bool tc_wait(TcSmem & S, unsigned long long * b, unsigned parity, unsigned code) {
+    for (unsigned i = 0; i < TC_SPIN; ++i) {
+        if (tc_mbar_try(b, parity)) return true;
+        if ((i & 255u) == 255u && *(volatile int *) &S.abort) return false;
+    }
+    atomicCAS(&g_tc_status, 0u, code);
+    *(volatile int *) &S.abort = 1;
+    return false;
+}
+__device__ __forceinline__ void tc_fence_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(unsigned long long * b) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(tc_smem_u32(b)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned idesc) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, 0, 0;\n"          // enable_input_d = 0: D = A*B (no accumulate)
+                 " tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}"
+                 :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc) : "memory");
+}
+// K-major, no swizzle: core matrix = 8 rows x 16 B contiguous; K-adjacent core matrix at
+// +128 B (leading byte offset), next 8-row group at +256 B (stride byte offset).
+__device__ __forceinline__ unsigned long long tc_desc(const void * smem) {
+    const unsigned a = tc_smem_u32(smem);
+    return (unsigned long long) ((a >> 4) & 0x3FFFu) | ((unsigned long long) (128u >> 4) << 16)
+         | ((unsigned long long) (256u >> 4) << 32) | (1ull << 46);
+}
+// s8 x s8 -> s32, M = 128, N = 128, both operands K-major.
+#define TC_IDESC (0x20u | (1u << 7) | (1u << 10) | ((TC_N >> 3) << 17) | ((TC_M >> 4) << 24))
+
+__device__ __forceinline__ void tc_ld32(unsigned taddr, int (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Offset of (row r, 16-byte K chunk kc) inside one 4 KB canonical operand block.
+__device__ __forceinline__ int tc_canon(int r, int kc) { return (r >> 3) * 256 + kc * 128 + (r & 7) * 16; }
+
+// ---------------------------------------------------------------------------
+// EPI 0: out (+)= scale * acc           (N tile = 128 rows of one weight segment)
+// EPI 1: SwiGLU + Q8_1                  (N tile = 64 gate rows | the same 64 up rows)
+// ---------------------------------------------------------------------------
+template <int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm g, const int max_tiles) {
+    extern __shared__ __align__(128) unsigned char tc_smem_raw[];
+    TcSmem & S = *reinterpret_cast<TcSmem *>(tc_smem_raw);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    // ---- set-up: barriers, TMEM, work list -------------------------------------
+    if (tid == 0) {
+        S.abort = 0;
+        for (int i = 0; i < TC_STAGES; ++i) { tc_mbar_init(&S.full[i], TC_LOADERS / 32); tc_mbar_init(&S.empty[i], 1 + TC_EPI_WARPS); }
+        for (int i = 0; i < TC_TBUF; ++i) { tc_mbar_init(&S.tfull[i], 1); tc_mbar_init(&S.tempty[i], TC_EPI_WARPS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(tc_smem_u32(&S.tmem_base)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (warp == 1) {
+        // Work list of M tiles (<= 128 slots of one expert) from the 64-slot plan tiles: consecutive
+        // tiles of the same expert are merged pairwise.  Dense GEMM: ceil(ntok/128) plain ranges.
+        int n = 0;
+        if (g.perm) {
+            int nt = *g.ntiles; if (nt > max_tiles) nt = max_tiles; if (nt > TC_MAX_TILES) nt = TC_MAX_TILES;
+            // lane-strided scan; a tile opens an M tile when it is the first of its expert or an even
+            // number of tiles after the first
+            int run_first = 0;          // index of the first tile of the current expert (carried across chunks)
+            for (int base = 0; base < nt; base += 32) {
+                const int t = base + lane;
+                int4 tl = make_int4(-1, 0, 0, 0), tp = make_int4(-2, 0, 0, 0), tn = make_int4(-3, 0, 0, 0);
+                if (t < nt) tl = reinterpret_cast<const int4 *>(g.tiles)[t];
+                if (t > 0 && t < nt) tp = reinterpret_cast<const int4 *>(g.tiles)[t - 1];
+                if (t + 1 < nt) tn = reinterpret_cast<const int4 *>(g.tiles)[t + 1];
+                const bool first = (t < nt) && (tl.x != tp.x);
+                // index of the first tile of my expert: max over lanes <= mine of (first ? t : -1), seeded by run_first
+                int f = first ? t : -1;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(LKB_FULL, f, o); if (lane >= o && v > f) f = v; }
+                if (f < 0) f = run_first;
+                const bool opens = (t < nt) && (((t - f) & 1) == 0);
+                const unsigned m = __ballot_sync(LKB_FULL, opens);
+                if (opens) {
+                    const int k = n + __popc(m & ((1u << lane) - 1u));
+                    S.mt_expert[k] = tl.x; S.mt_start[k] = tl.y;
+                    S.mt_count[k] = tl.z + ((tn.x == tl.x) ? tn.z : 0);
+                }
+                n += __popc(m);
+                run_first = __shfl_sync(LKB_FULL, f, 31);
+            }
+        } else {
+            n = (g.ntok + TC_M - 1) / TC_M;
+            for (int k = lane; k < n; k += 32) { S.mt_expert[k] = 0; S.mt_start[k] = k * TC_M; S.mt_count[k] = min(TC_M, g.ntok - k * TC_M); }
+        }
+        if (lane == 0) S.n_mtiles = n;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = S.tmem_base;
+    const int n_mt = S.n_mtiles;
+    const int n_rt = EPI ? g.N / 64 : g.N / TC_N;
+    const int n_items = n_mt * n_rt;
+    const int nstage_per_item = g.bpr / TC_KB;
+
+    // ============================ loaders (warps 0-3) ============================
+    if (warp < 4) {
+        unsigned it = 0;                                            // stage counter across items
+        for (int item = blockIdx.x; item < n_items && !*(volatile int *) &S.abort; item += gridDim.x) {
+            const int mt = item / n_rt, rt = item % n_rt;
+            const int expert = S.mt_expert[mt], tstart = S.mt_start[mt], tcnt = S.mt_count[mt];
+            // token t of the tile = thread tid: its activation row
+            int slot = -1;
+            if (tid < tcnt) slot = g.perm ? g.perm[tstart + tid] : tstart + tid;
+            const int ar = (slot >= 0) ? (slot >> g.a_shift) : -1;
+            // weight row n of the tile = thread tid
+            const uint4 * wq; const __half * wd;
+            {
+                const size_t eo = (size_t) expert * g.exp_stride;
+                if (EPI) {
+                    const int r = rt * 64 + (tid & 63);
+                    const int sg = tid >> 6;                        // 0: gate, 1: up
+                    wq = (const uint4 *) g.qs[sg] + eo + (size_t) r * g.bpr;
+                    wd = (const __half *) g.d[sg] + eo + (size_t) r * g.bpr;
+                } else {
+                    const int r = rt * TC_N + tid;
+                    const int seg = (r < g.seg_end[0]) ? 0 : (r < g.seg_end[1]) ? 1 : 2;
+                    const int sbase = seg ? g.seg_end[seg - 1] : 0;
+                    wq = (const uint4 *) g.qs[seg] + eo + (size_t) (r - sbase) * g.bpr;
+                    wd = (const __half *) g.d[seg] + eo + (size_t) (r - sbase) * g.bpr;
+                }
+            }
+            const int8_t * aq = g.aqs + (size_t) (ar < 0 ? 0 : ar) * g.bpr * 32;
+            const float2 * as = reinterpret_cast<const float2 *>(g.asc) + (size_t) (ar < 0 ? 0 : ar) * g.bpr;
+            for (int ks = 0; ks < nstage_per_item; ++ks, ++it) {
+                const int stg = it % TC_STAGES;
+                if (!tc_wait(S, &S.empty[stg], ((it / TC_STAGES) & 1u) ^ 1u, 10u)) break;
+                TcStage & T = S.st[stg];
+                const int kb0 = ks * TC_KB;
+                // activations: 4 blocks x 32 B of my token (zero rows for padding tokens)
+                uint4 av[TC_KB][2]; float2 sv[TC_KB];
+#pragma unroll
+                for (int j = 0; j < TC_KB; ++j) {
+                    if (ar >= 0) {
+                        av[j][0] = *reinterpret_cast<const uint4 *>(aq + (size_t) (kb0 + j) * 32);
+                        av[j][1] = *reinterpret_cast<const uint4 *>(aq + (size_t) (kb0 + j) * 32 + 16);
+                        sv[j] = as[kb0 + j];
+                    } else { av[j][0] = av[j][1] = make_uint4(0, 0, 0, 0); sv[j] = make_float2(0.0f, 0.0f); }
+                }
+                // weights: 4 blocks x 16 B of nibbles of my row
+                uint4 wv[TC_KB]; __half dv[TC_KB];
+#pragma unroll
+                for (int j = 0; j < TC_KB; ++j) { wv[j] = lkb_ldg_stream(wq + kb0 + j); dv[j] = wd[kb0 + j]; }
+#pragma unroll
+                for (int j = 0; j < TC_KB; ++j) {
+                    *reinterpret_cast<uint4 *>(T.A[j] + tc_canon(tid, 0)) = av[j][0];
+                    *reinterpret_cast<uint4 *>(T.A[j] + tc_canon(tid, 1)) = av[j][1];
+                    T.sc[j][tid] = sv[j];
+                    // byte i of the 16: element i (low nibble) | element i+16 (high nibble)
+                    uint4 lo, hi;
+                    lo.x = wv[j].x & 0x0F0F0F0Fu; hi.x = (wv[j].x >> 4) & 0x0F0F0F0Fu;
+                    lo.y = wv[j].y & 0x0F0F0F0Fu; hi.y = (wv[j].y >> 4) & 0x0F0F0F0Fu;
+                    lo.z = wv[j].z & 0x0F0F0F0Fu; hi.z = (wv[j].z >> 4) & 0x0F0F0F0Fu;
+                    lo.w = wv[j].w & 0x0F0F0F0Fu; hi.w = (wv[j].w >> 4) & 0x0F0F0F0Fu;
+                    *reinterpret_cast<uint4 *>(T.B[j] + tc_canon(tid, 0)) = lo;
+                    *reinterpret_cast<uint4 *>(T.B[j] + tc_canon(tid, 1)) = hi;
+                    T.d4[j][tid] = __half2float(dv[j]);
+                }
+                tc_fence_async();                                   // generic-proxy writes -> visible to the MMA
+                __syncwarp();
+                if (lane == 0) tc_mbar_arrive(&S.full[stg]);
+            }
+        }
+    }
+    // ============================ MMA issuer (warp 12) ===========================
+    else if (warp == 12) {
+        if (lane == 0) {
+            unsigned it = 0, blk = 0;
+            for (int item = blockIdx.x; item < n_items && !*(volatile int *) &S.abort; item += gridDim.x) {
+                bool ok = true;
+                for (int ks = 0; ks < nstage_per_item && ok; ++ks, ++it) {
+                    const int stg = it % TC_STAGES;
+                    if (!tc_wait(S, &S.full[stg], (it / TC_STAGES) & 1u, 20u)) { ok = false; break; }
+                    tc_fence_after();
+                    TcStage & T = S.st[stg];
+#pragma unroll
+                    for (int j = 0; j < TC_KB; ++j, ++blk) {
+                        const int tb = blk % TC_TBUF;
+                        if (!tc_wait(S, &S.tempty[tb], ((blk / TC_TBUF) & 1u) ^ 1u, 21u)) { ok = false; break; }
+                        tc_fence_after();
+                        tc_mma_i8(tmem + tb * TC_N, tc_desc(T.A[j]), tc_desc(T.B[j]), TC_IDESC);
+                        tc_commit(&S.tfull[tb]);                    // this block's result is ready
+                    }
+                    if (ok) tc_commit(&S.empty[stg]);               // the MMAs have finished reading the stage
+                }
+                if (!ok) break;
+            }
+        }
+    }
+    // ============================ epilogue (warps 4-11) ==========================
+    else {
+        const int ew = warp - 4;                    // 0..7
+        const int quad = warp & 3;                  // TMEM lane quadrant this warp may access
+        const int grp = ew >> 2;                    // column half
+        const int tok = quad * 32 + lane;           // token (TMEM lane) of this thread
+        const unsigned tlane = (unsigned) (quad * 32) << 16;
+        // EPI 0: columns [64 grp, 64 grp + 64).  EPI 1: gate [32 grp, +32) and up [64 + 32 grp, +32).
+        const int c0 = EPI ? 32 * grp : 64 * grp;
+        const int c1 = EPI ? 64 + 32 * grp : 64 * grp + 32;
+        unsigned it = 0, blk = 0;
+        for (int item = blockIdx.x; item < n_items && !*(volatile int *) &S.abort; item += gridDim.x) {
+            const int mt = item / n_rt, rt = item % n_rt;
+            const int tstart = S.mt_start[mt], tcnt = S.mt_count[mt];
+            const bool warp_live = quad * 32 < tcnt;          // padding-only warps skip the arithmetic
+            int slot = -1;
+            if (tok < tcnt) slot = g.perm ? g.perm[tstart + tok] : tstart + tok;
+            const int ar = (slot >= 0) ? (slot >> g.a_shift) : -1;
+            const float scl = (ar >= 0 && g.scale) ? g.scale[ar] : 1.0f;
+            float acc0[32], acc1[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) { acc0[i] = 0.0f; acc1[i] = 0.0f; }
+            bool ok = true;
+            for (int ks = 0; ks < nstage_per_item && ok; ++ks, ++it) {
+                const int stg = it % TC_STAGES;
+                if (!tc_wait(S, &S.full[stg], (it / TC_STAGES) & 1u, 30u)) { ok = false; break; }   // d4 / sc are in place
+                TcStage & T = S.st[stg];
+#pragma unroll 1
+                for (int j = 0; j < TC_KB; ++j, ++blk) {
+                    const int tb = blk % TC_TBUF;
+                    if (!tc_wait(S, &S.tfull[tb], (blk / TC_TBUF) & 1u, 31u)) { ok = false; break; }
+                    tc_fence_after();
+                    if (warp_live) {
+                        const float2 sc = T.sc[j][tok];
+                        const float nc = -sc.y;
+                        int sv[32];
+                        tc_ld32(tmem + tlane + tb * TC_N + c0, sv);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            const float4 da = *reinterpret_cast<const float4 *>(&T.d4[j][c0 + i]);
+                            acc0[i + 0] = fmaf(da.x, fmaf(sc.x, (float) sv[i + 0], nc), acc0[i + 0]);
+                            acc0[i + 1] = fmaf(da.y, fmaf(sc.x, (float) sv[i + 1], nc), acc0[i + 1]);
+                            acc0[i + 2] = fmaf(da.z, fmaf(sc.x, (float) sv[i + 2], nc), acc0[i + 2]);
+                            acc0[i + 3] = fmaf(da.w, fmaf(sc.x, (float) sv[i + 3], nc), acc0[i + 3]);
+                        }
+                        tc_ld32(tmem + tlane + tb * TC_N + c1, sv);
+                        tc_wait_ld();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) tc_mbar_arrive(&S.tempty[tb]);          // TMEM buffer is free again
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            const float4 db = *reinterpret_cast<const float4 *>(&T.d4[j][c1 + i]);
+                            acc1[i + 0] = fmaf(db.x, fmaf(sc.x, (float) sv[i + 0], nc), acc1[i + 0]);
+                            acc1[i + 1] = fmaf(db.y, fmaf(sc.x, (float) sv[i + 1], nc), acc1[i + 1]);
+                            acc1[i + 2] = fmaf(db.z, fmaf(sc.x, (float) sv[i + 2], nc), acc1[i + 2]);
+                            acc1[i + 3] = fmaf(db.w, fmaf(sc.x, (float) sv[i + 3], nc), acc1[i + 3]);
+                        }
+                    } else {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) tc_mbar_arrive(&S.tempty[tb]);
+                    }
+                }
+                if (!ok) break;
+                __syncwarp();
+                if (lane == 0) tc_mbar_arrive(&S.empty[stg]);                   // done with the stage's d4 / sc
+            }
+            if (!ok) break;
+            // ---- tile epilogue -----------------------------------------------------
+            if (slot >= 0) {
+                if (EPI) {
+                    // acc0 = gate rows, acc1 = the same 32 up rows: one Q8_1 block of this slot
+                    float v[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __fmul_rn(lkb_silu(__fmul_rn(acc0[i], scl)), __fmul_rn(acc1[i], scl));
+                    float am = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) am = fmaxf(am, fabsf(v[i]));
+                    // the sum in xor-butterfly order (16, 8, 4, 2, 1), as the warp quantiser produces it
+                    float t[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) t[i] = __fadd_rn(v[i], v[i + 16]);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) t[i] = __fadd_rn(t[i], t[i + 8]);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) t[i] = __fadd_rn(t[i], t[i + 4]);
+                    const float sum = __fadd_rn(__fadd_rn(t[0], t[2]), __fadd_rn(t[1], t[3]));
+                    const float d = __fdiv_rn(am, 127.0f);
+                    unsigned pk[8];
+#pragma unroll
+                    for (int w = 0; w < 8; ++w) {
+                        unsigned p = 0;
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) {
+                            const int q = (am == 0.0f) ? 0 : (int) roundf(__fdiv_rn(v[w * 4 + b], d));
+                            p |= ((unsigned) q & 0xFFu) << (8 * b);
+                        }
+                        pk[w] = p;
+                    }
+                    const int orow0 = rt * 64 + 32 * grp;              // first intermediate row of the block
+                    int8_t * oq = g.oqs + (size_t) slot * (g.okb * 32) + orow0;
+                    *reinterpret_cast<uint4 *>(oq) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    *reinterpret_cast<uint4 *>(oq + 16) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                    const __half2 ds = __floats2half2_rn(d, sum);
+                    reinterpret_cast<float2 *>(g.osc)[(size_t) slot * g.okb + orow0 / 32] =
+                        make_float2(__low2float(ds), __fmul_rn(8.0f, __high2float(ds)));
+                } else {
+                    float * p0 = g.out + (size_t) slot * g.out_ld + rt * TC_N + c0;
+                    float * p1 = g.out + (size_t) slot * g.out_ld + rt * TC_N + c1;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        float4 o0 = make_float4(__fmul_rn(acc0[i], scl), __fmul_rn(acc0[i + 1], scl), __fmul_rn(acc0[i + 2], scl), __fmul_rn(acc0[i + 3], scl));
+                        float4 o1 = make_float4(__fmul_rn(acc1[i], scl), __fmul_rn(acc1[i + 1], scl), __fmul_rn(acc1[i + 2], scl), __fmul_rn(acc1[i + 3], scl));
+                        if (g.add) {
+                            const float4 a0 = *reinterpret_cast<const float4 *>(p0 + i), a1 = *reinterpret_cast<const float4 *>(p1 + i);
+                            o0 = make_float4(__fadd_rn(a0.x, o0.x), __fadd_rn(a0.y, o0.y), __fadd_rn(a0.z, o0.z), __fadd_rn(a0.w, o0.w));
+                            o1 = make_float4(__fadd_rn(a1.x, o1.x), __fadd_rn(a1.y, o1.y), __fadd_rn(a1.z, o1.z), __fadd_rn(a1.w, o1.w));
+                        }
+                        *reinterpret_cast<float4 *>(p0 + i) = o0;
+                        *reinterpret_cast<float4 *>(p1 + i) = o1;
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- teardown: everyone meets, then the allocating warp frees TMEM ------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(512) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+static int g_tc_ready = 0;
+
+int lkb_gemm_tc_init() {
+    cudaError_t e = cudaFuncSetAttribute(k_pf_gemm_tc<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sizeof(TcSmem));
+    if (e != cudaSuccess) return -(int) e;
+    e = cudaFuncSetAttribute(k_pf_gemm_tc<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sizeof(TcSmem));
+    if (e != cudaSuccess) return -(int) e;
+    g_tc_ready = 1;
+    return LKB_OK;
+}
+
+// Shapes the tensor-core form covers; otherwise LKB_ERR_UNSUPPORTED (the caller falls back
+// to the CUDA-core form): out_ld / okb rows must allow 16-byte vector stores.
+int lkb_gemm_tc_launch(const lkb_pf_gemm * g, int epi, int max_tiles, cudaStream_t st) {
+    if (!g_tc_ready) return LKB_ERR_NOT_INIT;
+    if (g->bpr % TC_KB) return LKB_ERR_UNSUPPORTED;
+    if (epi) { if (g->N % 64 || (g->okb * 32) % 16) return LKB_ERR_UNSUPPORTED; }
+    else if (g->N % TC_N || g->out_ld % 4 || ((size_t) g->out & 15)) return LKB_ERR_UNSUPPORTED;
+    if (g->perm && max_tiles > TC_MAX_TILES) return LKB_ERR_UNSUPPORTED;
+    if (!g->perm && (g->ntok + TC_M - 1) / TC_M > TC_MAX_TILES) return LKB_ERR_UNSUPPORTED;
+    if (((size_t) g->aqs & 15) || ((size_t) g->asc & 7)) return LKB_ERR_UNSUPPORTED;
+    const int grid = lkb_context().sm_count;
+    if (epi) k_pf_gemm_tc<1><<<grid, TC_THREADS, sizeof(TcSmem), st>>>(*g, max_tiles);
+    else     k_pf_gemm_tc<0><<<grid, TC_THREADS, sizeof(TcSmem), st>>>(*g, max_tiles);
+    return lkb_check_launch();
+}
+
+extern "C" {
+int lkb_pf_gemm_status(void) {
+    unsigned v = 0, z = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof v) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_tc_status, &z, sizeof z);
+    return (int) v;
+}
+}

@@ -174,7 +174,7 @@ SHAPES_DENSE = [(256, 64, 130, False, False, False), (384, 48, 200, True, True, 
                 (512, 8, 64, False, True, True), (256, 368, 70, True, False, False)]
 
 
-@pytest.mark.parametrize("cfg", [0, -1])
+@pytest.mark.parametrize("cfg", [0, 1])
 @pytest.mark.parametrize("N,bpr,M,add,scale,three", SHAPES_DENSE)
 def test_gemm_dense(L, orc, cfg, N, bpr, M, add, scale, three):
     L.pf_gemm_config(cfg)
@@ -204,10 +204,11 @@ def test_gemm_dense(L, orc, cfg, N, bpr, M, add, scale, three):
     s = np.ones((M, 1)) if sc is None else sc[:, None].astype(np.float64)
     full = r64 * s + (o0 if add else 0.0)
     assert np.all(np.abs(got - full) <= 1e-5 * mag * s + 1e-6 * np.abs(full))
+    assert L.lib.lkb_pf_gemm_status() == 0                  # no bounded wait of the tensor-core form expired
     L.pf_gemm_config(-1)
 
 
-@pytest.mark.parametrize("cfg", [0, -1])
+@pytest.mark.parametrize("cfg", [0, 1])
 @pytest.mark.parametrize("E,rows,bpr,M,a_shift", [(8, 256, 64, 130, 2), (8, 384, 48, 257, 0), (64, 128, 8, 700, 2)])
 def test_gemm_moe(L, orc, cfg, E, rows, bpr, M, a_shift):
     L.pf_gemm_config(cfg)
@@ -241,10 +242,11 @@ def test_gemm_moe(L, orc, cfg, E, rows, bpr, M, a_shift):
     assert np.array_equal(got, ref)
     s = np.ones((NS, 1)) if sc is None else np.repeat(sc, 4)[:, None].astype(np.float64)
     assert np.all(np.abs(got - r64 * s) <= 1e-5 * mag * s)
+    assert L.lib.lkb_pf_gemm_status() == 0                  # no bounded wait of the tensor-core form expired
     L.pf_gemm_config(-1)
 
 
-@pytest.mark.parametrize("cfg", [0, -1])
+@pytest.mark.parametrize("cfg", [0, 1])
 def test_gemm_swiglu_fused_equals_unfused(L, orc, cfg):
     L.pf_gemm_config(cfg)
     rng = np.random.default_rng(31)
@@ -276,6 +278,7 @@ def test_gemm_swiglu_fused_equals_unfused(L, orc, cfg):
     tq, tsc, _ = orc.pf_swiglu(Yh, I, I // 32, v=v)
     flips = np.count_nonzero(host(oqs) != tq)
     assert flips <= 1e-4 * tq.size and np.max(np.abs(host(oqs).astype(np.int32) - tq)) <= 1
+    assert L.lib.lkb_pf_gemm_status() == 0                  # no bounded wait of the tensor-core form expired
     L.pf_gemm_config(-1)
 
 
