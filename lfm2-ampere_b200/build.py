@@ -5,7 +5,9 @@
 nvcc cross-compiles without a GPU.  The library is written next to this file so
 that it travels with the source tree; it is never installed into site-packages.
 """
+import os
 import pathlib
+import shlex
 import subprocess
 import sys
 
@@ -29,7 +31,8 @@ def build(force=False, verbose=False):
     if not force and not needs_build():
         return OUT
     srcs = [str(CSRC / s) for s in SOURCES if (CSRC / s).exists()]
-    cmd = ["nvcc"] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", str(OUT)] + srcs + ["-lcuda"]
+    extra = shlex.split(os.environ.get("LKB_NVCC_EXTRA", ""))          # e.g. -DTC_MAGIC=0 while tuning
+    cmd = ["nvcc"] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-o", str(OUT)] + srcs + ["-lcuda"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or r.returncode:
         sys.stderr.write(r.stdout + r.stderr)

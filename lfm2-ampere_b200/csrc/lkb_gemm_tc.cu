@@ -25,34 +25,44 @@
 // freeing TMEM.
 #include "lkb_device.cuh"
 
-#define TC_THREADS   416            // 13 warps: 4 loaders, 8 epilogue, 1 MMA issuer
+#define TC_THREADS   672            // 21 warps: 4 loaders, 16 epilogue, 1 MMA issuer
 #define TC_LOADERS   128
-#define TC_EPI_WARPS 8
+#define TC_EPI_WARPS 16
+#define TC_MMA_WARP  20
 #define TC_KB        4              // blocks per pipeline stage
-#define TC_STAGES    4
+#define TC_STAGES    3
 #define TC_TBUF      4              // TMEM buffers (128 columns each)
 #define TC_M         128            // tokens per tile
 #define TC_N         128            // weight rows (columns of D) per MMA
+#define TC_AHEAD     2              // stages of cp.async lookahead in the loaders
 #define TC_SPIN      (1u << 24)
 #define TC_MAX_TILES 1024           // 64-token plan tiles the work list can hold
+#ifndef TC_MAGIC
+#define TC_MAGIC 0                   // 1: int32 -> fp32 by the 1.5*2^23 bit trick (integer add + fp add) instead of
+                                     //    cvt.rn.f32.s32; measured 8% slower than the convert on B200, kept as a switch
+#endif
 
 struct TcStage {
     alignas(128) unsigned char A[TC_KB][TC_M * 32];      // activations, canonical layout, 4 KB per block
     alignas(128) unsigned char B[TC_KB][TC_N * 32];      // weights expanded to int8, 4 KB per block
     alignas(16)  float  d4[TC_KB][TC_N];                 // weight block scales as fp32
-    alignas(16)  float2 sc[TC_KB][TC_M];                 // (d8, 8*sum) per token
+    alignas(16)  float2 sc[TC_M][TC_KB];                 // (d8, 8*sum) per token
+    alignas(16)  unsigned char rawq[TC_N][TC_KB * 16 + 16];   // nibbles as they lie in the pack (+16: bank spread)
+    alignas(8)   __half rawd[TC_N][TC_KB];
 };
 
 struct TcSmem {
     TcStage st[TC_STAGES];
-    alignas(8) unsigned long long full[TC_STAGES], empty[TC_STAGES], tfull[TC_TBUF], tempty[TC_TBUF];
+    alignas(8) unsigned long long full[TC_STAGES], empty[TC_STAGES], tfull[TC_TBUF], tempty[TC_TBUF], qbar[4];
     unsigned tmem_base;
     int      abort;
     int      n_mtiles;
     // work list: M tiles of up to 128 slots: {expert, start in perm, count}
     int      mt_expert[TC_MAX_TILES], mt_start[TC_MAX_TILES], mt_count[TC_MAX_TILES];
+    float    vbuf[TC_M][65];        // SwiGLU epilogue: v = silu(g)*u of 64 intermediate rows per token (+1: bank spread)
 };
 
+__device__ unsigned long long g_tc_prof[16];   // tuning: cycles spent per wait class (CTA 0)
 __device__ unsigned g_tc_status;     // 0, or the code of the first bounded wait that expired
 
 // ---- PTX -------------------------------------------------------------------
@@ -79,6 +89,16 @@ __device__ __forceinline__ bool tc_wait(TcSmem & S, unsigned long long * b, unsi
     *(volatile int *) &S.abort = 1;
     return false;
 }
+#ifndef TC_PROF
+#define TC_PROF 0                    // 1: accumulate cycles per wait class (tuning builds only)
+#endif
+#if TC_PROF
+#define TC_TWAIT(acc, ...) ([&]() { const long long t0_ = TC_CLK(); const bool r_ = tc_wait(__VA_ARGS__); acc += TC_CLK() - t0_; return r_; })()
+#define TC_CLK() clock64()
+#else
+#define TC_TWAIT(acc, ...) tc_wait(__VA_ARGS__)
+#define TC_CLK() 0ll
+#endif
 __device__ __forceinline__ void tc_fence_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -109,7 +129,56 @@ __device__ __forceinline__ void tc_ld32(unsigned taddr, int (&r)[32]) {
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tc_ld16(unsigned taddr, int * r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+}
+// Two independent IEEE fused multiply-adds in one instruction (halves the issue slots of the epilogue).
+__device__ __forceinline__ float2 tc_ffma2(float2 a, float2 b, float2 c) {
+    unsigned long long ra, rb, rc, rd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+    float2 d;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
+__device__ __forceinline__ float tc_i2f(int s) {
+#if TC_MAGIC
+    return __fsub_rn(__int_as_float(s + 0x4B400000), 12582912.0f);      // exact for |s| < 2^22
+#else
+    return (float) s;
+#endif
+}
+// Two int32 block sums -> fp32, exactly.  |s| <= 32*15*127 < 2^22, so the integer s + 0x4B400000 read as a
+// float is 12582912 + s with no rounding, and subtracting 12582912 (one packed add) recovers float(s).
+__device__ __forceinline__ float2 tc_i2f2(int a, int b) {
+#if TC_MAGIC
+    unsigned long long r, m, o;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(a + 0x4B400000), "r"(b + 0x4B400000));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(m) : "f"(-12582912.0f));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(o) : "l"(r), "l"(m));
+    float2 d;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(o));
+    return d;
+#else
+    return make_float2((float) a, (float) b);
+#endif
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_cp16(void * dst, const void * src, bool valid) {
+    const unsigned n = valid ? 16u : 0u;                       // 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(tc_smem_u32(dst)), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void tc_cp8(void * dst, const void * src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" :: "r"(tc_smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void tc_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void tc_cp_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
 
 // Offset of (row r, 16-byte K chunk kc) inside one 4 KB canonical operand block.
 __device__ __forceinline__ int tc_canon(int r, int kc) { return (r >> 3) * 256 + kc * 128 + (r & 7) * 16; }
@@ -129,6 +198,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
         S.abort = 0;
         for (int i = 0; i < TC_STAGES; ++i) { tc_mbar_init(&S.full[i], TC_LOADERS / 32); tc_mbar_init(&S.empty[i], 1 + TC_EPI_WARPS); }
         for (int i = 0; i < TC_TBUF; ++i) { tc_mbar_init(&S.tfull[i], 1); tc_mbar_init(&S.tempty[i], TC_EPI_WARPS); }
+        for (int i = 0; i < 4; ++i) tc_mbar_init(&S.qbar[i], 4);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -182,89 +252,112 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
     const int nstage_per_item = g.bpr / TC_KB;
 
     // ============================ loaders (warps 0-3) ============================
+    // Thread tid owns token tid of the M tile and weight row tid of the N tile.  All global
+    // traffic is cp.async (16 B), issued TC_AHEAD stages ahead: activations and their scales land
+    // directly in the canonical operand layout, nibbles land in a raw staging row and are expanded
+    // to int8 from shared memory when their stage comes up.
     if (warp < 4) {
-        unsigned it = 0;                                            // stage counter across items
-        for (int item = blockIdx.x; item < n_items && !*(volatile int *) &S.abort; item += gridDim.x) {
-            const int mt = item / n_rt, rt = item % n_rt;
+        struct Cur { int item, ks, ar; const int8_t * aq; const float2 * as; const uint4 * wq; const __half * wd; };
+        auto setup = [&](Cur & c) {
+            if (c.item >= n_items) return;
+            const int mt = c.item / n_rt, rt = c.item % n_rt;
             const int expert = S.mt_expert[mt], tstart = S.mt_start[mt], tcnt = S.mt_count[mt];
-            // token t of the tile = thread tid: its activation row
             int slot = -1;
             if (tid < tcnt) slot = g.perm ? g.perm[tstart + tid] : tstart + tid;
-            const int ar = (slot >= 0) ? (slot >> g.a_shift) : -1;
-            // weight row n of the tile = thread tid
-            const uint4 * wq; const __half * wd;
-            {
-                const size_t eo = (size_t) expert * g.exp_stride;
-                if (EPI) {
-                    const int r = rt * 64 + (tid & 63);
-                    const int sg = tid >> 6;                        // 0: gate, 1: up
-                    wq = (const uint4 *) g.qs[sg] + eo + (size_t) r * g.bpr;
-                    wd = (const __half *) g.d[sg] + eo + (size_t) r * g.bpr;
-                } else {
-                    const int r = rt * TC_N + tid;
-                    const int seg = (r < g.seg_end[0]) ? 0 : (r < g.seg_end[1]) ? 1 : 2;
-                    const int sbase = seg ? g.seg_end[seg - 1] : 0;
-                    wq = (const uint4 *) g.qs[seg] + eo + (size_t) (r - sbase) * g.bpr;
-                    wd = (const __half *) g.d[seg] + eo + (size_t) (r - sbase) * g.bpr;
+            c.ar = (slot >= 0) ? (slot >> g.a_shift) : -1;
+            const size_t eo = (size_t) expert * g.exp_stride;
+            if (EPI) {
+                const int r = rt * 64 + (tid & 63);
+                const int sg = tid >> 6;                            // 0: gate, 1: up
+                c.wq = (const uint4 *) g.qs[sg] + eo + (size_t) r * g.bpr;
+                c.wd = (const __half *) g.d[sg] + eo + (size_t) r * g.bpr;
+            } else {
+                const int r = rt * TC_N + tid;
+                const int seg = (r < g.seg_end[0]) ? 0 : (r < g.seg_end[1]) ? 1 : 2;
+                const int sbase = seg ? g.seg_end[seg - 1] : 0;
+                c.wq = (const uint4 *) g.qs[seg] + eo + (size_t) (r - sbase) * g.bpr;
+                c.wd = (const __half *) g.d[seg] + eo + (size_t) (r - sbase) * g.bpr;
+            }
+            c.aq = g.aqs + (size_t) (c.ar < 0 ? 0 : c.ar) * g.bpr * 32;
+            c.as = reinterpret_cast<const float2 *>(g.asc) + (size_t) (c.ar < 0 ? 0 : c.ar) * g.bpr;
+        };
+        auto advance = [&](Cur & c) { if (++c.ks == nstage_per_item) { c.ks = 0; c.item += gridDim.x; setup(c); } };
+        int my_items = 0;
+        if ((int) blockIdx.x < n_items) my_items = (n_items - 1 - (int) blockIdx.x) / (int) gridDim.x + 1;
+        const unsigned total = (unsigned) my_items * (unsigned) nstage_per_item;
+        Cur ci, cc;
+        ci.item = cc.item = blockIdx.x; ci.ks = cc.ks = 0; ci.ar = cc.ar = -1;
+        setup(ci); cc = ci;
+        unsigned it_issue = 0;
+        bool ok = true;
+        long long pw_empty = 0, pw_cp = 0; const long long pt0 = clock64();
+        auto issue = [&]() {
+            // stage it_issue: wait for its buffer, then fire the copies
+            if (ok && it_issue < total) {
+                const int stg = it_issue % TC_STAGES;
+                if (!TC_TWAIT(pw_empty, S, &S.empty[stg], ((it_issue / TC_STAGES) & 1u) ^ 1u, 10u)) ok = false;
+                else {
+                    TcStage & T = S.st[stg];
+                    const int kb0 = ci.ks * TC_KB;
+                    const bool live = ci.ar >= 0;
+#pragma unroll
+                    for (int j = 0; j < TC_KB; ++j) {
+                        tc_cp16(T.A[j] + tc_canon(tid, 0), ci.aq + (size_t) (kb0 + j) * 32, live);
+                        tc_cp16(T.A[j] + tc_canon(tid, 1), ci.aq + (size_t) (kb0 + j) * 32 + 16, live);
+                        tc_cp16(T.rawq[tid] + j * 16, ci.wq + kb0 + j, true);
+                    }
+                    tc_cp16(&T.sc[tid][0], ci.as + kb0, live);
+                    tc_cp16(&T.sc[tid][2], ci.as + kb0 + 2, live);
+                    tc_cp8(T.rawd[tid], ci.wd + kb0);
+                    advance(ci);
                 }
             }
-            const int8_t * aq = g.aqs + (size_t) (ar < 0 ? 0 : ar) * g.bpr * 32;
-            const float2 * as = reinterpret_cast<const float2 *>(g.asc) + (size_t) (ar < 0 ? 0 : ar) * g.bpr;
-            for (int ks = 0; ks < nstage_per_item; ++ks, ++it) {
-                const int stg = it % TC_STAGES;
-                if (!tc_wait(S, &S.empty[stg], ((it / TC_STAGES) & 1u) ^ 1u, 10u)) break;
-                TcStage & T = S.st[stg];
-                const int kb0 = ks * TC_KB;
-                // activations: 4 blocks x 32 B of my token (zero rows for padding tokens)
-                uint4 av[TC_KB][2]; float2 sv[TC_KB];
+            tc_cp_commit();                                         // one group per call, possibly empty
+            ++it_issue;
+        };
+        for (int p = 0; p < TC_AHEAD; ++p) issue();
+        for (unsigned it = 0; it < total && ok; ++it) {
+            // stage `it` has landed once at most TC_AHEAD-1 newer groups are pending; publish it BEFORE
+            // blocking on the buffer of stage it+TC_AHEAD, so the copies really run ahead of the consumers
+            { const long long t0_ = TC_CLK(); tc_cp_wait<TC_AHEAD - 1>(); pw_cp += TC_CLK() - t0_; }
+            TcStage & T = S.st[it % TC_STAGES];
 #pragma unroll
-                for (int j = 0; j < TC_KB; ++j) {
-                    if (ar >= 0) {
-                        av[j][0] = *reinterpret_cast<const uint4 *>(aq + (size_t) (kb0 + j) * 32);
-                        av[j][1] = *reinterpret_cast<const uint4 *>(aq + (size_t) (kb0 + j) * 32 + 16);
-                        sv[j] = as[kb0 + j];
-                    } else { av[j][0] = av[j][1] = make_uint4(0, 0, 0, 0); sv[j] = make_float2(0.0f, 0.0f); }
-                }
-                // weights: 4 blocks x 16 B of nibbles of my row
-                uint4 wv[TC_KB]; __half dv[TC_KB];
-#pragma unroll
-                for (int j = 0; j < TC_KB; ++j) { wv[j] = lkb_ldg_stream(wq + kb0 + j); dv[j] = wd[kb0 + j]; }
-#pragma unroll
-                for (int j = 0; j < TC_KB; ++j) {
-                    *reinterpret_cast<uint4 *>(T.A[j] + tc_canon(tid, 0)) = av[j][0];
-                    *reinterpret_cast<uint4 *>(T.A[j] + tc_canon(tid, 1)) = av[j][1];
-                    T.sc[j][tid] = sv[j];
-                    // byte i of the 16: element i (low nibble) | element i+16 (high nibble)
-                    uint4 lo, hi;
-                    lo.x = wv[j].x & 0x0F0F0F0Fu; hi.x = (wv[j].x >> 4) & 0x0F0F0F0Fu;
-                    lo.y = wv[j].y & 0x0F0F0F0Fu; hi.y = (wv[j].y >> 4) & 0x0F0F0F0Fu;
-                    lo.z = wv[j].z & 0x0F0F0F0Fu; hi.z = (wv[j].z >> 4) & 0x0F0F0F0Fu;
-                    lo.w = wv[j].w & 0x0F0F0F0Fu; hi.w = (wv[j].w >> 4) & 0x0F0F0F0Fu;
-                    *reinterpret_cast<uint4 *>(T.B[j] + tc_canon(tid, 0)) = lo;
-                    *reinterpret_cast<uint4 *>(T.B[j] + tc_canon(tid, 1)) = hi;
-                    T.d4[j][tid] = __half2float(dv[j]);
-                }
-                tc_fence_async();                                   // generic-proxy writes -> visible to the MMA
-                __syncwarp();
-                if (lane == 0) tc_mbar_arrive(&S.full[stg]);
+            for (int j = 0; j < TC_KB; ++j) {
+                const uint4 wv = *reinterpret_cast<const uint4 *>(T.rawq[tid] + j * 16);
+                // byte i of the 16: element i (low nibble) | element i+16 (high nibble)
+                uint4 lo, hi;
+                lo.x = wv.x & 0x0F0F0F0Fu; hi.x = (wv.x >> 4) & 0x0F0F0F0Fu;
+                lo.y = wv.y & 0x0F0F0F0Fu; hi.y = (wv.y >> 4) & 0x0F0F0F0Fu;
+                lo.z = wv.z & 0x0F0F0F0Fu; hi.z = (wv.z >> 4) & 0x0F0F0F0Fu;
+                lo.w = wv.w & 0x0F0F0F0Fu; hi.w = (wv.w >> 4) & 0x0F0F0F0Fu;
+                *reinterpret_cast<uint4 *>(T.B[j] + tc_canon(tid, 0)) = lo;
+                *reinterpret_cast<uint4 *>(T.B[j] + tc_canon(tid, 1)) = hi;
+                T.d4[j][tid] = __half2float(T.rawd[tid][j]);
             }
+            tc_fence_async();                                       // generic-proxy writes -> visible to the MMA
+            __syncwarp();
+            if (lane == 0) tc_mbar_arrive(&S.full[it % TC_STAGES]);
+            issue();
         }
+        tc_cp_wait<0>();
+        if (blockIdx.x == 0 && tid == 0) { g_tc_prof[0] = pw_empty; g_tc_prof[1] = pw_cp; g_tc_prof[2] = clock64() - pt0; }
     }
-    // ============================ MMA issuer (warp 12) ===========================
-    else if (warp == 12) {
+    // ============================ MMA issuer (last warp) =========================
+    else if (warp == TC_MMA_WARP) {
         if (lane == 0) {
             unsigned it = 0, blk = 0;
+            long long pw_full = 0, pw_te = 0; const long long pt0 = clock64();
             for (int item = blockIdx.x; item < n_items && !*(volatile int *) &S.abort; item += gridDim.x) {
                 bool ok = true;
                 for (int ks = 0; ks < nstage_per_item && ok; ++ks, ++it) {
                     const int stg = it % TC_STAGES;
-                    if (!tc_wait(S, &S.full[stg], (it / TC_STAGES) & 1u, 20u)) { ok = false; break; }
+                    if (!TC_TWAIT(pw_full, S, &S.full[stg], (it / TC_STAGES) & 1u, 20u)) { ok = false; break; }
                     tc_fence_after();
                     TcStage & T = S.st[stg];
 #pragma unroll
                     for (int j = 0; j < TC_KB; ++j, ++blk) {
                         const int tb = blk % TC_TBUF;
-                        if (!tc_wait(S, &S.tempty[tb], ((blk / TC_TBUF) & 1u) ^ 1u, 21u)) { ok = false; break; }
+                        if (!TC_TWAIT(pw_te, S, &S.tempty[tb], ((blk / TC_TBUF) & 1u) ^ 1u, 21u)) { ok = false; break; }
                         tc_fence_after();
                         tc_mma_i8(tmem + tb * TC_N, tc_desc(T.A[j]), tc_desc(T.B[j]), TC_IDESC);
                         tc_commit(&S.tfull[tb]);                    // this block's result is ready
@@ -273,20 +366,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
                 }
                 if (!ok) break;
             }
+            if (blockIdx.x == 0) { g_tc_prof[4] = pw_full; g_tc_prof[5] = pw_te; g_tc_prof[6] = clock64() - pt0; g_tc_prof[7] = blk; }
         }
     }
-    // ============================ epilogue (warps 4-11) ==========================
+    // ============================ epilogue (warps 4-19) ==========================
+    // Four warps per TMEM lane quadrant, each folding 32 of the 128 columns: 32 accumulators
+    // per thread, four warps per scheduler to hide the TMEM read latency.
     else {
-        const int ew = warp - 4;                    // 0..7
+        const int ew = warp - 4;                    // 0..15
         const int quad = warp & 3;                  // TMEM lane quadrant this warp may access
-        const int grp = ew >> 2;                    // column half
+        const int sub = ew >> 2;                    // which 32 columns
         const int tok = quad * 32 + lane;           // token (TMEM lane) of this thread
         const unsigned tlane = (unsigned) (quad * 32) << 16;
-        // EPI 0: columns [64 grp, 64 grp + 64).  EPI 1: gate [32 grp, +32) and up [64 + 32 grp, +32).
-        const int c0 = EPI ? 32 * grp : 64 * grp;
-        const int c1 = EPI ? 64 + 32 * grp : 64 * grp + 32;
-        unsigned it = 0, blk = 0;
-        for (int item = blockIdx.x; item < n_items && !*(volatile int *) &S.abort; item += gridDim.x) {
+        // EPI 0: columns [32 sub, +32).  EPI 1: gate [16 sub, +16) -> acc[0..15], up [64 + 16 sub, +16) -> acc[16..31].
+        const int c0 = EPI ? 16 * sub : 32 * sub;
+        const int c1 = EPI ? 64 + 16 * sub : 32 * sub + 16;
+        unsigned it = 0, blk = 0, nitem = 0;
+        long long pw_full = 0, pw_tf = 0, pw_ld = 0, pw_tail = 0; const long long pt0 = clock64();
+        for (int item = blockIdx.x; item < n_items && !*(volatile int *) &S.abort; item += gridDim.x, ++nitem) {
             const int mt = item / n_rt, rt = item % n_rt;
             const int tstart = S.mt_start[mt], tcnt = S.mt_count[mt];
             const bool warp_live = quad * 32 < tcnt;          // padding-only warps skip the arithmetic
@@ -294,45 +391,47 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
             if (tok < tcnt) slot = g.perm ? g.perm[tstart + tok] : tstart + tok;
             const int ar = (slot >= 0) ? (slot >> g.a_shift) : -1;
             const float scl = (ar >= 0 && g.scale) ? g.scale[ar] : 1.0f;
-            float acc0[32], acc1[32];
+            float acc[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) { acc0[i] = 0.0f; acc1[i] = 0.0f; }
+            for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
             bool ok = true;
             for (int ks = 0; ks < nstage_per_item && ok; ++ks, ++it) {
                 const int stg = it % TC_STAGES;
-                if (!tc_wait(S, &S.full[stg], (it / TC_STAGES) & 1u, 30u)) { ok = false; break; }   // d4 / sc are in place
+                if (!TC_TWAIT(pw_full, S, &S.full[stg], (it / TC_STAGES) & 1u, 30u)) { ok = false; break; }   // d4 / sc are in place
                 TcStage & T = S.st[stg];
 #pragma unroll 1
                 for (int j = 0; j < TC_KB; ++j, ++blk) {
                     const int tb = blk % TC_TBUF;
-                    if (!tc_wait(S, &S.tfull[tb], (blk / TC_TBUF) & 1u, 31u)) { ok = false; break; }
+                    if (!TC_TWAIT(pw_tf, S, &S.tfull[tb], (blk / TC_TBUF) & 1u, 31u)) { ok = false; break; }
                     tc_fence_after();
                     if (warp_live) {
-                        const float2 sc = T.sc[j][tok];
-                        const float nc = -sc.y;
-                        int sv[32];
-                        tc_ld32(tmem + tlane + tb * TC_N + c0, sv);
-                        tc_wait_ld();
+                        const float2 sc = T.sc[tok][j];
+                        const float d8 = sc.x, nc = -sc.y;
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            const float4 da = *reinterpret_cast<const float4 *>(&T.d4[j][c0 + i]);
-                            acc0[i + 0] = fmaf(da.x, fmaf(sc.x, (float) sv[i + 0], nc), acc0[i + 0]);
-                            acc0[i + 1] = fmaf(da.y, fmaf(sc.x, (float) sv[i + 1], nc), acc0[i + 1]);
-                            acc0[i + 2] = fmaf(da.z, fmaf(sc.x, (float) sv[i + 2], nc), acc0[i + 2]);
-                            acc0[i + 3] = fmaf(da.w, fmaf(sc.x, (float) sv[i + 3], nc), acc0[i + 3]);
-                        }
-                        tc_ld32(tmem + tlane + tb * TC_N + c1, sv);
-                        tc_wait_ld();
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) tc_mbar_arrive(&S.tempty[tb]);          // TMEM buffer is free again
+                        for (int h = 0; h < 2; ++h) {
+                            int sv[16];
+                            { const long long t0_ = TC_CLK();
+                            tc_ld16(tmem + tlane + tb * TC_N + (h ? c1 : c0), sv);
+                            tc_wait_ld(); pw_ld += TC_CLK() - t0_; }
+                            if (h == 1) {
+                                tc_fence_before();
+                                __syncwarp();
+                                if (lane == 0) tc_mbar_arrive(&S.tempty[tb]);      // TMEM buffer is free again
+                            }
+                            const float * dp = &T.d4[j][h ? c1 : c0];
+#ifdef TC_ABLATE_MATH
+                            acc[h] += __int_as_float(sv[0] ^ sv[15]);
+#else
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            const float4 db = *reinterpret_cast<const float4 *>(&T.d4[j][c1 + i]);
-                            acc1[i + 0] = fmaf(db.x, fmaf(sc.x, (float) sv[i + 0], nc), acc1[i + 0]);
-                            acc1[i + 1] = fmaf(db.y, fmaf(sc.x, (float) sv[i + 1], nc), acc1[i + 1]);
-                            acc1[i + 2] = fmaf(db.z, fmaf(sc.x, (float) sv[i + 2], nc), acc1[i + 2]);
-                            acc1[i + 3] = fmaf(db.w, fmaf(sc.x, (float) sv[i + 3], nc), acc1[i + 3]);
+                            for (int i = 0; i < 16; i += 4) {
+                                const float4 dd = *reinterpret_cast<const float4 *>(dp + i);
+                                const int o = h * 16 + i;
+                                acc[o + 0] = fmaf(dd.x, fmaf(d8, tc_i2f(sv[i + 0]), nc), acc[o + 0]);
+                                acc[o + 1] = fmaf(dd.y, fmaf(d8, tc_i2f(sv[i + 1]), nc), acc[o + 1]);
+                                acc[o + 2] = fmaf(dd.z, fmaf(d8, tc_i2f(sv[i + 2]), nc), acc[o + 2]);
+                                acc[o + 3] = fmaf(dd.w, fmaf(d8, tc_i2f(sv[i + 3]), nc), acc[o + 3]);
+                            }
+#endif
                         }
                     } else {
                         tc_fence_before();
@@ -346,12 +445,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
             }
             if (!ok) break;
             // ---- tile epilogue -----------------------------------------------------
-            if (slot >= 0) {
-                if (EPI) {
-                    // acc0 = gate rows, acc1 = the same 32 up rows: one Q8_1 block of this slot
+            const long long tt0_ = TC_CLK();
+            if (EPI) {
+                // acc[0..7] = 16 gate rows, acc[8..15] = the same 16 up rows.  v goes through shared memory so
+                // that one thread sees the 32 rows of a Q8_1 block: subs (0,1) form block 0, (2,3) block 1.
+                if (slot >= 0) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float g0 = __fmul_rn(acc[2 * i], scl), g1 = __fmul_rn(acc[2 * i + 1], scl);
+                        const float u0 = __fmul_rn(acc[16 + 2 * i], scl), u1 = __fmul_rn(acc[16 + 2 * i + 1], scl);
+                        S.vbuf[tok][16 * sub + 2 * i]     = __fmul_rn(lkb_silu(g0), u0);
+                        S.vbuf[tok][16 * sub + 2 * i + 1] = __fmul_rn(lkb_silu(g1), u1);
+                    }
+                }
+                // the four warps of this quadrant meet (bounded, like every other wait)
+                __syncwarp();
+                if (lane == 0) tc_mbar_arrive(&S.qbar[quad]);
+                if (!tc_wait(S, &S.qbar[quad], nitem & 1u, 32u)) break;
+                if ((sub & 1) == 0 && slot >= 0) {
+                    const int b = sub >> 1;
                     float v[32];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __fmul_rn(lkb_silu(__fmul_rn(acc0[i], scl)), __fmul_rn(acc1[i], scl));
+                    for (int i = 0; i < 32; ++i) v[i] = S.vbuf[tok][32 * b + i];
                     float am = 0.0f;
 #pragma unroll
                     for (int i = 0; i < 32; ++i) am = fmaxf(am, fabsf(v[i]));
@@ -368,39 +483,38 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
                     unsigned pk[8];
 #pragma unroll
                     for (int w = 0; w < 8; ++w) {
-                        unsigned p = 0;
+                        unsigned pp = 0;
 #pragma unroll
-                        for (int b = 0; b < 4; ++b) {
-                            const int q = (am == 0.0f) ? 0 : (int) roundf(__fdiv_rn(v[w * 4 + b], d));
-                            p |= ((unsigned) q & 0xFFu) << (8 * b);
+                        for (int bb = 0; bb < 4; ++bb) {
+                            const int q = (am == 0.0f) ? 0 : (int) roundf(__fdiv_rn(v[w * 4 + bb], d));
+                            pp |= ((unsigned) q & 0xFFu) << (8 * bb);
                         }
-                        pk[w] = p;
+                        pk[w] = pp;
                     }
-                    const int orow0 = rt * 64 + 32 * grp;              // first intermediate row of the block
+                    const int orow0 = rt * 64 + 32 * b;                // first intermediate row of the block
                     int8_t * oq = g.oqs + (size_t) slot * (g.okb * 32) + orow0;
                     *reinterpret_cast<uint4 *>(oq) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                     *reinterpret_cast<uint4 *>(oq + 16) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
                     const __half2 ds = __floats2half2_rn(d, sum);
                     reinterpret_cast<float2 *>(g.osc)[(size_t) slot * g.okb + orow0 / 32] =
                         make_float2(__low2float(ds), __fmul_rn(8.0f, __high2float(ds)));
-                } else {
-                    float * p0 = g.out + (size_t) slot * g.out_ld + rt * TC_N + c0;
-                    float * p1 = g.out + (size_t) slot * g.out_ld + rt * TC_N + c1;
+                }
+            } else if (slot >= 0) {
+                float * p0 = g.out + (size_t) slot * g.out_ld + rt * TC_N + c0;
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        float4 o0 = make_float4(__fmul_rn(acc0[i], scl), __fmul_rn(acc0[i + 1], scl), __fmul_rn(acc0[i + 2], scl), __fmul_rn(acc0[i + 3], scl));
-                        float4 o1 = make_float4(__fmul_rn(acc1[i], scl), __fmul_rn(acc1[i + 1], scl), __fmul_rn(acc1[i + 2], scl), __fmul_rn(acc1[i + 3], scl));
-                        if (g.add) {
-                            const float4 a0 = *reinterpret_cast<const float4 *>(p0 + i), a1 = *reinterpret_cast<const float4 *>(p1 + i);
-                            o0 = make_float4(__fadd_rn(a0.x, o0.x), __fadd_rn(a0.y, o0.y), __fadd_rn(a0.z, o0.z), __fadd_rn(a0.w, o0.w));
-                            o1 = make_float4(__fadd_rn(a1.x, o1.x), __fadd_rn(a1.y, o1.y), __fadd_rn(a1.z, o1.z), __fadd_rn(a1.w, o1.w));
-                        }
-                        *reinterpret_cast<float4 *>(p0 + i) = o0;
-                        *reinterpret_cast<float4 *>(p1 + i) = o1;
+                for (int i = 0; i < 32; i += 4) {
+                    float4 o0 = make_float4(__fmul_rn(acc[i], scl), __fmul_rn(acc[i + 1], scl),
+                                            __fmul_rn(acc[i + 2], scl), __fmul_rn(acc[i + 3], scl));
+                    if (g.add) {
+                        const float4 a0 = *reinterpret_cast<const float4 *>(p0 + i);
+                        o0 = make_float4(__fadd_rn(a0.x, o0.x), __fadd_rn(a0.y, o0.y), __fadd_rn(a0.z, o0.z), __fadd_rn(a0.w, o0.w));
                     }
+                    *reinterpret_cast<float4 *>(p0 + i) = o0;
                 }
             }
+            pw_tail += TC_CLK() - tt0_;
         }
+        if (blockIdx.x == 0 && tid == 128) { g_tc_prof[8] = pw_full; g_tc_prof[9] = pw_tf; g_tc_prof[10] = clock64() - pt0; g_tc_prof[11] = pw_ld; g_tc_prof[12] = pw_tail; }
     }
 
     // ---- teardown: everyone meets, then the allocating warp frees TMEM ------------
@@ -433,7 +547,7 @@ int lkb_gemm_tc_launch(const lkb_pf_gemm * g, int epi, int max_tiles, cudaStream
     else if (g->N % TC_N || g->out_ld % 4 || ((size_t) g->out & 15)) return LKB_ERR_UNSUPPORTED;
     if (g->perm && max_tiles > TC_MAX_TILES) return LKB_ERR_UNSUPPORTED;
     if (!g->perm && (g->ntok + TC_M - 1) / TC_M > TC_MAX_TILES) return LKB_ERR_UNSUPPORTED;
-    if (((size_t) g->aqs & 15) || ((size_t) g->asc & 7)) return LKB_ERR_UNSUPPORTED;
+    if (((size_t) g->aqs & 15) || ((size_t) g->asc & 15)) return LKB_ERR_UNSUPPORTED;
     const int grid = lkb_context().sm_count;
     if (epi) k_pf_gemm_tc<1><<<grid, TC_THREADS, sizeof(TcSmem), st>>>(*g, max_tiles);
     else     k_pf_gemm_tc<0><<<grid, TC_THREADS, sizeof(TcSmem), st>>>(*g, max_tiles);
@@ -441,6 +555,11 @@ int lkb_gemm_tc_launch(const lkb_pf_gemm * g, int epi, int max_tiles, cudaStream
 }
 
 extern "C" {
+// Tuning hook (not in the public header): copies the 16 profiling counters of the last launch.
+__attribute__((visibility("default"))) int lkb_debug_gemm_prof(unsigned long long * out16) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    return cudaMemcpyFromSymbol(out16, g_tc_prof, 16 * sizeof(unsigned long long)) == cudaSuccess ? 0 : -1;
+}
 int lkb_pf_gemm_status(void) {
     unsigned v = 0, z = 0;
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
