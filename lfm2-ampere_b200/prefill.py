@@ -73,3 +73,103 @@ class PrefillStack:
     def macs_per_step(self):
         """Useful multiply-accumulates (slots only, as the reference counts them: tests/test_prefill.cu:634)."""
         return len(self.layers) * self.ns * (2 * I * H + H * I)
+
+
+def shard_layer(l, rank, world):
+    """The expert shard [rank*64/world, (rank+1)*64/world) of a layer: contiguous row ranges of the
+    stacked *_exps planes (views, no copy).  Router, bias and norm weights are replicated."""
+    import copy
+    per = E // world
+    e0, e1 = rank * per, (rank + 1) * per
+    s = copy.copy(l)
+    gb, db = I * (H // 32), H * (I // 32)                 # blocks per expert
+    s.gate_qs, s.gate_d = l.gate_qs[e0 * gb * 16:e1 * gb * 16], l.gate_d[e0 * gb:e1 * gb]
+    s.up_qs, s.up_d = l.up_qs[e0 * gb * 16:e1 * gb * 16], l.up_d[e0 * gb:e1 * gb]
+    s.down_qs, s.down_d = l.down_qs[e0 * db * 16:e1 * db * 16], l.down_d[e0 * db:e1 * db]
+    return s
+
+
+class PrefillStackEP:
+    """Expert-parallel prefill over torch.distributed (one process per GPU, NCCL).
+
+    Rank r holds tokens [r*m/G, (r+1)*m/G) of the chunk and the experts [r*64/G, (r+1)*64/G) of every
+    layer.  Norm, router, selection and the combine run on the token's home rank; the two grouped GEMMs
+    run on the expert's owner, fed by a token all-to-all (see ep.py).  Results are bit-identical to
+    PrefillStack on one GPU."""
+
+    def __init__(self, layers, m_total, rank, world, device="cuda", group=None):
+        from . import ep as _ep
+        self._ep = _ep
+        assert m_total % world == 0 and E % world == 0
+        self.rank, self.world, self.group = rank, world, group
+        self.layers = layers
+        self.shards = [shard_layer(l, rank, world) for l in layers]
+        self.m = m_total // world
+        m, cap = self.m, m_total * TOPK                          # worst case: every slot of the chunk lands here
+        self.cap = cap
+        self.max_tiles = cap // 64 + E
+        f32 = dict(dtype=torch.float32, device=device)
+        i32 = dict(dtype=torch.int32, device=device)
+        self.X = torch.zeros(m, H, **f32)
+        self.a_qs = torch.zeros(m, H, dtype=torch.int8, device=device)
+        self.a_sc = torch.zeros(m, H // 32, 2, **f32)
+        self.inv = torch.zeros(m, **f32)
+        self.h32 = torch.zeros(m, H, **f32)
+        self.sel = torch.zeros(m, E, **f32)
+        self.sig = torch.zeros(m, E, **f32)
+        self.idx = torch.zeros(m, TOPK, **i32)
+        self.w = torch.zeros(m, TOPK, **f32)
+        self.cnt = torch.zeros(E, **i32)
+        self.off = torch.zeros(E, **i32)
+        self.tiles = torch.zeros(self.max_tiles, 4, **i32)
+        self.ntiles = torch.zeros(1, **i32)
+        self.perm = torch.zeros(cap, **i32)
+        self.a2_qs = torch.zeros(cap, I, dtype=torch.int8, device=device)
+        self.a2_sc = torch.zeros(cap, I // 32, 2, **f32)
+        self.D = torch.zeros(cap, H, **f32)
+        self.n_qs = torch.zeros(m, H, dtype=torch.int8, device=device)
+        self.n_sc = torch.zeros(m, H // 32, 2, **f32)
+        self.n_inv = torch.zeros(m, **f32)
+        self.a = api.pf_act(self.a_qs, self.a_sc)
+        self.an = api.pf_act(self.n_qs, self.n_sc)
+        self.recv_slots = []                                     # per layer: slots this rank computed (load balance)
+
+    def _experts(self, li):
+        sh = self.shards[li]
+
+        def fn(le, recv):
+            qs, sc, inv = recv
+            n = int(le.numel())
+            if n == 0:
+                return self.D[:0]
+            api.zero_i32(self.cnt, E)
+            api.k_pf_moe_count(le, n, self.cnt)
+            api.k_pf_moe_plan(self.cnt, self.off, self.tiles, self.ntiles)
+            api.k_pf_moe_scatter(le, n, self.off, self.perm)
+            mt = n // 64 + E
+            g = api.make_pf_gemm([(sh.gate_qs, sh.gate_d), (sh.up_qs, sh.up_d)], [I, I, I], I, H // 32, qs, sc,
+                                 exp_stride=I * (H // 32), perm=self.perm, tiles=self.tiles, ntiles=self.ntiles,
+                                 a_shift=0, scale=inv, oqs=self.a2_qs, osc=self.a2_sc, okb=I // 32)
+            api.pf_gemm_swiglu(g, mt)
+            dn = api.make_pf_gemm([(sh.down_qs, sh.down_d)], [H, H, H], H, I // 32, self.a2_qs, self.a2_sc,
+                                  exp_stride=H * (I // 32), perm=self.perm, tiles=self.tiles, ntiles=self.ntiles,
+                                  a_shift=0, out=self.D, out_ld=H)
+            api.pf_gemm_moe(dn, mt)
+            return self.D[:n]
+        return fn
+
+    def layer(self, i):
+        l, m = self.layers[i], self.m
+        api.k_pf_norm(self.X, l.norm_w, 0, self.a, self.inv, self.h32, m)
+        api.k_pf_router(self.h32, m, l.router, l.rbias, self.inv, self.sel, self.sig)
+        api.k_pf_select(self.sel, self.sig, m, self.idx, self.w)
+        D, plan = self._ep.ep_moe_layer(self.idx, [self.a_qs, self.a_sc, self.inv], self._experts(i), self.world,
+                                        self.group)
+        self.recv_slots.append(sum(plan.recv_counts))
+        nxt = self.layers[(i + 1) % len(self.layers)]
+        api.k_pf_moe_combine_norm(self.X, D, self.w, nxt.norm_w, self.an, self.n_inv, m)
+
+    def step(self):
+        self.recv_slots = []
+        for i in range(len(self.layers)):
+            self.layer(i)
