@@ -222,6 +222,10 @@ int lkb_pf_swiglu(const float * Y, int ld, int up_off, int kb, lkb_pf_act a, int
  * picks the small form for m <= 256 (ref: src/engine.cu:1170-1176); so does this. */
 int lkb_pf_router(const float * H, int m, const float * Wr, const float * bias, const float * inv,
                   float * sel, float * sig, lkb_stream_t st);
+/* The tiled form for any m (what lkb_pf_router picks above 256 tokens).  A caller that splits one chunk
+ * over several GPUs uses it to keep the form -- and with it every logit bit -- independent of the split. */
+int lkb_pf_router_tiled(const float * H, int m, const float * Wr, const float * bias, const float * inv,
+                        float * sel, float * sig, lkb_stream_t st);
 int lkb_pf_router_small(const float * H, int m, const float * Wr, const float * bias, const float * inv,
                         float * sel, float * sig, lkb_stream_t st);
 /* ref: src/prefill.cuh:115-116  k_pf_select */

@@ -17,7 +17,7 @@ __all__ = [
     "k_quantize_q8_1", "k_rmsnorm_q8_1", "norm_produce", "k_gemv_q4_0", "k_gemv_q4_0_prod", "k_gemv_q4_0_3",
     "k_gemv_q4_0_exp2", "k_gemv_q4_0_exp", "k_swiglu", "k_moe_accum4", "k_moe_down_accum", "k_router_dot",
     "k_router_top4", "router_top4_softmax", "block_sumi", "k_pf_norm", "k_pf_quant_rows", "k_pf_swiglu",
-    "k_pf_router", "k_pf_router_small", "k_pf_select", "k_pf_moe_count", "k_pf_moe_plan", "k_pf_moe_scatter",
+    "k_pf_router", "k_pf_router_small", "k_pf_router_tiled", "k_pf_select", "k_pf_moe_count", "k_pf_moe_plan", "k_pf_moe_scatter",
     "pf_gemm_dense", "pf_gemm_moe", "pf_gemm_swiglu", "k_pf_moe_combine", "k_pf_moe_combine_norm",
     "k_pf_pack_q8_1", "zero_i32", "moe_layer_desc", "moe_scratch", "moe_ffn_decode", "moe_ffn_decode_stack",
     "layer_descs_to_device", "set_pdl", "pf_gemm_config", "sm_count",
@@ -148,6 +148,11 @@ def k_pf_swiglu(Y, ld, up_off, kb, a, rows):
 
 def k_pf_router(H, m, Wr, bias, inv, sel, sig):
     check(lib.lkb_pf_router(ptr(H), m, ptr(Wr), ptr(bias), ptr(inv), ptr(sel), ptr(sig), stream()), "k_pf_router")
+
+
+def k_pf_router_tiled(H, m, Wr, bias, inv, sel, sig):
+    check(lib.lkb_pf_router_tiled(ptr(H), m, ptr(Wr), ptr(bias), ptr(inv), ptr(sel), ptr(sig), stream()),
+          "k_pf_router_tiled")
 
 
 def k_pf_router_small(H, m, Wr, bias, inv, sel, sig):

@@ -528,14 +528,19 @@ int lkb_pf_router_small(const float * H, int m, const float * Wr, const float * 
     return lkb_check_launch();
 }
 
-int lkb_pf_router(const float * H, int m, const float * Wr, const float * bias, const float * inv,
-                  float * sel, float * sig, lkb_stream_t st) {
+int lkb_pf_router_tiled(const float * H, int m, const float * Wr, const float * bias, const float * inv,
+                        float * sel, float * sig, lkb_stream_t st) {
     LKB_REQUIRE_INIT();
     if (!H || !Wr || !bias || !inv || !sel || !sig) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    if (m <= 256) return lkb_pf_router_small(H, m, Wr, bias, inv, sel, sig, st);
     k_pf_router<<<(m + 31) / 32, 256, 0, (cudaStream_t) st>>>(H, m, Wr, bias, inv, sel, sig);
     return lkb_check_launch();
+}
+
+int lkb_pf_router(const float * H, int m, const float * Wr, const float * bias, const float * inv,
+                  float * sel, float * sig, lkb_stream_t st) {
+    if (m > 0 && m <= 256) return lkb_pf_router_small(H, m, Wr, bias, inv, sel, sig, st);
+    return lkb_pf_router_tiled(H, m, Wr, bias, inv, sel, sig, st);
 }
 
 int lkb_pf_select(const float * sel, const float * sig, int m, int * idx, float * w, lkb_stream_t st) {

@@ -105,6 +105,7 @@ class PrefillStackEP:
         self.layers = layers
         self.shards = [shard_layer(l, rank, world) for l in layers]
         self.m = m_total // world
+        self.m_total = m_total
         m, cap = self.m, m_total * TOPK                          # worst case: every slot of the chunk lands here
         self.cap = cap
         self.max_tiles = cap // 64 + E
@@ -161,7 +162,9 @@ class PrefillStackEP:
     def layer(self, i):
         l, m = self.layers[i], self.m
         api.k_pf_norm(self.X, l.norm_w, 0, self.a, self.inv, self.h32, m)
-        api.k_pf_router(self.h32, m, l.router, l.rbias, self.inv, self.sel, self.sig)
+        # the router form follows the CHUNK size, as on one GPU (ref: src/engine.cu:1170-1176)
+        router = api.k_pf_router_small if self.m_total <= 256 else api.k_pf_router_tiled
+        router(self.h32, m, l.router, l.rbias, self.inv, self.sel, self.sig)
         api.k_pf_select(self.sel, self.sig, m, self.idx, self.w)
         D, plan = self._ep.ep_moe_layer(self.idx, [self.a_qs, self.a_sc, self.inv], self._experts(i), self.world,
                                         self.group)
