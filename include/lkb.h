@@ -43,6 +43,7 @@ extern "C" {
 #define LKB_ERR_NOT_INIT    -10004   /* lkb_init() has not run for the current device */
 #define LKB_ERR_DEVICE      -10005   /* not an sm_100 device */
 #define LKB_ERR_TIMEOUT     -10006   /* a bounded device-side wait gave up (status word set) */
+#define LKB_ERR_SCRATCH     -10007   /* the shape needs more scratch than the library's built-in array holds */
 
 /* Model constants of the path.  ref: src/kernels.cuh:11-24 */
 #define LKB_HIDDEN      2048
@@ -190,6 +191,29 @@ int lkb_moe_ffn_decode(const lkb_moe_layer * layer, float * x, int * idx_out, fl
 int lkb_moe_ffn_decode_stack(const lkb_moe_layer * layers_dev, int n_layers, int softmax, float * x,
                              int * idx_out, float * w_out, const lkb_norm_prod_t * next,
                              const lkb_moe_scratch * scratch, lkb_stream_t st);
+
+/* lkb_moe_ffn_decode_stack for callers that must not allocate device memory.
+ * Who that is: an engine that, like the reference's, sizes one pack allocation plus its KV cache at start-up
+ * and hands the rest of the card to someone else; a plug-in living inside a host process whose memory pool
+ * owns every byte (a foreign cudaMalloc there fragments the pool or is simply forbidden); a latency-critical
+ * decode loop, where cudaMalloc/cudaFree would stall the whole device at an unpredictable moment.  Such a
+ * caller still owns its inputs and outputs (layers_dev, x, idx_out, w_out, next) but has nowhere to put the
+ * kernel's scratch, so here the scratch -- 64 router logits, the 2*4*1536 gate|up outputs and two barrier
+ * words, 49.7 KB for this model -- sits in a fixed LKB_STATIC_SCRATCH_BYTES array inside the library (every
+ * GPU that loads the library carries that array until the process exits).
+ * The caller states its model shape; a shape whose scratch does not fit the array is refused with
+ * LKB_ERR_SCRATCH, and a shape other than the one the kernel is built for (2048 / 1536 / 64 / 4) with
+ * LKB_ERR_SHAPE.  Nothing is allocated or freed, by this call or by anything it calls.
+ * The first call on a device looks up the array's device address (once per device, with that device
+ * current); make that first call outside any stream capture.  All calls share the one array, which keeps
+ * whatever the previous call left in it: the barrier words are cleared at the start of every call, the rest
+ * is overwritten before it is read.  Two calls that overlap on the GPU (different streams) race on it.
+ * No counterpart in the reference. */
+#define LKB_STATIC_SCRATCH_BYTES 65536
+#define LKB_STATIC_MAX_DEVICES   64
+int lkb_moe_ffn_decode_stack_static(const lkb_moe_layer * layers_dev, int n_layers, int hidden, int inter,
+                                    int n_experts, int top_k, int softmax, float * x, int * idx_out, float * w_out,
+                                    const lkb_norm_prod_t * next, lkb_stream_t st);
 
 /* ------------------------------------------------------------------ router */
 /* ref: src/kernels.cuh:543-547  k_router_dot<<<64,32>>> (sel/sig may be null) */

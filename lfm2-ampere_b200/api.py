@@ -20,7 +20,7 @@ __all__ = [
     "k_pf_router", "k_pf_router_small", "k_pf_router_tiled", "k_pf_select", "k_pf_moe_count", "k_pf_moe_plan", "k_pf_moe_scatter",
     "pf_gemm_dense", "pf_gemm_moe", "pf_gemm_swiglu", "k_pf_moe_combine", "k_pf_moe_combine_norm",
     "k_pf_pack_q8_1", "zero_i32", "moe_layer_desc", "moe_scratch", "moe_ffn_decode", "moe_ffn_decode_stack",
-    "layer_descs_to_device", "set_pdl", "pf_gemm_config", "sm_count",
+    "layer_descs_to_device", "moe_ffn_decode_stack_static", "set_pdl", "pf_gemm_config", "sm_count",
 ]
 
 
@@ -248,3 +248,11 @@ def moe_ffn_decode(desc, x, idx_out, w_out, next_np, scratch):
 def moe_ffn_decode_stack(layers_dev, n_layers, softmax, x, idx_out, w_out, next_np, scratch):
     check(lib.lkb_moe_ffn_decode_stack(ptr(layers_dev), n_layers, softmax, ptr(x), ptr(idx_out), ptr(w_out),
                                        _np(next_np), C.byref(scratch), stream()), "moe_ffn_decode_stack")
+
+
+def moe_ffn_decode_stack_static(layers_dev, n_layers, x, idx_out, w_out, next_np, hidden=2048, inter=1536,
+                                n_experts=64, top_k=4, softmax=0):
+    """lkb_moe_ffn_decode_stack with the kernel's scratch inside the library (allocates nothing)."""
+    check(lib.lkb_moe_ffn_decode_stack_static(ptr(layers_dev), n_layers, hidden, inter, n_experts, top_k, softmax,
+                                              ptr(x), ptr(idx_out), ptr(w_out), _np(next_np), stream()),
+          "moe_ffn_decode_stack_static")

@@ -642,6 +642,7 @@ const char * lkb_error_string(int s) {
     case LKB_ERR_NOT_INIT: return "lkb_init() has not run";
     case LKB_ERR_DEVICE: return "not an sm_100 device";
     case LKB_ERR_TIMEOUT: return "bounded device wait gave up";
+    case LKB_ERR_SCRATCH: return "shape needs more scratch than the built-in array (LKB_STATIC_SCRATCH_BYTES) holds";
     default: return s < 0 ? cudaGetErrorString((cudaError_t) (-s)) : "unknown";
     }
 }

@@ -593,4 +593,46 @@ int lkb_moe_ffn_decode_stack(const lkb_moe_layer * layers_dev, int n_layers, int
     return fused_launch(a, (cudaStream_t) st);
 }
 
+// ---------------------------------------------------------------------------
+// The same stack kernel for callers that may not allocate device memory: its global scratch
+// (router logits, gate|up outputs, barrier words) lives in a fixed array inside this library.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_scratch[LKB_STATIC_SCRATCH_BYTES];
+static void * g_static_scratch_addr[LKB_STATIC_MAX_DEVICES] = {};     // device address of the array, per device
+
+int lkb_moe_ffn_decode_stack_static(const lkb_moe_layer * layers_dev, int n_layers, int hidden, int inter,
+                                    int n_experts, int top_k, int softmax, float * x, int * idx_out, float * w_out,
+                                    const lkb_norm_prod_t * next, lkb_stream_t st) {
+    if (!layers_dev) return LKB_ERR_NULL;
+    if (hidden <= 0 || inter <= 0 || n_experts <= 0 || top_k <= 0) return LKB_ERR_SHAPE;
+    // bytes of scratch this shape needs, laid out in 256-byte aligned pieces
+    const size_t logits_b = (((size_t) n_experts * 4) + 255) & ~(size_t) 255;
+    const size_t gu_b = (((size_t) 2 * top_k * inter * 4) + 255) & ~(size_t) 255;
+    const size_t need = logits_b + gu_b + 256;
+    if (need > (size_t) LKB_STATIC_SCRATCH_BYTES) return LKB_ERR_SCRATCH;      // larger than the built-in array
+    if (hidden != LKB_HIDDEN || inter != LKB_MOE_INTER || n_experts != LKB_N_EXPERTS || top_k != LKB_TOP_K)
+        return LKB_ERR_SHAPE;                                                  // the kernel is built for one shape
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return -(int) e;
+    if (dev < 0 || dev >= LKB_STATIC_MAX_DEVICES) return LKB_ERR_DEVICE;
+    if (!g_static_scratch_addr[dev]) {
+        // First call on this device: the array's NAME is only a host-side handle; the kernel needs the
+        // address the array has on the current device.
+        void * p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p) return e != cudaSuccess ? -(int) e : LKB_ERR_DEVICE;
+        g_static_scratch_addr[dev] = p;
+    }
+    unsigned char * base = static_cast<unsigned char *>(g_static_scratch_addr[dev]);
+    FusedArgs a = {};
+    a.layers = layers_dev; a.n_layers = n_layers; a.x = x; a.idx_out = idx_out; a.w_out = w_out;
+    if (next && next->w) { a.final_norm_w = next->w; a.out_h32 = next->h32; a.out_yq8 = reinterpret_cast<lkb_q8blk *>(next->yq8); a.out_ssq = next->ssq; }
+    a.logits = reinterpret_cast<float *>(base);
+    a.gu = reinterpret_cast<float *>(base + logits_b);
+    a.bar = reinterpret_cast<unsigned *>(base + logits_b + gu_b);              // zeroed by the launcher before every launch
+    a.softmax = softmax;
+    return fused_launch(a, (cudaStream_t) st);
+}
+
 }  // extern "C"
