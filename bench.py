@@ -39,6 +39,9 @@ N_LAYERS = 40
 H, E, TOPK, I = 2048, 64, 4, 1536
 LAYER_BYTES = E * H * 4 + 2 * TOPK * I * (H // 32) * 18 + TOPK * H * (I // 32) * 18 + 3 * H * 4   # 21,782,528
 GATEUP_BYTES = 2 * TOPK * I * (H // 32) * 18 + 64 * 36 + 2 * TOPK * I * 4                          # per launch
+# DRAM traffic of the fused decode kernel per MoE layer, from one ncu capture of a 4-layer launch
+# (dram__bytes_read.sum + dram__bytes_write.sum = 87,156,736 + 2,285,312 B; it grows in proportion to the layers)
+FUSED_TRAFFIC_PER_LAYER = (87156736 + 2285312) / 4
 METRIC = "bs1 decode tok/s"
 UNIT = "tok/s"
 
@@ -289,7 +292,7 @@ def run_ours(args):
         ach = args.layers * LAYER_BYTES / (k_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "kernel": f"k_moe_ffn_stack (persistent, {args.layers} MoE layers per launch)",
                     "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
-                    "peak_kind": f"of {peak_kind}", "traffic": None,
+                    "peak_kind": f"of {peak_kind}", "traffic": args.layers * FUSED_TRAFFIC_PER_LAYER,
                     "algorithmic_bytes_per_launch": args.layers * LAYER_BYTES, "avg_launch_ms": k_ms}
         n_launch = args.steps
     else:

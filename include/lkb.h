@@ -280,6 +280,18 @@ int lkb_pf_moe_combine_norm(float * X, const float * D, const float * w, const f
                             float * inv_out, int m, lkb_stream_t st);
 int lkb_pf_pack_q8_1(lkb_pf_act a, int t, lkb_block_q8_1 * y, lkb_stream_t st);
 
+/* ------------------------------------------------ expert-parallel dispatch */
+/* Helpers of the multi-GPU prefill; no counterpart in the reference (single GPU).  A slot's activation
+ * travels as one LKB_EP_ROW_BYTES row: 2048 B quants | 512 B (d8, 8sum) | 1/rms | expert id on the owner.
+ * pack: row p = slot send_order[p] (token = slot >> 2), pos[slot] = p.  unpack: rows -> planar Q8_1 + inv +
+ * local expert ids.  combine_norm_gather: lkb_pf_moe_combine_norm with the D row of slot s at D[pos[s]]. */
+#define LKB_EP_ROW_BYTES (LKB_HIDDEN + (LKB_HIDDEN / 32) * 8 + 16)
+int lkb_ep_pack_rows(lkb_pf_act a, const float * inv, const int * idx, const int * send_order, int n,
+                     int experts_per_rank, void * out, int * pos, lkb_stream_t st);
+int lkb_ep_unpack_rows(const void * in, int n, lkb_pf_act a, float * inv, int * local_expert, lkb_stream_t st);
+int lkb_pf_moe_combine_norm_gather(float * X, const float * D, const int * pos, const float * w, const float * nw,
+                                   lkb_pf_act a, float * inv_out, int m, lkb_stream_t st);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

@@ -20,7 +20,7 @@ __all__ = [
     "k_pf_router", "k_pf_router_small", "k_pf_router_tiled", "k_pf_select", "k_pf_moe_count", "k_pf_moe_plan", "k_pf_moe_scatter",
     "pf_gemm_dense", "pf_gemm_moe", "pf_gemm_swiglu", "k_pf_moe_combine", "k_pf_moe_combine_norm",
     "k_pf_pack_q8_1", "zero_i32", "moe_layer_desc", "moe_scratch", "moe_ffn_decode", "moe_ffn_decode_stack",
-    "layer_descs_to_device", "moe_ffn_decode_stack_static", "set_pdl", "pf_gemm_config", "sm_count",
+    "layer_descs_to_device", "ep_pack_rows", "ep_unpack_rows", "k_pf_moe_combine_norm_gather", "moe_ffn_decode_stack_static", "set_pdl", "pf_gemm_config", "sm_count",
 ]
 
 
@@ -256,3 +256,21 @@ def moe_ffn_decode_stack_static(layers_dev, n_layers, x, idx_out, w_out, next_np
     check(lib.lkb_moe_ffn_decode_stack_static(ptr(layers_dev), n_layers, hidden, inter, n_experts, top_k, softmax,
                                               ptr(x), ptr(idx_out), ptr(w_out), _np(next_np), stream()),
           "moe_ffn_decode_stack_static")
+
+
+# ------------------------------------------------- expert-parallel helpers --
+EP_ROW_BYTES = 2048 + 512 + 16
+
+
+def ep_pack_rows(a, inv, idx, send_order, n, experts_per_rank, out, pos):
+    check(lib.lkb_ep_pack_rows(a, ptr(inv), ptr(idx), ptr(send_order), n, experts_per_rank, ptr(out), ptr(pos),
+                               stream()), "ep_pack_rows")
+
+
+def ep_unpack_rows(buf, n, a, inv, local_expert):
+    check(lib.lkb_ep_unpack_rows(ptr(buf), n, a, ptr(inv), ptr(local_expert), stream()), "ep_unpack_rows")
+
+
+def k_pf_moe_combine_norm_gather(X, D, pos, w, nw, a, inv_out, m):
+    check(lib.lkb_pf_moe_combine_norm_gather(ptr(X), ptr(D), ptr(pos), ptr(w), ptr(nw), a, ptr(inv_out), m, stream()),
+          "k_pf_moe_combine_norm_gather")

@@ -319,6 +319,74 @@ __global__ void __launch_bounds__(64) k_pf_pack_q8_1(const int8_t * __restrict__
 }
 
 // ---------------------------------------------------------------------------
+// Expert-parallel dispatch helpers (no counterpart in the reference, which is single-GPU).
+// A slot travels as ONE 2576-byte row: 2048 B of quants | 512 B of (d8, 8sum) pairs | 1/rms | expert id on the
+// owner | 8 B pad, so that a layer's dispatch is a single all-to-all.
+// ---------------------------------------------------------------------------
+#define EP_ROW_BYTES (LKB_HIDDEN + (LKB_HIDDEN / 32) * 8 + 16)        // 2576, a multiple of 16
+
+// Row p of `out` = the activation of slot send_order[p] (token = slot >> 2); pos[slot] = p.
+__global__ void __launch_bounds__(192) k_ep_pack(const int8_t * __restrict__ aqs, const float2 * __restrict__ asc,
+                                                 const float * __restrict__ inv, const int * __restrict__ idx,
+                                                 const int * __restrict__ send_order, int experts_per_rank,
+                                                 unsigned char * __restrict__ out, int * __restrict__ pos) {
+    const int p = blockIdx.x, i = threadIdx.x;
+    const int slot = send_order[p], t = slot >> 2;
+    uint4 * row = reinterpret_cast<uint4 *>(out + (size_t) p * EP_ROW_BYTES);
+    if (i < 128) row[i] = reinterpret_cast<const uint4 *>(aqs + (size_t) t * LKB_HIDDEN)[i];
+    else if (i < 160) row[i] = reinterpret_cast<const uint4 *>(asc + (size_t) t * (LKB_HIDDEN / 32))[i - 128];
+    else if (i == 160) {
+        const int e = idx[slot];
+        row[160] = make_uint4(__float_as_uint(inv[t]), (unsigned) (e % experts_per_rank), 0u, 0u);
+        pos[slot] = p;
+    }
+}
+
+__global__ void __launch_bounds__(192) k_ep_unpack(const unsigned char * __restrict__ in, int8_t * __restrict__ qs,
+                                                   float2 * __restrict__ sc, float * __restrict__ inv, int * __restrict__ le) {
+    const int p = blockIdx.x, i = threadIdx.x;
+    const uint4 * row = reinterpret_cast<const uint4 *>(in + (size_t) p * EP_ROW_BYTES);
+    if (i < 128) reinterpret_cast<uint4 *>(qs + (size_t) p * LKB_HIDDEN)[i] = row[i];
+    else if (i < 160) reinterpret_cast<uint4 *>(sc + (size_t) p * (LKB_HIDDEN / 32))[i - 128] = row[i];
+    else if (i == 160) { const uint4 v = row[160]; inv[p] = __uint_as_float(v.x); le[p] = (int) v.y; }
+}
+
+// combine + next norm with the four D rows of a token found through pos[] (their places in the returned buffer)
+__global__ void __launch_bounds__(256) k_pf_moe_combine_norm_gather(float * __restrict__ X, const float * __restrict__ D,
+                                                                    const int * __restrict__ pos, const float * __restrict__ w,
+                                                                    const float * __restrict__ nw, int8_t * __restrict__ aqs,
+                                                                    float2 * __restrict__ asc, float * __restrict__ inv_out) {
+    const int t = blockIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    __shared__ float s_sq[64];
+    float wk[LKB_TOP_K]; const float * dr[LKB_TOP_K];
+#pragma unroll
+    for (int k = 0; k < LKB_TOP_K; ++k) { wk[k] = w[t * 4 + k]; dr[k] = D + (size_t) pos[t * 4 + k] * LKB_HIDDEN; }
+    float * x = X + (size_t) t * LKB_HIDDEN;
+    int8_t * q = aqs + (size_t) t * LKB_HIDDEN;
+    float2 * sc = asc + (size_t) t * (LKB_HIDDEN / 32);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = tid + 256 * j;
+        float acc = 0.0f;
+#pragma unroll
+        for (int k = 0; k < LKB_TOP_K; ++k) acc = fmaf(wk[k], dr[k][i], acc);
+        const float xv = __fadd_rn(x[i], acc);
+        x[i] = xv;
+        const int b = warp + 8 * j;
+        const float uv = __fmul_rn(xv, nw[i]);
+        lkb_quant_store_planar(uv, q + b * 32, sc + b, lane);
+        const float sq = lkb_warp_sum(__fmul_rn(xv, xv));
+        if (lane == 0) s_sq[b] = sq;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const float sv = lkb_warp_sum(__fadd_rn(s_sq[lane], s_sq[lane + 32]));
+        if (lane == 0) inv_out[t] = rsqrtf(fmaf(sv, 1.0f / (float) LKB_HIDDEN, LKB_EPS));
+    }
+}
+
+// ---------------------------------------------------------------------------
 // CUDA-core form of the Q4_0 x Q8_1 GEMM (dense, grouped, SwiGLU epilogue).
 // CTA = 64 weight rows (EPI 1: 32 gate + the same 32 up rows) x one 64-token
 // tile; thread = rows (lane, lane+32) x 8 tokens, so a warp holds 32 consecutive
@@ -608,6 +676,34 @@ int lkb_pf_moe_combine_norm(float * X, const float * D, const float * w, const f
     if (!X || !D || !w || !nw || !a.qs || !a.sc || !inv_out) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
     k_pf_moe_combine_norm<<<m, 256, 0, (cudaStream_t) st>>>(X, D, w, nw, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out);
+    return lkb_check_launch();
+}
+
+int lkb_ep_pack_rows(lkb_pf_act a, const float * inv, const int * idx, const int * send_order, int n,
+                     int experts_per_rank, void * out, int * pos, lkb_stream_t st) {
+    LKB_REQUIRE_INIT();
+    if (!a.qs || !a.sc || !inv || !idx || !send_order || !out || !pos) return LKB_ERR_NULL;
+    if (n <= 0 || experts_per_rank <= 0) return n == 0 ? LKB_OK : LKB_ERR_SHAPE;
+    k_ep_pack<<<n, 192, 0, (cudaStream_t) st>>>(a.qs, reinterpret_cast<const float2 *>(a.sc), inv, idx, send_order,
+                                                experts_per_rank, static_cast<unsigned char *>(out), pos);
+    return lkb_check_launch();
+}
+
+int lkb_ep_unpack_rows(const void * in, int n, lkb_pf_act a, float * inv, int * local_expert, lkb_stream_t st) {
+    LKB_REQUIRE_INIT();
+    if (!in || !a.qs || !a.sc || !inv || !local_expert) return LKB_ERR_NULL;
+    if (n <= 0) return n == 0 ? LKB_OK : LKB_ERR_SHAPE;
+    k_ep_unpack<<<n, 192, 0, (cudaStream_t) st>>>(static_cast<const unsigned char *>(in), a.qs,
+                                                  reinterpret_cast<float2 *>(a.sc), inv, local_expert);
+    return lkb_check_launch();
+}
+
+int lkb_pf_moe_combine_norm_gather(float * X, const float * D, const int * pos, const float * w, const float * nw,
+                                   lkb_pf_act a, float * inv_out, int m, lkb_stream_t st) {
+    LKB_REQUIRE_INIT();
+    if (!X || !D || !pos || !w || !nw || !a.qs || !a.sc || !inv_out) return LKB_ERR_NULL;
+    if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
+    k_pf_moe_combine_norm_gather<<<m, 256, 0, (cudaStream_t) st>>>(X, D, pos, w, nw, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out);
     return lkb_check_launch();
 }
 

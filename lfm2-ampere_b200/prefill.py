@@ -135,42 +135,80 @@ class PrefillStackEP:
         self.an = api.pf_act(self.n_qs, self.n_sc)
         self.recv_slots = []                                     # per layer: slots this rank computed (load balance)
 
-    def _experts(self, li):
-        sh = self.shards[li]
+    def _alloc_ep(self, device):
+        """Buffers of the device-side dispatch (called once)."""
+        i32 = dict(dtype=torch.int32, device=device)
+        ns = self.m * TOPK
+        self.dest = torch.zeros(ns, **i32)
+        self.dcnt = torch.zeros(E, **i32)                       # slots per destination rank (first `world` entries)
+        self.doff = torch.zeros(E, **i32)
+        self.dtiles = torch.zeros(ns // 64 + E, 4, **i32)       # by-product of the plan kernel, unused
+        self.dnt = torch.zeros(1, **i32)
+        self.send_order = torch.zeros(ns, **i32)
+        self.pos = torch.zeros(ns, **i32)
+        self.counts = torch.zeros(2, self.world, **i32)         # [0] what I send to each rank, [1] what I receive
+        self.counts_host = torch.zeros(2, self.world, dtype=torch.int32).pin_memory()
+        self.send_buf = torch.zeros(ns, api.EP_ROW_BYTES, dtype=torch.uint8, device=device)
+        self.recv_buf = torch.zeros(self.cap, api.EP_ROW_BYTES, dtype=torch.uint8, device=device)
+        self.r_qs = torch.zeros(self.cap, H, dtype=torch.int8, device=device)
+        self.r_sc = torch.zeros(self.cap, H // 32, 2, dtype=torch.float32, device=device)
+        self.r_inv = torch.zeros(self.cap, dtype=torch.float32, device=device)
+        self.r_le = torch.zeros(self.cap, **i32)
+        self.r_act = api.pf_act(self.r_qs, self.r_sc)
+        self.d_back = torch.zeros(ns, H, dtype=torch.float32, device=device)
 
-        def fn(le, recv):
-            qs, sc, inv = recv
-            n = int(le.numel())
-            if n == 0:
-                return self.D[:0]
-            api.zero_i32(self.cnt, E)
-            api.k_pf_moe_count(le, n, self.cnt)
-            api.k_pf_moe_plan(self.cnt, self.off, self.tiles, self.ntiles)
-            api.k_pf_moe_scatter(le, n, self.off, self.perm)
-            mt = n // 64 + E
-            g = api.make_pf_gemm([(sh.gate_qs, sh.gate_d), (sh.up_qs, sh.up_d)], [I, I, I], I, H // 32, qs, sc,
-                                 exp_stride=I * (H // 32), perm=self.perm, tiles=self.tiles, ntiles=self.ntiles,
-                                 a_shift=0, scale=inv, oqs=self.a2_qs, osc=self.a2_sc, okb=I // 32)
-            api.pf_gemm_swiglu(g, mt)
-            dn = api.make_pf_gemm([(sh.down_qs, sh.down_d)], [H, H, H], H, I // 32, self.a2_qs, self.a2_sc,
-                                  exp_stride=H * (I // 32), perm=self.perm, tiles=self.tiles, ntiles=self.ntiles,
-                                  a_shift=0, out=self.D, out_ld=H)
-            api.pf_gemm_moe(dn, mt)
-            return self.D[:n]
-        return fn
+    def _experts(self, li, n):
+        """count / plan / scatter + the two grouped GEMMs over the n slots received for this rank's experts."""
+        sh = self.shards[li]
+        if n == 0:
+            return
+        api.zero_i32(self.cnt, E)
+        api.k_pf_moe_count(self.r_le, n, self.cnt)
+        api.k_pf_moe_plan(self.cnt, self.off, self.tiles, self.ntiles)
+        api.k_pf_moe_scatter(self.r_le, n, self.off, self.perm)
+        mt = n // 64 + E
+        g = api.make_pf_gemm([(sh.gate_qs, sh.gate_d), (sh.up_qs, sh.up_d)], [I, I, I], I, H // 32, self.r_qs, self.r_sc,
+                             exp_stride=I * (H // 32), perm=self.perm, tiles=self.tiles, ntiles=self.ntiles,
+                             a_shift=0, scale=self.r_inv, oqs=self.a2_qs, osc=self.a2_sc, okb=I // 32)
+        api.pf_gemm_swiglu(g, mt)
+        dn = api.make_pf_gemm([(sh.down_qs, sh.down_d)], [H, H, H], H, I // 32, self.a2_qs, self.a2_sc,
+                              exp_stride=H * (I // 32), perm=self.perm, tiles=self.tiles, ntiles=self.ntiles,
+                              a_shift=0, out=self.D, out_ld=H)
+        api.pf_gemm_moe(dn, mt)
 
     def layer(self, i):
-        l, m = self.layers[i], self.m
+        import torch.distributed as dist
+        l, m, G = self.layers[i], self.m, self.world
+        ns, per = m * TOPK, E // G
+        if not hasattr(self, "send_buf"):
+            self._alloc_ep(self.X.device)
         api.k_pf_norm(self.X, l.norm_w, 0, self.a, self.inv, self.h32, m)
         # the router form follows the CHUNK size, as on one GPU (ref: src/engine.cu:1170-1176)
         router = api.k_pf_router_small if self.m_total <= 256 else api.k_pf_router_tiled
         router(self.h32, m, l.router, l.rbias, self.inv, self.sel, self.sig)
         api.k_pf_select(self.sel, self.sig, m, self.idx, self.w)
-        D, plan = self._ep.ep_moe_layer(self.idx, [self.a_qs, self.a_sc, self.inv], self._experts(i), self.world,
-                                        self.group)
-        self.recv_slots.append(sum(plan.recv_counts))
+        # slots grouped by destination rank, ascending slot order inside a destination: the same stable
+        # count / plan / scatter kernels, keyed by owner rank instead of expert
+        torch.div(self.idx.view(-1), per, rounding_mode="floor", out=self.dest)
+        api.zero_i32(self.dcnt, E)
+        api.k_pf_moe_count(self.dest, ns, self.dcnt)
+        api.k_pf_moe_plan(self.dcnt, self.doff, self.dtiles, self.dnt)
+        api.k_pf_moe_scatter(self.dest, ns, self.doff, self.send_order)
+        self.counts[0].copy_(self.dcnt[:G])
+        dist.all_to_all_single(self.counts[1], self.counts[0], group=self.group)
+        api.ep_pack_rows(self.a, self.inv, self.idx, self.send_order, ns, per, self.send_buf, self.pos)
+        self.counts_host.copy_(self.counts, non_blocking=True)
+        torch.cuda.current_stream().synchronize()                 # the one host sync of the layer: split sizes
+        sc, rc = self.counts_host[0].tolist(), self.counts_host[1].tolist()
+        n = sum(rc)
+        dist.all_to_all_single(self.recv_buf[:n], self.send_buf, output_split_sizes=rc, input_split_sizes=sc,
+                               group=self.group)
+        api.ep_unpack_rows(self.recv_buf, n, self.r_act, self.r_inv, self.r_le)
+        self._experts(i, n)
+        dist.all_to_all_single(self.d_back, self.D[:n], output_split_sizes=sc, input_split_sizes=rc, group=self.group)
+        self.recv_slots.append(n)
         nxt = self.layers[(i + 1) % len(self.layers)]
-        api.k_pf_moe_combine_norm(self.X, D, self.w, nxt.norm_w, self.an, self.n_inv, m)
+        api.k_pf_moe_combine_norm_gather(self.X, self.d_back, self.pos, self.w, nxt.norm_w, self.an, self.n_inv, m)
 
     def step(self):
         self.recv_slots = []
