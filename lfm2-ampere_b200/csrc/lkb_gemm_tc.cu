@@ -14,10 +14,10 @@
 //     token: d8 / 8sum are per-thread scalars, the 32 intermediate rows of a Q8_1 output
 //     block sit in 32 registers of one thread, so the SwiGLU epilogue quantises with no
 //     shuffle at all (in the standard butterfly order: bit-identical to the unfused path);
-//   * warps 0-3 load: activations are gathered through `perm` and weights are expanded
-//     nibble -> int8 straight into the canonical K-major core-matrix layout (8 rows x
-//     16 B); warp 12 lane 0 issues the MMAs; warps 4-11 are the epilogue (two per TMEM
-//     lane quadrant, splitting the columns);
+//   * two loader warps (cp.async, two stages ahead): activations are gathered through `perm`
+//     straight into the canonical K-major core-matrix layout (8 rows x 16 B), nibbles are staged
+//     raw and expanded to int8 from shared memory; one thread of the last warp issues the MMAs;
+//     sixteen epilogue warps (four per TMEM lane quadrant, 32 columns each);
 //   * four TMEM buffers of 128 columns: MMAs run up to four blocks ahead of the epilogue;
 //   * persistent: one CTA per SM walks (row tile, 128-token tile) work items built from
 //     the device-side tile list, expert by expert, so an expert's weights stay in L2.
@@ -25,10 +25,12 @@
 // freeing TMEM.
 #include "lkb_device.cuh"
 
-#define TC_THREADS   672            // 21 warps: 4 loaders, 16 epilogue, 1 MMA issuer
-#define TC_LOADERS   128
+#define TC_LW        2              // loader warps; each loader thread serves TC_RPT tokens and TC_RPT weight rows
+#define TC_RPT       (128 / (32 * TC_LW))
+#define TC_THREADS   ((TC_LW + 16 + 1) * 32)   // loaders, 16 epilogue warps, 1 MMA-issuing warp
+#define TC_LOADERS   (32 * TC_LW)
 #define TC_EPI_WARPS 16
-#define TC_MMA_WARP  20
+#define TC_MMA_WARP  (TC_LW + 16)
 #define TC_KB        4              // blocks per pipeline stage
 #define TC_STAGES    3
 #define TC_TBUF      4              // TMEM buffers (128 columns each)
@@ -256,38 +258,45 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
     // traffic is cp.async (16 B), issued TC_AHEAD stages ahead: activations and their scales land
     // directly in the canonical operand layout, nibbles land in a raw staging row and are expanded
     // to int8 from shared memory when their stage comes up.
-    if (warp < 4) {
-        struct Cur { int item, ks, ar; const int8_t * aq; const float2 * as; const uint4 * wq; const __half * wd; };
+    if (warp < TC_LW) {
+        struct Cur { int item, ks; int ar[TC_RPT]; const int8_t * aq[TC_RPT]; const float2 * as[TC_RPT];
+                     const uint4 * wq[TC_RPT]; const __half * wd[TC_RPT]; };
         auto setup = [&](Cur & c) {
             if (c.item >= n_items) return;
             const int mt = c.item / n_rt, rt = c.item % n_rt;
             const int expert = S.mt_expert[mt], tstart = S.mt_start[mt], tcnt = S.mt_count[mt];
-            int slot = -1;
-            if (tid < tcnt) slot = g.perm ? g.perm[tstart + tid] : tstart + tid;
-            c.ar = (slot >= 0) ? (slot >> g.a_shift) : -1;
             const size_t eo = (size_t) expert * g.exp_stride;
-            if (EPI) {
-                const int r = rt * 64 + (tid & 63);
-                const int sg = tid >> 6;                            // 0: gate, 1: up
-                c.wq = (const uint4 *) g.qs[sg] + eo + (size_t) r * g.bpr;
-                c.wd = (const __half *) g.d[sg] + eo + (size_t) r * g.bpr;
-            } else {
-                const int r = rt * TC_N + tid;
-                const int seg = (r < g.seg_end[0]) ? 0 : (r < g.seg_end[1]) ? 1 : 2;
-                const int sbase = seg ? g.seg_end[seg - 1] : 0;
-                c.wq = (const uint4 *) g.qs[seg] + eo + (size_t) (r - sbase) * g.bpr;
-                c.wd = (const __half *) g.d[seg] + eo + (size_t) (r - sbase) * g.bpr;
+#pragma unroll
+            for (int q = 0; q < TC_RPT; ++q) {
+                const int rr = tid + q * TC_LOADERS;                // token of the M tile == weight row of the N tile
+                int slot = -1;
+                if (rr < tcnt) slot = g.perm ? g.perm[tstart + rr] : tstart + rr;
+                c.ar[q] = (slot >= 0) ? (slot >> g.a_shift) : -1;
+                if (EPI) {
+                    const int r = rt * 64 + (rr & 63);
+                    const int sg = rr >> 6;                         // 0: gate, 1: up
+                    c.wq[q] = (const uint4 *) g.qs[sg] + eo + (size_t) r * g.bpr;
+                    c.wd[q] = (const __half *) g.d[sg] + eo + (size_t) r * g.bpr;
+                } else {
+                    const int r = rt * TC_N + rr;
+                    const int seg = (r < g.seg_end[0]) ? 0 : (r < g.seg_end[1]) ? 1 : 2;
+                    const int sbase = seg ? g.seg_end[seg - 1] : 0;
+                    c.wq[q] = (const uint4 *) g.qs[seg] + eo + (size_t) (r - sbase) * g.bpr;
+                    c.wd[q] = (const __half *) g.d[seg] + eo + (size_t) (r - sbase) * g.bpr;
+                }
+                c.aq[q] = g.aqs + (size_t) (c.ar[q] < 0 ? 0 : c.ar[q]) * g.bpr * 32;
+                c.as[q] = reinterpret_cast<const float2 *>(g.asc) + (size_t) (c.ar[q] < 0 ? 0 : c.ar[q]) * g.bpr;
             }
-            c.aq = g.aqs + (size_t) (c.ar < 0 ? 0 : c.ar) * g.bpr * 32;
-            c.as = reinterpret_cast<const float2 *>(g.asc) + (size_t) (c.ar < 0 ? 0 : c.ar) * g.bpr;
         };
         auto advance = [&](Cur & c) { if (++c.ks == nstage_per_item) { c.ks = 0; c.item += gridDim.x; setup(c); } };
         int my_items = 0;
         if ((int) blockIdx.x < n_items) my_items = (n_items - 1 - (int) blockIdx.x) / (int) gridDim.x + 1;
         const unsigned total = (unsigned) my_items * (unsigned) nstage_per_item;
-        Cur ci, cc;
-        ci.item = cc.item = blockIdx.x; ci.ks = cc.ks = 0; ci.ar = cc.ar = -1;
-        setup(ci); cc = ci;
+        Cur ci;
+        ci.item = blockIdx.x; ci.ks = 0;
+#pragma unroll
+        for (int q = 0; q < TC_RPT; ++q) ci.ar[q] = -1;
+        setup(ci);
         unsigned it_issue = 0;
         bool ok = true;
         long long pw_empty = 0, pw_cp = 0; const long long pt0 = clock64();
@@ -299,16 +308,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
                 else {
                     TcStage & T = S.st[stg];
                     const int kb0 = ci.ks * TC_KB;
-                    const bool live = ci.ar >= 0;
 #pragma unroll
-                    for (int j = 0; j < TC_KB; ++j) {
-                        tc_cp16(T.A[j] + tc_canon(tid, 0), ci.aq + (size_t) (kb0 + j) * 32, live);
-                        tc_cp16(T.A[j] + tc_canon(tid, 1), ci.aq + (size_t) (kb0 + j) * 32 + 16, live);
-                        tc_cp16(T.rawq[tid] + j * 16, ci.wq + kb0 + j, true);
+                    for (int q = 0; q < TC_RPT; ++q) {
+                        const int rr = tid + q * TC_LOADERS;
+                        const bool live = ci.ar[q] >= 0;
+#pragma unroll
+                        for (int j = 0; j < TC_KB; ++j) {
+                            tc_cp16(T.A[j] + tc_canon(rr, 0), ci.aq[q] + (size_t) (kb0 + j) * 32, live);
+                            tc_cp16(T.A[j] + tc_canon(rr, 1), ci.aq[q] + (size_t) (kb0 + j) * 32 + 16, live);
+                            tc_cp16(T.rawq[rr] + j * 16, ci.wq[q] + kb0 + j, true);
+                        }
+                        tc_cp16(&T.sc[rr][0], ci.as[q] + kb0, live);
+                        tc_cp16(&T.sc[rr][2], ci.as[q] + kb0 + 2, live);
+                        tc_cp8(T.rawd[rr], ci.wd[q] + kb0);
                     }
-                    tc_cp16(&T.sc[tid][0], ci.as + kb0, live);
-                    tc_cp16(&T.sc[tid][2], ci.as + kb0 + 2, live);
-                    tc_cp8(T.rawd[tid], ci.wd + kb0);
                     advance(ci);
                 }
             }
@@ -322,17 +335,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
             { const long long t0_ = TC_CLK(); tc_cp_wait<TC_AHEAD - 1>(); pw_cp += TC_CLK() - t0_; }
             TcStage & T = S.st[it % TC_STAGES];
 #pragma unroll
-            for (int j = 0; j < TC_KB; ++j) {
-                const uint4 wv = *reinterpret_cast<const uint4 *>(T.rawq[tid] + j * 16);
-                // byte i of the 16: element i (low nibble) | element i+16 (high nibble)
-                uint4 lo, hi;
-                lo.x = wv.x & 0x0F0F0F0Fu; hi.x = (wv.x >> 4) & 0x0F0F0F0Fu;
-                lo.y = wv.y & 0x0F0F0F0Fu; hi.y = (wv.y >> 4) & 0x0F0F0F0Fu;
-                lo.z = wv.z & 0x0F0F0F0Fu; hi.z = (wv.z >> 4) & 0x0F0F0F0Fu;
-                lo.w = wv.w & 0x0F0F0F0Fu; hi.w = (wv.w >> 4) & 0x0F0F0F0Fu;
-                *reinterpret_cast<uint4 *>(T.B[j] + tc_canon(tid, 0)) = lo;
-                *reinterpret_cast<uint4 *>(T.B[j] + tc_canon(tid, 1)) = hi;
-                T.d4[j][tid] = __half2float(T.rawd[tid][j]);
+            for (int q = 0; q < TC_RPT; ++q) {
+                const int rr = tid + q * TC_LOADERS;
+#pragma unroll
+                for (int j = 0; j < TC_KB; ++j) {
+                    const uint4 wv = *reinterpret_cast<const uint4 *>(T.rawq[rr] + j * 16);
+                    // byte i of the 16: element i (low nibble) | element i+16 (high nibble)
+                    uint4 lo, hi;
+                    lo.x = wv.x & 0x0F0F0F0Fu; hi.x = (wv.x >> 4) & 0x0F0F0F0Fu;
+                    lo.y = wv.y & 0x0F0F0F0Fu; hi.y = (wv.y >> 4) & 0x0F0F0F0Fu;
+                    lo.z = wv.z & 0x0F0F0F0Fu; hi.z = (wv.z >> 4) & 0x0F0F0F0Fu;
+                    lo.w = wv.w & 0x0F0F0F0Fu; hi.w = (wv.w >> 4) & 0x0F0F0F0Fu;
+                    *reinterpret_cast<uint4 *>(T.B[j] + tc_canon(rr, 0)) = lo;
+                    *reinterpret_cast<uint4 *>(T.B[j] + tc_canon(rr, 1)) = hi;
+                    T.d4[j][rr] = __half2float(T.rawd[rr][j]);
+                }
             }
             tc_fence_async();                                       // generic-proxy writes -> visible to the MMA
             __syncwarp();
@@ -373,7 +390,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
     // Four warps per TMEM lane quadrant, each folding 32 of the 128 columns: 32 accumulators
     // per thread, four warps per scheduler to hide the TMEM read latency.
     else {
-        const int ew = warp - 4;                    // 0..15
+        const int ew = warp - TC_LW;                // 0..15
         const int quad = warp & 3;                  // TMEM lane quadrant this warp may access
         const int sub = ew >> 2;                    // which 32 columns
         const int tok = quad * 32 + lane;           // token (TMEM lane) of this thread
@@ -409,27 +426,30 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
                         const float d8 = sc.x, nc = -sc.y;
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
+                            // 16 columns at a time keeps the live registers under the 96-register budget (no spills)
                             int sv[16];
-                            { const long long t0_ = TC_CLK();
                             tc_ld16(tmem + tlane + tb * TC_N + (h ? c1 : c0), sv);
-                            tc_wait_ld(); pw_ld += TC_CLK() - t0_; }
+                            // the weight scales of these 16 columns come from shared memory while the TMEM read is in flight
+                            const float * dp = &T.d4[j][h ? c1 : c0];
+                            float4 dd[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) dd[i] = *reinterpret_cast<const float4 *>(dp + 4 * i);
+                            { const long long t0_ = TC_CLK(); tc_wait_ld(); pw_ld += TC_CLK() - t0_; }
                             if (h == 1) {
                                 tc_fence_before();
                                 __syncwarp();
                                 if (lane == 0) tc_mbar_arrive(&S.tempty[tb]);      // TMEM buffer is free again
                             }
-                            const float * dp = &T.d4[j][h ? c1 : c0];
 #ifdef TC_ABLATE_MATH
                             acc[h] += __int_as_float(sv[0] ^ sv[15]);
 #else
 #pragma unroll
                             for (int i = 0; i < 16; i += 4) {
-                                const float4 dd = *reinterpret_cast<const float4 *>(dp + i);
                                 const int o = h * 16 + i;
-                                acc[o + 0] = fmaf(dd.x, fmaf(d8, tc_i2f(sv[i + 0]), nc), acc[o + 0]);
-                                acc[o + 1] = fmaf(dd.y, fmaf(d8, tc_i2f(sv[i + 1]), nc), acc[o + 1]);
-                                acc[o + 2] = fmaf(dd.z, fmaf(d8, tc_i2f(sv[i + 2]), nc), acc[o + 2]);
-                                acc[o + 3] = fmaf(dd.w, fmaf(d8, tc_i2f(sv[i + 3]), nc), acc[o + 3]);
+                                acc[o + 0] = fmaf(dd[i / 4].x, fmaf(d8, tc_i2f(sv[i + 0]), nc), acc[o + 0]);
+                                acc[o + 1] = fmaf(dd[i / 4].y, fmaf(d8, tc_i2f(sv[i + 1]), nc), acc[o + 1]);
+                                acc[o + 2] = fmaf(dd[i / 4].z, fmaf(d8, tc_i2f(sv[i + 2]), nc), acc[o + 2]);
+                                acc[o + 3] = fmaf(dd[i / 4].w, fmaf(d8, tc_i2f(sv[i + 3]), nc), acc[o + 3]);
                             }
 #endif
                         }
@@ -514,7 +534,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
             }
             pw_tail += TC_CLK() - tt0_;
         }
-        if (blockIdx.x == 0 && tid == 128) { g_tc_prof[8] = pw_full; g_tc_prof[9] = pw_tf; g_tc_prof[10] = clock64() - pt0; g_tc_prof[11] = pw_ld; g_tc_prof[12] = pw_tail; }
+        if (blockIdx.x == 0 && tid == TC_LOADERS) { g_tc_prof[8] = pw_full; g_tc_prof[9] = pw_tf; g_tc_prof[10] = clock64() - pt0; g_tc_prof[11] = pw_ld; g_tc_prof[12] = pw_tail; }
     }
 
     // ---- teardown: everyone meets, then the allocating warp frees TMEM ------------
