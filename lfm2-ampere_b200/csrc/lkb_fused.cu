@@ -99,11 +99,12 @@ __device__ __forceinline__ void grid_arrive(unsigned * bar, FusedSmem & S) {
         S.bar_target = (ticket / gridDim.x + 1u) * gridDim.x;
     }
 }
-__device__ __forceinline__ bool grid_wait(unsigned * bar, unsigned * status, FusedSmem & S, unsigned code) {
+__device__ __forceinline__ bool grid_wait(unsigned * bar, unsigned * status, FusedSmem & S, unsigned code,
+                                          unsigned spin_limit = SPIN_LIMIT) {
     if (threadIdx.x == 0) {
         const unsigned target = S.bar_target;
         bool ok = false;
-        for (unsigned i = 0; i < SPIN_LIMIT; ++i) {
+        for (unsigned i = 0; i < spin_limit; ++i) {
             if (ld_acquire(bar) >= target) { ok = true; break; }
             if ((i & 1023u) == 1023u && ld_acquire(status) != 0u) break;
         }
@@ -190,6 +191,8 @@ __device__ __forceinline__ void load_xregs(const lkb_q8blk * xq, int bpr, int la
 
 // Optional phase timestamps (clock64 of thread 0) for tuning: [cta][layer][16].
 static unsigned long long * g_fused_timing = nullptr;
+static int g_fused_absent_cta = -1;              // test hook, see lkb_debug_fused_absent_cta
+static unsigned g_fused_spin_limit = 0;          // 0: default
 #define FUSED_STAMP(slot) do { if (a.timing && tid == 0 && l < 4) a.timing[((size_t) cta * 4 + l) * 16 + (slot)] = clock64(); } while (0)
 
 
@@ -237,6 +240,8 @@ struct FusedArgs {
     unsigned *            bar;         // scratch [2]: {barrier counter, status}
     int                   softmax;
     unsigned long long *  timing;
+    int                   absent_cta;  // test hook: this CTA leaves at once and never arrives (-1: none)
+    unsigned              spin_limit;  // iterations a grid-barrier wait may spin
 };
 
 // Blocks b = warp + 16 j (j = 0..3) of the 2048-vector belong to this warp, element `lane`.
@@ -275,6 +280,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nct = gridDim.x, cta = blockIdx.x;
     unsigned * status = a.bar + 1;
+    if ((int) blockIdx.x == a.absent_cta) return;          // host-requested: the others' bounded waits must expire
 
     // static partition of the layer's rows over the CTAs (balanced, contiguous)
     const int GU_TOTAL = 2 * LKB_TOP_K * LKB_MOE_INTER;
@@ -334,7 +340,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
         if (cta < LKB_N_EXPERTS && tid == 0) a.logits[cta] = __fmul_rn(S.sel[0], S.inv);
         FUSED_STAMP(2);
         grid_arrive(a.bar, S);
-        if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 1u)) return;
+        if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 1u, a.spin_limit)) return;
         FUSED_STAMP(3);
 
         // ---- C: selection (every CTA, warp 0; the softmax gate takes the 64-thread path) ----
@@ -441,7 +447,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
 #pragma unroll
             for (int j = 0; j < 4; ++j) nw[j] = L[l + 1].norm_w[(warp + FUSED_WARPS * j) * 32 + lane];
         }
-        if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 2u)) return;
+        if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 2u, a.spin_limit)) return;
         FUSED_STAMP(6);
 
         // ---- F: SwiGLU + Q8_1 (every CTA), down rows, residual ---------------------
@@ -516,7 +522,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
         grid_arrive(a.bar, S);
         if (l + 1 < a.n_layers && tid < (int) (sizeof(lkb_moe_layer) / 8))
             reinterpret_cast<unsigned long long *>(&S.ly)[tid] = reinterpret_cast<const unsigned long long *>(&L[l + 1])[tid];
-        if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 3u)) return;
+        if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 3u, a.spin_limit)) return;
     }
 
     // optional: the quantised, un-normalised activation of the final x for the caller's next consumer
@@ -556,6 +562,8 @@ static int fused_launch(FusedArgs & a, cudaStream_t st) {
     cudaError_t e = cudaMemsetAsync(a.bar, 0, 2 * sizeof(unsigned), st);
     if (e != cudaSuccess) return -(int) e;
     a.timing = g_fused_timing;
+    a.absent_cta = g_fused_absent_cta;
+    a.spin_limit = g_fused_spin_limit ? g_fused_spin_limit : SPIN_LIMIT;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid); cfg.blockDim = dim3(FUSED_THREADS); cfg.dynamicSmemBytes = sizeof(FusedSmem); cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -571,6 +579,13 @@ extern "C" {
 
 // Tuning hook (not part of the public header): device buffer of [#CTAs][4 layers][16] clock64 stamps, or null.
 __attribute__((visibility("default"))) int lkb_debug_fused_timing(unsigned long long * buf) { g_fused_timing = buf; return LKB_OK; }
+
+// Test hook (not in the public header): the next launches run WITHOUT CTA `cta` (it returns at once), so every
+// other CTA's first grid-barrier wait runs out after `spin_limit` polls and the kernel ends with a status code
+// instead of hanging.  cta = -1 restores normal operation.  Nothing faults, traps or spins without a bound.
+__attribute__((visibility("default"))) int lkb_debug_fused_absent_cta(int cta, unsigned spin_limit) {
+    g_fused_absent_cta = cta; g_fused_spin_limit = spin_limit; return LKB_OK;
+}
 
 int lkb_moe_ffn_decode(const lkb_moe_layer * layer, float * x, int * idx_out, float * w_out,
                        const lkb_norm_prod_t * next, const lkb_moe_scratch * scratch, lkb_stream_t st) {

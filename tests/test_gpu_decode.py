@@ -376,3 +376,33 @@ def test_fused_stack_is_bit_identical_to_kernel_sequence(L):
     h2, y2, s2 = nan_f32(2048), empty_blocks(64), nan_f32(64)
     L.norm_produce(st.x, 2048, L.norm_prod(nw, h2, y2, s2))
     assert torch.equal(h32, h2) and torch.equal(yq8, y2) and torch.equal(ssq, s2)
+
+
+def test_bounded_wait_reports_status_and_context_survives(L):
+    """A CTA that never arrives (requested from the host) makes the other CTAs' bounded grid-barrier wait run out:
+    the kernel ends with a status code, nothing hangs or faults, and the next launch is correct again."""
+    import ctypes
+    import importlib
+    synth = importlib.import_module("lfm2-ampere_b200.synth")
+    decode = importlib.import_module("lfm2-ampere_b200.decode")
+    layers = synth.make_model(2, seed=55)
+    st = decode.DecodeStack(layers)
+    x0 = torch.randn(2048, device="cuda", generator=torch.Generator("cuda").manual_seed(3))
+    st.x.copy_(x0)
+    st.step_fused()
+    torch.cuda.synchronize()
+    good = st.x.clone()
+    assert st.status() == 0
+    L.lib.lkb_debug_fused_absent_cta.argtypes = [ctypes.c_int, ctypes.c_uint]
+    L.lib.lkb_debug_fused_absent_cta(5, 1 << 14)             # CTA 5 stays away; waits give up after 16384 polls
+    try:
+        st.x.copy_(x0)
+        st.step_fused()
+        torch.cuda.synchronize()                              # returns: the wait is bounded
+        assert st.status() == 1001                            # grid barrier 1 of layer 0 expired
+    finally:
+        L.lib.lkb_debug_fused_absent_cta(-1, 0)
+    st.x.copy_(x0)
+    st.step_fused()
+    torch.cuda.synchronize()
+    assert st.status() == 0 and torch.equal(st.x, good)
