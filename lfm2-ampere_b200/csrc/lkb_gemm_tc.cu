@@ -299,7 +299,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
         setup(ci);
         unsigned it_issue = 0;
         bool ok = true;
-        long long pw_empty = 0, pw_cp = 0; const long long pt0 = clock64();
+        long long pw_empty = 0, pw_cp = 0, pw_fence = 0, pw_unpack = 0; const long long pt0 = clock64();
         auto issue = [&]() {
             // stage it_issue: wait for its buffer, then fire the copies
             if (ok && it_issue < total) {
@@ -334,6 +334,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
             // blocking on the buffer of stage it+TC_AHEAD, so the copies really run ahead of the consumers
             { const long long t0_ = TC_CLK(); tc_cp_wait<TC_AHEAD - 1>(); pw_cp += TC_CLK() - t0_; }
             TcStage & T = S.st[it % TC_STAGES];
+            const long long tu0_ = TC_CLK();
 #pragma unroll
             for (int q = 0; q < TC_RPT; ++q) {
                 const int rr = tid + q * TC_LOADERS;
@@ -351,13 +352,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
                     T.d4[j][rr] = __half2float(T.rawd[rr][j]);
                 }
             }
+            const long long tf0_ = TC_CLK(); pw_unpack += tf0_ - tu0_;
             tc_fence_async();                                       // generic-proxy writes -> visible to the MMA
+            pw_fence += TC_CLK() - tf0_;
             __syncwarp();
             if (lane == 0) tc_mbar_arrive(&S.full[it % TC_STAGES]);
             issue();
         }
         tc_cp_wait<0>();
-        if (blockIdx.x == 0 && tid == 0) { g_tc_prof[0] = pw_empty; g_tc_prof[1] = pw_cp; g_tc_prof[2] = clock64() - pt0; }
+        if (blockIdx.x == 0 && tid == 0) { g_tc_prof[0] = pw_empty; g_tc_prof[1] = pw_cp; g_tc_prof[2] = clock64() - pt0; g_tc_prof[13] = pw_fence; g_tc_prof[14] = pw_unpack; }
     }
     // ============================ MMA issuer (last warp) =========================
     else if (warp == TC_MMA_WARP) {
