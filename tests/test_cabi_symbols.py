@@ -54,3 +54,26 @@ def test_compute_calls_fail_loudly_without_init(lkb):
     assert lkb.lib.lkb_router_dot(p, p, p, None, None, None, None, 0.0, None) == -10004
     assert lkb.lib.lkb_pf_moe_plan(p, p, p, p, None) == -10004
     assert b"lkb_init" in lkb.lib.lkb_error_string(-10004)
+
+
+def test_cpp_shim_compiles_and_links(lkb, tmp_path):
+    """An engine-style C++ caller written against include/lkb_shim.hpp (the reference's kernel names)
+    compiles and links against liblkb.so (no device needed for that)."""
+    import subprocess
+    src = tmp_path / "caller.cpp"
+    src.write_text('''#include "lkb_shim.hpp"
+int moe_layer(lk::stream_t st, const float * h, const float * router, const float * rbias, float * logits, int * idx, float * w,
+              const void * gq, const void * gd, const void * uq, const void * ud, const void * dq, const void * dd,
+              lk::block_q8_1 * xq, lk::block_q8_1 * xq2, float * gu, float * x, const float * ssq, lk::LKNormProd np) {
+    lk::k_router_dot(st, h, router, logits, rbias, nullptr, nullptr, ssq, LKB_EPS);
+    lk::k_router_top4(st, logits, rbias, idx, w);
+    lk::k_gemv_q4_0_exp2(st, gq, gd, uq, ud, xq, 1536, 64, 1536, 0, idx, nullptr, nullptr, nullptr, nullptr, gu, gu + 6144, ssq, LKB_EPS);
+    lk::k_swiglu(st, gu, gu + 6144, 6144, nullptr, xq2, dq, idx, 2048, 48, 2 << 20);
+    return lk::k_moe_down_accum(st, dq, dd, xq2, 2048, 48, 2048, 48, idx, w, x, np);
+}
+int main() { return lkb_sm_count() < 0; }
+''')
+    exe = tmp_path / "caller"
+    subprocess.run(["g++", "-std=c++17", "-I", str(lkb.ROOT / "include"), str(src), "-o", str(exe),
+                    str(lkb.LIB_PATH), f"-Wl,-rpath,{lkb.LIB_PATH.parent}"], check=True)
+    assert subprocess.run([str(exe)]).returncode == 0
