@@ -292,6 +292,31 @@ int lkb_ep_unpack_rows(const void * in, int n, lkb_pf_act a, float * inv, int * 
 int lkb_pf_moe_combine_norm_gather(float * X, const float * D, const int * pos, const float * w, const float * nw,
                                    lkb_pf_act a, float * inv_out, int m, lkb_stream_t st);
 
+/* ---- output projection (Q6_K), argmax, embedding row ----------------------------------------------
+ * Q6_K planes as the reference lays them out: per 256-element super-block ql[128] (low nibbles), qh[64]
+ * (2 high bits), sc[16] (int8 sub-block scales) and one fp16 d.  ref: src/quant.cuh:171-250
+ *
+ * lkb_gemv_q6_K: y[r] = ninv * sum over row r of Q6_K weight x Q8_1 activation, in the shipped integer form
+ * (lane L owns elements 8L..8L+7 of every super-block; one fp32 term per lane and super-block; xor butterfly).
+ * ssq != NULL folds the producer's 1/rms (lkb_norm_produce) into the result; NULL means ninv = 1.
+ * sbpr = super-blocks per row (K / 256).  sbpr == 8 with 16-byte aligned planes takes the streaming kernel,
+ * anything else a plain warp-per-row kernel with the same arithmetic.
+ * ref: src/kernels.cu:426-478 (k_gemv_q6_K_dp4a), src/kernels.cu:359 (k_gemv_q6_K, same arguments) */
+int lkb_gemv_q6_K(const void * ql, const void * qh, const void * sc, const void * d, const lkb_block_q8_1 * xq,
+                  int out_rows, int sbpr, float * y, const float * ssq, float eps, lkb_stream_t st);
+/* Bounded-wait status of the streaming kernel: 0, or the code of the wait that gave up (then cleared).
+ * No counterpart in the reference. */
+int lkb_gemv_q6_K_status(void);
+/* Two-stage argmax, lowest index among equal maxima.  Stage 1 writes ceil(n / 1024) partial (value, index)
+ * pairs; stage 2 reduces n partials, stores the token id and, when d_pos is non-null, adds 1 to it (the
+ * reference advances its device-side position in the same kernel).  ref: src/kernels.cu:954-995 */
+int lkb_argmax_part(const float * v, int n, float * pv, int * pi, lkb_stream_t st);
+int lkb_argmax_final(const float * pv, const int * pi, int n, int * d_token, int * d_pos, lkb_stream_t st);
+/* x[0..n) = dequantised row *d_token of a Q6_K matrix with n columns (n % 256 == 0).
+ * ref: src/kernels.cu:855-868 (k_embed_q6_K), src/quant.cuh:171-190 */
+int lkb_embed_q6_K(const void * ql, const void * qh, const void * sc, const void * d, const int * d_token, int n,
+                   float * x, lkb_stream_t st);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

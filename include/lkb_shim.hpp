@@ -93,6 +93,19 @@ inline int k_pf_moe_combine_norm(stream_t st, int m, float * X, const float * D,
     return check(lkb_pf_moe_combine_norm(X, D, w, nw, a, inv_out, m, st), "k_pf_moe_combine_norm"); }
 inline int k_pf_pack_q8_1(stream_t st, PfAct a, int t, block_q8_1 * y) { return check(lkb_pf_pack_q8_1(a, t, y, st), "k_pf_pack_q8_1"); }
 
+// ---- output projection, argmax, embedding row (ref: src/kernels.cu:359, 426, 855, 954-995) ----------------
+inline int k_gemv_q6_K(stream_t st, const uint8_t * ql, const uint8_t * qh, const int8_t * sc, const void * d, const block_q8_1 * xq,
+                       int out_rows, int sbpr, float * y, const float * ssq, float eps) {
+    return check(lkb_gemv_q6_K(ql, qh, sc, d, xq, out_rows, sbpr, y, ssq, eps, st), "k_gemv_q6_K"); }
+inline int k_gemv_q6_K_dp4a(stream_t st, const uint8_t * ql, const uint8_t * qh, const int8_t * sc, const void * d, const block_q8_1 * xq,
+                            int out_rows, int sbpr, float * y, const float * ssq, float eps) {
+    return check(lkb_gemv_q6_K(ql, qh, sc, d, xq, out_rows, sbpr, y, ssq, eps, st), "k_gemv_q6_K_dp4a"); }
+inline int k_argmax_part(stream_t st, const float * v, int n, float * pv, int * pi) { return check(lkb_argmax_part(v, n, pv, pi, st), "k_argmax_part"); }
+inline int k_argmax_final(stream_t st, const float * pv, const int * pi, int n, int * d_token, int * d_pos) {
+    return check(lkb_argmax_final(pv, pi, n, d_token, d_pos, st), "k_argmax_final"); }
+inline int k_embed_q6_K(stream_t st, const uint8_t * ql, const uint8_t * qh, const int8_t * sc, const void * d, const int * d_token, int n, float * x) {
+    return check(lkb_embed_q6_K(ql, qh, sc, d, d_token, n, x, st), "k_embed_q6_K"); }
+
 // ---- host launchers, same signatures as the reference's (ref: src/prefill.cuh:69-71) ---------------------
 inline void pf_gemm_dense(const PfGemm & g, stream_t st) { check(lkb_pf_gemm_dense(&g, st), "pf_gemm_dense"); }
 inline void pf_gemm_moe(const PfGemm & g, int max_tiles, stream_t st) { check(lkb_pf_gemm_moe(&g, max_tiles, st), "pf_gemm_moe"); }

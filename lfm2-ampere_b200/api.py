@@ -21,6 +21,7 @@ __all__ = [
     "pf_gemm_dense", "pf_gemm_moe", "pf_gemm_swiglu", "k_pf_moe_combine", "k_pf_moe_combine_norm",
     "k_pf_pack_q8_1", "zero_i32", "moe_layer_desc", "moe_scratch", "moe_ffn_decode", "moe_ffn_decode_stack",
     "layer_descs_to_device", "ep_pack_rows", "ep_unpack_rows", "k_pf_moe_combine_norm_gather", "moe_ffn_decode_stack_static", "set_pdl", "pf_gemm_config", "sm_count",
+    "k_gemv_q6_K", "k_argmax_part", "k_argmax_final", "k_embed_q6_K", "gemv_q6_K_status",
 ]
 
 
@@ -274,3 +275,25 @@ def ep_unpack_rows(buf, n, a, inv, local_expert):
 def k_pf_moe_combine_norm_gather(X, D, pos, w, nw, a, inv_out, m):
     check(lib.lkb_pf_moe_combine_norm_gather(ptr(X), ptr(D), ptr(pos), ptr(w), ptr(nw), a, ptr(inv_out), m, stream()),
           "k_pf_moe_combine_norm_gather")
+
+
+# ------------------------------------------------ output projection / embedding --
+def k_gemv_q6_K(ql, qh, sc, d, xq, out_rows, sbpr, y, ssq=None, eps=1e-5):
+    check(lib.lkb_gemv_q6_K(ptr(ql), ptr(qh), ptr(sc), ptr(d), ptr(xq), out_rows, sbpr, ptr(y), ptr(ssq), eps, stream()),
+          "k_gemv_q6_K")
+
+
+def gemv_q6_K_status():
+    return lib.lkb_gemv_q6_K_status()
+
+
+def k_argmax_part(v, n, pv, pi):
+    check(lib.lkb_argmax_part(ptr(v), n, ptr(pv), ptr(pi), stream()), "k_argmax_part")
+
+
+def k_argmax_final(pv, pi, n, d_token, d_pos=None):
+    check(lib.lkb_argmax_final(ptr(pv), ptr(pi), n, ptr(d_token), ptr(d_pos), stream()), "k_argmax_final")
+
+
+def k_embed_q6_K(ql, qh, sc, d, d_token, n, x):
+    check(lib.lkb_embed_q6_K(ptr(ql), ptr(qh), ptr(sc), ptr(d), ptr(d_token), n, ptr(x), stream()), "k_embed_q6_K")

@@ -626,6 +626,8 @@ int lkb_init(int device) {
     if (r != LKB_OK) return r;
     r = lkb_fused_init();
     if (r != LKB_OK) return r;
+    r = lkb_lmhead_init();
+    if (r != LKB_OK) return r;
     c.inited = 1;
     return LKB_OK;
 }

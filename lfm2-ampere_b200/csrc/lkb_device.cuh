@@ -161,3 +161,4 @@ lkb_ctx & lkb_context();
 int lkb_check_launch();        // cudaGetLastError -> status
 int lkb_prefill_init();        // per-device attributes of the prefill kernels
 int lkb_fused_init();          // ... of the fused decode kernel
+int lkb_lmhead_init();         // ... of the Q6_K streaming GEMV

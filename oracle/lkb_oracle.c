@@ -665,3 +665,87 @@ ORC_API int orc_num_threads(void) {
 #endif
     return n;
 }
+
+/* ========================================================================= */
+/* Q6_K lm_head (the row the path feeds next): src/quant.cuh:171-250,          */
+/* src/kernels.cu:426-478 (k_gemv_q6_K_dp4a), 855-868 (k_embed_q6_K).          */
+/* Planar super-block of 256 weights: ql[128], qh[64], int8 scales[16], fp16 d. */
+/* ========================================================================= */
+
+/* 6-bit value of element idx: src/quant.cuh:171-195 (== tools/gguf.py:179-204). */
+static inline int q6_at(const uint8_t * QL, const uint8_t * QH, int idx) {
+    const int n = (idx >= 128) ? 128 : 0, r = idx - n;
+    const int ql = QL[(n >> 1) + (r & 63)], qh = QH[(n >> 2) + (r & 31)];
+    const int lo = (r >= 64) ? (ql >> 4) : (ql & 15);
+    return lo | (((qh >> (2 * (r >> 5))) & 3) << 4);
+}
+ORC_API int orc_q6_at(const uint8_t * QL, const uint8_t * QH, int idx) { return q6_at(QL, QH, idx); }
+
+/* Integer group sums a[row][sb][lane] = sum_{t<8} (q6(8*lane+t) - 32) * xq[sb*256 + 8*lane + t] (exact). */
+ORC_API void orc_q6_group_sums(const uint8_t * ql, const uint8_t * qh, const int8_t * aq, int rows, int sbpr, int32_t * out) {
+#pragma omp parallel for if (rows > 64)
+    for (int r = 0; r < rows; ++r)
+        for (int sb = 0; sb < sbpr; ++sb) {
+            const size_t blk = (size_t) r * sbpr + sb;
+            for (int L = 0; L < 32; ++L) {
+                int32_t a = 0;
+                for (int t = 0; t < 8; ++t) a += (q6_at(ql + blk * 128, qh + blk * 64, 8 * L + t) - 32) * (int32_t) aq[sb * 256 + 8 * L + t];
+                out[(blk * 32) + L] = a;
+            }
+        }
+}
+
+/* lm_head GEMV in the shipped (dp4a) order: lane L owns elements 8L..8L+7 of every super-block;
+ * acc = fma(d, d8 * float(a * scale), acc) over super-blocks ascending; butterfly; * ninv.
+ * src/kernels.cu:426-478. */
+ORC_API void orc_gemv_q6_K(const uint8_t * ql, const uint8_t * qh, const int8_t * sc, const uint16_t * d,
+                           const int8_t * aq, const uint16_t * ad16, int rows, int sbpr, float ninv, float * y) {
+#pragma omp parallel for if (rows > 64)
+    for (int r = 0; r < rows; ++r) {
+        float lane[32];
+        for (int L = 0; L < 32; ++L) {
+            float acc = 0.0f;
+            for (int sb = 0; sb < sbpr; ++sb) {
+                const size_t blk = (size_t) r * sbpr + sb;
+                int32_t a = 0;
+                for (int t = 0; t < 8; ++t) a += (q6_at(ql + blk * 128, qh + blk * 64, 8 * L + t) - 32) * (int32_t) aq[sb * 256 + 8 * L + t];
+                const float d8 = orc_f16_to_f32(ad16[sb * 8 + (L >> 2)]);
+                const float t2 = d8 * (float) (a * (int32_t) sc[blk * 16 + (L >> 1)]);
+                acc = fmaf(orc_f16_to_f32(d[blk]), t2, acc);
+            }
+            lane[L] = acc;
+        }
+        y[r] = butterfly32(lane) * ninv;
+    }
+}
+
+/* float64 statement + sum|terms| per row (terms at 16-element scale-group granularity). */
+ORC_API void orc_gemv_q6_K_f64(const uint8_t * ql, const uint8_t * qh, const int8_t * sc, const uint16_t * d,
+                               const int8_t * aq, const float * ad32, int rows, int sbpr, double * y, double * mag) {
+#pragma omp parallel for if (rows > 64)
+    for (int r = 0; r < rows; ++r) {
+        double acc = 0.0, am = 0.0;
+        for (int sb = 0; sb < sbpr; ++sb) {
+            const size_t blk = (size_t) r * sbpr + sb;
+            for (int g = 0; g < 16; ++g) {
+                long a = 0;
+                for (int t = 0; t < 16; ++t) a += (long) (q6_at(ql + blk * 128, qh + blk * 64, 16 * g + t) - 32) * aq[sb * 256 + 16 * g + t];
+                const double term = (double) orc_f16_to_f32(d[blk]) * (double) ad32[sb * 8 + (g >> 1)] * (double) sc[blk * 16 + g] * (double) a;
+                acc += term; am += fabs(term);
+            }
+        }
+        y[r] = acc;
+        if (mag) mag[r] = am;
+    }
+}
+
+/* One embedding row: x[i] = (d * float(scale)) * float(q6 - 32).  src/kernels.cu:855-868. */
+ORC_API void orc_embed_q6_K(const uint8_t * ql, const uint8_t * qh, const int8_t * sc, const uint16_t * d,
+                            int token, int sbpr, float * x) {
+    for (int i = 0; i < sbpr * 256; ++i) {
+        const size_t blk = (size_t) token * sbpr + i / 256;
+        const int e = i % 256;
+        const float t = orc_f16_to_f32(d[blk]) * (float) sc[blk * 16 + e / 16];
+        x[i] = t * (float) (q6_at(ql + blk * 128, qh + blk * 64, e) - 32);
+    }
+}

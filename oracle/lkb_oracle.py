@@ -421,3 +421,45 @@ def pf_pack_q8_1(qs, sc, t):
 
 def num_threads():
     return int(_lib.orc_num_threads())
+
+
+# ------------------------------------------------------------ Q6_K lm_head --
+def gemv_q6_K(ql, qh, sc, d, act, rows, sbpr=8, ninv=1.0):
+    """act = (q, d16, s16) of the activation; shipped (dp4a) summation order."""
+    ql, qh = _c(ql, np.uint8).reshape(-1), _c(qh, np.uint8).reshape(-1)
+    sc, d = _c(sc, np.int8).reshape(-1), _c(d, np.uint16).reshape(-1)
+    q, d16 = _c(act[0], np.int8), _c(act[1], np.uint16)
+    y = np.empty(rows, np.float32)
+    _lib.orc_gemv_q6_K(_p(ql, _u8p), _p(qh, _u8p), _p(sc, _i8p), _p(d, _u16p), _p(q, _i8p), _p(d16, _u16p),
+                       rows, sbpr, C.c_float(ninv), _p(y, _f32p))
+    return y
+
+
+def gemv_q6_K_f64(ql, qh, sc, d, q, d8_f32, rows, sbpr=8):
+    ql, qh = _c(ql, np.uint8).reshape(-1), _c(qh, np.uint8).reshape(-1)
+    sc, d = _c(sc, np.int8).reshape(-1), _c(d, np.uint16).reshape(-1)
+    q, d8 = _c(q, np.int8), _c(d8_f32, np.float32)
+    y, mag = np.empty(rows, np.float64), np.empty(rows, np.float64)
+    _lib.orc_gemv_q6_K_f64(_p(ql, _u8p), _p(qh, _u8p), _p(sc, _i8p), _p(d, _u16p), _p(q, _i8p), _p(d8, _f32p),
+                           rows, sbpr, _p(y, _f64p), _p(mag, _f64p))
+    return y, mag
+
+
+def q6_group_sums(ql, qh, aq, rows, sbpr=8):
+    ql, qh, aq = _c(ql, np.uint8).reshape(-1), _c(qh, np.uint8).reshape(-1), _c(aq, np.int8)
+    out = np.empty((rows, sbpr, 32), np.int32)
+    _lib.orc_q6_group_sums(_p(ql, _u8p), _p(qh, _u8p), _p(aq, _i8p), rows, sbpr, _p(out, _i32p))
+    return out
+
+
+def embed_q6_K(ql, qh, sc, d, token, sbpr=8):
+    ql, qh = _c(ql, np.uint8).reshape(-1), _c(qh, np.uint8).reshape(-1)
+    sc, d = _c(sc, np.int8).reshape(-1), _c(d, np.uint16).reshape(-1)
+    x = np.empty(sbpr * 256, np.float32)
+    _lib.orc_embed_q6_K(_p(ql, _u8p), _p(qh, _u8p), _p(sc, _i8p), _p(d, _u16p), token, sbpr, _p(x, _f32p))
+    return x
+
+
+def dequant_q6_K(ql, qh, sc, d, nblk):
+    """All weights of nblk super-blocks as float32 (via the embed formula)."""
+    return embed_q6_K(ql, qh, sc, d, 0, sbpr=nblk)

@@ -55,6 +55,7 @@ def quant_cases(ref):
     ns = _functions(ref / "tests" / "make_quant_fixture.py", ["q8_1_quantize"], {"np": np})
     out = {}
     k = 0
+    k6 = 0
     for _ in range(ncase):
         kind, nblk, nplanes, _pad = struct.unpack_from("<IIIf", raw, pos)
         pos += 16
@@ -70,7 +71,18 @@ def quant_cases(ref):
         pos += 4 * nx
         exact, fp32 = struct.unpack_from("<ff", raw, pos)
         pos += 8
-        if kind != 0:            # Q6_K cases belong to the lm_head, outside this path
+        if kind != 0:            # Q6_K cases (token_embd / lm_head rows): stored under their own keys
+            qi, d8, rawsum = ns["q8_1_quantize"](x, nblk * 8)
+            out[f"k{k6}_ql"] = np.frombuffer(planes[0], np.uint8).copy()
+            out[f"k{k6}_qh"] = np.frombuffer(planes[1], np.uint8).copy()
+            out[f"k{k6}_sc"] = np.frombuffer(planes[2], np.int8).copy()
+            out[f"k{k6}_d"] = np.frombuffer(planes[3], np.uint16).copy()
+            out[f"k{k6}_x"] = x
+            out[f"k{k6}_expected_exact"] = np.float32(exact)
+            out[f"k{k6}_expected_fp32"] = np.float32(fp32)
+            out[f"k{k6}_ref_q"] = qi.astype(np.int8)
+            out[f"k{k6}_ref_d8"] = d8.astype(np.float32)
+            k6 += 1
             continue
         qs = np.frombuffer(planes[0], np.uint8).reshape(nblk, 16).copy()
         d = np.frombuffer(planes[1], np.uint16).copy()
@@ -88,6 +100,7 @@ def quant_cases(ref):
         out[f"c{k}_ref_sumi"] = sumi
         k += 1
     out["ncases"] = np.int32(k)
+    out["ncases_q6k"] = np.int32(k6)
     np.savez_compressed(OUT / "quant_q4_cases.npz", **out)
     print("quant_q4_cases.npz:", k, "cases")
 

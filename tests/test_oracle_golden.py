@@ -90,3 +90,56 @@ def test_zero_and_subnormal_blocks(orc):
     assert np.all(q[:32] == 0) and d16[0] == 0 and s16[0] == 0
     assert np.max(np.abs(q[32:])) == 127 and q.min() >= -127
     assert 0 < d16[1] < 0x0400                               # fp16 subnormal scale kept, not flushed
+
+
+def test_q6k_fixture_known_answers(orc, golden_dir):
+    """ref/quant_fixture.bin: the four Q6_K cases (token_embd / lm_head rows).
+
+    Decode + per-sub-block scale order are pinned by feeding the fixture's own quants and fp32 d8
+    through the checker's float64 GEMV: it must reproduce expected_exact to float32 resolution
+    (tests/make_quant_fixture.py:60-70,90-102).  The shipped fp32 form with fp16 d8 must stay inside the
+    reference's own Q6_K gate of 5e-2 relative (tests/test_quant.cu:162-163) and far tighter against
+    float64 over the same fp16 scales.
+    """
+    g = np.load(golden_dir / "quant_q4_cases.npz")
+    assert int(g["ncases_q6k"]) == 4
+    for k in range(4):
+        ql, qh, sc, d, x = (g[f"k{k}_{n}"] for n in ("ql", "qh", "sc", "d", "x"))
+        sb = d.size
+        y64, _ = orc.gemv_q6_K_f64(ql, qh, sc, d, g[f"k{k}_ref_q"], g[f"k{k}_ref_d8"], 1, sb)
+        exp = float(g[f"k{k}_expected_exact"])
+        assert abs(y64[0] - exp) <= 1e-6 * max(1.0, abs(exp)), (k, y64[0], exp)
+        # dequantised row . x in float64 == the fixture's fp32-path value to fp32 accumulation error
+        w = orc.dequant_q6_K(ql, qh, sc, d, sb)
+        exp32 = float(g[f"k{k}_expected_fp32"])
+        assert abs(float(w.astype(np.float64) @ x.astype(np.float64)) - exp32) <= 1e-3 * max(1.0, abs(exp32))
+        if sb == 8:
+            # shipped order on the checker's own fp16-scale quantisation
+            act = orc.quantize_q8_1(x)
+            y = orc.gemv_q6_K(ql, qh, sc, d, act, 1, sb)
+            assert abs(float(y[0]) - exp) <= 5e-2 * max(1.0, abs(exp))
+            y64b, mag = orc.gemv_q6_K_f64(ql, qh, sc, d, act[0], _f16(act[1]), 1, sb)
+            assert abs(float(y[0]) - y64b[0]) <= 1e-5 * mag[0]
+
+
+def test_q6k_group_sums_and_embed(orc):
+    """Integer group sums against a plain numpy decode; embed row == dequant row."""
+    rng = np.random.default_rng(61)
+    rows, sb = 24, 8
+    ql = rng.integers(0, 256, (rows, sb, 128), dtype=np.uint8)
+    qh = rng.integers(0, 256, (rows, sb, 64), dtype=np.uint8)
+    sc = rng.integers(-128, 128, (rows, sb, 16), dtype=np.int8)
+    d = np.abs(rng.normal(0, 1e-3, (rows, sb))).astype(np.float16).view(np.uint16)
+    aq = rng.integers(-127, 128, sb * 256, dtype=np.int8)
+    # numpy decode of element e of a super-block (src/quant.cuh:171-190 layout)
+    e = np.arange(256)
+    n, r = (e >= 128) * 128, e % 128
+    qlb = ql[:, :, (n >> 1) + (r & 63)].astype(np.int32)
+    qhb = qh[:, :, (n >> 2) + (r & 31)].astype(np.int32)
+    q6 = np.where(r >= 64, qlb >> 4, qlb & 15) | (((qhb >> (2 * (r >> 5))) & 3) << 4)
+    w = q6 - 32
+    gs = (w * aq.reshape(sb, 256)[None].astype(np.int32)).reshape(rows, sb, 32, 8).sum(-1)
+    assert np.array_equal(orc.q6_group_sums(ql, qh, aq, rows, sb), gs)
+    deq = (_f16(d).reshape(rows, sb, 1) * np.repeat(sc, 16, axis=2).astype(np.float32)) * w.astype(np.float32)
+    for t in (0, 7, rows - 1):
+        assert np.array_equal(orc.embed_q6_K(ql, qh, sc, d, t, sb), deq[t].reshape(-1))
