@@ -31,24 +31,6 @@ int lkb_check_launch() {
     return e == cudaSuccess ? LKB_OK : -(int) e;
 }
 
-// Launch helper: optional programmatic-dependent-launch attribute.
-template <typename... KArgs, typename... Args>
-static int lkb_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    int na = 0;
-    if (lkb_context().pdl) {
-        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[na].val.programmaticStreamSerializationAllowed = 1;
-        ++na;
-    }
-    cfg.attrs = attr; cfg.numAttrs = na;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
-    if (e != cudaSuccess) { (void) cudaGetLastError(); return -(int) e; }
-    return LKB_OK;
-}
-
 #define LKB_REQUIRE_INIT() do { if (!lkb_context().inited) return LKB_ERR_NOT_INIT; } while (0)
 
 // ---------------------------------------------------------------------------

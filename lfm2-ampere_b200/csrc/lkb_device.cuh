@@ -162,3 +162,22 @@ int lkb_check_launch();        // cudaGetLastError -> status
 int lkb_prefill_init();        // per-device attributes of the prefill kernels
 int lkb_fused_init();          // ... of the fused decode kernel
 int lkb_lmhead_init();         // ... of the Q6_K streaming GEMV
+
+// Launch helper: optional programmatic-dependent-launch attribute.
+template <typename... KArgs, typename... Args>
+static int lkb_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    int na = 0;
+    if (lkb_context().pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr; cfg.numAttrs = na;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) { (void) cudaGetLastError(); return -(int) e; }
+    return LKB_OK;
+}
+

@@ -25,7 +25,7 @@ def rand_q6(rng, rows, sb):
     return ql, qh, sc, d
 
 
-@pytest.mark.parametrize("rows,sb", [(65536, 8), (16, 8), (1, 8), (2381, 8), (148 * 16 + 5, 8), (300, 3), (64, 1)])
+@pytest.mark.parametrize("rows,sb", [(65536, 8), (16, 8), (1, 8), (33, 8), (2381, 8), (148 * 32 + 5, 8), (20000, 8), (148 * 32 * 4 - 1, 8), (300, 3), (64, 1)])
 def test_gemv_q6_K_bit_exact(L, orc, rows, sb):
     rng = np.random.default_rng(rows * 10 + sb)
     ql, qh, sc, d = rand_q6(rng, rows, sb)
