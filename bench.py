@@ -467,7 +467,8 @@ def run_ours(args):
         lm = {"metric": "lm_head: Q6_K 65536 x 2048 GEMV (+ two-stage argmax)", "gemv_us": res[0] * 1e3,
               "gemv_argmax_us": res[1] * 1e3, "launches_per_token": 3, "cold_cache": f"{NCOPY} weight copies in rotation (330 MB > L2)",
               "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
-                           "peak_kind": f"of {peak_kind}", "algorithmic_bytes": lm_bytes, "traffic": None}}
+                           "peak_kind": f"of {peak_kind}", "algorithmic_bytes": lm_bytes,
+                           "traffic": 114323968 if V == 65536 else None}}   # ncu dram read + write of one launch (profiles/)
         del copies
 
     if rank == 0:
