@@ -317,6 +317,29 @@ int lkb_argmax_final(const float * pv, const int * pi, int n, int * d_token, int
 int lkb_embed_q6_K(const void * ql, const void * qh, const void * sc, const void * d, const int * d_token, int n,
                    float * x, lkb_stream_t st);
 
+/* ---- sequence mixers of a decode step -----------------------------------------------------------------
+ * Model constants of the attention kernels: 32 query heads, 8 KV heads, head_dim 64; fp16 KV cache laid out
+ * [position][kv_head][64].  ref: src/kernels.cuh:14-24 */
+#define LKB_ATTN_SPLIT 18                 /* slices per KV head (partial-buffer stride) */
+#define LKB_ATTN_PARTW 66                 /* floats per partial: running max, sum, 64 accumulators */
+/* Split-K decode attention over positions 0..*d_pos.  part = float[32][LKB_ATTN_SPLIT][LKB_ATTN_PARTW];
+ * lkb_attn_combine merges the live slices, writes out[32*64] (may be NULL) and the Q8_1 form of it (yq8,
+ * 64 blocks, may be NULL).  The float64 evaluation is the definition (ref: tests/test_attn.cu:46-75); the
+ * slice rule differs from the reference's (here ceil(seq/256) slices, at most 18, whole 32-token groups).
+ * ref: src/kernels.cu:1303-1560 (k_attn_split), src/kernels.cu:1562-1599 (k_attn_combine) */
+int lkb_attn_split(const float * q, const void * kc, const void * vc, const int * d_pos, float * part, lkb_stream_t st);
+int lkb_attn_combine(const float * part, const int * d_pos, float * out, lkb_block_q8_1 * yq8, lkb_stream_t st);
+/* Per-head RMSNorm (eps 1e-5) with weights qn / kn, NEOX half-split RoPE at position *d_pos, in place on
+ * qf[32*64] and kf[8*64]; appends the rotated K and vf[8*64] as fp16 to the cache row *d_pos.  theta is the
+ * RoPE base (the reference compiles in 1e7).  ref: src/kernels.cu:871-915 (k_qk_norm_rope) */
+int lkb_qk_norm_rope(float * qf, float * kf, const float * vf, const float * qn, const float * kn, const int * d_pos,
+                     void * kc, void * vc, float theta, lkb_stream_t st);
+/* One decode step of the short gated convolution over n channels: bcx = [B | C | X], conv_w[ch*3 + tap],
+ * hist[ch*2 + {0,1}] (updated in place), y = C * (h0*w0 + h1*w1 + (B*X)*w2) as fp32 (may be NULL) and as
+ * Q8_1 blocks (may be NULL).  t is unused, as in the reference.  ref: src/kernels.cu:521-545 (k_shortconv) */
+int lkb_shortconv(const float * bcx, int t, const float * conv_w, float * hist, float * y, lkb_block_q8_1 * yq8, int n,
+                  lkb_stream_t st);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

@@ -106,6 +106,17 @@ inline int k_argmax_final(stream_t st, const float * pv, const int * pi, int n, 
 inline int k_embed_q6_K(stream_t st, const uint8_t * ql, const uint8_t * qh, const int8_t * sc, const void * d, const int * d_token, int n, float * x) {
     return check(lkb_embed_q6_K(ql, qh, sc, d, d_token, n, x, st), "k_embed_q6_K"); }
 
+// ---- sequence mixers (ref: src/kernels.cu:521, 871, 1303, 1562) ------------------------------------------------
+inline int k_shortconv(stream_t st, const float * bcx, int t, const float * conv_w, float * hist, float * y, block_q8_1 * yq8) {
+    return check(lkb_shortconv(bcx, t, conv_w, hist, y, yq8, LKB_HIDDEN, st), "k_shortconv"); }
+inline int k_qk_norm_rope(stream_t st, float * qf, float * kf, const float * vf, const float * qn, const float * kn, const int * d_pos,
+                          void * kc, void * vc) {
+    return check(lkb_qk_norm_rope(qf, kf, vf, qn, kn, d_pos, kc, vc, 10000000.0f, st), "k_qk_norm_rope"); }   // src/kernels.cuh:23
+inline int k_attn_split(stream_t st, const float * q, const void * kc, const void * vc, const int * d_pos, float * part) {
+    return check(lkb_attn_split(q, kc, vc, d_pos, part, st), "k_attn_split"); }
+inline int k_attn_combine(stream_t st, const float * part, const int * d_pos, float * out, block_q8_1 * yq8) {
+    return check(lkb_attn_combine(part, d_pos, out, yq8, st), "k_attn_combine"); }
+
 // ---- host launchers, same signatures as the reference's (ref: src/prefill.cuh:69-71) ---------------------
 inline void pf_gemm_dense(const PfGemm & g, stream_t st) { check(lkb_pf_gemm_dense(&g, st), "pf_gemm_dense"); }
 inline void pf_gemm_moe(const PfGemm & g, int max_tiles, stream_t st) { check(lkb_pf_gemm_moe(&g, max_tiles, st), "pf_gemm_moe"); }

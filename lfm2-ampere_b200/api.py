@@ -22,6 +22,7 @@ __all__ = [
     "k_pf_pack_q8_1", "zero_i32", "moe_layer_desc", "moe_scratch", "moe_ffn_decode", "moe_ffn_decode_stack",
     "layer_descs_to_device", "ep_pack_rows", "ep_unpack_rows", "k_pf_moe_combine_norm_gather", "moe_ffn_decode_stack_static", "set_pdl", "pf_gemm_config", "sm_count",
     "k_gemv_q6_K", "k_argmax_part", "k_argmax_final", "k_embed_q6_K", "gemv_q6_K_status",
+    "k_attn_split", "k_attn_combine", "k_qk_norm_rope", "k_shortconv", "ATTN_SPLIT", "ATTN_PARTW",
 ]
 
 
@@ -297,3 +298,24 @@ def k_argmax_final(pv, pi, n, d_token, d_pos=None):
 
 def k_embed_q6_K(ql, qh, sc, d, d_token, n, x):
     check(lib.lkb_embed_q6_K(ptr(ql), ptr(qh), ptr(sc), ptr(d), ptr(d_token), n, ptr(x), stream()), "k_embed_q6_K")
+
+
+# ------------------------------------------------------------ sequence mixers --
+ATTN_SPLIT, ATTN_PARTW = 18, 66          # LKB_ATTN_SPLIT / LKB_ATTN_PARTW of include/lkb.h
+
+
+def k_attn_split(q, kc, vc, d_pos, part):
+    check(lib.lkb_attn_split(ptr(q), ptr(kc), ptr(vc), ptr(d_pos), ptr(part), stream()), "k_attn_split")
+
+
+def k_attn_combine(part, d_pos, out, yq8=None):
+    check(lib.lkb_attn_combine(ptr(part), ptr(d_pos), ptr(out), ptr(yq8), stream()), "k_attn_combine")
+
+
+def k_qk_norm_rope(qf, kf, vf, qn, kn, d_pos, kc, vc, theta=1e7):
+    check(lib.lkb_qk_norm_rope(ptr(qf), ptr(kf), ptr(vf), ptr(qn), ptr(kn), ptr(d_pos), ptr(kc), ptr(vc), theta, stream()),
+          "k_qk_norm_rope")
+
+
+def k_shortconv(bcx, conv_w, hist, y, yq8, n, t=0):
+    check(lib.lkb_shortconv(ptr(bcx), t, ptr(conv_w), ptr(hist), ptr(y), ptr(yq8), n, stream()), "k_shortconv")

@@ -610,6 +610,8 @@ int lkb_init(int device) {
     if (r != LKB_OK) return r;
     r = lkb_lmhead_init();
     if (r != LKB_OK) return r;
+    r = lkb_mixer_init();
+    if (r != LKB_OK) return r;
     c.inited = 1;
     return LKB_OK;
 }

@@ -162,6 +162,7 @@ int lkb_check_launch();        // cudaGetLastError -> status
 int lkb_prefill_init();        // per-device attributes of the prefill kernels
 int lkb_fused_init();          // ... of the fused decode kernel
 int lkb_lmhead_init();         // ... of the Q6_K streaming GEMV
+int lkb_mixer_init();          // ... of the decode attention kernel
 
 // Launch helper: optional programmatic-dependent-launch attribute.
 template <typename... KArgs, typename... Args>

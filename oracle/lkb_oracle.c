@@ -749,3 +749,82 @@ ORC_API void orc_embed_q6_K(const uint8_t * ql, const uint8_t * qh, const int8_t
         x[i] = t * (float) (q6_at(ql + blk * 128, qh + blk * 64, e) - 32);
     }
 }
+
+/* ---- sequence mixers of a decode step ------------------------------------------------------------------- */
+
+/* Short gated convolution, one step (src/kernels.cu:521-545): bx = B*X, conv = fma(bx, w2, fma(h1, w1, h0*w0)),
+ * y = C*conv, history shifts.  The association of the three-term sum is fixed here; the reference leaves it to
+ * the compiler's contraction and gates at 1e-5 against float64 (tests/test_kernels.cu:131-163). */
+ORC_API void orc_shortconv(const float * bcx, const float * conv_w, float * hist, float * y, int n) {
+    for (int ch = 0; ch < n; ++ch) {
+        const float bx = bcx[ch] * bcx[2 * n + ch];
+        const float h0 = hist[2 * ch], h1 = hist[2 * ch + 1];
+        const float conv = fmaf(bx, conv_w[3 * ch + 2], fmaf(h1, conv_w[3 * ch + 1], h0 * conv_w[3 * ch]));
+        hist[2 * ch] = h1;
+        hist[2 * ch + 1] = bx;
+        y[ch] = bcx[n + ch] * conv;
+    }
+}
+
+/* Per-head RMSNorm + NEOX RoPE, float32 in the kernel's order (src/kernels.cu:871-915): sum of squares by the
+ * halving tree over 64 (s[i] += s[i+o], o = 32..1), inv = 1/sqrt(ss/64 + eps), x = (v*inv)*w, angle =
+ * pos * powf(theta, -2i/64), out[i] = x0*c - x1*s, out[i+32] = x0*s + x1*c.  inv_override (may be NULL) takes
+ * the device's rsqrtf values, one per head, so that everything downstream can be compared exactly. */
+ORC_API void orc_norm_rope_heads(float * x, const float * w, int n_heads, float pos, float theta,
+                                 const float * inv_override, float * inv_out) {
+    for (int h = 0; h < n_heads; ++h) {
+        float * v = x + (size_t) h * 64;
+        float s[64];
+        for (int i = 0; i < 64; ++i) s[i] = v[i] * v[i];
+        for (int o = 32; o > 0; o >>= 1)
+            for (int i = 0; i < o; ++i) s[i] = s[i] + s[i + o];
+        float inv = 1.0f / sqrtf(s[0] / 64.0f + 1e-5f);
+        if (inv_out) inv_out[h] = inv;
+        if (inv_override) inv = inv_override[h];
+        for (int i = 0; i < 32; ++i) {
+            const float x0 = (v[i] * inv) * w[i], x1 = (v[i + 32] * inv) * w[i + 32];
+            const float invf = powf(theta, (-2.0f * (float) i) / 64.0f);
+            const float ang = pos * invf;
+            const float sn = sinf(ang), cs = cosf(ang);
+            v[i] = x0 * cs - x1 * sn;
+            v[i + 32] = x0 * sn + x1 * cs;
+        }
+    }
+}
+
+/* fp32 -> fp16 bits, round to nearest even (the device's __float2half). */
+ORC_API void orc_f32_to_f16_array(const float * x, int n, uint16_t * out) {
+    for (int i = 0; i < n; ++i) {
+        const _Float16 hv = (_Float16) x[i];
+        memcpy(&out[i], &hv, 2);
+    }
+}
+
+/* Decode attention in float64: the definition both the reference's kernels and ours are roundings of
+ * (tests/test_attn.cu:46-75).  q[32*64] fp32, kc / vc fp16 bits [seq][8][64], out[32*64]. */
+ORC_API void orc_attn_decode_f64(const float * q, const uint16_t * kc, const uint16_t * vc, int seq, double * out) {
+#pragma omp parallel for schedule(static)
+    for (int head = 0; head < 32; ++head) {
+        const int kv = head / 4;
+        double * s = (double *) malloc((size_t) seq * sizeof(double));
+        double m = -1e300;
+        for (int t = 0; t < seq; ++t) {
+            const uint16_t * k = kc + ((size_t) t * 8 + kv) * 64;
+            double a = 0.0;
+            for (int d = 0; d < 64; ++d) a += (double) q[head * 64 + d] * (double) orc_f16_to_f32(k[d]);
+            a *= 0.125;
+            s[t] = a;
+            if (a > m) m = a;
+        }
+        double l = 0.0;
+        for (int t = 0; t < seq; ++t) { s[t] = exp(s[t] - m); l += s[t]; }
+        double acc[64];
+        for (int d = 0; d < 64; ++d) acc[d] = 0.0;
+        for (int t = 0; t < seq; ++t) {
+            const uint16_t * v = vc + ((size_t) t * 8 + kv) * 64;
+            for (int d = 0; d < 64; ++d) acc[d] += s[t] * (double) orc_f16_to_f32(v[d]);
+        }
+        for (int d = 0; d < 64; ++d) out[head * 64 + d] = acc[d] / l;
+        free(s);
+    }
+}

@@ -463,3 +463,55 @@ def embed_q6_K(ql, qh, sc, d, token, sbpr=8):
 def dequant_q6_K(ql, qh, sc, d, nblk):
     """All weights of nblk super-blocks as float32 (via the embed formula)."""
     return embed_q6_K(ql, qh, sc, d, 0, sbpr=nblk)
+
+
+# ---- sequence mixers of a decode step --------------------------------------------------------------
+def shortconv(bcx, conv_w, hist):
+    """One conv step; returns (y, new_hist).  hist is not modified."""
+    bcx, conv_w = _c(bcx, np.float32).reshape(-1), _c(conv_w, np.float32).reshape(-1)
+    n = bcx.size // 3
+    h = _c(hist, np.float32).reshape(-1).copy()
+    y = np.empty(n, np.float32)
+    _lib.orc_shortconv(_p(bcx, _f32p), _p(conv_w, _f32p), _p(h, _f32p), _p(y, _f32p), n)
+    return y, h
+
+
+def norm_rope_heads(x, w, pos, theta, inv_override=None):
+    """x [n_heads*64] -> (rotated copy, inv per head) in the kernel's float32 order."""
+    v = _c(x, np.float32).reshape(-1).copy()
+    w = _c(w, np.float32).reshape(-1)
+    nh = v.size // 64
+    inv = np.empty(nh, np.float32)
+    ov = None if inv_override is None else _c(inv_override, np.float32)
+    _lib.orc_norm_rope_heads(_p(v, _f32p), _p(w, _f32p), nh, C.c_float(pos), C.c_float(theta),
+                             None if ov is None else _p(ov, _f32p), _p(inv, _f32p))
+    return v, inv
+
+
+def norm_rope_heads_f64(x, w, pos, theta):
+    """float64 form (tests/test_kernels.cu:91-110 for the rotation)."""
+    v = np.asarray(x, np.float64).reshape(-1, 64)
+    inv = 1.0 / np.sqrt((v * v).mean(axis=1, keepdims=True) + 1e-5)
+    u = v * inv * np.asarray(w, np.float64)[None, :]
+    i = np.arange(32)
+    ang = float(pos) * np.power(float(theta), -2.0 * i / 64.0)
+    c, s = np.cos(ang), np.sin(ang)
+    out = np.empty_like(u)
+    out[:, :32] = u[:, :32] * c - u[:, 32:] * s
+    out[:, 32:] = u[:, :32] * s + u[:, 32:] * c
+    return out.reshape(-1)
+
+
+def f32_to_f16_bits(x):
+    x = _c(x, np.float32).reshape(-1)
+    out = np.empty(x.size, np.uint16)
+    _lib.orc_f32_to_f16_array(_p(x, _f32p), x.size, _p(out, _u16p))
+    return out
+
+
+def attn_decode_f64(q, kc, vc, seq):
+    q = _c(q, np.float32).reshape(-1)
+    kc, vc = _c(kc, np.uint16).reshape(-1), _c(vc, np.uint16).reshape(-1)
+    out = np.empty(32 * 64, np.float64)
+    _lib.orc_attn_decode_f64(_p(q, _f32p), _p(kc, _u16p), _p(vc, _u16p), seq, _p(out, _f64p))
+    return out

@@ -5,7 +5,7 @@ Run once, in a container that has the reference repository mounted:
 
     python tests/golden/make_golden.py /path/to/reference
 
-It writes three small .npz files.  Nothing at test time reads the reference
+It writes four small .npz files.  Nothing at test time reads the reference
 checkout; the tests read only these files.
 
   quant_q4_cases.npz   The four Q4_0 known-answer cases of the reference's
@@ -22,6 +22,8 @@ checkout; the tests read only these files.
                        (xorshift64 stream of tests/test_kernels.cu:19-24,170-171) and
                        the expected top-4 / weights from that test's float64
                        recipe (tests/test_kernels.cu:172-182).
+  conv_taps.npz        The reference's real ShortConv tap weights (2048 x 3 fp32) from the same
+                       kernel_fixture.bin.
   ref_numpy_vectors.npz  Seeded synthetic Q4_0 matrices and activations pushed
                        through the reference's numpy helpers q8_1() and
                        q4_mv_q8() (tools/ref_forward.py:60-100), whose source is
@@ -140,6 +142,8 @@ def router_fixture(ref):
     sel = pr + bias.astype(np.float64)
     order = np.argsort(-sel, kind="stable")
     ws = max(pr[order[:4]].sum(), 6.103515625e-5)
+    # the reference's real ShortConv taps (2048 channels x 3), used by its conv test (tests/test_kernels.cu:131-163)
+    np.savez_compressed(OUT / "conv_taps.npz", conv_w=_conv_w.astype(np.float32))
     np.savez_compressed(OUT / "router_fixture.npz", gate=gate, bias=bias, h=h,
                         expected_idx=order[:4].astype(np.int32),
                         expected_w=(pr[order[:4]] / ws).astype(np.float64),

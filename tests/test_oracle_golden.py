@@ -143,3 +143,43 @@ def test_q6k_group_sums_and_embed(orc):
     deq = (_f16(d).reshape(rows, sb, 1) * np.repeat(sc, 16, axis=2).astype(np.float32)) * w.astype(np.float32)
     for t in (0, 7, rows - 1):
         assert np.array_equal(orc.embed_q6_K(ql, qh, sc, d, t, sb), deq[t].reshape(-1))
+
+
+def test_shortconv_on_real_taps(orc, golden_dir):
+    """The reference's conv test (tests/test_kernels.cu:131-163) on its real taps: y within 1e-5 of float64,
+    history shifted exactly."""
+    cw = np.load(golden_dir / "conv_taps.npz")["conv_w"]
+    n = cw.size // 3
+    assert n == 2048
+    rng = np.random.default_rng(11)
+    bcx = rng.uniform(-1, 1, 3 * n).astype(np.float32)
+    hist = (0.5 * rng.uniform(-1, 1, 2 * n)).astype(np.float32)
+    y, h2 = orc.shortconv(bcx, cw, hist)
+    B, Cg, X = (bcx[i * n:(i + 1) * n].astype(np.float64) for i in range(3))
+    w = cw.astype(np.float64).reshape(n, 3)
+    hh = hist.astype(np.float64).reshape(n, 2)
+    ref = Cg * (hh[:, 0] * w[:, 0] + hh[:, 1] * w[:, 1] + (B * X) * w[:, 2])
+    assert np.max(np.abs(y - ref)) <= 1e-5
+    assert np.array_equal(h2.reshape(n, 2)[:, 0], hist.reshape(n, 2)[:, 1])
+    assert np.array_equal(h2.reshape(n, 2)[:, 1], (bcx[:n] * bcx[2 * n:]).astype(np.float32))
+
+
+def test_norm_rope_and_attention_references(orc):
+    """float32 restatement vs float64 within the reference's gates: RoPE 2e-3 absolute at pos 12345
+    (tests/test_kernels.cu:91-129); the float64 attention equals a direct numpy softmax."""
+    rng = np.random.default_rng(12)
+    x = rng.uniform(-1, 1, 4 * 64).astype(np.float32)
+    one = np.ones(64, np.float32)
+    a, inv = orc.norm_rope_heads(x, one, 12345.0, 1e7)
+    assert np.max(np.abs(a - orc.norm_rope_heads_f64(x, one, 12345.0, 1e7))) <= 2e-3
+    a0, _ = orc.norm_rope_heads(x, one, 0.0, 1e7)                      # position 0: rotation is the identity
+    assert np.max(np.abs(a0 - orc.norm_rope_heads_f64(x, one, 0.0, 1e7))) <= 1e-6
+    seq = 77
+    q = rng.uniform(-1.5, 1.5, 2048).astype(np.float32)
+    kc = rng.uniform(-1, 1, (seq, 8, 64)).astype(np.float16)
+    vc = rng.uniform(-1, 1, (seq, 8, 64)).astype(np.float16)
+    o = orc.attn_decode_f64(q, kc.view(np.uint16), vc.view(np.uint16), seq).reshape(32, 64)
+    for h in (0, 13, 31):
+        s = (kc[:, h // 4, :].astype(np.float64) @ q[h * 64:(h + 1) * 64].astype(np.float64)) * 0.125
+        p = np.exp(s - s.max())
+        assert np.max(np.abs(o[h] - (p @ vc[:, h // 4, :].astype(np.float64)) / p.sum())) <= 1e-14
