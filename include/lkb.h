@@ -175,6 +175,32 @@ typedef struct {
     float *    gu;
     unsigned * sync;
 } lkb_moe_scratch;
+/* Sequence mixer of one layer for the whole-step kernel (lkb_decode_layers): the short convolution
+ * (is_attn == 0: in_proj 6144 x 2048, conv taps, two-tap history, out_proj) or GQA attention (is_attn != 0:
+ * q / k / v projections 2048 / 512 / 512 x 2048, per-head norm weights, this layer's fp16 KV cache,
+ * attn_output).  All weight planes are Q4_0 planar (qs, d) with 64 blocks per row.
+ * ref: src/engine.cu:136-145 (struct Layer) */
+typedef struct {
+    int           is_attn;
+    int           reserved;
+    const float * attn_norm;                        /* fp32[2048], the norm in front of the mixer */
+    const void *  in_qs;  const void * in_d;        /* conv: in_proj */
+    const float * conv_w;                           /* conv: fp32[2048*3] */
+    float *       hist;                             /* conv: fp32[2048*2], updated in place */
+    const void *  wq_qs;  const void * wq_d;
+    const void *  wk_qs;  const void * wk_d;
+    const void *  wv_qs;  const void * wv_d;
+    const float * qnorm;  const float * knorm;      /* fp32[64] each */
+    void *        kc;     void * vc;                /* fp16 [max_seq][8][64] */
+    const void *  out_qs; const void * out_d;       /* out_proj / attn_output, 2048 x 2048 */
+} lkb_mixer_layer;
+/* Caller-owned global scratch of the whole-step kernel, beside lkb_moe_scratch. */
+#define LKB_STEP_SCRATCH_MX   3072                  /* floats: q | k | v of an attention layer, or the conv output */
+#define LKB_STEP_SCRATCH_PART (32 * 18 * 66)        /* floats: attention partials */
+typedef struct {
+    float * mx;
+    float * part;
+} lkb_step_scratch;
 /* One launch for one batch-1 MoE FFN layer: x (the residual stream, fp32[2048]) is
  * normalised-and-quantised with layer->norm_w, routed, pushed through the four chosen
  * experts and updated in place; idx_out/w_out (optional) receive the selection; `next`
@@ -191,6 +217,20 @@ int lkb_moe_ffn_decode(const lkb_moe_layer * layer, float * x, int * idx_out, fl
 int lkb_moe_ffn_decode_stack(const lkb_moe_layer * layers_dev, int n_layers, int softmax, float * x,
                              int * idx_out, float * w_out, const lkb_norm_prod_t * next,
                              const lkb_moe_scratch * scratch, lkb_stream_t st);
+
+/* All n_layers layers of a batch-1 decode step in ONE persistent launch: per layer the sequence mixer
+ * (mixers_dev[l]) and the MoE FFN (moe_dev[l]), with x the residual stream updated in place.  xq_first is
+ * layer 0's normalised Q8_1 activation (from lkb_rmsnorm_q8_1 with layer 0's attn_norm); every later norm is
+ * evaluated inside.  Attention layers read the position from *d_pos, append the new K / V row to their cache
+ * and attend over positions 0..*d_pos.  `next` (w != null) receives the quantised raw activation and ssq of
+ * the final x for the output projection.  Results are bit-identical to the kernel-by-kernel sequence
+ * (lkb_gemv_q4_0 / lkb_shortconv / lkb_gemv_q4_0_3 / lkb_qk_norm_rope / lkb_attn_split / lkb_attn_combine /
+ * lkb_gemv_q4_0_prod, then the MoE kernels).  Status word as for lkb_moe_ffn_decode (400/500+layer = a mixer
+ * copy, 1000+10*layer+n = grid barrier n).  No counterpart in the reference (its step is a 343-node graph,
+ * ref: src/engine.cu:1336-1342). */
+int lkb_decode_layers(const lkb_moe_layer * moe_dev, const lkb_mixer_layer * mixers_dev, int n_layers, float * x,
+                      const lkb_block_q8_1 * xq_first, const int * d_pos, float theta, const lkb_norm_prod_t * next,
+                      const lkb_moe_scratch * scratch, const lkb_step_scratch * step_scratch, lkb_stream_t st);
 
 /* lkb_moe_ffn_decode_stack for callers that must not allocate device memory.
  * Who that is: an engine that, like the reference's, sizes one pack allocation plus its KV cache at start-up

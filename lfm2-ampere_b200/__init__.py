@@ -48,6 +48,20 @@ class MoeScratch(C.Structure):
     _fields_ = [("logits", C.c_void_p), ("gu", C.c_void_p), ("sync", C.c_void_p)]
 
 
+class MixerLayer(C.Structure):
+    """lkb_mixer_layer"""
+    _fields_ = [("is_attn", C.c_int), ("reserved", C.c_int), ("attn_norm", C.c_void_p),
+                ("in_qs", C.c_void_p), ("in_d", C.c_void_p), ("conv_w", C.c_void_p), ("hist", C.c_void_p),
+                ("wq_qs", C.c_void_p), ("wq_d", C.c_void_p), ("wk_qs", C.c_void_p), ("wk_d", C.c_void_p),
+                ("wv_qs", C.c_void_p), ("wv_d", C.c_void_p), ("qnorm", C.c_void_p), ("knorm", C.c_void_p),
+                ("kc", C.c_void_p), ("vc", C.c_void_p), ("out_qs", C.c_void_p), ("out_d", C.c_void_p)]
+
+
+class StepScratch(C.Structure):
+    """lkb_step_scratch"""
+    _fields_ = [("mx", C.c_void_p), ("part", C.c_void_p)]
+
+
 class PfGemm(C.Structure):
     """lkb_pf_gemm"""
     _fields_ = [("qs", C.c_void_p * 3), ("d", C.c_void_p * 3), ("seg_end", C.c_int * 3), ("N", C.c_int),

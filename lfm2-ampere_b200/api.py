@@ -10,7 +10,7 @@ import ctypes as C
 
 import torch
 
-from . import MoeLayer, MoeScratch, NormProd, PfAct, PfGemm, check, lib
+from . import MixerLayer, MoeLayer, MoeScratch, NormProd, PfAct, PfGemm, StepScratch, check, lib
 
 __all__ = [
     "ptr", "stream", "norm_prod", "pf_act", "make_pf_gemm",
@@ -23,6 +23,7 @@ __all__ = [
     "layer_descs_to_device", "ep_pack_rows", "ep_unpack_rows", "k_pf_moe_combine_norm_gather", "moe_ffn_decode_stack_static", "set_pdl", "pf_gemm_config", "sm_count",
     "k_gemv_q6_K", "k_argmax_part", "k_argmax_final", "k_embed_q6_K", "gemv_q6_K_status",
     "k_attn_split", "k_attn_combine", "k_qk_norm_rope", "k_shortconv", "ATTN_SPLIT", "ATTN_PARTW",
+    "mixer_layer_desc", "step_scratch", "decode_layers",
 ]
 
 
@@ -319,3 +320,23 @@ def k_qk_norm_rope(qf, kf, vf, qn, kn, d_pos, kc, vc, theta=1e7):
 
 def k_shortconv(bcx, conv_w, hist, y, yq8, n, t=0):
     check(lib.lkb_shortconv(ptr(bcx), t, ptr(conv_w), ptr(hist), ptr(y), ptr(yq8), n, stream()), "k_shortconv")
+
+
+# ------------------------------------------------------------ whole-step kernel --
+def mixer_layer_desc(mx, hist=None, kc=None, vc=None):
+    """lkb_mixer_layer from a model.Mixer plus this layer's state (conv history or KV cache)."""
+    if mx.is_attn:
+        return MixerLayer(1, 0, ptr(mx.attn_norm), None, None, None, None, ptr(mx.wq[0]), ptr(mx.wq[1]), ptr(mx.wk[0]),
+                          ptr(mx.wk[1]), ptr(mx.wv[0]), ptr(mx.wv[1]), ptr(mx.qnorm), ptr(mx.knorm), ptr(kc), ptr(vc),
+                          ptr(mx.out_qs), ptr(mx.out_d))
+    return MixerLayer(0, 0, ptr(mx.attn_norm), ptr(mx.in_qs), ptr(mx.in_d), ptr(mx.conv_w), ptr(hist), None, None, None,
+                      None, None, None, None, None, None, None, ptr(mx.out_qs), ptr(mx.out_d))
+
+
+def step_scratch(mx, part):
+    return StepScratch(ptr(mx), ptr(part))
+
+
+def decode_layers(moe_dev, mixers_dev, n_layers, x, xq_first, d_pos, theta, next_np, scratch, sscratch):
+    check(lib.lkb_decode_layers(ptr(moe_dev), ptr(mixers_dev), n_layers, ptr(x), ptr(xq_first), ptr(d_pos), theta,
+                                _np(next_np), C.byref(scratch), C.byref(sscratch), stream()), "decode_layers")

@@ -19,7 +19,7 @@
 // Every wait (grid barrier, mbarrier) is bounded: on expiry the CTA records a code in
 // the status word and leaves; the other CTAs' waits then expire too.
 #include <cooperative_groups.h>
-#include "lkb_device.cuh"
+#include "lkb_attn.cuh"
 
 #define FUSED_THREADS 512
 #define FUSED_WARPS   (FUSED_THREADS / 32)
@@ -52,6 +52,8 @@ struct FusedSmem {
     int    abort;
     unsigned bar_target;
     alignas(8) lkb_moe_layer ly;          // this layer's descriptor (staged: a global read costs ~1 us of latency)
+    alignas(8) lkb_mixer_layer mx;        // whole-step kernel: this layer's sequence-mixer descriptor
+    alignas(8) unsigned long long mbar_mi, mbar_mo;   // whole-step kernel: mixer input rows / output rows staged
     alignas(8) unsigned long long mbar_gu[N_GU_CH];
     alignas(8) unsigned long long mbar_dn[N_DN_CH];
     alignas(8) unsigned long long mbar_rt;
@@ -242,6 +244,13 @@ struct FusedArgs {
     unsigned long long *  timing;
     int                   absent_cta;  // test hook: this CTA leaves at once and never arrives (-1: none)
     unsigned              spin_limit;  // iterations a grid-barrier wait may spin
+    // whole-step kernel only
+    const lkb_mixer_layer * mixers;    // device array [n_layers]
+    const lkb_q8blk *     xq_first;    // layer 0's normalised Q8_1 activation (lkb_rmsnorm_q8_1)
+    const int *           d_pos;       // device-side position
+    float                 theta;       // RoPE base
+    float *               mxbuf;       // scratch [3072]: q | k | v of an attention layer, or the conv output
+    float *               part;        // scratch [32][LKB_ATTN_SPLIT][LKB_ATTN_PARTW]
 };
 
 // Blocks b = warp + 16 j (j = 0..3) of the 2048-vector belong to this warp, element `lane`.
@@ -274,6 +283,54 @@ __device__ __forceinline__ void fused_quant_u(FusedSmem & S, const float (&xv)[4
     __syncthreads();
 }
 
+
+// ---------------------------------------------------------------------------
+// Whole-step kernel: the sequence mixers in front of every MoE FFN.
+// Mixer weight rows are static, so they are requested a phase ahead of their use into staging that the
+// MoE phases have finished with: input-projection rows into gu_q / gu_d, output-projection rows into
+// dn_q / dn_d.  Attention staging (two cp.async stages per warp) also lives in the gu_q .. dn_d range.
+// ---------------------------------------------------------------------------
+typedef AtSmem<2> AtSmem2;
+static_assert(sizeof(AtSmem2) <= offsetof(FusedSmem, router), "attention staging must end before the live per-layer state");
+#define MIX_QKV_ROWS (LKB_HIDDEN + 2 * AT_KVH * AT_D)      // 3072 logical rows: q | k | v
+
+// One thread: request this CTA's mixer input rows.  Conv: channels [dn0, dn0+n_dn) of B, C and X (rows ch,
+// 2048+ch, 4096+ch of in_proj) -> staged rows s*n_dn + j.  Attention: logical rows [a0, a1) of q | k | v.
+__device__ __forceinline__ void mix_issue_in(FusedSmem & S, const lkb_mixer_layer & mx, int dn0, int n_dn, int a0, int a1) {
+    fence_proxy_async();
+    if (!mx.is_attn) {
+        mbar_expect_tx(&S.mbar_mi, 3u * (unsigned) n_dn * GU_BPR * 18u);
+        for (int s = 0; s < 3; ++s) {
+            const size_t blk = ((size_t) s * LKB_HIDDEN + dn0) * GU_BPR;
+            bulk_g2s(S.gu_q + (size_t) s * n_dn * GU_BPR * 16, (const uint4 *) mx.in_qs + blk, (unsigned) n_dn * GU_BPR * 16u, &S.mbar_mi);
+            bulk_g2s(S.gu_d + (size_t) s * n_dn * GU_BPR, (const __half *) mx.in_d + blk, (unsigned) n_dn * GU_BPR * 2u, &S.mbar_mi);
+        }
+    } else {
+        mbar_expect_tx(&S.mbar_mi, (unsigned) (a1 - a0) * GU_BPR * 18u);
+        unsigned char * sq = S.gu_q; __half * sd = S.gu_d;
+        for (int g = a0; g < a1; ) {
+            const int seg = g < LKB_HIDDEN ? 0 : (g < LKB_HIDDEN + AT_KVH * AT_D ? 1 : 2);
+            const int base = seg == 0 ? 0 : (seg == 1 ? LKB_HIDDEN : LKB_HIDDEN + AT_KVH * AT_D);
+            const int end = seg == 0 ? LKB_HIDDEN : (seg == 1 ? LKB_HIDDEN + AT_KVH * AT_D : MIX_QKV_ROWS);
+            const int n = min(a1, end) - g;
+            const void * q = seg == 0 ? mx.wq_qs : (seg == 1 ? mx.wk_qs : mx.wv_qs);
+            const void * d = seg == 0 ? mx.wq_d : (seg == 1 ? mx.wk_d : mx.wv_d);
+            const size_t blk = (size_t) (g - base) * GU_BPR;
+            bulk_g2s(sq, (const uint4 *) q + blk, (unsigned) n * GU_BPR * 16u, &S.mbar_mi);
+            bulk_g2s(sd, (const __half *) d + blk, (unsigned) n * GU_BPR * 2u, &S.mbar_mi);
+            sq += (size_t) n * GU_BPR * 16; sd += (size_t) n * GU_BPR; g += n;
+        }
+    }
+}
+// One thread: request this CTA's rows [dn0, dn0+n_dn) of the mixer's output projection.
+__device__ __forceinline__ void mix_issue_out(FusedSmem & S, const lkb_mixer_layer & mx, int dn0, int n_dn) {
+    fence_proxy_async();
+    mbar_expect_tx(&S.mbar_mo, (unsigned) n_dn * GU_BPR * 18u);
+    bulk_g2s(S.dn_q, (const uint4 *) mx.out_qs + (size_t) dn0 * GU_BPR, (unsigned) n_dn * GU_BPR * 16u, &S.mbar_mo);
+    bulk_g2s(S.dn_d, (const __half *) mx.out_d + (size_t) dn0 * GU_BPR, (unsigned) n_dn * GU_BPR * 2u, &S.mbar_mo);
+}
+
+template <bool MIX>
 __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedArgs a) {
     extern __shared__ __align__(128) unsigned char fused_smem_raw[];
     FusedSmem & S = *reinterpret_cast<FusedSmem *>(fused_smem_raw);
@@ -295,6 +352,8 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
         for (int i = 0; i < N_GU_CH; ++i) mbar_init(&S.mbar_gu[i], 1);
         for (int i = 0; i < N_DN_CH; ++i) mbar_init(&S.mbar_dn[i], 1);
         mbar_init(&S.mbar_rt, 1);
+        mbar_init(&S.mbar_mi, 1);
+        mbar_init(&S.mbar_mo, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -311,11 +370,139 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
 
     if (tid < (int) (sizeof(lkb_moe_layer) / 8))
         reinterpret_cast<unsigned long long *>(&S.ly)[tid] = reinterpret_cast<const unsigned long long *>(&L[0])[tid];
+    // whole-step kernel: row ranges of the mixers, layer 0's descriptor and weight rows
+    const int qa0 = (int) (((long long) cta * MIX_QKV_ROWS) / nct), qa1 = (int) (((long long) (cta + 1) * MIX_QKV_ROWS) / nct);
+    int pos = 0;
+    float anw[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if constexpr (MIX) {
+        pos = __ldg(a.d_pos);
+        if (tid < (int) (sizeof(lkb_mixer_layer) / 8))
+            reinterpret_cast<unsigned long long *>(&S.mx)[tid] = reinterpret_cast<const unsigned long long *>(&a.mixers[0])[tid];
+    }
     __syncthreads();
+    if constexpr (MIX) {
+        if (tid == 0) {
+            mix_issue_in(S, S.mx, dn0, n_dn, qa0, qa1);
+            if (!S.mx.is_attn) mix_issue_out(S, S.mx, dn0, n_dn);
+        }
+    }
 
     for (int l = 0; l < a.n_layers; ++l) {
         const lkb_moe_layer & ly = S.ly;
         const unsigned par = (unsigned) (l & 1);
+
+        if constexpr (MIX) {
+            const lkb_mixer_layer & mx = S.mx;
+            const bool is_attn = mx.is_attn != 0;
+            // ---- M0: the mixer's input activation: layer 0 arrives normalised and quantised; later layers
+            //          quantise raw u = x * attn_norm_w and carry 1/rms into the consumer (S.inv) ----
+            if (l == 0) {
+                for (int i = tid; i < LKB_HIDDEN / 32 * 9; i += FUSED_THREADS)
+                    reinterpret_cast<int *>(S.xq)[i] = reinterpret_cast<const int *>(a.xq_first)[i];
+                if (tid == 0) S.inv = 1.0f;
+                __syncthreads();
+            } else {
+                float xv[4], uv[4];
+                fused_load_u(S, a.x, anw, xv, uv);
+                fused_quant_u(S, xv, uv);
+            }
+            // ---- M1: input projection rows of this CTA (staged a phase ago) ----
+            {
+                int xq[2][8]; float d8[2], s8[2];
+                load_xregs<2>(S.xq, GU_BPR, lane, xq, d8, s8);
+                const float ninv = S.inv;
+                const int nrows = is_attn ? (qa1 - qa0) : 3 * n_dn;
+                float * mixv = &S.dot[0][0];
+                if (!mbar_wait(&S.mbar_mi, par)) { if (lane == 0) { atomicCAS(status, 0u, 400u + l); S.abort = 1; } }
+                else {
+                    for (int j = warp; j < nrows; j += FUSED_WARPS) {
+                        const float acc = lkb_warp_sum(smem_row_partial<2>(S.gu_q + (size_t) j * GU_BPR * 16, S.gu_d + (size_t) j * GU_BPR,
+                                                                           GU_BPR, lane, xq, d8, s8));
+                        if (lane == 0) {
+                            const float v = __fmul_rn(acc, ninv);
+                            if (is_attn) a.mxbuf[qa0 + j] = v; else mixv[j] = v;
+                        }
+                    }
+                }
+                if (!is_attn) {
+                    // short convolution on this CTA's channels: B, C, X of a channel are rows j, n_dn + j, 2 n_dn + j
+                    __syncthreads();
+                    if (tid < n_dn) {
+                        const int ch = dn0 + tid;
+                        const float bx = __fmul_rn(mixv[tid], mixv[2 * n_dn + tid]);
+                        const float2 h = *reinterpret_cast<const float2 *>(mx.hist + 2 * ch);
+                        const float conv = fmaf(bx, mx.conv_w[3 * ch + 2], fmaf(h.y, mx.conv_w[3 * ch + 1], __fmul_rn(h.x, mx.conv_w[3 * ch])));
+                        *reinterpret_cast<float2 *>(mx.hist + 2 * ch) = make_float2(h.y, bx);
+                        a.mxbuf[ch] = __fmul_rn(mixv[n_dn + tid], conv);
+                    }
+                }
+            }
+            grid_arrive(a.bar, S);
+            if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 4u, a.spin_limit)) return;
+            const int seq_len = pos + 1;
+            if (is_attn) {
+                // ---- M2: one slice of one KV head per CTA; the query heads' norm + rotation are redone by every
+                //          slice, the new K / V row is written by the slice that contains it (the last one) ----
+                const int nsl = at_slices(seq_len), chunk = at_chunk(seq_len, nsl);
+                const int kvh = cta & (AT_KVH - 1), sp = cta >> 3;
+                const int t0 = sp * chunk, t1 = min(t0 + chunk, seq_len);
+                if (sp < nsl && t0 < t1) {                                  // CTA-uniform
+                    AtSmem2 & A = *reinterpret_cast<AtSmem2 *>(fused_smem_raw);
+                    __half * kc = reinterpret_cast<__half *>(mx.kc), * vc = reinterpret_cast<__half *>(mx.vc);
+                    if (warp < AT_GQA) {
+                        const float * qh = a.mxbuf + (size_t) (kvh * AT_GQA + warp) * AT_D;
+                        float y0, y1;
+                        at_norm_rope(__ldcg(qh + lane), __ldcg(qh + lane + 32), mx.qnorm, (float) pos, a.theta, lane, y0, y1);
+                        reinterpret_cast<float *>(&A.q[lane])[warp] = y0;
+                        reinterpret_cast<float *>(&A.q[lane + 32])[warp] = y1;
+                    } else if (warp == AT_GQA && t1 == seq_len) {
+                        const float * kh = a.mxbuf + LKB_HIDDEN + (size_t) kvh * AT_D;
+                        const float * vh = a.mxbuf + LKB_HIDDEN + AT_KVH * AT_D + (size_t) kvh * AT_D;
+                        float y0, y1;
+                        at_norm_rope(__ldcg(kh + lane), __ldcg(kh + lane + 32), mx.knorm, (float) pos, a.theta, lane, y0, y1);
+                        const size_t off = ((size_t) pos * AT_KVH + kvh) * AT_D;
+                        kc[off + lane] = __float2half(y0); kc[off + lane + 32] = __float2half(y1);
+                        vc[off + lane] = __float2half(__ldcg(vh + lane)); vc[off + lane + 32] = __float2half(__ldcg(vh + lane + 32));
+                        __threadfence();
+                    }
+                    __syncthreads();
+                    at_slice<2>(A, kc, vc, kvh, sp, t0, t1, a.part);
+                }
+                grid_arrive(a.bar, S);
+                if (tid == 0) mix_issue_out(S, mx, dn0, n_dn);              // the attention staging is idle again
+                if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 5u, a.spin_limit)) return;
+            }
+            // ---- M3: the mixer's 2048 outputs (attention: merged from the slices; conv: from the other CTAs),
+            //          quantised by every CTA; then this CTA's output-projection rows, added to the residual ----
+            {
+                float o[4]; int q[4]; float d[4], sm[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i = (warp + FUSED_WARPS * j) * 32 + lane;
+                    o[j] = is_attn ? at_combine(a.part, i >> 6, i & 63, seq_len) : __ldcg(a.mxbuf + i);
+                }
+                quant4(o, q, d, sm);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int b = warp + FUSED_WARPS * j;
+                    S.xq[b].qs[lane] = (int8_t) q[j];
+                    if (lane == 0) S.xq[b].ds = __floats2half2_rn(d[j], sm[j]);
+                }
+                __syncthreads();
+                int xq[2][8]; float d8[2], s8[2];
+                load_xregs<2>(S.xq, GU_BPR, lane, xq, d8, s8);
+                if (!mbar_wait(&S.mbar_mo, par)) { if (lane == 0) { atomicCAS(status, 0u, 500u + l); S.abort = 1; } }
+                else {
+                    for (int j = warp; j < n_dn; j += FUSED_WARPS) {
+                        const float acc = lkb_warp_sum(smem_row_partial<2>(S.dn_q + (size_t) j * GU_BPR * 16, S.dn_d + (size_t) j * GU_BPR,
+                                                                           GU_BPR, lane, xq, d8, s8));
+                        if (lane == 0) a.x[dn0 + j] = __fadd_rn(__ldcg(a.x + dn0 + j), acc);
+                    }
+                }
+            }
+            grid_arrive(a.bar, S);
+            if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 6u, a.spin_limit)) return;
+        }
 
         // ---- A: u = x*w; the 64 router CTAs produce their logit; arrive ----------
         FUSED_STAMP(0);
@@ -446,6 +633,13 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
             }
 #pragma unroll
             for (int j = 0; j < 4; ++j) nw[j] = L[l + 1].norm_w[(warp + FUSED_WARPS * j) * 32 + lane];
+            if constexpr (MIX) {
+                // gate|up staging is idle from here to the next layer's selection: the next mixer's input rows
+                if (tid == 0) mix_issue_in(S, a.mixers[l + 1], dn0, n_dn, qa0, qa1);
+                const float * an = a.mixers[l + 1].attn_norm;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) anw[j] = an[(warp + FUSED_WARPS * j) * 32 + lane];
+            }
         }
         if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 2u, a.spin_limit)) return;
         FUSED_STAMP(6);
@@ -522,6 +716,14 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
         grid_arrive(a.bar, S);
         if (l + 1 < a.n_layers && tid < (int) (sizeof(lkb_moe_layer) / 8))
             reinterpret_cast<unsigned long long *>(&S.ly)[tid] = reinterpret_cast<const unsigned long long *>(&L[l + 1])[tid];
+        if constexpr (MIX) {
+            if (l + 1 < a.n_layers) {
+                if (tid < (int) (sizeof(lkb_mixer_layer) / 8))
+                    reinterpret_cast<unsigned long long *>(&S.mx)[tid] = reinterpret_cast<const unsigned long long *>(&a.mixers[l + 1])[tid];
+                // down staging is idle until the next layer's selection: a conv mixer's output rows
+                if (tid == 0 && !a.mixers[l + 1].is_attn) mix_issue_out(S, a.mixers[l + 1], dn0, n_dn);
+            }
+        }
         if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 3u, a.spin_limit)) return;
     }
 
@@ -543,8 +745,10 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
 static int g_fused_ready = 0;
 
 int lkb_fused_init() {
-    const cudaError_t e = cudaFuncSetAttribute(k_moe_ffn_stack, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int) sizeof(FusedSmem));
+    cudaError_t e = cudaFuncSetAttribute(k_moe_ffn_stack<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int) sizeof(FusedSmem));
+    if (e != cudaSuccess) return -(int) e;
+    e = cudaFuncSetAttribute(k_moe_ffn_stack<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sizeof(FusedSmem));
     if (e != cudaSuccess) return -(int) e;
     g_fused_ready = 1;
     return LKB_OK;
@@ -570,7 +774,7 @@ static int fused_launch(FusedArgs & a, cudaStream_t st) {
     attr[0].id = cudaLaunchAttributeCooperative;
     attr[0].val.cooperative = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, k_moe_ffn_stack, a);
+    e = a.mixers ? cudaLaunchKernelEx(&cfg, k_moe_ffn_stack<true>, a) : cudaLaunchKernelEx(&cfg, k_moe_ffn_stack<false>, a);
     if (e != cudaSuccess) { (void) cudaGetLastError(); return -(int) e; }
     return LKB_OK;
 }
@@ -605,6 +809,21 @@ int lkb_moe_ffn_decode_stack(const lkb_moe_layer * layers_dev, int n_layers, int
     a.layers = layers_dev; a.n_layers = n_layers; a.x = x; a.idx_out = idx_out; a.w_out = w_out;
     if (next && next->w) { a.final_norm_w = next->w; a.out_h32 = next->h32; a.out_yq8 = reinterpret_cast<lkb_q8blk *>(next->yq8); a.out_ssq = next->ssq; }
     a.logits = scratch->logits; a.gu = scratch->gu; a.bar = scratch->sync; a.softmax = softmax;
+    return fused_launch(a, (cudaStream_t) st);
+}
+
+int lkb_decode_layers(const lkb_moe_layer * moe_dev, const lkb_mixer_layer * mixers_dev, int n_layers, float * x,
+                      const lkb_block_q8_1 * xq_first, const int * d_pos, float theta, const lkb_norm_prod_t * next,
+                      const lkb_moe_scratch * scratch, const lkb_step_scratch * step_scratch, lkb_stream_t st) {
+    if (!moe_dev || !mixers_dev || !scratch || !step_scratch || !xq_first || !d_pos) return LKB_ERR_NULL;
+    if (!step_scratch->mx || !step_scratch->part) return LKB_ERR_NULL;
+    if (!(theta > 1.0f)) return LKB_ERR_SHAPE;
+    FusedArgs a = {};
+    a.layers = moe_dev; a.n_layers = n_layers; a.x = x;
+    if (next && next->w) { a.final_norm_w = next->w; a.out_h32 = next->h32; a.out_yq8 = reinterpret_cast<lkb_q8blk *>(next->yq8); a.out_ssq = next->ssq; }
+    a.logits = scratch->logits; a.gu = scratch->gu; a.bar = scratch->sync; a.softmax = 0;
+    a.mixers = mixers_dev; a.xq_first = reinterpret_cast<const lkb_q8blk *>(xq_first); a.d_pos = d_pos; a.theta = theta;
+    a.mxbuf = step_scratch->mx; a.part = step_scratch->part;
     return fused_launch(a, (cudaStream_t) st);
 }
 

@@ -86,8 +86,8 @@ def make_full_model(n_layers=40, seed=1234, device="cuda", vocab=VOCAB, moe_laye
 
 
 class DecodeStep:
-    """One token per step(); moe_impl 'fused' = one persistent launch per MoE layer, 'kernels' = the reference's
-    five launches per MoE layer."""
+    """One token per step(); moe_impl 'mega' = all layers in one persistent launch (lkb_decode_layers), 'fused' =
+    one persistent launch per MoE layer, 'kernels' = the reference's five launches per MoE layer."""
 
     def __init__(self, model: Model, max_seq=4352, moe_impl="fused", device="cuda", pf_bytes=2 << 20):
         self.m, self.moe_impl, self.max_seq, self.pf_bytes = model, moe_impl, max_seq, pf_bytes
@@ -125,6 +125,23 @@ class DecodeStep:
         self._np_next = [api.norm_prod(w, None, self.xq, self.ssq) for w in nxt]
         per_moe = 1 if moe_impl == "fused" else 5
         self.launches_per_step = 2 + sum((5 if mx.is_attn else 3) for mx in model.mixers) + per_moe * n + 3
+        if moe_impl == "mega":
+            self.launches_per_step = 6
+            ci = ai = 0
+            descs = []
+            for mx in model.mixers:
+                if mx.is_attn:
+                    descs.append(api.mixer_layer_desc(mx, kc=self.kc[ai], vc=self.vc[ai]))
+                    ai += 1
+                else:
+                    descs.append(api.mixer_layer_desc(mx, hist=self.hist[ci]))
+                    ci += 1
+            self._mx_descs = descs
+            self.mixers_dev = api.layer_descs_to_device(descs)
+            self.moe_dev = api.layer_descs_to_device(self._descs)
+            self.mxbuf = torch.zeros(3072, **f32)
+            self._sscratch = api.step_scratch(self.mxbuf, self.part)
+            self._np_out = api.norm_prod(model.out_norm, None, self.xq, self.ssq)
 
     def fill_kv(self, upto, seed=5):
         """Pre-fill the KV caches with N(0,1) up to position `upto` and set the position there."""
@@ -145,6 +162,11 @@ class DecodeStep:
         m, bpr = self.m, H // 32
         api.k_embed_q6_K(*m.emb, self.d_token, H, self.x)
         api.k_rmsnorm_q8_1(self.x, m.mixers[0].attn_norm, H, 1e-5, None, None, self.xq)     # layer 0 only
+        if self.moe_impl == "mega":
+            api.decode_layers(self.moe_dev, self.mixers_dev, len(m.mixers), self.x, self.xq, self.d_pos, m.theta,
+                              self._np_out, self._scratch, self._sscratch)
+            self._tail()
+            return
         ci = ai = 0
         for i, (mx, l) in enumerate(zip(m.mixers, m.moe)):
             ssq = None if i == 0 else self.ssq             # layer 0's input is already normalised
@@ -172,6 +194,9 @@ class DecodeStep:
                              l.down_qs, self.idx, H, I // 32, self.pf_bytes)
                 api.k_moe_down_accum(l.down_qs, l.down_d, self.xq2, H, I // 32, H, I // 32, self.idx, self.w, self.x,
                                      self._np_next[i])
-        api.k_gemv_q6_K(*m.emb, self.xq, self.vocab, SBPR, self.logits_v, self.ssq, 1e-5)
+        self._tail()
+
+    def _tail(self):
+        api.k_gemv_q6_K(*self.m.emb, self.xq, self.vocab, SBPR, self.logits_v, self.ssq, 1e-5)
         api.k_argmax_part(self.logits_v, self.vocab, self.am_v, self.am_i)
         api.k_argmax_final(self.am_v, self.am_i, self.am_v.numel(), self.d_token, self.d_pos)

@@ -107,7 +107,7 @@ def test_step_variants_agree_and_advance(M, lkb):
     k_rows = host(ds.kc[0, pos0:pos0 + steps]).astype(np.float32)
     assert np.all(np.abs(k_rows).sum(axis=(1, 2)) > 0)     # every step appended a K row
     assert float(ds.kc[0, pos0 + steps].abs().sum().item()) == 0.0
-    for impl, graph in (("kernels", True), ("fused", False), ("fused", True)):
+    for impl, graph in (("kernels", True), ("fused", False), ("fused", True), ("mega", False), ("mega", True)):
         t, x, _ = _run(M, model, impl, graph, steps, pos0)
         assert t == ref_t, (impl, graph, t, ref_t)
         for a, b in zip(x, ref_x):
