@@ -176,18 +176,34 @@ __device__ __forceinline__ void at_slice(AtSmem<STAGES> & S, const __half * __re
     }
 }
 
-// Output (head, d) from the live slices' partials.  ref: src/kernels.cu:1562-1599
+// Output (head, d) from the live slices' partials: M = max m_s; L = sum l_s e_s; A = sum a_s e_s with
+// e_s = exp(m_s - M), both sums as fma chains over ascending s; result A / L.  All loads of a pass are issued
+// before the first is used (fixed trip count, predicated), so the merge costs two memory round trips.
+// ref: src/kernels.cu:1562-1599
 __device__ __forceinline__ float at_combine(const float * __restrict__ part, int head, int d, int seq_len) {
     const int nsl = at_slices(seq_len);
     const int chunk = at_chunk(seq_len, nsl);
+    const int nlive = min(nsl, (seq_len + chunk - 1) / chunk);
     const float * P = part + (size_t) head * LKB_ATTN_SPLIT * LKB_ATTN_PARTW;
+    float mv[LKB_ATTN_SPLIT], lv[LKB_ATTN_SPLIT], av[LKB_ATTN_SPLIT];
+#pragma unroll
+    for (int s = 0; s < LKB_ATTN_SPLIT; ++s) {
+        const bool live = s < nlive;
+        mv[s] = live ? __ldcg(P + s * LKB_ATTN_PARTW) : -1e30f;
+        lv[s] = live ? __ldcg(P + s * LKB_ATTN_PARTW + 1) : 0.0f;
+        av[s] = live ? __ldcg(P + s * LKB_ATTN_PARTW + 2 + d) : 0.0f;
+    }
     float M = -1e30f;
-    for (int s = 0; s < nsl && s * chunk < seq_len; ++s) M = fmaxf(M, __ldcg(P + s * LKB_ATTN_PARTW));
+#pragma unroll
+    for (int s = 0; s < LKB_ATTN_SPLIT; ++s) M = fmaxf(M, mv[s]);
     float L = 0.0f, A = 0.0f;
-    for (int s = 0; s < nsl && s * chunk < seq_len; ++s) {
-        const float e = __expf(__fsub_rn(__ldcg(P + s * LKB_ATTN_PARTW), M));
-        L = fmaf(__ldcg(P + s * LKB_ATTN_PARTW + 1), e, L);
-        A = fmaf(__ldcg(P + s * LKB_ATTN_PARTW + 2 + d), e, A);
+#pragma unroll
+    for (int s = 0; s < LKB_ATTN_SPLIT; ++s) {
+        if (s < nlive) {
+            const float e = __expf(__fsub_rn(mv[s], M));
+            L = fmaf(lv[s], e, L);
+            A = fmaf(av[s], e, A);
+        }
     }
     return __fdiv_rn(A, L);
 }

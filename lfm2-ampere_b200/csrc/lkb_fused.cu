@@ -45,6 +45,7 @@ struct FusedSmem {
     float  ssq[LKB_HIDDEN / 32];
     float  sel[LKB_N_EXPERTS];
     float  sig[LKB_N_EXPERTS];
+    alignas(16) unsigned key[LKB_N_EXPERTS];      // order-preserving integer image of sel
     float  dot[LKB_TOP_K][MAX_DN_ROWS];
     int    idx[LKB_TOP_K];
     float  wk[LKB_TOP_K];
@@ -191,11 +192,11 @@ __device__ __forceinline__ void load_xregs(const lkb_q8blk * xq, int bpr, int la
     }
 }
 
-// Optional phase timestamps (clock64 of thread 0) for tuning: [cta][layer][16].
+// Optional phase timestamps (clock64 of thread 0) for tuning: [cta][layer][32].
 static unsigned long long * g_fused_timing = nullptr;
 static int g_fused_absent_cta = -1;              // test hook, see lkb_debug_fused_absent_cta
 static unsigned g_fused_spin_limit = 0;          // 0: default
-#define FUSED_STAMP(slot) do { if (a.timing && tid == 0 && l < 4) a.timing[((size_t) cta * 4 + l) * 16 + (slot)] = clock64(); } while (0)
+#define FUSED_STAMP(slot) do { if (a.timing && tid == 0 && l < 4) a.timing[((size_t) cta * 4 + l) * 32 + (slot)] = clock64(); } while (0)
 
 
 // Four independent 32-element blocks quantised together: the same operations per block
@@ -394,6 +395,14 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
         if constexpr (MIX) {
             const lkb_mixer_layer & mx = S.mx;
             const bool is_attn = mx.is_attn != 0;
+            FUSED_STAMP(16);
+            // conv state of this CTA's channels, requested before anything waits
+            float2 cv_h = make_float2(0.0f, 0.0f); float cv_w0 = 0.0f, cv_w1 = 0.0f, cv_w2 = 0.0f;
+            if (!is_attn && tid < n_dn) {
+                const int ch = dn0 + tid;
+                cv_h = *reinterpret_cast<const float2 *>(mx.hist + 2 * ch);
+                cv_w0 = __ldg(mx.conv_w + 3 * ch); cv_w1 = __ldg(mx.conv_w + 3 * ch + 1); cv_w2 = __ldg(mx.conv_w + 3 * ch + 2);
+            }
             // ---- M0: the mixer's input activation: layer 0 arrives normalised and quantised; later layers
             //          quantise raw u = x * attn_norm_w and carry 1/rms into the consumer (S.inv) ----
             if (l == 0) {
@@ -406,6 +415,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
                 fused_load_u(S, a.x, anw, xv, uv);
                 fused_quant_u(S, xv, uv);
             }
+            FUSED_STAMP(17);
             // ---- M1: input projection rows of this CTA (staged a phase ago) ----
             {
                 int xq[2][8]; float d8[2], s8[2];
@@ -430,15 +440,16 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
                     if (tid < n_dn) {
                         const int ch = dn0 + tid;
                         const float bx = __fmul_rn(mixv[tid], mixv[2 * n_dn + tid]);
-                        const float2 h = *reinterpret_cast<const float2 *>(mx.hist + 2 * ch);
-                        const float conv = fmaf(bx, mx.conv_w[3 * ch + 2], fmaf(h.y, mx.conv_w[3 * ch + 1], __fmul_rn(h.x, mx.conv_w[3 * ch])));
-                        *reinterpret_cast<float2 *>(mx.hist + 2 * ch) = make_float2(h.y, bx);
+                        const float conv = fmaf(bx, cv_w2, fmaf(cv_h.y, cv_w1, __fmul_rn(cv_h.x, cv_w0)));
+                        *reinterpret_cast<float2 *>(mx.hist + 2 * ch) = make_float2(cv_h.y, bx);
                         a.mxbuf[ch] = __fmul_rn(mixv[n_dn + tid], conv);
                     }
                 }
             }
+            FUSED_STAMP(18);
             grid_arrive(a.bar, S);
             if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 4u, a.spin_limit)) return;
+            FUSED_STAMP(19);
             const int seq_len = pos + 1;
             if (is_attn) {
                 // ---- M2: one slice of one KV head per CTA; the query heads' norm + rotation are redone by every
@@ -468,18 +479,25 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
                     __syncthreads();
                     at_slice<2>(A, kc, vc, kvh, sp, t0, t1, a.part);
                 }
+                FUSED_STAMP(20);
                 grid_arrive(a.bar, S);
-                if (tid == 0) mix_issue_out(S, mx, dn0, n_dn);              // the attention staging is idle again
+                if (tid == 32) mix_issue_out(S, mx, dn0, n_dn);             // the attention staging is idle again
                 if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 5u, a.spin_limit)) return;
+                FUSED_STAMP(21);
+                // merge of the slices: one head per CTA (every CTA reading every partial would cost 150 KB of
+                // L2 sectors per CTA), published through mxbuf like a conv output
+                if (cta < AT_HEADS && tid < AT_D) a.mxbuf[cta * AT_D + tid] = at_combine(a.part, cta, tid, seq_len);
+                grid_arrive(a.bar, S);
+                if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 7u, a.spin_limit)) return;
+                FUSED_STAMP(25);
             }
-            // ---- M3: the mixer's 2048 outputs (attention: merged from the slices; conv: from the other CTAs),
-            //          quantised by every CTA; then this CTA's output-projection rows, added to the residual ----
+            // ---- M3: the mixer's 2048 outputs, written by their owner CTAs, quantised by every CTA; then this CTA's output-projection rows, added to the residual ----
             {
                 float o[4]; int q[4]; float d[4], sm[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int i = (warp + FUSED_WARPS * j) * 32 + lane;
-                    o[j] = is_attn ? at_combine(a.part, i >> 6, i & 63, seq_len) : __ldcg(a.mxbuf + i);
+                    o[j] = __ldcg(a.mxbuf + i);
                 }
                 quant4(o, q, d, sm);
 #pragma unroll
@@ -489,6 +507,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
                     if (lane == 0) S.xq[b].ds = __floats2half2_rn(d[j], sm[j]);
                 }
                 __syncthreads();
+                FUSED_STAMP(22);
                 int xq[2][8]; float d8[2], s8[2];
                 load_xregs<2>(S.xq, GU_BPR, lane, xq, d8, s8);
                 if (!mbar_wait(&S.mbar_mo, par)) { if (lane == 0) { atomicCAS(status, 0u, 500u + l); S.abort = 1; } }
@@ -500,8 +519,10 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
                     }
                 }
             }
+            FUSED_STAMP(23);
             grid_arrive(a.bar, S);
             if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 6u, a.spin_limit)) return;
+            FUSED_STAMP(24);
         }
 
         // ---- A: u = x*w; the 64 router CTAs produce their logit; arrive ----------
@@ -527,21 +548,24 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
         if (cta < LKB_N_EXPERTS && tid == 0) a.logits[cta] = __fmul_rn(S.sel[0], S.inv);
         FUSED_STAMP(2);
         grid_arrive(a.bar, S);
+        // static data of the selection, fetched while the barrier completes
+        float rb0 = 0.0f, rb1 = 0.0f;
+        if (warp == 0 && ly.rbias) { rb0 = __ldg(ly.rbias + lane); rb1 = __ldg(ly.rbias + lane + 32); }
         if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 1u, a.spin_limit)) return;
         FUSED_STAMP(3);
 
         // ---- C: selection (every CTA, warp 0; the softmax gate takes the 64-thread path) ----
         if (!a.softmax) {
             if (warp == 0) {
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int e = lane + 32 * h;
-                    const float lg = __ldcg(a.logits + e);
-                    const float g = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-lg)));
-                    S.sig[e] = g;
-                    S.sel[e] = __fadd_rn(g, ly.rbias ? ly.rbias[e] : 0.0f);
-                }
-                __syncwarp();
+                // both logits are requested before either is used: a shared-memory store between two global
+                // loads would serialise them (the compiler cannot prove the pointers distinct)
+                const float lg0 = __ldcg(a.logits + lane), lg1 = __ldcg(a.logits + lane + 32);
+                const float g0 = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-lg0)));
+                const float g1 = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-lg1)));
+                S.sig[lane] = g0; S.sig[lane + 32] = g1;
+                const float s0 = __fadd_rn(g0, rb0), s1 = __fadd_rn(g1, rb1);
+                S.sel[lane] = s0; S.sel[lane + 32] = s1;
+                S.key[lane] = lkb_orderable(s0); S.key[lane + 32] = lkb_orderable(s1);
             }
         } else {
             if (tid < LKB_N_EXPERTS) S.sel[tid] = __ldcg(a.logits + tid);
@@ -561,26 +585,48 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
                 pn = __fdiv_rn(p, den);
             }
             __syncthreads();
-            if (tid < LKB_N_EXPERTS) { S.sig[tid] = pn; S.sel[tid] = __fadd_rn(pn, ly.rbias ? ly.rbias[tid] : 0.0f); }
-            __syncthreads();
+            if (tid < LKB_N_EXPERTS) {
+                const float sv = __fadd_rn(pn, ly.rbias ? ly.rbias[tid] : 0.0f);
+                S.sig[tid] = pn; S.sel[tid] = sv; S.key[tid] = lkb_orderable(sv);
+            }
         }
         FUSED_STAMP(8);
-        if (warp == 0) {
-            int ord[LKB_TOP_K]; float wv[LKB_TOP_K];
-            lkb_router_select(S.sel, S.sig, lane, ord, wv);
-            if (lane == 0) {
+        // Top-4 by rank counting over the whole CTA: expert e's rank is the number of experts that beat it
+        // ("greater value wins, equal value -> lower index", ref: src/kernels.cuh:515-541); the experts of rank
+        // 0..3 are the selection, in rank order.  Thread t compares expert t>>3 with experts (t&7)*8 .. +7 and the
+        // eight partial counts are summed by shuffles: no serial rounds.  Same winners as lkb_router_select.
+        __syncthreads();                                            // keys of all 64 experts are in S.key
+        {
+            const int e = tid >> 3, j0 = (tid & 7) * 8;
+            const unsigned ke = S.key[e];
+            const uint4 ka = *reinterpret_cast<const uint4 *>(&S.key[j0]), kb = *reinterpret_cast<const uint4 *>(&S.key[j0 + 4]);
+            const unsigned kj[8] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
+            int cnt = 0;
 #pragma unroll
-                for (int k = 0; k < LKB_TOP_K; ++k) { S.idx[k] = ord[k]; S.wk[k] = wv[k]; }
-                if (cta == 0) {
+            for (int i = 0; i < 8; ++i) cnt += (kj[i] > ke || (kj[i] == ke && j0 + i < e)) ? 1 : 0;
+            cnt += __shfl_xor_sync(LKB_FULL, cnt, 1);
+            cnt += __shfl_xor_sync(LKB_FULL, cnt, 2);
+            cnt += __shfl_xor_sync(LKB_FULL, cnt, 4);
+            if ((tid & 7) == 0 && cnt < LKB_TOP_K) S.idx[cnt] = e;
+        }
+        __syncthreads();
+        FUSED_STAMP(13);
+        if (warp == 0 && lane == 0) {
+            // weights: unbiased gate values of the winners, renormalised (sum clamped), in rank order
+            float wv[LKB_TOP_K], wsum = 0.0f;
 #pragma unroll
-                    for (int k = 0; k < LKB_TOP_K; ++k) {
-                        if (a.idx_out) a.idx_out[l * 4 + k] = ord[k];
-                        if (a.w_out) a.w_out[l * 4 + k] = wv[k];
-                    }
+            for (int k = 0; k < LKB_TOP_K; ++k) { wv[k] = S.sig[S.idx[k]]; wsum = __fadd_rn(wsum, wv[k]); }
+            if (wsum < LKB_TOPK_GUARD) wsum = LKB_TOPK_GUARD;
+#pragma unroll
+            for (int k = 0; k < LKB_TOP_K; ++k) { wv[k] = __fdiv_rn(wv[k], wsum); S.wk[k] = wv[k]; }
+            if (cta == 0) {
+#pragma unroll
+                for (int k = 0; k < LKB_TOP_K; ++k) {
+                    if (a.idx_out) a.idx_out[l * 4 + k] = S.idx[k];
+                    if (a.w_out) a.w_out[l * 4 + k] = wv[k];
                 }
             }
         }
-        __syncthreads();
         FUSED_STAMP(9);
         // ---- D: request every weight row of the layer, one issuing lane per chunk ---
         if (lane == 0) {
@@ -635,7 +681,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
             for (int j = 0; j < 4; ++j) nw[j] = L[l + 1].norm_w[(warp + FUSED_WARPS * j) * 32 + lane];
             if constexpr (MIX) {
                 // gate|up staging is idle from here to the next layer's selection: the next mixer's input rows
-                if (tid == 0) mix_issue_in(S, a.mixers[l + 1], dn0, n_dn, qa0, qa1);
+                if (tid == 32) mix_issue_in(S, a.mixers[l + 1], dn0, n_dn, qa0, qa1);   // not thread 0: it polls the barrier
                 const float * an = a.mixers[l + 1].attn_norm;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) anw[j] = an[(warp + FUSED_WARPS * j) * 32 + lane];
@@ -721,7 +767,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
                 if (tid < (int) (sizeof(lkb_mixer_layer) / 8))
                     reinterpret_cast<unsigned long long *>(&S.mx)[tid] = reinterpret_cast<const unsigned long long *>(&a.mixers[l + 1])[tid];
                 // down staging is idle until the next layer's selection: a conv mixer's output rows
-                if (tid == 0 && !a.mixers[l + 1].is_attn) mix_issue_out(S, a.mixers[l + 1], dn0, n_dn);
+                if (tid == 32 && !a.mixers[l + 1].is_attn) mix_issue_out(S, a.mixers[l + 1], dn0, n_dn);
             }
         }
         if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 3u, a.spin_limit)) return;
@@ -781,7 +827,7 @@ static int fused_launch(FusedArgs & a, cudaStream_t st) {
 
 extern "C" {
 
-// Tuning hook (not part of the public header): device buffer of [#CTAs][4 layers][16] clock64 stamps, or null.
+// Tuning hook (not part of the public header): device buffer of [#CTAs][4 layers][32] clock64 stamps, or null.
 __attribute__((visibility("default"))) int lkb_debug_fused_timing(unsigned long long * buf) { g_fused_timing = buf; return LKB_OK; }
 
 // Test hook (not in the public header): the next launches run WITHOUT CTA `cta` (it returns at once), so every
