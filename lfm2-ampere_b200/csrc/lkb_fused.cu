@@ -93,13 +93,15 @@ __device__ __forceinline__ unsigned ld_acquire(const unsigned * p) {
 // Grid barrier over gridDim.x CTAs on a monotonically increasing counter (zeroed by
 // the launcher), split into arrive and wait so that independent work can sit between
 // them.  Both are called by every thread; thread 0 does the global traffic.
+// Every CTA executes the same sequence of barriers, so the k-th barrier completes when the
+// counter reaches (k+1)*gridDim.x: the arrival is a fire-and-forget reduction (no returned
+// ticket to wait for) and the waiter starts polling at once.
 // wait returns false if it expired or another CTA reported a fault.
 __device__ __forceinline__ void grid_arrive(unsigned * bar, FusedSmem & S) {
     __syncthreads();                                   // this CTA's global writes are issued
     if (threadIdx.x == 0) {
-        __threadfence();
-        const unsigned ticket = atomicAdd(bar, 1u);
-        S.bar_target = (ticket / gridDim.x + 1u) * gridDim.x;
+        S.bar_target += gridDim.x;
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" :: "l"(bar) : "memory");
     }
 }
 __device__ __forceinline__ bool grid_wait(unsigned * bar, unsigned * status, FusedSmem & S, unsigned code,
@@ -350,6 +352,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
 
     if (tid == 0) {
         S.abort = 0;
+        S.bar_target = 0u;
         for (int i = 0; i < N_GU_CH; ++i) mbar_init(&S.mbar_gu[i], 1);
         for (int i = 0; i < N_DN_CH; ++i) mbar_init(&S.mbar_dn[i], 1);
         mbar_init(&S.mbar_rt, 1);
