@@ -32,14 +32,20 @@ int main(void) {
     printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(lkb_pf_act), sizeof(lkb_norm_prod_t), sizeof(lkb_pf_gemm),
            offsetof(lkb_pf_gemm, exp_stride), offsetof(lkb_pf_gemm, aqs), offsetof(lkb_pf_gemm, a_shift),
            offsetof(lkb_pf_gemm, okb), sizeof(lkb_block_q8_1));
+    printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(lkb_moe_layer), offsetof(lkb_moe_layer, softmax), sizeof(lkb_moe_scratch),
+           sizeof(lkb_mixer_layer), offsetof(lkb_mixer_layer, attn_norm), offsetof(lkb_mixer_layer, kc),
+           offsetof(lkb_mixer_layer, out_d), sizeof(lkb_step_scratch));
     return 0;
 }''')
     exe = tmp_path / "layout"
     subprocess.run(["gcc", "-I", str(lkb.ROOT / "include"), str(src), "-o", str(exe)], check=True)
     got = [int(v) for v in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
     G = lkb.PfGemm
+    X = lkb.MixerLayer
     assert got == [ctypes.sizeof(lkb.PfAct), ctypes.sizeof(lkb.NormProd), ctypes.sizeof(G), G.exp_stride.offset,
-                   G.aqs.offset, G.a_shift.offset, G.okb.offset, 36]
+                   G.aqs.offset, G.a_shift.offset, G.okb.offset, 36,
+                   ctypes.sizeof(lkb.MoeLayer), lkb.MoeLayer.softmax.offset, ctypes.sizeof(lkb.MoeScratch),
+                   ctypes.sizeof(X), X.attn_norm.offset, X.kc.offset, X.out_d.offset, ctypes.sizeof(lkb.StepScratch)]
 
 
 def test_compute_calls_fail_loudly_without_init(lkb):

@@ -118,3 +118,31 @@ def test_step_variants_agree_and_advance(M, lkb):
     finally:
         lkb.set_pdl(False)
     assert t == ref_t and all(np.array_equal(a, b) for a, b in zip(x, ref_x))
+
+
+def test_new_entry_points_reject_bad_arguments(M, lkb):
+    """Null pointers and shape preconditions come back as LkbError (status codes), never as a fault."""
+    f = torch.zeros(4096, device="cuda")
+    i = torch.zeros(4, dtype=torch.int32, device="cuda")
+    u8 = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    with pytest.raises(lkb.LkbError):
+        lkb.k_gemv_q6_K(None, u8, u8, u8, u8, 16, 8, f)
+    with pytest.raises(lkb.LkbError):
+        lkb.k_gemv_q6_K(u8, u8, u8, u8, u8, 0, 8, f)
+    with pytest.raises(lkb.LkbError):
+        lkb.k_argmax_part(f, 0, f, i)
+    with pytest.raises(lkb.LkbError):
+        lkb.k_embed_q6_K(u8, u8, u8, u8, i, 100, f)            # n % 256 != 0
+    with pytest.raises(lkb.LkbError):
+        lkb.k_attn_split(None, u8, u8, i, f)
+    with pytest.raises(lkb.LkbError):
+        lkb.k_attn_combine(f, i, None, None)                   # nothing to write
+    with pytest.raises(lkb.LkbError):
+        lkb.k_qk_norm_rope(f, f, f, f, f, i, u8, u8, theta=0.5)
+    model = M.make_full_model(n_layers=1, seed=1, vocab=2048)
+    ds = M.DecodeStep(model, max_seq=16, moe_impl="mega")
+    with pytest.raises(lkb.LkbError):
+        lkb.decode_layers(ds.moe_dev, None, 1, ds.x, ds.xq, ds.d_pos, 1e6, None, ds._scratch, ds._sscratch)
+    with pytest.raises(lkb.LkbError):
+        lkb.decode_layers(ds.moe_dev, ds.mixers_dev, 0, ds.x, ds.xq, ds.d_pos, 1e6, None, ds._scratch, ds._sscratch)
+    torch.cuda.synchronize()
