@@ -380,6 +380,26 @@ int lkb_qk_norm_rope(float * qf, float * kf, const float * vf, const float * qn,
 int lkb_shortconv(const float * bcx, int t, const float * conv_w, float * hist, float * y, lkb_block_q8_1 * yq8, int n,
                   lkb_stream_t st);
 
+/* ---- sequence mixers of batched prefill (a chunk of m tokens at positions P .. P+m-1) -------------------
+ * With lkb_pf_gemm_dense for the in / out / q|k|v / output projections they complete a full-model prefill
+ * chunk.  The per-token kernels evaluate their decode twins' arithmetic: a chunk leaves the same conv history,
+ * KV rows and activations as m decode steps.
+ * lkb_pf_embed: x[t][0..n) = dequantised Q6_K row toks[t].                         ref: src/prefill.cu:856-868
+ * lkb_pf_conv: Y = in_proj output [m][6144] (B | C | X); planar Q8_1 rows of C * conv into a; hist is read.
+ * lkb_pf_conv_hist: the two-tap history after the chunk (run after lkb_pf_conv).   ref: src/prefill.cu:937-970
+ * lkb_pf_qknr: Y = q|k|v output [m][3072]; per-head RMSNorm + NEOX RoPE (base theta; the reference compiles in
+ *   1e7); Q leaves as fp16 [m][2048] pre-scaled by 1/8, K and V are appended to the cache.  ref: src/prefill.cu:975-1016
+ * lkb_pf_attn: causal GQA attention of the chunk's queries qh over cache positions 0 .. P+m-1, o = fp32 [m][2048].
+ *   Definition: float64 softmax over the fp16 inputs; P is rounded to fp16 before the P V product, as in the
+ *   reference (gate 4e-3 absolute, ref: tests/test_prefill.cu:244-289).              ref: src/prefill.cu:1029-1268 */
+int lkb_pf_embed(const void * ql, const void * qh, const void * sc, const void * d, const int * toks, float * x, int n, int m,
+                 lkb_stream_t st);
+int lkb_pf_conv(const float * Y, const float * cw, const float * hist, lkb_pf_act a, int m, lkb_stream_t st);
+int lkb_pf_conv_hist(const float * Y, int m, float * hist, lkb_stream_t st);
+int lkb_pf_qknr(const float * Y, const float * qn, const float * kn, int P, void * qh, void * kc, void * vc, int m, float theta,
+                lkb_stream_t st);
+int lkb_pf_attn(const void * qh, int m, int P, const void * kc, const void * vc, float * o, lkb_stream_t st);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

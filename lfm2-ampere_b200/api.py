@@ -24,6 +24,7 @@ __all__ = [
     "k_gemv_q6_K", "k_argmax_part", "k_argmax_final", "k_embed_q6_K", "gemv_q6_K_status",
     "k_attn_split", "k_attn_combine", "k_qk_norm_rope", "k_shortconv", "ATTN_SPLIT", "ATTN_PARTW",
     "mixer_layer_desc", "step_scratch", "decode_layers",
+    "k_pf_embed", "k_pf_conv", "k_pf_conv_hist", "k_pf_qknr", "k_pf_attn",
 ]
 
 
@@ -340,3 +341,24 @@ def step_scratch(mx, part):
 def decode_layers(moe_dev, mixers_dev, n_layers, x, xq_first, d_pos, theta, next_np, scratch, sscratch):
     check(lib.lkb_decode_layers(ptr(moe_dev), ptr(mixers_dev), n_layers, ptr(x), ptr(xq_first), ptr(d_pos), theta,
                                 _np(next_np), C.byref(scratch), C.byref(sscratch), stream()), "decode_layers")
+
+
+# ------------------------------------------------------------ prefill mixers --
+def k_pf_embed(ql, qh, sc, d, toks, x, n, m):
+    check(lib.lkb_pf_embed(ptr(ql), ptr(qh), ptr(sc), ptr(d), ptr(toks), ptr(x), n, m, stream()), "k_pf_embed")
+
+
+def k_pf_conv(Y, cw, hist, a, m):
+    check(lib.lkb_pf_conv(ptr(Y), ptr(cw), ptr(hist), a, m, stream()), "k_pf_conv")
+
+
+def k_pf_conv_hist(Y, m, hist):
+    check(lib.lkb_pf_conv_hist(ptr(Y), m, ptr(hist), stream()), "k_pf_conv_hist")
+
+
+def k_pf_qknr(Y, qn, kn, P, qh, kc, vc, m, theta=1e7):
+    check(lib.lkb_pf_qknr(ptr(Y), ptr(qn), ptr(kn), P, ptr(qh), ptr(kc), ptr(vc), m, theta, stream()), "k_pf_qknr")
+
+
+def k_pf_attn(qh, m, P, kc, vc, o):
+    check(lib.lkb_pf_attn(ptr(qh), m, P, ptr(kc), ptr(vc), ptr(o), stream()), "k_pf_attn")

@@ -13,6 +13,7 @@
 #define AT_G       32                       // tokens per warp group
 #define AT_ROW     72                       // halfs per staged row: 64 + 8 padding (144 B: conflict-free 16-B reads)
 #define AT_SCALE   0.125f                   // 1/sqrt(64), exact.  ref: src/kernels.cuh:24
+#define AT_QKV     (LKB_HIDDEN + 2 * AT_KVH * AT_D)   // 3072: one token's q | k | v
 
 __host__ __device__ __forceinline__ int at_slices(int seq_len) {
     int s = (seq_len + 255) / 256;

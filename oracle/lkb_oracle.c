@@ -828,3 +828,34 @@ ORC_API void orc_attn_decode_f64(const float * q, const uint16_t * kc, const uin
         free(s);
     }
 }
+
+/* Causal GQA attention of a chunk in float64 over the fp16 inputs (tests/test_prefill.cu:259-286): query t
+ * (fp16 bits, [m][2048], already carrying the 1/8 scale) at position P + t sees keys 0 .. P + t. */
+ORC_API void orc_pf_attn_f64(const uint16_t * qh, int m, int P, const uint16_t * kc, const uint16_t * vc, double * out) {
+#pragma omp parallel for collapse(2) schedule(dynamic, 4)
+    for (int t = 0; t < m; ++t)
+        for (int h = 0; h < 32; ++h) {
+            const int kv = h / 4, qp = P + t;
+            double * sc = (double *) malloc((size_t) (qp + 1) * sizeof(double));
+            double q[64];
+            for (int d = 0; d < 64; ++d) q[d] = (double) orc_f16_to_f32(qh[(size_t) t * 2048 + h * 64 + d]);
+            double mx = -1e300;
+            for (int j = 0; j <= qp; ++j) {
+                const uint16_t * k = kc + ((size_t) j * 8 + kv) * 64;
+                double s = 0.0;
+                for (int d = 0; d < 64; ++d) s += q[d] * (double) orc_f16_to_f32(k[d]);
+                sc[j] = s;
+                if (s > mx) mx = s;
+            }
+            double l = 0.0, acc[64];
+            for (int d = 0; d < 64; ++d) acc[d] = 0.0;
+            for (int j = 0; j <= qp; ++j) {
+                const double p = exp(sc[j] - mx);
+                l += p;
+                const uint16_t * v = vc + ((size_t) j * 8 + kv) * 64;
+                for (int d = 0; d < 64; ++d) acc[d] += p * (double) orc_f16_to_f32(v[d]);
+            }
+            for (int d = 0; d < 64; ++d) out[(size_t) t * 2048 + h * 64 + d] = acc[d] / l;
+            free(sc);
+        }
+}

@@ -515,3 +515,21 @@ def attn_decode_f64(q, kc, vc, seq):
     out = np.empty(32 * 64, np.float64)
     _lib.orc_attn_decode_f64(_p(q, _f32p), _p(kc, _u16p), _p(vc, _u16p), seq, _p(out, _f64p))
     return out
+
+
+def pf_attn_f64(qh, m, P, kc, vc):
+    """Causal chunk attention in float64 over fp16 bit patterns; returns [m, 2048]."""
+    qh, kc, vc = (_c(a, np.uint16).reshape(-1) for a in (qh, kc, vc))
+    out = np.empty((m, 2048), np.float64)
+    _lib.orc_pf_attn_f64(_p(qh, _u16p), m, P, _p(kc, _u16p), _p(vc, _u16p), _p(out, _f64p))
+    return out
+
+
+def pf_conv(Y, conv_w, hist):
+    """Chunk convolution = the decode step applied token by token.  Y [m, 6144]; returns (v [m, 2048], hist')."""
+    Y = _c(Y, np.float32)
+    h = _c(hist, np.float32).reshape(-1).copy()
+    out = np.empty((Y.shape[0], 2048), np.float32)
+    for t in range(Y.shape[0]):
+        out[t], h = shortconv(Y[t], conv_w, h)
+    return out, h
