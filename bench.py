@@ -536,6 +536,54 @@ def run_ours(args):
                                                 "against %.3f GB here" % (nbytes / 1e9)} if (ctx == 4096 and args.layers == 40) else None}
         del fm
 
+    # ---------------------------------------------------------------- full-model prefill chunk
+    fpf = None
+    if not args.no_full and not args.no_prefill and world == 1:
+        model_mod = importlib.import_module("lfm2-ampere_b200.model")
+        m = args.pf_tokens
+        fm = model_mod.make_full_model(n_layers=args.layers, seed=4321, moe_layers=layers)
+        stt = model_mod.DecodeStep(fm, max_seq=m + 8, moe_impl="kernels")
+        pc = model_mod.PrefillChunk(fm, m, stt)
+        tok_hm = torch.randint(0, 65536, (m,), dtype=torch.int32).pin_memory()
+        nxt_h = torch.zeros(1, dtype=torch.int32).pin_memory()
+        pc.toks.copy_(tok_hm)
+
+        def fpf_step(e2e=False):
+            if e2e:
+                pc.toks.copy_(tok_hm, non_blocking=True)
+            stt.hist.zero_()
+            pc.step(P=0)
+            if e2e:                                            # the new position comes back to the host
+                nxt_h.copy_(stt.d_pos, non_blocking=True)
+                st.synchronize()
+        fpf_step()
+        torch.cuda.synchronize()
+        ev0.record()
+        for _ in range(args.pf_steps):
+            fpf_step()
+        ev1.record()
+        torch.cuda.synchronize()
+        t_pf = ev0.elapsed_time(ev1) / args.pf_steps
+        ev0.record()
+        for _ in range(args.pf_steps):
+            fpf_step(e2e=True)
+        ev1.record()
+        torch.cuda.synchronize()
+        t_pf_e2e = ev0.elapsed_time(ev1) / args.pf_steps
+        if lkb.lib.lkb_pf_gemm_status() != 0:
+            raise SystemExit("full-model prefill: a bounded wait of the tensor-core GEMM expired")
+        attn_macs = sum(mx.is_attn for mx in fm.mixers) * 32 * 64 * 2 * (m * (m + 1) // 2)
+        fpf = {"metric": "%dk prefill tok/s, full model chunk" % (m // 1024), "tokens": m, "value": m / (t_pf * 1e-3), "unit": UNIT,
+               "ms_per_step": t_pf,
+               "workload": "embedding rows -> %d layers [dense Q4_0 x Q8_1 GEMMs + chunk conv | causal GQA flash attention] + "
+                           "MoE grouped GEMMs; KV caches and conv histories left ready for decoding" % args.layers,
+               "e2e": {"value": m / (t_pf_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 4 * m, "d2h_bytes_per_step": 4},
+               "gemm_tmacs": pc.macs_per_step() / (t_pf * 1e-3) / 1e12, "attention_tmacs_total": attn_macs / 1e12,
+               "gpu_launches_per_step": pc.launches_per_step,
+               "published_reference": {"value": 21188.0, "unit": UNIT, "hardware": "RTX 3090 Ti, real weights, 4096 tokens",
+                                       "ratio": (m / (t_pf * 1e-3)) / 21188.0} if (m == 4096 and args.layers == 40) else None}
+        del pc, stt, fm
+
     if rank == 0:
         clocks = sampler.stop()          # sampled over every timed region above (decode, e2e, prefill, lm_head, full step)
         cb, _ = cpu_baseline() if world == 1 and not args.no_cpu else (None, None)
@@ -552,7 +600,7 @@ def run_ours(args):
                           "decode_impl": args.decode_impl, "cuda_graph": use_graph, "pdl": (not args.no_pdl) and not fused},
                "e2e": {"value": e2e_tok_s, "unit": UNIT, "h2d_bytes_per_step": H * 4, "d2h_bytes_per_step": H * 4},
                "gpu_launches": n_launch,
-               "roofline": roofline, "cpu_baseline": cb, "clocks": clocks, "prefill": pf, "lm_head": lm, "full_step": full}
+               "roofline": roofline, "cpu_baseline": cb, "clocks": clocks, "prefill": pf, "lm_head": lm, "full_step": full, "full_prefill": fpf}
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()

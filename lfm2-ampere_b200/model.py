@@ -200,3 +200,66 @@ class DecodeStep:
         api.k_gemv_q6_K(*self.m.emb, self.xq, self.vocab, SBPR, self.logits_v, self.ssq, 1e-5)
         api.k_argmax_part(self.logits_v, self.vocab, self.am_v, self.am_i)
         api.k_argmax_final(self.am_v, self.am_i, self.am_v.numel(), self.d_token, self.d_pos)
+
+
+class PrefillChunk:
+    """Full-model batched prefill of one chunk of m tokens at positions P .. P+m-1: the host-side call sequence of
+    the reference's pf_chunk() (ref: src/engine.cu:1024-1250) over the C ABI.  Sequence mixers run as dense
+    Q4_0 x Q8_1 GEMMs (tcgen05) around the chunk kernels of lkb_pfmix.cu; the MoE FFN is prefill.PrefillStack's
+    layer body, whose fused combine + norm hands the next layer its quantised activation.  Leaves the conv
+    histories and KV caches of `state` (a DecodeStep) exactly where decoding continues from."""
+
+    def __init__(self, model: Model, m: int, state: "DecodeStep", device="cuda"):
+        from .prefill import PrefillStack
+        self.m_, self.model, self.state = m, model, state
+        self.moe = PrefillStack(model.moe, m, device)
+        f32 = dict(dtype=torch.float32, device=device)
+        self.X, self.a_qs, self.a_sc, self.inv = self.moe.X, self.moe.a_qs, self.moe.a_sc, self.moe.inv
+        self.a = self.moe.a
+        self.Y = torch.zeros(m, CONV_ROWS, **f32)                       # in_proj output, or q|k|v (first 3072 columns' worth)
+        self.qh = torch.zeros(m, H, dtype=torch.float16, device=device)
+        self.o = torch.zeros(m, H, **f32)
+        self.toks = torch.zeros(m, dtype=torch.int32, device=device)
+        n_attn = sum(mx.is_attn for mx in model.mixers)
+        self.launches_per_step = 1 + 1 + sum((6 if mx.is_attn else 4) for mx in model.mixers) + 9 * len(model.mixers)
+
+    def macs_per_step(self):
+        m, n = self.m_, len(self.model.mixers)
+        n_attn = sum(mx.is_attn for mx in self.model.mixers)
+        dense = (n - n_attn) * (CONV_ROWS + H) * H + n_attn * (H + 2 * N_KV * HEAD_DIM + H) * H
+        return m * dense + self.moe.macs_per_step()
+
+    def step(self, P=0):
+        m, md, st, moe = self.m_, self.model, self.state, self.moe
+        bpr = H // 32
+        api.k_pf_embed(*md.emb, self.toks, self.X, H, m)
+        norm_ready = False
+        ci = ai = 0
+        n = len(md.mixers)
+        for i, mx in enumerate(md.mixers):
+            if not norm_ready:
+                api.k_pf_norm(self.X, mx.attn_norm, 1 if i == 0 else 0, self.a, self.inv, None, m)
+            scale = None if i == 0 else self.inv
+            if mx.is_attn:
+                g = api.make_pf_gemm([mx.wq, mx.wk, mx.wv], [H, H + N_KV * HEAD_DIM, H + 2 * N_KV * HEAD_DIM],
+                                     H + 2 * N_KV * HEAD_DIM, bpr, self.a_qs, self.a_sc, ntok=m, scale=scale,
+                                     out=self.Y, out_ld=H + 2 * N_KV * HEAD_DIM)
+                api.pf_gemm_dense(g)
+                api.k_pf_qknr(self.Y, mx.qnorm, mx.knorm, P, self.qh, st.kc[ai], st.vc[ai], m, md.theta)
+                api.k_pf_attn(self.qh, m, P, st.kc[ai], st.vc[ai], self.o)
+                api.k_pf_quant_rows(self.o, H, bpr, self.a, m)
+                ai += 1
+            else:
+                g = api.make_pf_gemm([(mx.in_qs, mx.in_d)], [CONV_ROWS] * 3, CONV_ROWS, bpr, self.a_qs, self.a_sc, ntok=m,
+                                     scale=scale, out=self.Y, out_ld=CONV_ROWS)
+                api.pf_gemm_dense(g)
+                api.k_pf_conv(self.Y, mx.conv_w, st.hist[ci], self.a, m)
+                api.k_pf_conv_hist(self.Y, m, st.hist[ci])
+                ci += 1
+            og = api.make_pf_gemm([(mx.out_qs, mx.out_d)], [H] * 3, H, bpr, self.a_qs, self.a_sc, ntok=m,
+                                  out=self.X, out_ld=H, add=1)
+            api.pf_gemm_dense(og)
+            nxt = md.mixers[i + 1].attn_norm if i + 1 < n else md.out_norm
+            moe.layer(i, next_norm_w=nxt, next_act=(self.a, self.inv))
+            norm_ready = True
+        st.d_pos.fill_(P + m)

@@ -46,7 +46,10 @@ class PrefillStack:
         self.an = api.pf_act(self.n_qs, self.n_sc)
         self.launches_per_step = 9 * len(layers)        # kernels per layer (the memset is not a kernel)
 
-    def layer(self, i):
+    def layer(self, i, next_norm_w=None, next_act=None):
+        """One MoE FFN layer over the chunk.  next_norm_w / next_act = (PfAct, inv): where the fused combine + norm
+        puts the next consumer's quantised activation (the full model: the next mixer's attn_norm, into the live
+        activation buffers); by default the next layer's ffn_norm into scratch."""
         l, m = self.layers[i], self.m
         api.k_pf_norm(self.X, l.norm_w, 0, self.a, self.inv, self.h32, m)
         api.k_pf_router(self.h32, m, l.router, l.rbias, self.inv, self.sel, self.sig)
@@ -63,8 +66,9 @@ class PrefillStack:
                               exp_stride=H * (I // 32), perm=self.perm, tiles=self.tiles, ntiles=self.ntiles,
                               a_shift=0, out=self.D, out_ld=H)
         api.pf_gemm_moe(dn, self.max_tiles)
-        nxt = self.layers[(i + 1) % len(self.layers)]
-        api.k_pf_moe_combine_norm(self.X, self.D, self.w, nxt.norm_w, self.an, self.n_inv, m)
+        if next_norm_w is None:
+            next_norm_w, next_act = self.layers[(i + 1) % len(self.layers)].norm_w, (self.an, self.n_inv)
+        api.k_pf_moe_combine_norm(self.X, self.D, self.w, next_norm_w, next_act[0], next_act[1], m)
 
     def step(self):
         for i in range(len(self.layers)):

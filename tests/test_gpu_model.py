@@ -146,3 +146,45 @@ def test_new_entry_points_reject_bad_arguments(M, lkb):
     with pytest.raises(lkb.LkbError):
         lkb.decode_layers(ds.moe_dev, ds.mixers_dev, 0, ds.x, ds.xq, ds.d_pos, 1e6, None, ds._scratch, ds._sscratch)
     torch.cuda.synchronize()
+
+
+def _prefill_and_decode(M, n_layers, m, seed):
+    model = M.make_full_model(n_layers=n_layers, seed=seed, vocab=4096)
+    toks = torch.randint(0, 4096, (m,), dtype=torch.int32, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3))
+    ds = M.DecodeStep(model, max_seq=m + 8, moe_impl="kernels")
+    xs = []
+    for t in range(m):
+        ds.d_token.copy_(toks[t:t + 1])
+        ds.step()
+        xs.append(ds.x.clone())
+    st = M.DecodeStep(model, max_seq=m + 8, moe_impl="mega")
+    pc = M.PrefillChunk(model, m, st)
+    pc.toks.copy_(toks)
+    pc.step(P=0)
+    torch.cuda.synchronize()
+    return ds, torch.stack(xs), st, pc
+
+
+def test_prefill_chunk_agrees_with_token_by_token_decode(M, lkb):
+    """Prefill of m tokens against m decode steps fed the same tokens.  The two paths round differently (GEMM block
+    order vs GEMV lane order; fp16 Q / P in the chunk attention, as in the reference), and top-4 routing amplifies a
+    1e-3 difference into a different expert for some tokens, so beyond the first layer the comparison is
+    statistical: medians over tokens.  One conv + MoE layer must agree to rounding for every token."""
+    rows = lambda a, b: ((a.float() - b.float()).flatten(1).norm(dim=1) / b.float().flatten(1).norm(dim=1))
+    m = 48
+    ds, xs, st, pc = _prefill_and_decode(M, 1, m, 9)
+    assert lkb.lib.lkb_pf_gemm_status() == 0 and int(st.d_pos.item()) == m
+    e1 = rows(pc.X, xs)                                                 # chunk conv (history across tokens) + MoE vs decode:
+    assert float(e1.median()) < 1e-6 and float(e1.max()) < 2e-2         # fp32 rounding, except where a Q8_1 rounding flips
+    assert float(rows(st.hist[:1], ds.hist[:1]).max()) < 1e-5
+    ds, xs, st, pc = _prefill_and_decode(M, 3, m, 9)                    # conv, conv, attention
+    assert torch.isfinite(pc.X).all()
+    assert float(rows(pc.X, xs).median()) < 5e-2                        # Q8_1 rounding flips accumulate over layers
+    assert float(rows(st.kc[0, :m], ds.kc[0, :m]).median()) < 5e-2 and float(rows(st.vc[0, :m], ds.vc[0, :m]).median()) < 5e-2
+    assert float(rows(st.kc[0, :1], ds.kc[0, :1]).max()) < 1e-3          # the first token has no history: rounding only
+    assert float(st.kc[0, m:].abs().sum().item()) == 0.0                # nothing written past the chunk
+    # decoding continues from the prefilled state
+    st.d_token.fill_(7)
+    st.step()
+    torch.cuda.synchronize()
+    assert int(st.d_pos.item()) == m + 1 and 0 <= int(st.d_token.item()) < 4096 and st.status() == 0
