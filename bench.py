@@ -584,6 +584,63 @@ def run_ours(args):
                                        "ratio": (m / (t_pf * 1e-3)) / 21188.0} if (m == 4096 and args.layers == 40) else None}
         del pc, stt, fm
 
+    # ---------------------------------------------------------------- long context (configuration 4)
+    longc = None
+    if args.long_ctx and world == 1 and not args.no_full:
+        model_mod = importlib.import_module("lfm2-ampere_b200.model")
+        fm = model_mod.make_full_model(n_layers=args.layers, seed=4321, moe_layers=layers)
+        LC = 131072
+        ds = model_mod.DecodeStep(fm, max_seq=LC + 64, moe_impl="mega")
+        # chunked prefill: 32768 tokens in 8192-token chunks, timed per chunk (attention cost grows with the prefix)
+        CH = 8192
+        pc = model_mod.PrefillChunk(fm, CH, ds)
+        pc.toks.copy_(torch.randint(0, 65536, (CH,), dtype=torch.int32, device="cuda"))
+        pc.step(P=0)
+        ds.hist.zero_()
+        torch.cuda.synchronize()
+        chunk_ms = []
+        ev_all0, ev_all1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev_all0.record()
+        for c in range(4):
+            ev0.record()
+            pc.step(P=c * CH)
+            ev1.record()
+            torch.cuda.synchronize()
+            chunk_ms.append(ev0.elapsed_time(ev1))
+        ev_all1.record()
+        torch.cuda.synchronize()
+        pf32 = 4 * CH / (sum(chunk_ms) * 1e-3)
+        del pc
+        # decode at 131072 positions of context
+        ds.fill_kv(LC)
+        ds.d_token.fill_(11)
+        ds.step()
+        torch.cuda.synchronize()
+        gL = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gL):
+            ds.step()
+        ds.d_pos.fill_(LC)
+        for _ in range(3):
+            gL.replay()
+        torch.cuda.synchronize()
+        nst = min(args.steps, 20)
+        ev0.record()
+        for _ in range(nst):
+            gL.replay()
+        ev1.record()
+        torch.cuda.synchronize()
+        t_l = ev0.elapsed_time(ev1) / nst
+        nb = ds.bytes_per_step(LC)
+        longc = {"decode_ctx_131072": {"value": 1e3 / t_l, "unit": UNIT, "ms_per_step": t_l, "bytes_per_step": nb,
+                                       "roofline": {"bound": "hbm", "achieved": nb / (t_l * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
+                                                    "frac": nb / (t_l * 1e-3) / 1e9 / hbm_peak, "peak_kind": f"of {peak_kind}"},
+                                       "published_reference": {"value": 184.94, "unit": UNIT, "hardware": "RTX 3090 Ti, context 131040"}},
+                 "prefill_32768_in_8192_chunks": {"value": pf32, "unit": UNIT, "chunk_ms": chunk_ms,
+                                                  "published_reference": {"value": 18190.0, "unit": UNIT, "hardware": "RTX 3090 Ti"}}}
+        if ds.status() != 0:
+            raise SystemExit("long-context decode: a bounded device-side wait expired")
+        del gL, ds, fm
+
     if rank == 0:
         clocks = sampler.stop()          # sampled over every timed region above (decode, e2e, prefill, lm_head, full step)
         cb, _ = cpu_baseline() if world == 1 and not args.no_cpu else (None, None)
@@ -600,7 +657,7 @@ def run_ours(args):
                           "decode_impl": args.decode_impl, "cuda_graph": use_graph, "pdl": (not args.no_pdl) and not fused},
                "e2e": {"value": e2e_tok_s, "unit": UNIT, "h2d_bytes_per_step": H * 4, "d2h_bytes_per_step": H * 4},
                "gpu_launches": n_launch,
-               "roofline": roofline, "cpu_baseline": cb, "clocks": clocks, "prefill": pf, "lm_head": lm, "full_step": full, "full_prefill": fpf}
+               "roofline": roofline, "cpu_baseline": cb, "clocks": clocks, "prefill": pf, "lm_head": lm, "full_step": full, "full_prefill": fpf, "long_context": longc}
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -617,6 +674,7 @@ def main():
     ap.add_argument("--pf-steps", type=int, default=3)
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-lmhead", action="store_true")
+    ap.add_argument("--long-ctx", action="store_true", help="also time decode at 131072 positions of context and a chunked 32768-token prefill")
     ap.add_argument("--no-full", action="store_true", help="skip the full-model decode step (configuration 2)")
     ap.add_argument("--ctx", type=int, default=4096, help="KV positions pre-filled for the full decode step")
     ap.add_argument("--lm-steps", type=int, default=90)

@@ -117,6 +117,17 @@ inline int k_attn_split(stream_t st, const float * q, const void * kc, const voi
 inline int k_attn_combine(stream_t st, const float * part, const int * d_pos, float * out, block_q8_1 * yq8) {
     return check(lkb_attn_combine(part, d_pos, out, yq8, st), "k_attn_combine"); }
 
+// ---- prefill mixers (ref: src/prefill.cu:856, 937, 960, 975, 1029) -----------------------------------------------
+inline int k_pf_embed(stream_t st, int m, const uint8_t * ql, const uint8_t * qh, const int8_t * sc, const void * d, const int * toks, float * x) {
+    return check(lkb_pf_embed(ql, qh, sc, d, toks, x, LKB_HIDDEN, m, st), "k_pf_embed"); }
+inline int k_pf_conv(stream_t st, int m, const float * Y, const float * cw, const float * hist, PfAct a) {
+    return check(lkb_pf_conv(Y, cw, hist, a, m, st), "k_pf_conv"); }
+inline int k_pf_conv_hist(stream_t st, const float * Y, int m, float * hist) { return check(lkb_pf_conv_hist(Y, m, hist, st), "k_pf_conv_hist"); }
+inline int k_pf_qknr(stream_t st, int m, const float * Y, const float * qn, const float * kn, int P, void * qh, void * kc, void * vc) {
+    return check(lkb_pf_qknr(Y, qn, kn, P, qh, kc, vc, m, 10000000.0f, st), "k_pf_qknr"); }
+inline int k_pf_attn(stream_t st, const void * qh, int m, int P, const void * kc, const void * vc, float * o) {
+    return check(lkb_pf_attn(qh, m, P, kc, vc, o, st), "k_pf_attn"); }
+
 // ---- host launchers, same signatures as the reference's (ref: src/prefill.cuh:69-71) ---------------------
 inline void pf_gemm_dense(const PfGemm & g, stream_t st) { check(lkb_pf_gemm_dense(&g, st), "pf_gemm_dense"); }
 inline void pf_gemm_moe(const PfGemm & g, int max_tiles, stream_t st) { check(lkb_pf_gemm_moe(&g, max_tiles, st), "pf_gemm_moe"); }

@@ -183,3 +183,29 @@ def test_norm_rope_and_attention_references(orc):
         s = (kc[:, h // 4, :].astype(np.float64) @ q[h * 64:(h + 1) * 64].astype(np.float64)) * 0.125
         p = np.exp(s - s.max())
         assert np.max(np.abs(o[h] - (p @ vc[:, h // 4, :].astype(np.float64)) / p.sum())) <= 1e-14
+
+
+def test_chunk_references(orc, golden_dir):
+    """The float64 causal attention equals a direct numpy softmax; the chunk convolution is the decode step applied
+    token by token (history carried)."""
+    rng = np.random.default_rng(21)
+    m, P = 9, 5
+    S = m + P
+    K = rng.standard_normal((S, 8, 64)).astype(np.float16)
+    V = rng.standard_normal((S, 8, 64)).astype(np.float16)
+    Q = (rng.standard_normal((m, 2048)) * 0.2).astype(np.float16)
+    o = orc.pf_attn_f64(Q.view(np.uint16), m, P, K.view(np.uint16), V.view(np.uint16))
+    for t, h in ((0, 0), (4, 13), (8, 31)):
+        q = Q[t, h * 64:(h + 1) * 64].astype(np.float64)
+        s = K[:P + t + 1, h // 4].astype(np.float64) @ q
+        p = np.exp(s - s.max())
+        assert np.max(np.abs(o[t, h * 64:(h + 1) * 64] - (p @ V[:P + t + 1, h // 4].astype(np.float64)) / p.sum())) < 1e-13
+    cw = np.load(golden_dir / "conv_taps.npz")["conv_w"]
+    Y = rng.uniform(-1, 1, (4, 6144)).astype(np.float32)
+    hist = rng.uniform(-0.5, 0.5, 4096).astype(np.float32)
+    v, h2 = orc.pf_conv(Y, cw, hist)
+    bx = Y[:, :2048] * Y[:, 4096:]
+    assert np.array_equal(h2.reshape(2048, 2)[:, 1], bx[3]) and np.array_equal(h2.reshape(2048, 2)[:, 0], bx[2])
+    w = cw.astype(np.float64).reshape(2048, 3)
+    ref3 = Y[3, 2048:4096].astype(np.float64) * (bx[1] * w[:, 0] + bx[2] * w[:, 1] + bx[3].astype(np.float64) * w[:, 2])
+    assert np.max(np.abs(v[3] - ref3)) < 1e-5
