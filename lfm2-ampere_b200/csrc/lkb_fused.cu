@@ -343,11 +343,15 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
     if ((int) blockIdx.x == a.absent_cta) return;          // host-requested: the others' bounded waits must expire
 
     // static partition of the layer's rows over the CTAs (balanced, contiguous)
-    const int GU_TOTAL = 2 * LKB_TOP_K * LKB_MOE_INTER;
-    const int gu0 = (int) (((long long) cta * GU_TOTAL) / nct), gu1 = (int) (((long long) (cta + 1) * GU_TOTAL) / nct);
+    // A CTA owns (expert slot k, intermediate row r) PAIRS p = k*1536 + r, i.e. the gate row and the up row of
+    // the same intermediate element, so it can form silu(g)*u itself and publish one value instead of two.
+    // Staging: gate rows of the pairs at [0, n_gu), their up rows at [gu_pad, gu_pad + n_gu).
+    const int GU_PAIRS = LKB_TOP_K * LKB_MOE_INTER;
+    const int gu0 = (int) (((long long) cta * GU_PAIRS) / nct), gu1 = (int) (((long long) (cta + 1) * GU_PAIRS) / nct);
     const int dn0 = (int) (((long long) cta * LKB_HIDDEN) / nct), dn1 = (int) (((long long) (cta + 1) * LKB_HIDDEN) / nct);
     const int n_gu = gu1 - gu0, n_dn = dn1 - dn0;
-    const int n_gu_ch = (n_gu + CH_ROWS - 1) / CH_ROWS;
+    const int gu_half_ch = (n_gu + CH_ROWS - 1) / CH_ROWS, gu_pad = gu_half_ch * CH_ROWS;
+    const int n_gu_ch = 2 * gu_half_ch;
     const int dn_ch_per_k = (n_dn + CH_ROWS - 1) / CH_ROWS;
 
     if (tid == 0) {
@@ -636,9 +640,11 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
             fence_proxy_async();
             for (int c = warp; c < n_gu_ch + LKB_TOP_K * dn_ch_per_k; c += FUSED_WARPS) {
                 if (c < n_gu_ch) {
-                    const int j0 = c * CH_ROWS, j1 = min(n_gu, j0 + CH_ROWS);
-                    issue_gu_rows(ly, S.idx, gu0 + j0, gu0 + j1, S.gu_q + (size_t) j0 * GU_BPR * 16,
-                                  S.gu_d + (size_t) j0 * GU_BPR, &S.mbar_gu[c]);
+                    const int up = c >= gu_half_ch, ch = up ? c - gu_half_ch : c;
+                    const int j0 = ch * CH_ROWS, j1 = min(n_gu, j0 + CH_ROWS);
+                    const int g0 = up * GU_PAIRS + gu0, s0 = up * gu_pad + j0;       // logical rows: gate 0..6143, up 6144..12287
+                    issue_gu_rows(ly, S.idx, g0 + j0, g0 + j1, S.gu_q + (size_t) s0 * GU_BPR * 16,
+                                  S.gu_d + (size_t) s0 * GU_BPR, &S.mbar_gu[c]);
                 } else {
                     const int cc = c - n_gu_ch, k = cc / dn_ch_per_k, ch = cc % dn_ch_per_k;
                     const int j0 = ch * CH_ROWS, j1 = min(n_dn, j0 + CH_ROWS);
@@ -661,14 +667,20 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
             load_xregs<2>(S.xq, GU_BPR, lane, xq, d8, s8);
             const float ninv = S.inv;
             for (int j = warp; j < n_gu; j += FUSED_WARPS) {
-                if (!mbar_wait(&S.mbar_gu[j / CH_ROWS], par)) {
+                if (!mbar_wait(&S.mbar_gu[j / CH_ROWS], par) || !mbar_wait(&S.mbar_gu[gu_half_ch + j / CH_ROWS], par)) {
                     if (lane == 0) { atomicCAS(status, 0u, 200u + l); S.abort = 1; }
                     break;
                 }
-                const float acc = lkb_warp_sum(smem_row_partial<2>(S.gu_q + (size_t) j * GU_BPR * 16, S.gu_d + (size_t) j * GU_BPR,
-                                                                   GU_BPR, lane, xq, d8, s8));
-                // logical row g = (half*4 + k)*1536 + row: the stand-alone kernel's y_a | y_b layout
-                if (lane == 0) a.gu[gu0 + j] = __fmul_rn(acc, ninv);
+                float pg = smem_row_partial<2>(S.gu_q + (size_t) j * GU_BPR * 16, S.gu_d + (size_t) j * GU_BPR, GU_BPR, lane, xq, d8, s8);
+                float pu = smem_row_partial<2>(S.gu_q + (size_t) (gu_pad + j) * GU_BPR * 16, S.gu_d + (size_t) (gu_pad + j) * GU_BPR,
+                                               GU_BPR, lane, xq, d8, s8);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    pg = __fadd_rn(pg, __shfl_xor_sync(LKB_FULL, pg, o));
+                    pu = __fadd_rn(pu, __shfl_xor_sync(LKB_FULL, pu, o));
+                }
+                // v = silu(gate) * up of pair gu0 + j (the stand-alone k_swiglu's arithmetic on the two GEMV outputs)
+                if (lane == 0) a.gu[gu0 + j] = __fmul_rn(lkb_silu(__fmul_rn(pg, ninv)), __fmul_rn(pu, ninv));
             }
         }
         FUSED_STAMP(5);
@@ -695,15 +707,9 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
 
         // ---- F: SwiGLU + Q8_1 (every CTA), down rows, residual ---------------------
         {
-            const int GU = LKB_TOP_K * LKB_MOE_INTER;             // 6144 = 192 blocks, 12 per warp
-            float g[12], u[12], v[12], d[12], sm[12]; int q[12];
+            float v[12], d[12], sm[12]; int q[12];                // 6144 values = 192 blocks, 12 per warp
 #pragma unroll
-            for (int j = 0; j < 12; ++j) {
-                const int i = (warp + FUSED_WARPS * j) * 32 + lane;
-                g[j] = __ldcg(a.gu + i); u[j] = __ldcg(a.gu + GU + i);
-            }
-#pragma unroll
-            for (int j = 0; j < 12; ++j) v[j] = __fmul_rn(lkb_silu(g[j]), u[j]);
+            for (int j = 0; j < 12; ++j) v[j] = __ldcg(a.gu + (warp + FUSED_WARPS * j) * 32 + lane);
             FUSED_STAMP(10);
             quantN<12>(v, q, d, sm);
 #pragma unroll
@@ -810,8 +816,9 @@ static int fused_launch(FusedArgs & a, cudaStream_t st) {
     if (a.final_norm_w && (!a.out_yq8 || !a.out_ssq)) return LKB_ERR_NULL;
     int grid = lkb_context().sm_count;
     // every CTA's share must fit the shared-memory staging
-    const int GU_TOTAL = 2 * LKB_TOP_K * LKB_MOE_INTER;
-    if ((GU_TOTAL + grid - 1) / grid > MAX_GU_ROWS || (LKB_HIDDEN + grid - 1) / grid > MAX_DN_ROWS) return LKB_ERR_DEVICE;
+    const int pairs = (LKB_TOP_K * LKB_MOE_INTER + grid - 1) / grid;          // gate rows, then (chunk-aligned) as many up rows
+    if ((pairs + CH_ROWS - 1) / CH_ROWS * CH_ROWS + pairs > MAX_GU_ROWS || 2 * ((pairs + CH_ROWS - 1) / CH_ROWS) > N_GU_CH ||
+        (LKB_HIDDEN + grid - 1) / grid > MAX_DN_ROWS) return LKB_ERR_DEVICE;
     cudaError_t e = cudaMemsetAsync(a.bar, 0, 2 * sizeof(unsigned), st);
     if (e != cudaSuccess) return -(int) e;
     a.timing = g_fused_timing;
