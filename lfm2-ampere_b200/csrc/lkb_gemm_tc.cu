@@ -328,28 +328,35 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
             tc_cp_commit();                                         // one group per call, possibly empty
             ++it_issue;
         };
-        for (int p = 0; p < TC_AHEAD; ++p) issue();
-        for (unsigned it = 0; it < total && ok; ++it) {
-            // stage `it` has landed once at most TC_AHEAD-1 newer groups are pending; publish it BEFORE
-            // blocking on the buffer of stage it+TC_AHEAD, so the copies really run ahead of the consumers
-            { const long long t0_ = TC_CLK(); tc_cp_wait<TC_AHEAD - 1>(); pw_cp += TC_CLK() - t0_; }
+        // Expansion and publication of one landed stage.
+        auto publish = [&](unsigned it) {
             TcStage & T = S.st[it % TC_STAGES];
             const long long tu0_ = TC_CLK();
+            // every raw read of the stage first, then the expansion: a store between two loads would order them
+            // (the compiler cannot tell the staging arrays apart through the computed offsets)
+            uint4 wv[TC_RPT][TC_KB];
+            uint2 dv[TC_RPT];
 #pragma unroll
             for (int q = 0; q < TC_RPT; ++q) {
                 const int rr = tid + q * TC_LOADERS;
 #pragma unroll
+                for (int j = 0; j < TC_KB; ++j) wv[q][j] = *reinterpret_cast<const uint4 *>(T.rawq[rr] + j * 16);
+                dv[q] = *reinterpret_cast<const uint2 *>(T.rawd[rr]);               // the row's four fp16 block scales
+            }
+#pragma unroll
+            for (int q = 0; q < TC_RPT; ++q) {
+                const int rr = tid + q * TC_LOADERS;
+                const __half2 d01 = *reinterpret_cast<const __half2 *>(&dv[q].x), d23 = *reinterpret_cast<const __half2 *>(&dv[q].y);
+                const float df[4] = {__low2float(d01), __high2float(d01), __low2float(d23), __high2float(d23)};
+#pragma unroll
                 for (int j = 0; j < TC_KB; ++j) {
-                    const uint4 wv = *reinterpret_cast<const uint4 *>(T.rawq[rr] + j * 16);
                     // byte i of the 16: element i (low nibble) | element i+16 (high nibble)
-                    uint4 lo, hi;
-                    lo.x = wv.x & 0x0F0F0F0Fu; hi.x = (wv.x >> 4) & 0x0F0F0F0Fu;
-                    lo.y = wv.y & 0x0F0F0F0Fu; hi.y = (wv.y >> 4) & 0x0F0F0F0Fu;
-                    lo.z = wv.z & 0x0F0F0F0Fu; hi.z = (wv.z >> 4) & 0x0F0F0F0Fu;
-                    lo.w = wv.w & 0x0F0F0F0Fu; hi.w = (wv.w >> 4) & 0x0F0F0F0Fu;
-                    *reinterpret_cast<uint4 *>(T.B[j] + tc_canon(rr, 0)) = lo;
-                    *reinterpret_cast<uint4 *>(T.B[j] + tc_canon(rr, 1)) = hi;
-                    T.d4[j][rr] = __half2float(T.rawd[rr][j]);
+                    const uint4 w = wv[q][j];
+                    *reinterpret_cast<uint4 *>(T.B[j] + tc_canon(rr, 0)) =
+                        make_uint4(w.x & 0x0F0F0F0Fu, w.y & 0x0F0F0F0Fu, w.z & 0x0F0F0F0Fu, w.w & 0x0F0F0F0Fu);
+                    *reinterpret_cast<uint4 *>(T.B[j] + tc_canon(rr, 1)) =
+                        make_uint4((w.x >> 4) & 0x0F0F0F0Fu, (w.y >> 4) & 0x0F0F0F0Fu, (w.z >> 4) & 0x0F0F0F0Fu, (w.w >> 4) & 0x0F0F0F0Fu);
+                    T.d4[j][rr] = df[j];
                 }
             }
             const long long tf0_ = TC_CLK(); pw_unpack += tf0_ - tu0_;
@@ -357,7 +364,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
             pw_fence += TC_CLK() - tf0_;
             __syncwarp();
             if (lane == 0) tc_mbar_arrive(&S.full[it % TC_STAGES]);
-            issue();
+        };
+        // Publishing runs as far ahead as the copies: a stage is expanded and published as soon as its copies have
+        // landed, BEFORE the loader blocks on the buffer of the next stage to request.  (Blocking first delayed the
+        // publication of a stage that had landed long ago until the epilogue released an older buffer, and the MMA
+        // issuer starved for the length of one expansion per stage.)
+        for (int p = 0; p < TC_AHEAD; ++p) issue();                 // stages 0 .. TC_AHEAD-1 requested
+        unsigned pub = 0;                                           // stages [0, pub) are published
+        while (pub < total && ok) {
+            // everything requested so far must land; then publish all of it, then request one more stage
+            { const long long t0_ = TC_CLK(); tc_cp_wait<0>(); pw_cp += TC_CLK() - t0_; }
+            const unsigned have = it_issue < total ? it_issue : total;
+            for (; pub < have; ++pub) publish(pub);
+            issue();                                                // blocks until the epilogue has released the buffer
         }
         tc_cp_wait<0>();
         if (blockIdx.x == 0 && tid == 0) { g_tc_prof[0] = pw_empty; g_tc_prof[1] = pw_cp; g_tc_prof[2] = clock64() - pt0; g_tc_prof[13] = pw_fence; g_tc_prof[14] = pw_unpack; }
