@@ -28,7 +28,6 @@ template <int STAGES>
 struct AtWarp {
     __half k[STAGES][AT_G][AT_ROW];
     __half v[STAGES][AT_G][AT_ROW];
-    float4 p[AT_G];
 };
 template <int STAGES>
 struct AtSmem {
@@ -59,18 +58,38 @@ __device__ __forceinline__ void at_norm_rope(float a, float b, const float * __r
     y1 = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs));
 }
 
+// Warp-level tensor-core step: D(16x8, fp32) += A(16x16, fp16, row) * B(16x8, fp16, col).
+__device__ __forceinline__ void at_mma(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// x = hi + lo with hi, lo fp16: the pair carries x to ~2^-22 relative, so fp16 tensor-core operands lose nothing
+// that fp32 arithmetic would have kept.
+__device__ __forceinline__ void at_split(float x0, float x1, unsigned & hi, unsigned & lo) {
+    const __half2 h = __floats2half2_rn(x0, x1);
+    const float2 hf = __half22float2(h);
+    const __half2 l = __floats2half2_rn(__fsub_rn(x0, hf.x), __fsub_rn(x1, hf.y));
+    hi = *reinterpret_cast<const unsigned *>(&h);
+    lo = *reinterpret_cast<const unsigned *>(&l);
+}
+
 // One slice [t0, t1) of one KV head: warps 0..7 of the CTA stream their 32-token groups of K and V through
 // private cp.async rings, keep their own online softmax and are merged at the end into
-// part[(kvh*4 + h)][sp] = {max, sum, acc[64]}.  Every thread of the CTA must call this (it contains CTA
-// barriers); S.q must be filled and visible (a CTA barrier after the fill) before the call.
+// part[(kvh*4 + h)][sp] = {max, sum, acc[64]}.
+// The four query heads of the KV head are the rows of a 16-row tensor-core tile (rows 4..15 are zero): per group
+// S = Q K^T is 4 token tiles x 4 dim steps of m16n8k16, O += P V is 2 token steps x 8 dim tiles, with Q and P each
+// carried as an fp16 (hi, lo) pair so the products are those of fp32 operands.  Lane (g = lane / 4, t4 = lane % 4)
+// with g < 4 owns head g: scores of tokens 8 nt + 2 t4 + {0, 1} and output dims 8 nd + 2 t4 + {0, 1}.  This form needs
+// ~300 instructions per group and warp where the scalar form needed ~1000, which is what makes the slice
+// HBM-bound instead of issue-bound at long context.
+// Every thread of the CTA must call this (it contains CTA barriers); S.q must be filled and visible (a CTA
+// barrier after the fill) before the call.
 template <int STAGES>
 __device__ __forceinline__ void at_slice(AtSmem<STAGES> & S, const __half * __restrict__ kc, const __half * __restrict__ vc,
                                          int kvh, int sp, int t0, int t1, float * __restrict__ part) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t4 = lane & 3;
     const bool worker = warp < AT_WARPS;
-    float m[AT_GQA], l[AT_GQA], acc[AT_GQA][2];
-#pragma unroll
-    for (int h = 0; h < AT_GQA; ++h) { m[h] = -1e30f; l[h] = 0.0f; acc[h][0] = acc[h][1] = 0.0f; }
     if (worker) {
         AtWarp<STAGES> & W = S.w[warp];
         const int ngrp = (t1 - t0 + AT_G - 1) / AT_G;       // groups of this slice; warp w owns w, w+8, ...
@@ -95,67 +114,101 @@ __device__ __forceinline__ void at_slice(AtSmem<STAGES> & S, const __half * __re
         };
 #pragma unroll
         for (int i = 0; i < STAGES - 1; ++i) issue(i);
+        // Q fragments (rows 0..3 = heads, scaled by the exact 1/8): register pair kk holds dims 16 kk + 2 t4 + {0,1}
+        // (a0) and + 8 (a2) of head g, as hi and lo parts; rows 8..15 (a1, a3) and heads g >= 4 are zero
+        unsigned qh0[4], qh2[4], ql0[4], ql2[4];
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            const int d0 = kk * 16 + 2 * t4;
+            float v0 = 0.0f, v1 = 0.0f, v2 = 0.0f, v3 = 0.0f;
+            if (g < AT_GQA) {
+                v0 = __fmul_rn(reinterpret_cast<const float *>(&S.q[d0])[g], AT_SCALE);
+                v1 = __fmul_rn(reinterpret_cast<const float *>(&S.q[d0 + 1])[g], AT_SCALE);
+                v2 = __fmul_rn(reinterpret_cast<const float *>(&S.q[d0 + 8])[g], AT_SCALE);
+                v3 = __fmul_rn(reinterpret_cast<const float *>(&S.q[d0 + 9])[g], AT_SCALE);
+            }
+            at_split(v0, v1, qh0[kk], ql0[kk]);
+            at_split(v2, v3, qh2[kk], ql2[kk]);
+        }
+        float m = -1e30f, l = 0.0f;                         // running max and (per-lane partial) sum of head g
+        float o[8][4];
+#pragma unroll
+        for (int nd = 0; nd < 8; ++nd) { o[nd][0] = o[nd][1] = o[nd][2] = o[nd][3] = 0.0f; }
         for (int i = 0; i < mine; ++i) {
             issue(i + STAGES - 1);
             at_wait_group<STAGES - 1>();
             __syncwarp();
             const int st = i % STAGES, g0 = t0 + (warp + i * AT_WARPS) * AT_G;
-            const bool live = g0 + lane < t1;
-            // scores of token g0 + lane against the four heads.  q is re-read from shared memory in every
-            // iteration (the opaque zero stops the compiler from hoisting 64 float4 into registers).
-            int zero;
-            asm volatile("mov.u32 %0, 0;" : "=r"(zero));
-            const float4 * Q = S.q + zero;
-            float s[AT_GQA] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll 2
-            for (int c = 0; c < 8; ++c) {
-                const uint4 kw = *reinterpret_cast<const uint4 *>(&W.k[st][lane][c * 8]);
-                const __half2 * k2 = reinterpret_cast<const __half2 *>(&kw);
+            // S = Q K^T: s[nt][0..1] = scores of head g against tokens g0 + 8 nt + 2 t4 + {0, 1}
+            float s[4][4];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 kf = __half22float2(k2[e]);
-                    const float4 qa = Q[c * 8 + 2 * e], qb = Q[c * 8 + 2 * e + 1];
-                    s[0] = fmaf(qa.x, kf.x, s[0]); s[1] = fmaf(qa.y, kf.x, s[1]); s[2] = fmaf(qa.z, kf.x, s[2]); s[3] = fmaf(qa.w, kf.x, s[3]);
-                    s[0] = fmaf(qb.x, kf.y, s[0]); s[1] = fmaf(qb.y, kf.y, s[1]); s[2] = fmaf(qb.z, kf.y, s[2]); s[3] = fmaf(qb.w, kf.y, s[3]);
+            for (int nt = 0; nt < 4; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f; }
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    const __half * kp = &W.k[st][nt * 8 + g][kk * 16 + 2 * t4];
+                    const unsigned b0 = *reinterpret_cast<const unsigned *>(kp), b1 = *reinterpret_cast<const unsigned *>(kp + 8);
+                    at_mma(s[nt], qh0[kk], 0u, qh2[kk], 0u, b0, b1);
+                    at_mma(s[nt], ql0[kk], 0u, ql2[kk], 0u, b0, b1);
                 }
             }
-            float sc[AT_GQA], pr[AT_GQA];
+            float mx = -1e30f;
 #pragma unroll
-            for (int h = 0; h < AT_GQA; ++h) {
-                s[h] = live ? __fmul_rn(s[h], AT_SCALE) : -1e30f;
-                float mx = s[h];
+            for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(LKB_FULL, mx, o));
-                const float mn = fmaxf(m[h], mx);
-                sc[h] = __expf(__fsub_rn(m[h], mn));
-                pr[h] = live ? __expf(__fsub_rn(s[h], mn)) : 0.0f;
-                l[h] = fmaf(l[h], sc[h], lkb_warp_sum(pr[h]));
-                m[h] = mn;
+                for (int e = 0; e < 2; ++e) {
+                    if (g0 + nt * 8 + 2 * t4 + e >= t1) s[nt][e] = -1e30f;      // past the slice
+                    mx = fmaxf(mx, s[nt][e]);
+                }
+            mx = fmaxf(mx, __shfl_xor_sync(LKB_FULL, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(LKB_FULL, mx, 2));
+            const float mn = fmaxf(m, mx);
+            const float alpha = __expf(__fsub_rn(m, mn));
+            m = mn;
+            float ls = 0.0f;
+            unsigned ph[4], pl[4];                          // P of tokens 8 nt + 2 t4 + {0,1} as fp16 hi / lo pairs
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const float p0 = (s[nt][0] <= -1e30f) ? 0.0f : __expf(__fsub_rn(s[nt][0], mn));
+                const float p1 = (s[nt][1] <= -1e30f) ? 0.0f : __expf(__fsub_rn(s[nt][1], mn));
+                ls = __fadd_rn(ls, __fadd_rn(p0, p1));
+                at_split(p0, p1, ph[nt], pl[nt]);
             }
-            W.p[lane] = make_float4(pr[0], pr[1], pr[2], pr[3]);
-            __syncwarp();
-            // acc[h][dims 2*lane, 2*lane+1] = acc * sc + sum_j p[j][h] * V[j][dims]
+            l = fmaf(l, alpha, ls);
 #pragma unroll
-            for (int h = 0; h < AT_GQA; ++h) { acc[h][0] = __fmul_rn(acc[h][0], sc[h]); acc[h][1] = __fmul_rn(acc[h][1], sc[h]); }
-#pragma unroll 8
-            for (int j = 0; j < AT_G; ++j) {
-                const float2 vf = __half22float2(*reinterpret_cast<const __half2 *>(&W.v[st][j][2 * lane]));
-                const float4 p = W.p[j];
-                acc[0][0] = fmaf(p.x, vf.x, acc[0][0]); acc[0][1] = fmaf(p.x, vf.y, acc[0][1]);
-                acc[1][0] = fmaf(p.y, vf.x, acc[1][0]); acc[1][1] = fmaf(p.y, vf.y, acc[1][1]);
-                acc[2][0] = fmaf(p.z, vf.x, acc[2][0]); acc[2][1] = fmaf(p.z, vf.y, acc[2][1]);
-                acc[3][0] = fmaf(p.w, vf.x, acc[3][0]); acc[3][1] = fmaf(p.w, vf.y, acc[3][1]);
+            for (int nd = 0; nd < 8; ++nd) { o[nd][0] = __fmul_rn(o[nd][0], alpha); o[nd][1] = __fmul_rn(o[nd][1], alpha); }
+            // O += P V: token step ks uses P tiles 2 ks (a0) and 2 ks + 1 (a2); V tiles come transposed from shared memory
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks) {
+#pragma unroll
+                for (int nd = 0; nd < 8; nd += 2) {
+                    const int mat = lane >> 3, rr = lane & 7;
+                    const __half * vp = &W.v[st][ks * 16 + (mat & 1) * 8 + rr][(nd + (mat >> 1)) * 8];
+                    unsigned b0, b1, b2, b3;
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"((unsigned) __cvta_generic_to_shared(vp)));
+                    at_mma(o[nd], ph[2 * ks], 0u, ph[2 * ks + 1], 0u, b0, b1);
+                    at_mma(o[nd], pl[2 * ks], 0u, pl[2 * ks + 1], 0u, b0, b1);
+                    at_mma(o[nd + 1], ph[2 * ks], 0u, ph[2 * ks + 1], 0u, b2, b3);
+                    at_mma(o[nd + 1], pl[2 * ks], 0u, pl[2 * ks + 1], 0u, b2, b3);
+                }
             }
             __syncwarp();
         }
         at_wait_group<0>();
+        l = __fadd_rn(l, __shfl_xor_sync(LKB_FULL, l, 1));
+        l = __fadd_rn(l, __shfl_xor_sync(LKB_FULL, l, 2));
         // a warp parks its accumulators in its own, now idle, K staging
         __syncwarp();
         float * wacc = reinterpret_cast<float *>(&W.k[0][0][0]);
+        if (g < AT_GQA) {
+            if (t4 == 0) { S.m[warp][g] = m; S.l[warp][g] = l; }
 #pragma unroll
-        for (int h = 0; h < AT_GQA; ++h) {
-            if (lane == 0) { S.m[warp][h] = m[h]; S.l[warp][h] = l[h]; }
-            wacc[h * AT_D + 2 * lane] = acc[h][0]; wacc[h * AT_D + 2 * lane + 1] = acc[h][1];
+            for (int nd = 0; nd < 8; ++nd) {
+                wacc[g * AT_D + nd * 8 + 2 * t4] = o[nd][0];
+                wacc[g * AT_D + nd * 8 + 2 * t4 + 1] = o[nd][1];
+            }
         }
     }
     __syncthreads();
