@@ -1,4 +1,5 @@
-// lkb_fused.cu - one persistent cooperative kernel for the batch-1 MoE FFN stack.
+// lkb_fused.cu - one persistent cooperative kernel for the batch-1 MoE FFN stack and, as its template
+// variant with sequence mixers in front of every MoE layer, for all layers of a whole decode step.
 //
 // The reference runs five kernels per MoE layer (router dot, top-4, gate|up GEMV,
 // SwiGLU quantiser, down GEMV + accumulate; ref: src/engine.cu:739-811).  On B200 a
@@ -11,7 +12,13 @@
 //     async copies (TMA, no multicast) into ~150 KB of shared memory, completion
 //     tracked by mbarriers per 8-row chunk, so the whole 21 MB is in flight at once
 //     and arithmetic starts as chunks land;
-//   * the next layer's router row is requested while the down projection runs.
+//   * a CTA owns the gate row and the up row of the same intermediate elements, so it forms
+//     silu(gate)*up itself and publishes one value per pair; every CTA then quantises the 6144
+//     values it needs for its down rows;
+//   * the next layer's router row is requested while the down projection runs;
+//   * whole-step variant (MIX): the mixers' weight rows are static, so they are requested a phase
+//     ahead into staging the MoE phases have finished with; a conv mixer adds two grid barriers
+//     per layer, an attention mixer four (see the M0..M3 phases in the kernel).
 // Arithmetic per output is exactly that of the stand-alone kernels (lane-strided
 // blocks, xor butterfly, fixed k = 0..3 order), so results are bit-identical to the
 // five-kernel sequence.
@@ -241,7 +248,7 @@ struct FusedArgs {
     int *                 idx_out;     // optional [n_layers][4]
     float *               w_out;       // optional [n_layers][4]
     float *               logits;      // scratch [64]
-    float *               gu;          // scratch [2*4*1536]
+    float *               gu;          // scratch [2*4*1536]: silu(gate)*up of the 4*1536 pairs in its first half
     unsigned *            bar;         // scratch [2]: {barrier counter, status}
     int                   softmax;
     unsigned long long *  timing;
@@ -661,7 +668,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
         __syncwarp();
         FUSED_STAMP(4);
 
-        // ---- E: gate|up rows of this CTA ------------------------------------------
+        // ---- E: gate and up rows of this CTA's pairs, silu(gate)*up published -----
         {
             int xq[2][8]; float d8[2], s8[2];
             load_xregs<2>(S.xq, GU_BPR, lane, xq, d8, s8);
@@ -705,7 +712,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
         if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 2u, a.spin_limit)) return;
         FUSED_STAMP(6);
 
-        // ---- F: SwiGLU + Q8_1 (every CTA), down rows, residual ---------------------
+        // ---- F: Q8_1 of the 6144 published values (every CTA), down rows, residual --
         {
             float v[12], d[12], sm[12]; int q[12];                // 6144 values = 192 blocks, 12 per warp
 #pragma unroll
