@@ -40,7 +40,7 @@ H, E, TOPK, I = 2048, 64, 4, 1536
 LAYER_BYTES = E * H * 4 + 2 * TOPK * I * (H // 32) * 18 + TOPK * H * (I // 32) * 18 + 3 * H * 4   # 21,782,528
 GATEUP_BYTES = 2 * TOPK * I * (H // 32) * 18 + 64 * 36 + 2 * TOPK * I * 4                          # per launch
 # DRAM traffic of the fused decode kernel per MoE layer, from one ncu capture of a 4-layer launch
-# (dram__bytes_read.sum + dram__bytes_write.sum = 87,156,736 + 2,285,312 B; it grows in proportion to the layers)
+# (dram__bytes_read.sum + dram__bytes_write.sum = 87,141,120 + 2,562,816 B; it grows in proportion to the layers)
 FUSED_TRAFFIC_PER_LAYER = (87141120 + 2562816) / 4
 METRIC = "bs1 decode tok/s"
 UNIT = "tok/s"
