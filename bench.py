@@ -342,13 +342,25 @@ def run_ours(args):
         Xd = Xh.cuda()
         Yh = torch.empty(ml, H, dtype=torch.float32).pin_memory()
 
+        pf_graph = None
+
         def pf_step(e2e=False):
             ps.X.copy_(Xh if e2e else Xd, non_blocking=True)
-            ps.step()
+            if pf_graph is not None:
+                pf_graph.replay()
+            else:
+                ps.step()
             if e2e:
                 Yh.copy_(ps.X, non_blocking=True)
                 st.synchronize()
         pf_step()
+        if not ep and not args.no_graph:
+            # one CUDA graph for the step's ~9 launches per layer (the expert-parallel step has a host sync per layer)
+            torch.cuda.synchronize()
+            pf_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(pf_graph):
+                ps.step()
+            pf_step()
         barrier()
         ev0.record()
         for _ in range(args.pf_steps):
@@ -398,7 +410,7 @@ def run_ours(args):
             imbalance = float(cnt.max() / max(1.0, cnt.mean()))
             launches = args.pf_steps * ps.launches_per_step
         pf = {"metric": "4k prefill tok/s (40-layer MoE-FFN stack)", "tokens": m, "value": m / (pms * 1e-3), "unit": UNIT,
-              "ms_per_step": pms, "scaling": "strong",
+              "ms_per_step": pms, "scaling": "strong", "cuda_graph": pf_graph is not None,
               "parallelism": (f"expert-parallel x{world}: {E // world} experts and {ml} tokens per GPU, token all-to-all "
                               "(NCCL) before and after the grouped GEMMs") if ep else "single GPU",
               "e2e": {"value": m / (pms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": m * H * 4,
