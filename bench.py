@@ -483,6 +483,38 @@ def run_ours(args):
                            "traffic": 114323968 if V == 65536 else None}}   # ncu dram read + write of one launch (profiles/)
         del copies
 
+    # ---------------------------------------------------------------- Q4_0 x Q8_1 GEMV size sweep (configuration 0 and up)
+    sweep = None
+    if not args.no_sweep:
+        gen2 = torch.Generator(device="cuda").manual_seed(9)
+        xq_s = torch.empty(H // 32 * 36, dtype=torch.uint8, device="cuda")
+        lkb.k_quantize_q8_1(torch.randn(H, device="cuda", generator=gen2), xq_s, H // 32)
+        lkb.set_pdl(False)
+        sweep = []
+        for rows in (2048, 6144, 65536, 262144):
+            nbytes = rows * (H // 32) * 18 + H // 32 * 36 + rows * 4
+            ncopy = min(160, max(2, (400 << 20) // nbytes + 1))            # rotate >= 400 MB of weights: every launch streams from HBM
+            ws = [(torch.randint(0, 256, (rows * (H // 32) * 16,), dtype=torch.uint8, device="cuda", generator=gen2),
+                   (torch.rand(rows * (H // 32), device="cuda", generator=gen2) * 0.02).half()) for _ in range(ncopy)]
+            ys = torch.empty(rows, device="cuda")
+            nl = max(ncopy, 24)
+            for i in range(3):
+                lkb.k_gemv_q4_0(ws[i % ncopy][0], ws[i % ncopy][1], xq_s, rows, H // 32, ys)
+            torch.cuda.synchronize()
+            gs = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gs):
+                for i in range(nl):
+                    lkb.k_gemv_q4_0(ws[i % ncopy][0], ws[i % ncopy][1], xq_s, rows, H // 32, ys)
+            gs.replay()
+            barrier()
+            ev0.record()
+            gs.replay()
+            ev1.record()
+            barrier()
+            us = max_over_ranks(ev0.elapsed_time(ev1)) / nl * 1e3
+            sweep.append({"rows": rows, "k": H, "bytes": nbytes, "us": us, "GBs": nbytes / us / 1e3, "frac": nbytes / us / 1e3 / hbm_peak})
+            del ws, gs
+
     # ---------------------------------------------------------------- full decode step (configuration 2)
     full = None
     if not args.no_full:
@@ -669,7 +701,7 @@ def run_ours(args):
                           "decode_impl": args.decode_impl, "cuda_graph": use_graph, "pdl": (not args.no_pdl) and not fused},
                "e2e": {"value": e2e_tok_s, "unit": UNIT, "h2d_bytes_per_step": H * 4, "d2h_bytes_per_step": H * 4},
                "gpu_launches": n_launch,
-               "roofline": roofline, "cpu_baseline": cb, "clocks": clocks, "prefill": pf, "lm_head": lm, "full_step": full, "full_prefill": fpf, "long_context": longc}
+               "roofline": roofline, "cpu_baseline": cb, "clocks": clocks, "prefill": pf, "lm_head": lm, "gemv_sweep": sweep, "full_step": full, "full_prefill": fpf, "long_context": longc}
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -686,6 +718,7 @@ def main():
     ap.add_argument("--pf-steps", type=int, default=3)
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-lmhead", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the GEMV size sweep")
     ap.add_argument("--long-ctx", action="store_true", help="also time decode at 131072 positions of context and a chunked 32768-token prefill")
     ap.add_argument("--no-full", action="store_true", help="skip the full-model decode step (configuration 2)")
     ap.add_argument("--ctx", type=int, default=4096, help="KV positions pre-filled for the full decode step")
