@@ -335,7 +335,7 @@ def run_ours(args):
         m = args.pf_tokens
         del graph
         ep = world > 1
-        ps = prefill.PrefillStackEP(layers, m, rank, world) if ep else prefill.PrefillStack(layers, m)
+        ps = prefill.PrefillStackEP(layers, m, rank, world, dispatch=args.ep_dispatch) if ep else prefill.PrefillStack(layers, m)
         ml = m // world
         Xall = np.random.default_rng(5).standard_normal((m, H)).astype(np.float32)
         Xh = torch.from_numpy(Xall[rank * ml:(rank + 1) * ml].copy()).pin_memory()       # this rank's tokens
@@ -399,7 +399,11 @@ def run_ours(args):
         macs = args.layers * m * TOPK * (2 * I * H + H * I)
         tmacs = macs / (pms * 1e-3) / 1e12
         if ep:
-            mine = torch.tensor([float(sum(ps.recv_slots))], device="cuda", dtype=torch.float64)
+            est = torch.tensor([ps.status()], device="cuda")
+            dist.all_reduce(est, op=dist.ReduceOp.MAX)                       # every rank leaves together
+            if int(est.item()) != 0:
+                raise SystemExit(f"expert-parallel exchange reported status {int(est.item())} (a bounded wait expired)")
+            mine = torch.as_tensor(ps.recv_slots).sum().to("cuda", torch.float64).reshape(1)
             mx, sm = mine.clone(), mine.clone()
             dist.all_reduce(mx, op=dist.ReduceOp.MAX)
             dist.all_reduce(sm, op=dist.ReduceOp.SUM)
@@ -412,7 +416,10 @@ def run_ours(args):
         pf = {"metric": "4k prefill tok/s (40-layer MoE-FFN stack)", "tokens": m, "value": m / (pms * 1e-3), "unit": UNIT,
               "ms_per_step": pms, "scaling": "strong", "cuda_graph": pf_graph is not None,
               "parallelism": (f"expert-parallel x{world}: {E // world} experts and {ml} tokens per GPU, token all-to-all "
-                              "(NCCL) before and after the grouped GEMMs") if ep else "single GPU",
+                              "before and after the grouped GEMMs, " + ("NCCL all_to_all_single with one host sync per layer"
+                                                                        if args.ep_dispatch == "nccl" else
+                                                                        "peer-memory stores over NVLink with device-side flags, no host sync"))
+              if ep else "single GPU",
               "e2e": {"value": m / (pms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": m * H * 4,
                       "d2h_bytes_per_step": m * H * 4},
               "gemm_tmacs": tmacs,
@@ -716,6 +723,8 @@ def main():
     ap.add_argument("--layers", type=int, default=N_LAYERS)
     ap.add_argument("--pf-tokens", type=int, default=4096)
     ap.add_argument("--pf-steps", type=int, default=3)
+    ap.add_argument("--ep-dispatch", choices=["nccl", "peer"], default="peer",
+                    help="token exchange of the expert-parallel prefill (N > 1): NCCL all-to-all, or this library's peer-memory kernels")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-lmhead", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the GEMV size sweep")

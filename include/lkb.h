@@ -401,6 +401,42 @@ int lkb_pf_qknr(const float * Y, const float * qn, const float * kn, int P, void
                 lkb_stream_t st);
 int lkb_pf_attn(const void * qh, int m, int P, const void * kc, const void * vc, float * o, lkb_stream_t st);
 
+/* ---- expert-parallel prefill over NVLink peer memory (no host round trip, no NCCL on the data path) ----------------
+ * No counterpart in the reference (it is single-GPU).  Every rank owns four buffers in symmetric memory, mapped into
+ * every peer; lkb_ep_peers holds the G peer views of each (index = rank, own rank included):
+ *   cmat   int[G*G]            count matrix, row s = rows rank s sends to each rank
+ *   flags  int[3*8]            arrival flags (phase 0 counts, 1 dispatched rows, 2 returned rows) per source rank
+ *   recv   byte[cap][2576]     dispatched rows (LKB_EP_ROW_BYTES each), cap = worst case = every slot of the chunk
+ *   dback  float[slots][2048]  this rank's D rows, in its send order
+ * epoch must grow by one per layer call (flags are never reset); status (device int, 0 = fine) receives a code when a
+ * bounded wait expires: 1 counts, 2 / 3 / 4 = lkb_ep_wait of phase 0 / 1 / 2.  A wait lasts at most the limit set by
+ * lkb_ep_set_wait_limit_ms (default 5000 ms; 1..60000); once a code is recorded the later waits return at once.
+ * lkb_ep_counts_exchange: dcnt[G] = rows I send to each rank; leaves offs[3*G+1] (send bases, receive offsets, return
+ *   bases, rows received).   lkb_ep_pack_push: row p of my send order -> its owner's recv buffer; doff[g] = first
+ *   position of destination g in my send order; pos[slot] = p.   lkb_ep_push_back: my received rows' D -> home ranks.
+ * The *_dev entries are the plan / unpack kernels with the live row count read from device memory. */
+typedef struct {
+    void * cmat[8];
+    void * flags[8];
+    void * recv[8];
+    void * dback[8];
+} lkb_ep_peers;
+/* No counterpart in the reference: the exchange over peer memory described above. */
+int lkb_ep_set_wait_limit_ms(int ms);
+int lkb_ep_counts_exchange(const int * dcnt, const lkb_ep_peers * peers, int me, int G, int epoch, int * offs, int * status,
+                           lkb_stream_t st);
+/* No counterpart in the reference: dispatch, arrival wait and return of the exchange described above. */
+int lkb_ep_pack_push(lkb_pf_act a, const float * inv, const int * idx, const int * send_order, const int * doff, const int * offs,
+                     int n, int experts_per_rank, const lkb_ep_peers * peers, int me, int G, int epoch, int * pos, unsigned * done,
+                     lkb_stream_t st);
+int lkb_ep_wait(const int * flags, int phase, int G, int epoch, int * status, lkb_stream_t st);
+int lkb_ep_push_back(const float * D, const int * offs, int max_rows, const lkb_ep_peers * peers, int me, int G, int epoch,
+                     unsigned * done, lkb_stream_t st);
+/* No counterpart in the reference: the unpack / count / scatter kernels with the live row count on the device. */
+int lkb_ep_unpack_rows_dev(const void * in, int n, const int * n_dev, lkb_pf_act a, float * inv, int * local_expert, lkb_stream_t st);
+int lkb_pf_moe_count_dev(const int * idx, int n, const int * n_dev, int * cnt, lkb_stream_t st);
+int lkb_pf_moe_scatter_dev(const int * idx, int n, const int * n_dev, const int * off, int * perm, lkb_stream_t st);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

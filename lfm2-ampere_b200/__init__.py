@@ -62,6 +62,11 @@ class StepScratch(C.Structure):
     _fields_ = [("mx", C.c_void_p), ("part", C.c_void_p)]
 
 
+class EpPeers(C.Structure):
+    """lkb_ep_peers"""
+    _fields_ = [("cmat", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("recv", C.c_void_p * 8), ("dback", C.c_void_p * 8)]
+
+
 class PfGemm(C.Structure):
     """lkb_pf_gemm"""
     _fields_ = [("qs", C.c_void_p * 3), ("d", C.c_void_p * 3), ("seg_end", C.c_int * 3), ("N", C.c_int),

@@ -10,7 +10,7 @@ import ctypes as C
 
 import torch
 
-from . import MixerLayer, MoeLayer, MoeScratch, NormProd, PfAct, PfGemm, StepScratch, check, lib
+from . import EpPeers, MixerLayer, MoeLayer, MoeScratch, NormProd, PfAct, PfGemm, StepScratch, check, lib
 
 __all__ = [
     "ptr", "stream", "norm_prod", "pf_act", "make_pf_gemm",
@@ -25,6 +25,8 @@ __all__ = [
     "k_attn_split", "k_attn_combine", "k_qk_norm_rope", "k_shortconv", "ATTN_SPLIT", "ATTN_PARTW",
     "mixer_layer_desc", "step_scratch", "decode_layers",
     "k_pf_embed", "k_pf_conv", "k_pf_conv_hist", "k_pf_qknr", "k_pf_attn",
+    "ep_peers", "ep_set_wait_limit_ms", "ep_counts_exchange", "ep_pack_push", "ep_wait", "ep_push_back", "ep_unpack_rows_dev", "k_pf_moe_count_dev",
+    "k_pf_moe_scatter_dev",
 ]
 
 
@@ -362,3 +364,45 @@ def k_pf_qknr(Y, qn, kn, P, qh, kc, vc, m, theta=1e7):
 
 def k_pf_attn(qh, m, P, kc, vc, o):
     check(lib.lkb_pf_attn(ptr(qh), m, P, ptr(kc), ptr(vc), ptr(o), stream()), "k_pf_attn")
+
+
+# ------------------------------------------------ expert-parallel exchange over peer memory --
+def ep_peers(cmat_ptrs, flag_ptrs, recv_ptrs, dback_ptrs):
+    """lkb_ep_peers from four lists of per-rank device addresses (ints)."""
+    p = EpPeers()
+    for g, (a, b, c_, d) in enumerate(zip(cmat_ptrs, flag_ptrs, recv_ptrs, dback_ptrs)):
+        p.cmat[g], p.flags[g], p.recv[g], p.dback[g] = a, b, c_, d
+    return p
+
+
+def ep_counts_exchange(dcnt, peers, me, G, epoch, offs, status):
+    check(lib.lkb_ep_counts_exchange(ptr(dcnt), C.byref(peers), me, G, epoch, ptr(offs), ptr(status), stream()), "ep_counts_exchange")
+
+
+def ep_pack_push(a, inv, idx, send_order, doff, offs, n, experts_per_rank, peers, me, G, epoch, pos, done):
+    check(lib.lkb_ep_pack_push(a, ptr(inv), ptr(idx), ptr(send_order), ptr(doff), ptr(offs), n, experts_per_rank, C.byref(peers),
+                               me, G, epoch, ptr(pos), ptr(done), stream()), "ep_pack_push")
+
+
+def ep_set_wait_limit_ms(ms):
+    check(lib.lkb_ep_set_wait_limit_ms(int(ms)), "ep_set_wait_limit_ms")
+
+
+def ep_wait(flags, phase, G, epoch, status):
+    check(lib.lkb_ep_wait(ptr(flags), phase, G, epoch, ptr(status), stream()), "ep_wait")
+
+
+def ep_push_back(D, offs, max_rows, peers, me, G, epoch, done):
+    check(lib.lkb_ep_push_back(ptr(D), ptr(offs), max_rows, C.byref(peers), me, G, epoch, ptr(done), stream()), "ep_push_back")
+
+
+def ep_unpack_rows_dev(buf, n, n_dev, a, inv, local_expert):
+    check(lib.lkb_ep_unpack_rows_dev(ptr(buf), n, ptr(n_dev), a, ptr(inv), ptr(local_expert), stream()), "ep_unpack_rows_dev")
+
+
+def k_pf_moe_count_dev(idx, n, n_dev, cnt):
+    check(lib.lkb_pf_moe_count_dev(ptr(idx), n, ptr(n_dev), ptr(cnt), stream()), "k_pf_moe_count_dev")
+
+
+def k_pf_moe_scatter_dev(idx, n, n_dev, off, perm):
+    check(lib.lkb_pf_moe_scatter_dev(ptr(idx), n, ptr(n_dev), ptr(off), ptr(perm), stream()), "k_pf_moe_scatter_dev")

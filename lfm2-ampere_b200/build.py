@@ -14,7 +14,7 @@ import sys
 HERE = pathlib.Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OUT = HERE / "liblkb.so"
-SOURCES = ["lkb_decode.cu", "lkb_prefill.cu", "lkb_gemm_tc.cu", "lkb_fused.cu", "lkb_lmhead.cu", "lkb_mixer.cu", "lkb_pfmix.cu"]
+SOURCES = ["lkb_decode.cu", "lkb_prefill.cu", "lkb_gemm_tc.cu", "lkb_fused.cu", "lkb_lmhead.cu", "lkb_mixer.cu", "lkb_pfmix.cu", "lkb_ep.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "-Xcompiler", "-O3", "-shared", "-cudart", "static"]
 

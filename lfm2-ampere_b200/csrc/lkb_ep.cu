@@ -1,0 +1,219 @@
+// lkb_ep.cu - expert-parallel prefill over NVLink peer memory: the token exchange without a host round trip.
+//
+// One process per GPU.  Every rank owns four buffers in symmetric memory (same size on every rank, each mapped into
+// every peer): the G x G count matrix, three rows of arrival flags, the receive buffer for dispatched rows and the
+// buffer its own D rows come back into.  Kernels write straight into a PEER's buffers with ordinary stores over
+// NVLink and publish them with a system-scope release store of the layer's epoch into that peer's flag word; the
+// consumer polls its OWN flag words (local memory) with acquire loads.  Plain stores only: nothing here goes
+// through the switch's reduction or broadcast units, and no bulk-copy engine touches peer memory.  Every wait is bounded: on expiry the kernel records a code in the caller's status word and returns.
+//
+// Order inside a layer (all on the rank's one stream):
+//   counts_exchange   my row of the count matrix -> every rank (so every rank knows who sends how much to whom);
+//                     wait for all G rows; derive this rank's offsets
+//   pack_push         a dispatched slot's 2576-byte row goes straight into its owner's receive buffer at
+//                     (rows lower ranks send there) + (its index among my rows for that owner): the owner sees
+//                     source-ascending, slot-ascending rows -- the order that makes results bit-identical to 1 GPU
+//   wait(rows)        then unpack / count / plan / scatter / grouped GEMMs with the row count read from device memory
+//   push_back         D rows return to the slot's home rank, into its return buffer in ITS send order
+//   wait(back)        then the rank-order combine
+// A rank can be at most one phase ahead of its slowest peer, which is what makes buffer reuse across layers safe.
+#include "lkb_device.cuh"
+
+#define EP_ROW_BYTES (LKB_HIDDEN + (LKB_HIDDEN / 32) * 8 + 16)        // == LKB_EP_ROW_BYTES
+#define EP_MAX_RANKS 8
+#define EP_SPIN      (1u << 26)
+
+struct EpPeers {                      // peer views of the four symmetric buffers, indexed by rank
+    int *           cmat[EP_MAX_RANKS];
+    int *           flags[EP_MAX_RANKS];
+    unsigned char * recv[EP_MAX_RANKS];
+    float *         dback[EP_MAX_RANKS];
+};
+
+__device__ __forceinline__ void ep_st_release(int * p, int v) { asm volatile("st.release.sys.global.s32 [%0], %1;" :: "l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ int ep_ld_acquire(const int * p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long ep_now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Thread s waits until flags[phase][s] reaches epoch.  The wait ends after limit_ns (and, should the timer stand
+// still, after EP_SPIN polls): it then records `code` in *status and returns false; a code already there ends it too.
+__device__ __forceinline__ bool ep_wait_flag(const int * flags, int phase, int s, int epoch, int * status, int code,
+                                             unsigned long long limit_ns) {
+    const int * f = flags + phase * EP_MAX_RANKS + s;
+    const unsigned long long t0 = ep_now_ns();
+    for (unsigned i = 0; i < EP_SPIN; ++i) {
+        if (ep_ld_acquire(f) >= epoch) return true;
+        if ((i & 63u) == 63u) {
+            if (*(volatile int *) status != 0) return false;
+            if (ep_now_ns() - t0 > limit_ns) break;
+        }
+    }
+    atomicCAS(status, 0, code);
+    return false;
+}
+
+// offs layout (ints): [0, G) send_base[g]: first row of mine inside rank g's receive buffer
+//                     [G, 2G) recv_off[s]: first row of source s inside my receive buffer
+//                     [2G, 3G) back_base[s]: first row of my block inside source s's return buffer (its send order)
+//                     [3G] n_recv
+__global__ void __launch_bounds__(64) k_ep_counts_exchange(const int * __restrict__ dcnt, EpPeers P, int me, int G, int epoch,
+                                                           int * __restrict__ offs, int * __restrict__ status,
+                                                           unsigned long long limit_ns) {
+    const int t = threadIdx.x;
+    if (t < G * G) P.cmat[t / G][me * G + (t % G)] = dcnt[t % G];       // my row, into every rank's matrix
+    __threadfence_system();
+    __syncthreads();
+    if (t < G) ep_st_release(P.flags[t] + 0 * EP_MAX_RANKS + me, epoch);
+    __shared__ int ok;
+    if (t == 0) ok = 1;
+    __syncthreads();
+    if (t < G && !ep_wait_flag(P.flags[me], 0, t, epoch, status, 1, limit_ns)) ok = 0;
+    __syncthreads();
+    if (!ok) return;
+    const int * C = P.cmat[me];                                          // my copy: C[s*G + g] = rows s sends to g
+    if (t < G) {
+        int sb = 0, ro = 0, bb = 0;
+        for (int s = 0; s < me; ++s) sb += __ldcg(C + s * G + t);        // rows lower ranks send to rank t
+        for (int s = 0; s < t; ++s) ro += __ldcg(C + s * G + me);        // rows lower sources send to me
+        for (int g = 0; g < me; ++g) bb += __ldcg(C + t * G + g);        // rows source t sends to lower ranks
+        offs[t] = sb; offs[G + t] = ro; offs[2 * G + t] = bb;
+    }
+    if (t == 0) {
+        int n = 0;
+        for (int s = 0; s < G; ++s) n += __ldcg(C + s * G + me);
+        offs[3 * G] = n;
+    }
+}
+
+// Row p of my send order (slot send_order[p], destination rank = its expert's owner) -> the owner's receive buffer.
+// doff[g] = first position of destination g in my send order.  The last CTA to finish publishes the rows.
+__global__ void __launch_bounds__(192) k_ep_pack_push(const int8_t * __restrict__ aqs, const float2 * __restrict__ asc,
+                                                      const float * __restrict__ inv, const int * __restrict__ idx,
+                                                      const int * __restrict__ send_order, const int * __restrict__ doff,
+                                                      const int * __restrict__ offs, int experts_per_rank, EpPeers P, int me, int G,
+                                                      int epoch, int * __restrict__ pos, unsigned * __restrict__ done) {
+    const int p = blockIdx.x, i = threadIdx.x;
+    const int slot = send_order[p], t = slot >> 2;
+    const int e = idx[slot], dest = e / experts_per_rank;
+    uint4 * row = reinterpret_cast<uint4 *>(P.recv[dest] + (size_t) (offs[dest] + p - doff[dest]) * EP_ROW_BYTES);
+    if (i < 128) row[i] = reinterpret_cast<const uint4 *>(aqs + (size_t) t * LKB_HIDDEN)[i];
+    else if (i < 160) row[i] = reinterpret_cast<const uint4 *>(asc + (size_t) t * (LKB_HIDDEN / 32))[i - 128];
+    else if (i == 160) {
+        row[160] = make_uint4(__float_as_uint(inv[t]), (unsigned) (e % experts_per_rank), 0u, 0u);
+        pos[slot] = p;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (i == 0 && atomicAdd(done, 1u) == gridDim.x - 1) {
+        *done = 0u;
+        __threadfence_system();
+        for (int g = 0; g < G; ++g) ep_st_release(P.flags[g] + 1 * EP_MAX_RANKS + me, epoch);
+    }
+}
+
+// Wait until every source has published `phase` for this epoch.
+__global__ void __launch_bounds__(32) k_ep_wait(const int * __restrict__ flags, int phase, int G, int epoch, int * __restrict__ status,
+                                                unsigned long long limit_ns) {
+    if ((int) threadIdx.x < G) ep_wait_flag(flags, phase, threadIdx.x, epoch, status, 2 + phase, limit_ns);
+}
+
+// Received row r (source s = the block it lies in, j = its index inside that block) -> source s's return buffer,
+// row back_base[s] + j of ITS send order.  grid = upper bound of rows; rows >= n_recv exit.  One CTA per row.
+__global__ void __launch_bounds__(256) k_ep_push_back(const float * __restrict__ D, const int * __restrict__ offs, EpPeers P, int me, int G,
+                                                      int epoch, unsigned * __restrict__ done) {
+    const int n = offs[3 * G];
+    for (int r = blockIdx.x; r < n; r += gridDim.x) {
+        int s = 0;
+        while (s + 1 < G && r >= offs[G + s + 1]) ++s;
+        const int j = r - offs[G + s];
+        const uint4 * src = reinterpret_cast<const uint4 *>(D + (size_t) r * LKB_HIDDEN);
+        uint4 * dst = reinterpret_cast<uint4 *>(P.dback[s] + (size_t) (offs[2 * G + s] + j) * LKB_HIDDEN);
+        dst[threadIdx.x] = src[threadIdx.x];
+        dst[threadIdx.x + 256] = src[threadIdx.x + 256];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(done, 1u) == gridDim.x - 1) {
+        *done = 0u;
+        __threadfence_system();
+        for (int g = 0; g < G; ++g) ep_st_release(P.flags[g] + 2 * EP_MAX_RANKS + me, epoch);
+    }
+    (void) me;
+}
+
+static int ep_peers(EpPeers & P, const void * const * cmat, const void * const * flags, const void * const * recv,
+                    const void * const * dback, int G) {
+    if (!cmat || !flags || !recv || !dback) return LKB_ERR_NULL;
+    if (G < 1 || G > EP_MAX_RANKS) return LKB_ERR_SHAPE;
+    for (int g = 0; g < G; ++g) {
+        if (!cmat[g] || !flags[g] || !recv[g] || !dback[g]) return LKB_ERR_NULL;
+        P.cmat[g] = (int *) cmat[g]; P.flags[g] = (int *) flags[g]; P.recv[g] = (unsigned char *) recv[g]; P.dback[g] = (float *) dback[g];
+    }
+    return LKB_OK;
+}
+
+static unsigned long long g_ep_limit_ns = 5000ull * 1000000ull;
+
+extern "C" {
+
+int lkb_ep_set_wait_limit_ms(int ms) {
+    if (ms <= 0 || ms > 60000) return LKB_ERR_SHAPE;
+    g_ep_limit_ns = (unsigned long long) ms * 1000000ull;
+    return LKB_OK;
+}
+
+int lkb_ep_counts_exchange(const int * dcnt, const lkb_ep_peers * peers, int me, int G, int epoch, int * offs, int * status,
+                           lkb_stream_t st) {
+    if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
+    if (!dcnt || !peers || !offs || !status) return LKB_ERR_NULL;
+    EpPeers P = {};
+    const int r = ep_peers(P, peers->cmat, peers->flags, peers->recv, peers->dback, G);
+    if (r != LKB_OK) return r;
+    if (me < 0 || me >= G || epoch <= 0) return LKB_ERR_SHAPE;
+    k_ep_counts_exchange<<<1, 64, 0, (cudaStream_t) st>>>(dcnt, P, me, G, epoch, offs, status, g_ep_limit_ns);
+    return lkb_check_launch();
+}
+
+int lkb_ep_pack_push(lkb_pf_act a, const float * inv, const int * idx, const int * send_order, const int * doff, const int * offs,
+                     int n, int experts_per_rank, const lkb_ep_peers * peers, int me, int G, int epoch, int * pos, unsigned * done,
+                     lkb_stream_t st) {
+    if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
+    if (!a.qs || !a.sc || !inv || !idx || !send_order || !doff || !offs || !peers || !pos || !done) return LKB_ERR_NULL;
+    EpPeers P = {};
+    const int r = ep_peers(P, peers->cmat, peers->flags, peers->recv, peers->dback, G);
+    if (r != LKB_OK) return r;
+    if (n <= 0 || experts_per_rank <= 0 || me < 0 || me >= G) return LKB_ERR_SHAPE;
+    k_ep_pack_push<<<n, 192, 0, (cudaStream_t) st>>>(reinterpret_cast<const int8_t *>(a.qs), reinterpret_cast<const float2 *>(a.sc), inv,
+                                                     idx, send_order, doff, offs, experts_per_rank, P, me, G, epoch, pos, done);
+    return lkb_check_launch();
+}
+
+int lkb_ep_wait(const int * flags, int phase, int G, int epoch, int * status, lkb_stream_t st) {
+    if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
+    if (!flags || !status) return LKB_ERR_NULL;
+    if (phase < 0 || phase > 2 || G < 1 || G > EP_MAX_RANKS) return LKB_ERR_SHAPE;
+    k_ep_wait<<<1, 32, 0, (cudaStream_t) st>>>(flags, phase, G, epoch, status, g_ep_limit_ns);
+    return lkb_check_launch();
+}
+
+int lkb_ep_push_back(const float * D, const int * offs, int max_rows, const lkb_ep_peers * peers, int me, int G, int epoch,
+                     unsigned * done, lkb_stream_t st) {
+    if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
+    if (!D || !offs || !peers || !done) return LKB_ERR_NULL;
+    EpPeers P = {};
+    const int r = ep_peers(P, peers->cmat, peers->flags, peers->recv, peers->dback, G);
+    if (r != LKB_OK) return r;
+    if (max_rows <= 0 || me < 0 || me >= G) return LKB_ERR_SHAPE;
+    int grid = lkb_context().sm_count * 8;                   // rows are walked with a grid stride: the live count is on the device
+    if (grid > max_rows) grid = max_rows;
+    k_ep_push_back<<<grid, 256, 0, (cudaStream_t) st>>>(D, offs, P, me, G, epoch, done);
+    return lkb_check_launch();
+}
+
+}  // extern "C"

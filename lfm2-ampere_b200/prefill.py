@@ -99,12 +99,21 @@ class PrefillStackEP:
     Rank r holds tokens [r*m/G, (r+1)*m/G) of the chunk and the experts [r*64/G, (r+1)*64/G) of every
     layer.  Norm, router, selection and the combine run on the token's home rank; the two grouped GEMMs
     run on the expert's owner, fed by a token all-to-all (see ep.py).  Results are bit-identical to
-    PrefillStack on one GPU."""
+    PrefillStack on one GPU.
 
-    def __init__(self, layers, m_total, rank, world, device="cuda", group=None):
+    dispatch="nccl": three all_to_all_single calls per layer and one host sync for the split sizes.
+    dispatch="peer": the exchange kernels of lkb_ep.cu write rows straight into the owner's buffers in symmetric
+    memory (NVLink peer stores + release/acquire flags); counts stay on the device, the host never waits."""
+
+    def __init__(self, layers, m_total, rank, world, device="cuda", group=None, dispatch="nccl"):
         from . import ep as _ep
         self._ep = _ep
         assert m_total % world == 0 and E % world == 0
+        if dispatch not in ("nccl", "peer"):
+            raise ValueError("dispatch must be 'nccl' or 'peer'")
+        if dispatch == "peer" and world > 8:
+            raise ValueError("peer dispatch covers one NVSwitch domain: at most 8 ranks")
+        self.dispatch = dispatch
         self.rank, self.world, self.group = rank, world, group
         self.layers = layers
         self.shards = [shard_layer(l, rank, world) for l in layers]
@@ -152,14 +161,85 @@ class PrefillStackEP:
         self.pos = torch.zeros(ns, **i32)
         self.counts = torch.zeros(2, self.world, **i32)         # [0] what I send to each rank, [1] what I receive
         self.counts_host = torch.zeros(2, self.world, dtype=torch.int32).pin_memory()
-        self.send_buf = torch.zeros(ns, api.EP_ROW_BYTES, dtype=torch.uint8, device=device)
-        self.recv_buf = torch.zeros(self.cap, api.EP_ROW_BYTES, dtype=torch.uint8, device=device)
+        if self.dispatch == "peer":
+            self._alloc_peer(device)                            # recv_buf and d_back live in symmetric memory
+        else:
+            self.send_buf = torch.zeros(ns, api.EP_ROW_BYTES, dtype=torch.uint8, device=device)
+            self.recv_buf = torch.zeros(self.cap, api.EP_ROW_BYTES, dtype=torch.uint8, device=device)
+            self.d_back = torch.zeros(ns, H, dtype=torch.float32, device=device)
         self.r_qs = torch.zeros(self.cap, H, dtype=torch.int8, device=device)
         self.r_sc = torch.zeros(self.cap, H // 32, 2, dtype=torch.float32, device=device)
         self.r_inv = torch.zeros(self.cap, dtype=torch.float32, device=device)
         self.r_le = torch.zeros(self.cap, **i32)
         self.r_act = api.pf_act(self.r_qs, self.r_sc)
-        self.d_back = torch.zeros(ns, H, dtype=torch.float32, device=device)
+
+    def _alloc_peer(self, device):
+        """Symmetric buffers of the peer dispatch (count matrix, flags, receive rows, returned D rows) carved out
+        of one allocation, and the per-rank address tables the kernels take."""
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        G, ns = self.world, self.m * TOPK
+        al = lambda n: (n + 255) // 256 * 256
+        sizes = [al(4 * G * G), al(4 * 3 * 8), al(self.cap * api.EP_ROW_BYTES), al(ns * H * 4)]
+        offs = [0]
+        for n in sizes[:-1]:
+            offs.append(offs[-1] + n)
+        dev = torch.device(device) if not isinstance(device, torch.device) else device
+        if dev.index is None:
+            dev = torch.device("cuda", torch.cuda.current_device())
+        self.symm = symm.empty(sum(sizes), dtype=torch.uint8, device=dev)
+        self.symm.zero_()
+        grp = self.group if self.group is not None else dist.group.WORLD
+        self.symm_handle = symm.rendezvous(self.symm, grp)
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)                             # nobody publishes a flag before everyone has zeroed
+        base = [int(b) for b in self.symm_handle.buffer_ptrs]
+        self.peers = api.ep_peers(*[[b + o for b in base] for o in offs])
+        cut = lambda k: self.symm[offs[k]:offs[k] + sizes[k]]
+        self.flags = cut(1).view(torch.int32)
+        self.recv_buf = cut(2)[:self.cap * api.EP_ROW_BYTES].view(self.cap, api.EP_ROW_BYTES)
+        self.d_back = cut(3)[:ns * H * 4].view(torch.float32).view(ns, H)
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.ep_offs = torch.zeros(3 * G + 1, **i32)
+        self.ep_status = torch.zeros(1, **i32)
+        self.ep_done = torch.zeros(2, **i32)
+        self.nrecv = torch.zeros(max(1, len(self.layers)), **i32)
+        self.epoch = 0
+
+    def status(self):
+        """0, or the code of the exchange wait that ran out (peer dispatch)."""
+        return int(self.ep_status.item()) if hasattr(self, "ep_status") else 0
+
+    def _experts_dev(self, li):
+        """_experts with the received-row count left on the device (peer dispatch)."""
+        sh, n_dev, cap = self.shards[li], self.ep_offs[3 * self.world:], self.cap
+        api.zero_i32(self.cnt, E)
+        api.k_pf_moe_count_dev(self.r_le, cap, n_dev, self.cnt)
+        api.k_pf_moe_plan(self.cnt, self.off, self.tiles, self.ntiles)
+        api.k_pf_moe_scatter_dev(self.r_le, cap, n_dev, self.off, self.perm)
+        g = api.make_pf_gemm([(sh.gate_qs, sh.gate_d), (sh.up_qs, sh.up_d)], [I, I, I], I, H // 32, self.r_qs, self.r_sc,
+                             exp_stride=I * (H // 32), perm=self.perm, tiles=self.tiles, ntiles=self.ntiles,
+                             a_shift=0, scale=self.r_inv, oqs=self.a2_qs, osc=self.a2_sc, okb=I // 32)
+        api.pf_gemm_swiglu(g, self.max_tiles)
+        dn = api.make_pf_gemm([(sh.down_qs, sh.down_d)], [H, H, H], H, I // 32, self.a2_qs, self.a2_sc,
+                              exp_stride=H * (I // 32), perm=self.perm, tiles=self.tiles, ntiles=self.ntiles,
+                              a_shift=0, out=self.D, out_ld=H)
+        api.pf_gemm_moe(dn, self.max_tiles)
+
+    def _exchange_peer(self, i):
+        """counts -> rows to their owners -> experts -> D rows home, all on the stream."""
+        G, ns, per, me = self.world, self.m * TOPK, E // self.world, self.rank
+        self.epoch += 1
+        ep = self.epoch
+        api.ep_counts_exchange(self.dcnt, self.peers, me, G, ep, self.ep_offs, self.ep_status)
+        api.ep_pack_push(self.a, self.inv, self.idx, self.send_order, self.doff, self.ep_offs, ns, per, self.peers, me, G, ep,
+                         self.pos, self.ep_done[0:])
+        api.ep_wait(self.flags, 1, G, ep, self.ep_status)
+        api.ep_unpack_rows_dev(self.recv_buf, self.cap, self.ep_offs[3 * G:], self.r_act, self.r_inv, self.r_le)
+        self._experts_dev(i)
+        api.ep_push_back(self.D, self.ep_offs, self.cap, self.peers, me, G, ep, self.ep_done[1:])
+        api.ep_wait(self.flags, 2, G, ep, self.ep_status)
+        self.nrecv[i:i + 1].copy_(self.ep_offs[3 * G:3 * G + 1])
 
     def _experts(self, li, n):
         """count / plan / scatter + the two grouped GEMMs over the n slots received for this rank's experts."""
@@ -184,7 +264,7 @@ class PrefillStackEP:
         import torch.distributed as dist
         l, m, G = self.layers[i], self.m, self.world
         ns, per = m * TOPK, E // G
-        if not hasattr(self, "send_buf"):
+        if not hasattr(self, "send_order"):
             self._alloc_ep(self.X.device)
         api.k_pf_norm(self.X, l.norm_w, 0, self.a, self.inv, self.h32, m)
         # the router form follows the CHUNK size, as on one GPU (ref: src/engine.cu:1170-1176)
@@ -198,6 +278,11 @@ class PrefillStackEP:
         api.k_pf_moe_count(self.dest, ns, self.dcnt)
         api.k_pf_moe_plan(self.dcnt, self.doff, self.dtiles, self.dnt)
         api.k_pf_moe_scatter(self.dest, ns, self.doff, self.send_order)
+        nxt = self.layers[(i + 1) % len(self.layers)]
+        if self.dispatch == "peer":
+            self._exchange_peer(i)
+            api.k_pf_moe_combine_norm_gather(self.X, self.d_back, self.pos, self.w, nxt.norm_w, self.an, self.n_inv, m)
+            return
         self.counts[0].copy_(self.dcnt[:G])
         dist.all_to_all_single(self.counts[1], self.counts[0], group=self.group)
         api.ep_pack_rows(self.a, self.inv, self.idx, self.send_order, ns, per, self.send_buf, self.pos)
@@ -211,10 +296,11 @@ class PrefillStackEP:
         self._experts(i, n)
         dist.all_to_all_single(self.d_back, self.D[:n], output_split_sizes=sc, input_split_sizes=rc, group=self.group)
         self.recv_slots.append(n)
-        nxt = self.layers[(i + 1) % len(self.layers)]
         api.k_pf_moe_combine_norm_gather(self.X, self.d_back, self.pos, self.w, nxt.norm_w, self.an, self.n_inv, m)
 
     def step(self):
         self.recv_slots = []
         for i in range(len(self.layers)):
             self.layer(i)
+        if self.dispatch == "peer":
+            self.recv_slots = self.nrecv                       # device tensor: read it after the step, if at all

@@ -1,5 +1,6 @@
-"""Expert-parallel prefill on 2+ GPUs == the single-GPU prefill, bit for bit.  Needs >= 2 B200s
-(skipped on a single-GPU box)."""
+"""Expert-parallel prefill on 2+ GPUs == the single-GPU prefill, bit for bit, through both exchanges: NCCL
+all-to-all and the peer-memory kernels.  Needs >= 2 B200s (skipped on a single-GPU box).  The exchange's bounded
+wait is exercised on one GPU with a flag that nothing sets."""
 import importlib
 import os
 import socket
@@ -18,7 +19,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, m, n_layers, out):
+def _worker(rank, world, port, m, n_layers, out, dispatch):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -30,17 +31,26 @@ def _worker(rank, world, port, m, n_layers, out):
     layers = synth.make_model(n_layers, seed=4242, device=f"cuda:{rank}", zipf_s=1.1)     # same model on every rank
     gen = torch.Generator(device=f"cuda:{rank}").manual_seed(9)
     X = torch.randn(m, 2048, device=f"cuda:{rank}", generator=gen)
-    ep = prefill.PrefillStackEP(layers, m, rank, world, device=f"cuda:{rank}")
+    ep = prefill.PrefillStackEP(layers, m, rank, world, device=f"cuda:{rank}", dispatch=dispatch)
     ml = m // world
     ep.X.copy_(X[rank * ml:(rank + 1) * ml])
     ep.step()
     torch.cuda.synchronize()
+    if dispatch == "peer":                                   # a second step over the same buffers: flags and epochs carry on
+        first = ep.X.clone()
+        ep.X.copy_(X[rank * ml:(rank + 1) * ml])
+        ep.step()
+        torch.cuda.synchronize()
+        assert torch.equal(first, ep.X)
     ref = prefill.PrefillStack(layers, m, device=f"cuda:{rank}")
     ref.X.copy_(X)
     ref.step()
     torch.cuda.synchronize()
     ok = torch.equal(ep.X, ref.X[rank * ml:(rank + 1) * ml]) and bool(torch.isfinite(ep.X).all())
-    status = lkb.lib.lkb_pf_gemm_status()
+    status = lkb.lib.lkb_pf_gemm_status() | ep.status()
+    slots = torch.as_tensor(ep.recv_slots).sum().to(f"cuda:{rank}", torch.int64).reshape(1)
+    dist.all_reduce(slots)
+    ok = ok and int(slots.item()) == n_layers * m * 4        # every slot of the chunk was computed exactly once
     t = torch.tensor([1 if (ok and status == 0) else 0], device=f"cuda:{rank}")
     dist.all_reduce(t, op=dist.ReduceOp.MIN)
     if rank == 0:
@@ -48,11 +58,34 @@ def _worker(rank, world, port, m, n_layers, out):
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("dispatch", ["nccl", "peer"])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_ep_prefill_bitwise_equals_single_gpu(world, tmp_path):
+def test_ep_prefill_bitwise_equals_single_gpu(world, dispatch, tmp_path):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     out = str(tmp_path / "ok")
-    mp.spawn(_worker, args=(world, _free_port(), 512, 2, out), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), 512, 2, out, dispatch), nprocs=world, join=True)
     assert open(out).read() == "1"
+
+
+def test_ep_wait_runs_out_and_reports(lkb):
+    """A wait on a flag nobody publishes ends by itself, records its code, and leaves the context usable."""
+    lkb.init(0)
+    flags = torch.zeros(24, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lkb.ep_set_wait_limit_ms(200)
+    try:
+        flags[8:10] = 3                                       # phase 1, sources 0 and 1 have published epoch 3
+        lkb.ep_wait(flags, 1, 2, 3, status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        lkb.ep_wait(flags, 1, 2, 4, status)                   # epoch 4 never comes
+        torch.cuda.synchronize()
+        assert int(status.item()) == 3
+        lkb.ep_wait(flags, 2, 2, 1, status)                   # a recorded code ends later waits at once, code unchanged
+        torch.cuda.synchronize()
+        assert int(status.item()) == 3
+    finally:
+        lkb.ep_set_wait_limit_ms(5000)
+    assert float(torch.ones(4, device="cuda").sum().item()) == 4.0
