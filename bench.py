@@ -354,11 +354,12 @@ def run_ours(args):
                 Yh.copy_(ps.X, non_blocking=True)
                 st.synchronize()
         pf_step()
-        if not ep and not args.no_graph:
-            # one CUDA graph for the step's ~9 launches per layer (the expert-parallel step has a host sync per layer)
+        if (not ep or args.ep_dispatch == "peer") and not args.no_graph:
+            # one CUDA graph for the step's launches (the NCCL exchange has a host sync per layer and cannot be captured)
             torch.cuda.synchronize()
+            barrier()
             pf_graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(pf_graph):
+            with torch.cuda.graph(pf_graph, capture_error_mode="thread_local"):
                 ps.step()
             pf_step()
         barrier()
@@ -408,7 +409,7 @@ def run_ours(args):
             dist.all_reduce(mx, op=dist.ReduceOp.MAX)
             dist.all_reduce(sm, op=dist.ReduceOp.SUM)
             imbalance = float(mx.item() / (sm.item() / world))
-            launches = None
+            launches = args.pf_steps * ps.launches_per_step * world
         else:
             cnt = ps.cnt.cpu().numpy()
             imbalance = float(cnt.max() / max(1.0, cnt.mean()))
@@ -427,7 +428,7 @@ def run_ours(args):
               "gpu_launches": launches,
               "roofline": {"bound": "tensor", "achieved": 2 * tmacs, "unit": "TOP/s (int8)",
                            "peak": (int8_peak or 4500.0) * world, "frac": 2 * tmacs / ((int8_peak or 4500.0) * world),
-                           "peak_kind": ("of measured here: torch._int_mm 8192^3, best of 5, per GPU" if int8_peak else
+                           "peak_kind": (f"of measured here: torch._int_mm 8192^3, best of 5, on rank 0's GPU, x {world} GPUs" if int8_peak else
                                          "of nominal dense int8 (MEASURED_PEAKS.json records no int8 figure)"),
                            "nominal_int8_tops": 4500.0,
                            "note": "the per-block fp32 scale epilogue on the CUDA cores, not the MMA, bounds this kernel"}}

@@ -408,7 +408,8 @@ int lkb_pf_attn(const void * qh, int m, int P, const void * kc, const void * vc,
  *   flags  int[3*8]            arrival flags (phase 0 counts, 1 dispatched rows, 2 returned rows) per source rank
  *   recv   byte[cap][2576]     dispatched rows (LKB_EP_ROW_BYTES each), cap = worst case = every slot of the chunk
  *   dback  float[slots][2048]  this rank's D rows, in its send order
- * epoch must grow by one per layer call (flags are never reset); status (device int, 0 = fine) receives a code when a
+ * epoch is a device int the caller zeroes once: lkb_ep_counts_exchange advances it by one per layer and the other
+ * kernels read it (flags are never reset, and nothing on the host changes from layer to layer); status (device int, 0 = fine) receives a code when a
  * bounded wait expires: 1 counts, 2 / 3 / 4 = lkb_ep_wait of phase 0 / 1 / 2.  A wait lasts at most the limit set by
  * lkb_ep_set_wait_limit_ms (default 5000 ms; 1..60000); once a code is recorded the later waits return at once.
  * lkb_ep_counts_exchange: dcnt[G] = rows I send to each rank; leaves offs[3*G+1] (send bases, receive offsets, return
@@ -423,15 +424,15 @@ typedef struct {
 } lkb_ep_peers;
 /* No counterpart in the reference: the exchange over peer memory described above. */
 int lkb_ep_set_wait_limit_ms(int ms);
-int lkb_ep_counts_exchange(const int * dcnt, const lkb_ep_peers * peers, int me, int G, int epoch, int * offs, int * status,
+int lkb_ep_counts_exchange(const int * dcnt, const lkb_ep_peers * peers, int me, int G, int * epoch, int * offs, int * status,
                            lkb_stream_t st);
 /* No counterpart in the reference: dispatch, arrival wait and return of the exchange described above. */
 int lkb_ep_pack_push(lkb_pf_act a, const float * inv, const int * idx, const int * send_order, const int * doff, const int * offs,
-                     int n, int experts_per_rank, const lkb_ep_peers * peers, int me, int G, int epoch, int * pos, unsigned * done,
+                     int n, int experts_per_rank, const lkb_ep_peers * peers, int me, int G, const int * epoch, int * pos, unsigned * done,
                      lkb_stream_t st);
-int lkb_ep_wait(const int * flags, int phase, int G, int epoch, int * status, lkb_stream_t st);
-int lkb_ep_push_back(const float * D, const int * offs, int max_rows, const lkb_ep_peers * peers, int me, int G, int epoch,
-                     unsigned * done, lkb_stream_t st);
+int lkb_ep_wait(const int * flags, int phase, int G, const int * epoch, int * status, lkb_stream_t st);
+int lkb_ep_push_back(const float * D, const int * offs, int max_rows, const lkb_ep_peers * peers, int me, int G,
+                     const int * epoch, unsigned * done, lkb_stream_t st);
 /* No counterpart in the reference: the unpack / count / scatter kernels with the live row count on the device. */
 int lkb_ep_unpack_rows_dev(const void * in, int n, const int * n_dev, lkb_pf_act a, float * inv, int * local_expert, lkb_stream_t st);
 int lkb_pf_moe_count_dev(const int * idx, int n, const int * n_dev, int * cnt, lkb_stream_t st);

@@ -376,12 +376,12 @@ def ep_peers(cmat_ptrs, flag_ptrs, recv_ptrs, dback_ptrs):
 
 
 def ep_counts_exchange(dcnt, peers, me, G, epoch, offs, status):
-    check(lib.lkb_ep_counts_exchange(ptr(dcnt), C.byref(peers), me, G, epoch, ptr(offs), ptr(status), stream()), "ep_counts_exchange")
+    check(lib.lkb_ep_counts_exchange(ptr(dcnt), C.byref(peers), me, G, ptr(epoch), ptr(offs), ptr(status), stream()), "ep_counts_exchange")
 
 
 def ep_pack_push(a, inv, idx, send_order, doff, offs, n, experts_per_rank, peers, me, G, epoch, pos, done):
     check(lib.lkb_ep_pack_push(a, ptr(inv), ptr(idx), ptr(send_order), ptr(doff), ptr(offs), n, experts_per_rank, C.byref(peers),
-                               me, G, epoch, ptr(pos), ptr(done), stream()), "ep_pack_push")
+                               me, G, ptr(epoch), ptr(pos), ptr(done), stream()), "ep_pack_push")
 
 
 def ep_set_wait_limit_ms(ms):
@@ -389,11 +389,11 @@ def ep_set_wait_limit_ms(ms):
 
 
 def ep_wait(flags, phase, G, epoch, status):
-    check(lib.lkb_ep_wait(ptr(flags), phase, G, epoch, ptr(status), stream()), "ep_wait")
+    check(lib.lkb_ep_wait(ptr(flags), phase, G, ptr(epoch), ptr(status), stream()), "ep_wait")
 
 
 def ep_push_back(D, offs, max_rows, peers, me, G, epoch, done):
-    check(lib.lkb_ep_push_back(ptr(D), ptr(offs), max_rows, C.byref(peers), me, G, epoch, ptr(done), stream()), "ep_push_back")
+    check(lib.lkb_ep_push_back(ptr(D), ptr(offs), max_rows, C.byref(peers), me, G, ptr(epoch), ptr(done), stream()), "ep_push_back")
 
 
 def ep_unpack_rows_dev(buf, n, n_dev, a, inv, local_expert):

@@ -8,7 +8,8 @@
 // through the switch's reduction or broadcast units, and no bulk-copy engine touches peer memory.  Every wait is bounded: on expiry the kernel records a code in the caller's status word and returns.
 //
 // Order inside a layer (all on the rank's one stream):
-//   counts_exchange   my row of the count matrix -> every rank (so every rank knows who sends how much to whom);
+//   counts_exchange   advance the epoch (a device int, so the whole step can be captured in a CUDA graph);
+//                     my row of the count matrix -> every rank (so every rank knows who sends how much to whom);
 //                     wait for all G rows; derive this rank's offsets
 //   pack_push         a dispatched slot's 2576-byte row goes straight into its owner's receive buffer at
 //                     (rows lower ranks send there) + (its index among my rows for that owner): the owner sees
@@ -62,10 +63,11 @@ __device__ __forceinline__ bool ep_wait_flag(const int * flags, int phase, int s
 //                     [G, 2G) recv_off[s]: first row of source s inside my receive buffer
 //                     [2G, 3G) back_base[s]: first row of my block inside source s's return buffer (its send order)
 //                     [3G] n_recv
-__global__ void __launch_bounds__(64) k_ep_counts_exchange(const int * __restrict__ dcnt, EpPeers P, int me, int G, int epoch,
+__global__ void __launch_bounds__(64) k_ep_counts_exchange(const int * __restrict__ dcnt, EpPeers P, int me, int G, int * __restrict__ epoch_dev,
                                                            int * __restrict__ offs, int * __restrict__ status,
                                                            unsigned long long limit_ns) {
     const int t = threadIdx.x;
+    const int epoch = *epoch_dev + 1;                                    // this layer's epoch; stored back at the end
     if (t < G * G) P.cmat[t / G][me * G + (t % G)] = dcnt[t % G];       // my row, into every rank's matrix
     __threadfence_system();
     __syncthreads();
@@ -88,6 +90,7 @@ __global__ void __launch_bounds__(64) k_ep_counts_exchange(const int * __restric
         int n = 0;
         for (int s = 0; s < G; ++s) n += __ldcg(C + s * G + me);
         offs[3 * G] = n;
+        *epoch_dev = epoch;                                              // every thread read the old value before the first barrier
     }
 }
 
@@ -97,7 +100,8 @@ __global__ void __launch_bounds__(192) k_ep_pack_push(const int8_t * __restrict_
                                                       const float * __restrict__ inv, const int * __restrict__ idx,
                                                       const int * __restrict__ send_order, const int * __restrict__ doff,
                                                       const int * __restrict__ offs, int experts_per_rank, EpPeers P, int me, int G,
-                                                      int epoch, int * __restrict__ pos, unsigned * __restrict__ done) {
+                                                      const int * __restrict__ epoch_dev, int * __restrict__ pos,
+                                                      unsigned * __restrict__ done) {
     const int p = blockIdx.x, i = threadIdx.x;
     const int slot = send_order[p], t = slot >> 2;
     const int e = idx[slot], dest = e / experts_per_rank;
@@ -113,20 +117,22 @@ __global__ void __launch_bounds__(192) k_ep_pack_push(const int8_t * __restrict_
     if (i == 0 && atomicAdd(done, 1u) == gridDim.x - 1) {
         *done = 0u;
         __threadfence_system();
+        const int epoch = *epoch_dev;
         for (int g = 0; g < G; ++g) ep_st_release(P.flags[g] + 1 * EP_MAX_RANKS + me, epoch);
     }
 }
 
 // Wait until every source has published `phase` for this epoch.
-__global__ void __launch_bounds__(32) k_ep_wait(const int * __restrict__ flags, int phase, int G, int epoch, int * __restrict__ status,
-                                                unsigned long long limit_ns) {
+__global__ void __launch_bounds__(32) k_ep_wait(const int * __restrict__ flags, int phase, int G, const int * __restrict__ epoch_dev,
+                                                int * __restrict__ status, unsigned long long limit_ns) {
+    const int epoch = *epoch_dev;
     if ((int) threadIdx.x < G) ep_wait_flag(flags, phase, threadIdx.x, epoch, status, 2 + phase, limit_ns);
 }
 
 // Received row r (source s = the block it lies in, j = its index inside that block) -> source s's return buffer,
 // row back_base[s] + j of ITS send order.  grid = upper bound of rows; rows >= n_recv exit.  One CTA per row.
 __global__ void __launch_bounds__(256) k_ep_push_back(const float * __restrict__ D, const int * __restrict__ offs, EpPeers P, int me, int G,
-                                                      int epoch, unsigned * __restrict__ done) {
+                                                      const int * __restrict__ epoch_dev, unsigned * __restrict__ done) {
     const int n = offs[3 * G];
     for (int r = blockIdx.x; r < n; r += gridDim.x) {
         int s = 0;
@@ -142,6 +148,7 @@ __global__ void __launch_bounds__(256) k_ep_push_back(const float * __restrict__
     if (threadIdx.x == 0 && atomicAdd(done, 1u) == gridDim.x - 1) {
         *done = 0u;
         __threadfence_system();
+        const int epoch = *epoch_dev;
         for (int g = 0; g < G; ++g) ep_st_release(P.flags[g] + 2 * EP_MAX_RANKS + me, epoch);
     }
     (void) me;
@@ -168,23 +175,23 @@ int lkb_ep_set_wait_limit_ms(int ms) {
     return LKB_OK;
 }
 
-int lkb_ep_counts_exchange(const int * dcnt, const lkb_ep_peers * peers, int me, int G, int epoch, int * offs, int * status,
+int lkb_ep_counts_exchange(const int * dcnt, const lkb_ep_peers * peers, int me, int G, int * epoch, int * offs, int * status,
                            lkb_stream_t st) {
     if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
-    if (!dcnt || !peers || !offs || !status) return LKB_ERR_NULL;
+    if (!dcnt || !peers || !epoch || !offs || !status) return LKB_ERR_NULL;
     EpPeers P = {};
     const int r = ep_peers(P, peers->cmat, peers->flags, peers->recv, peers->dback, G);
     if (r != LKB_OK) return r;
-    if (me < 0 || me >= G || epoch <= 0) return LKB_ERR_SHAPE;
+    if (me < 0 || me >= G) return LKB_ERR_SHAPE;
     k_ep_counts_exchange<<<1, 64, 0, (cudaStream_t) st>>>(dcnt, P, me, G, epoch, offs, status, g_ep_limit_ns);
     return lkb_check_launch();
 }
 
 int lkb_ep_pack_push(lkb_pf_act a, const float * inv, const int * idx, const int * send_order, const int * doff, const int * offs,
-                     int n, int experts_per_rank, const lkb_ep_peers * peers, int me, int G, int epoch, int * pos, unsigned * done,
+                     int n, int experts_per_rank, const lkb_ep_peers * peers, int me, int G, const int * epoch, int * pos, unsigned * done,
                      lkb_stream_t st) {
     if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
-    if (!a.qs || !a.sc || !inv || !idx || !send_order || !doff || !offs || !peers || !pos || !done) return LKB_ERR_NULL;
+    if (!a.qs || !a.sc || !inv || !idx || !send_order || !doff || !offs || !peers || !epoch || !pos || !done) return LKB_ERR_NULL;
     EpPeers P = {};
     const int r = ep_peers(P, peers->cmat, peers->flags, peers->recv, peers->dback, G);
     if (r != LKB_OK) return r;
@@ -194,18 +201,18 @@ int lkb_ep_pack_push(lkb_pf_act a, const float * inv, const int * idx, const int
     return lkb_check_launch();
 }
 
-int lkb_ep_wait(const int * flags, int phase, int G, int epoch, int * status, lkb_stream_t st) {
+int lkb_ep_wait(const int * flags, int phase, int G, const int * epoch, int * status, lkb_stream_t st) {
     if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
-    if (!flags || !status) return LKB_ERR_NULL;
+    if (!flags || !epoch || !status) return LKB_ERR_NULL;
     if (phase < 0 || phase > 2 || G < 1 || G > EP_MAX_RANKS) return LKB_ERR_SHAPE;
     k_ep_wait<<<1, 32, 0, (cudaStream_t) st>>>(flags, phase, G, epoch, status, g_ep_limit_ns);
     return lkb_check_launch();
 }
 
-int lkb_ep_push_back(const float * D, const int * offs, int max_rows, const lkb_ep_peers * peers, int me, int G, int epoch,
-                     unsigned * done, lkb_stream_t st) {
+int lkb_ep_push_back(const float * D, const int * offs, int max_rows, const lkb_ep_peers * peers, int me, int G,
+                     const int * epoch, unsigned * done, lkb_stream_t st) {
     if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
-    if (!D || !offs || !peers || !done) return LKB_ERR_NULL;
+    if (!D || !offs || !peers || !epoch || !done) return LKB_ERR_NULL;
     EpPeers P = {};
     const int r = ep_peers(P, peers->cmat, peers->flags, peers->recv, peers->dback, G);
     if (r != LKB_OK) return r;

@@ -115,6 +115,8 @@ class PrefillStackEP:
             raise ValueError("peer dispatch covers one NVSwitch domain: at most 8 ranks")
         self.dispatch = dispatch
         self.rank, self.world, self.group = rank, world, group
+        # this library's kernels per layer (memsets, the torch division and NCCL's own kernels not counted)
+        self.launches_per_step = (18 if dispatch == "peer" else 14) * len(layers)
         self.layers = layers
         self.shards = [shard_layer(l, rank, world) for l in layers]
         self.m = m_total // world
@@ -204,7 +206,7 @@ class PrefillStackEP:
         self.ep_status = torch.zeros(1, **i32)
         self.ep_done = torch.zeros(2, **i32)
         self.nrecv = torch.zeros(max(1, len(self.layers)), **i32)
-        self.epoch = 0
+        self.ep_epoch = torch.zeros(1, **i32)                      # advanced on the device, once per layer
 
     def status(self):
         """0, or the code of the exchange wait that ran out (peer dispatch)."""
@@ -229,8 +231,7 @@ class PrefillStackEP:
     def _exchange_peer(self, i):
         """counts -> rows to their owners -> experts -> D rows home, all on the stream."""
         G, ns, per, me = self.world, self.m * TOPK, E // self.world, self.rank
-        self.epoch += 1
-        ep = self.epoch
+        ep = self.ep_epoch
         api.ep_counts_exchange(self.dcnt, self.peers, me, G, ep, self.ep_offs, self.ep_status)
         api.ep_pack_push(self.a, self.inv, self.idx, self.send_order, self.doff, self.ep_offs, ns, per, self.peers, me, G, ep,
                          self.pos, self.ep_done[0:])

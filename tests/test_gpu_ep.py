@@ -42,6 +42,14 @@ def _worker(rank, world, port, m, n_layers, out, dispatch):
         ep.step()
         torch.cuda.synchronize()
         assert torch.equal(first, ep.X)
+        graph = torch.cuda.CUDAGraph()                       # nothing in the step depends on the host: it replays from a graph
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            ep.step()
+        for _ in range(2):
+            ep.X.copy_(X[rank * ml:(rank + 1) * ml])
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(first, ep.X)
     ref = prefill.PrefillStack(layers, m, device=f"cuda:{rank}")
     ref.X.copy_(X)
     ref.step()
@@ -76,14 +84,15 @@ def test_ep_wait_runs_out_and_reports(lkb):
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     lkb.ep_set_wait_limit_ms(200)
     try:
+        epoch = lambda e: torch.tensor([e], dtype=torch.int32, device="cuda")
         flags[8:10] = 3                                       # phase 1, sources 0 and 1 have published epoch 3
-        lkb.ep_wait(flags, 1, 2, 3, status)
+        lkb.ep_wait(flags, 1, 2, epoch(3), status)
         torch.cuda.synchronize()
         assert int(status.item()) == 0
-        lkb.ep_wait(flags, 1, 2, 4, status)                   # epoch 4 never comes
+        lkb.ep_wait(flags, 1, 2, epoch(4), status)                   # epoch 4 never comes
         torch.cuda.synchronize()
         assert int(status.item()) == 3
-        lkb.ep_wait(flags, 2, 2, 1, status)                   # a recorded code ends later waits at once, code unchanged
+        lkb.ep_wait(flags, 2, 2, epoch(1), status)                   # a recorded code ends later waits at once, code unchanged
         torch.cuda.synchronize()
         assert int(status.item()) == 3
     finally:
