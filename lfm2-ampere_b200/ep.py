@@ -79,3 +79,21 @@ def ep_moe_layer(idx, payloads, expert_fn, world, group=None, n_experts=N_EXPERT
     D = torch.empty_like(d_back)
     D.index_copy_(0, plan.send_order, d_back)                       # send order -> slot order
     return D, plan
+
+
+def peer_offsets(count_matrix, me):
+    """Offset tables of the peer-memory exchange on rank `me` (the arithmetic of k_ep_counts_exchange in
+    csrc/lkb_ep.cu, restated on the host for tests and for callers that plan on the CPU).
+
+    count_matrix[s][g] = rows rank s sends to rank g.  Returns (send_base, recv_off, back_base, n_recv):
+      send_base[g]  first row of my block inside rank g's receive buffer   = rows lower ranks send to g
+      recv_off[s]   first row of source s inside my receive buffer         = rows lower sources send to me
+      back_base[s]  first row of my block inside source s's return buffer  = rows s sends to lower ranks
+    Receive buffers are therefore source-ascending, return buffers are in the sender's own send order
+    (destination-ascending): exactly what all_to_all_single leaves with these split sizes."""
+    C = [list(map(int, row)) for row in count_matrix]
+    G = len(C)
+    send_base = [sum(C[s][g] for s in range(me)) for g in range(G)]
+    recv_off = [sum(C[s][me] for s in range(t)) for t in range(G)]
+    back_base = [sum(C[t][g] for g in range(me)) for t in range(G)]
+    return send_base, recv_off, back_base, sum(C[s][me] for s in range(G))

@@ -104,3 +104,49 @@ def _worker_skew(rank, world, port):
     assert torch.equal(D, torch.full((m_loc * 4, H), 2.0 * (rank + 1)))
     dist.barrier()
     dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,skew", [(2, 0.0), (4, 0.0), (8, 0.0), (8, 1.3), (4, 3.0)])
+def test_peer_offsets_place_rows_like_all_to_all(world, skew):
+    """The peer-memory exchange writes row p of a rank's send order to
+    send_base[dest] + (p - first position of dest), and returns received row r to
+    back_base[source] + (r - recv_off[source]).  Simulated for every rank at once: receive buffers must
+    equal the source-ascending concatenation an all-to-all produces, no row may be written twice, and the
+    return trip must land every row back at its own send position."""
+    ep = importlib.import_module("lfm2-ampere_b200.ep")
+    rng = np.random.default_rng(world * 10 + int(skew * 10))
+    m_loc = 48
+    p = 1.0 / np.arange(1, 65) ** skew
+    p /= p.sum()
+    plans, C = [], np.zeros((world, world), np.int64)
+    for r in range(world):
+        idx = np.stack([rng.choice(64, size=4, replace=False, p=p) for _ in range(m_loc)]).astype(np.int32)
+        plan = ep.EPPlan(torch.from_numpy(idx), world)
+        plans.append(plan)
+        C[r] = plan.send_counts
+    tables = [ep.peer_offsets(C, me) for me in range(world)]
+    recv = [np.full(int(C[:, g].sum()), -1, np.int64) for g in range(world)]      # holds (source << 32) | send position
+    for s in range(world):
+        send_base = tables[s][0]
+        doff = np.concatenate([[0], np.cumsum(C[s])[:-1]])
+        dest_of = np.repeat(np.arange(world), C[s])
+        for pos in range(plans[s].n_send):
+            g = int(dest_of[pos])
+            row = send_base[g] + pos - int(doff[g])
+            assert recv[g][row] == -1, "two rows written to one place"
+            recv[g][row] = (s << 32) | pos
+    for g in range(world):
+        expect = np.concatenate([(s << 32) | (np.concatenate([[0], np.cumsum(C[s])[:-1]])[g] + np.arange(C[s][g]))
+                                 for s in range(world)]) if len(recv[g]) else np.zeros(0, np.int64)
+        assert np.array_equal(recv[g], expect), "receive buffer is not the source-ascending all-to-all order"
+        assert tables[g][3] == len(recv[g])
+    back = [np.full(plans[s].n_send, -1, np.int64) for s in range(world)]
+    for g in range(world):
+        _, recv_off, back_base, n = tables[g]
+        for r in range(n):
+            s = max(t for t in range(world) if recv_off[t] <= r and C[t][g] > 0 and r < recv_off[t] + C[t][g])
+            dst = back_base[s] + r - recv_off[s]
+            assert back[s][dst] == -1
+            back[s][dst] = recv[g][r] & 0xFFFFFFFF
+    for s in range(world):
+        assert np.array_equal(back[s], np.arange(plans[s].n_send)), "a returned row missed its send position"
