@@ -25,7 +25,9 @@
 // freeing TMEM.
 #include "lkb_device.cuh"
 
+#ifndef TC_LW
 #define TC_LW        2              // loader warps; each loader thread serves TC_RPT tokens and TC_RPT weight rows
+#endif
 #define TC_RPT       (128 / (32 * TC_LW))
 #define TC_THREADS   ((TC_LW + 16 + 1) * 32)   // loaders, 16 epilogue warps, 1 MMA-issuing warp
 #define TC_LOADERS   (32 * TC_LW)
@@ -39,6 +41,17 @@
 #define TC_AHEAD     2              // stages of cp.async lookahead in the loaders
 #define TC_SPIN      (1u << 24)
 #define TC_MAX_TILES 1024           // 64-token plan tiles the work list can hold
+// Epilogue shape switches (defaults = the fastest measured on B200; the others are kept for ablation):
+#ifndef TC_LD8
+#define TC_LD8 1                     // 1: TMEM is read 8 columns at a time (four reads per block); 0: 16 columns (two reads)
+#endif
+#ifndef TC_FFMA2
+#define TC_FFMA2 1                   // 1: both FMAs of a value pair as fma.rn.f32x2 (same IEEE roundings, half the issue slots):
+                                     //    72.0 -> 65.8 ms per 40-layer step; with TC_LD8 0: 67.4 ms
+#endif
+#ifndef TC_UNROLLJ
+#define TC_UNROLLJ 1                 // 1: the four blocks of a stage unrolled, TMEM buffer index and parity static: 65.8 -> 65.1 ms
+#endif
 #ifndef TC_MAGIC
 #define TC_MAGIC 0                   // 1: int32 -> fp32 by the 1.5*2^23 bit trick (integer add + fp add) instead of
                                      //    cvt.rn.f32.s32; measured 8% slower than the convert on B200, kept as a switch
@@ -64,7 +77,14 @@ struct TcSmem {
     float    vbuf[TC_M][65];        // SwiGLU epilogue: v = silu(g)*u of 64 intermediate rows per token (+1: bank spread)
 };
 
-__device__ unsigned long long g_tc_prof[16];   // tuning: cycles spent per wait class (CTA 0)
+__device__ unsigned long long g_tc_prof[32];   // tuning: cycles spent per wait class (CTA 0)
+#if TC_PROF
+#define TC_TL_N 2048
+__device__ long long g_tc_tl[8][TC_TL_N];   // tuning: per-block timestamps of CTA 0 (MMA thread: 0-2, epilogue warps: 3-5, 6-7)
+#define TC_TL(row, b, v) do { if (blockIdx.x == 0 && (b) < TC_TL_N) g_tc_tl[row][b] = (v); } while (0)
+#else
+#define TC_TL(row, b, v) do { } while (0)
+#endif
 __device__ unsigned g_tc_status;     // 0, or the code of the first bounded wait that expired
 
 // ---- PTX -------------------------------------------------------------------
@@ -135,6 +155,11 @@ __device__ __forceinline__ void tc_ld16(unsigned taddr, int * r) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
                    "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_ld8(unsigned taddr, int * r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                  : "r"(taddr) : "memory");
 }
 // Two independent IEEE fused multiply-adds in one instruction (halves the issue slots of the epilogue).
@@ -396,10 +421,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
 #pragma unroll
                     for (int j = 0; j < TC_KB; ++j, ++blk) {
                         const int tb = blk % TC_TBUF;
+                        TC_TL(0, blk, TC_CLK());
                         if (!TC_TWAIT(pw_te, S, &S.tempty[tb], ((blk / TC_TBUF) & 1u) ^ 1u, 21u)) { ok = false; break; }
+                        TC_TL(1, blk, TC_CLK());
                         tc_fence_after();
                         tc_mma_i8(tmem + tb * TC_N, tc_desc(T.A[j]), tc_desc(T.B[j]), TC_IDESC);
                         tc_commit(&S.tfull[tb]);                    // this block's result is ready
+                        TC_TL(2, blk, TC_CLK());
                     }
                     if (ok) tc_commit(&S.empty[stg]);               // the MMAs have finished reading the stage
                 }
@@ -421,7 +449,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
         const int c0 = EPI ? 16 * sub : 32 * sub;
         const int c1 = EPI ? 64 + 16 * sub : 32 * sub + 16;
         unsigned it = 0, blk = 0, nitem = 0;
-        long long pw_full = 0, pw_tf = 0, pw_ld = 0, pw_tail = 0; const long long pt0 = clock64();
+        long long pw_full = 0, pw_tf = 0, pw_ld = 0, pw_tail = 0, pw_math = 0, pw_rel = 0; const long long pt0 = clock64();
         for (int item = blockIdx.x; item < n_items && !*(volatile int *) &S.abort; item += gridDim.x, ++nitem) {
             const int mt = item / n_rt, rt = item % n_rt;
             const int tstart = S.mt_start[mt], tcnt = S.mt_count[mt];
@@ -438,14 +466,74 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
                 const int stg = it % TC_STAGES;
                 if (!TC_TWAIT(pw_full, S, &S.full[stg], (it / TC_STAGES) & 1u, 30u)) { ok = false; break; }   // d4 / sc are in place
                 TcStage & T = S.st[stg];
+#if TC_UNROLLJ
+                static_assert(TC_KB == TC_TBUF, "block j of a stage lands in TMEM buffer j");
+                const unsigned tpar = it & 1u;                     // == (blk / TC_TBUF) & 1 for every block of the stage
+#pragma unroll
+#else
 #pragma unroll 1
+#endif
                 for (int j = 0; j < TC_KB; ++j, ++blk) {
+#if TC_UNROLLJ
+                    const int tb = j;
+#else
                     const int tb = blk % TC_TBUF;
-                    if (!TC_TWAIT(pw_tf, S, &S.tfull[tb], (blk / TC_TBUF) & 1u, 31u)) { ok = false; break; }
+                    const unsigned tpar = (blk / TC_TBUF) & 1u;
+#endif
+                    if (lane == 0 && warp == TC_LW) TC_TL(3, blk, TC_CLK());
+                    if (lane == 0 && warp == TC_LW + 15) TC_TL(6, blk, TC_CLK());
+                    if (!TC_TWAIT(pw_tf, S, &S.tfull[tb], tpar, 31u)) { ok = false; break; }
+                    if (lane == 0 && warp == TC_LW) TC_TL(4, blk, TC_CLK());
+                    if (lane == 0 && warp == TC_LW + 15) TC_TL(7, blk, TC_CLK());
                     tc_fence_after();
                     if (warp_live) {
                         const float2 sc = T.sc[tok][j];
                         const float d8 = sc.x, nc = -sc.y;
+#if TC_LD8
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            // 8 columns at a time: few enough live registers that the three passes below stay
+                            // separate (eight independent converts, then eight inner, then eight outer FMAs)
+                            const int col = ((q & 2) ? c1 : c0) + 8 * (q & 1);
+                            int sv[8];
+                            const long long tl0_ = TC_CLK();
+                            tc_ld8(tmem + tlane + tb * TC_N + col, sv);
+                            const float4 da = *reinterpret_cast<const float4 *>(&T.d4[j][col]);
+                            const float4 db = *reinterpret_cast<const float4 *>(&T.d4[j][col + 4]);
+                            tc_wait_ld();
+                            const long long tl1_ = TC_CLK(); pw_ld += tl1_ - tl0_;
+                            if (q == 3) {
+                                tc_fence_before();
+                                __syncwarp();
+                                if (lane == 0) tc_mbar_arrive(&S.tempty[tb]);      // TMEM buffer is free again
+                            }
+                            const long long tl2_ = TC_CLK(); pw_rel += tl2_ - tl1_;
+#if TC_FFMA2
+                            // two IEEE FMAs per issue slot: same roundings, half the FMA instructions
+                            const float2 d8p = make_float2(d8, d8), ncp = make_float2(nc, nc);
+                            const float2 ddp[4] = {make_float2(da.x, da.y), make_float2(da.z, da.w), make_float2(db.x, db.y), make_float2(db.z, db.w)};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                float2 f = make_float2(tc_i2f(sv[2 * i]), tc_i2f(sv[2 * i + 1]));
+                                f = tc_ffma2(d8p, f, ncp);
+                                const float2 r = tc_ffma2(ddp[i], f, make_float2(acc[8 * q + 2 * i], acc[8 * q + 2 * i + 1]));
+                                acc[8 * q + 2 * i] = r.x; acc[8 * q + 2 * i + 1] = r.y;
+                            }
+#if TC_PROF
+                            pw_math += TC_CLK() - tl2_ + (__float_as_int(acc[8 * q]) == 0x7fc12345 ? 1 : 0);   // keeps the clock read after the math
+#endif
+#else
+                            float f[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) f[i] = tc_i2f(sv[i]);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) f[i] = fmaf(d8, f[i], nc);
+                            const float dd8[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) acc[8 * q + i] = fmaf(dd8[i], f[i], acc[8 * q + i]);
+#endif
+                        }
+#else
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
                             // 16 columns at a time keeps the live registers under the 96-register budget (no spills)
@@ -461,9 +549,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
                                 tc_fence_before();
                                 __syncwarp();
                                 if (lane == 0) tc_mbar_arrive(&S.tempty[tb]);      // TMEM buffer is free again
+                                if (lane == 0 && warp == TC_LW) TC_TL(5, blk, TC_CLK());
                             }
 #ifdef TC_ABLATE_MATH
                             acc[h] += __int_as_float(sv[0] ^ sv[15]);
+#else
+#if TC_FFMA2
+#pragma unroll
+                            for (int i = 0; i < 16; i += 4) {
+                                const int o = h * 16 + i;
+                                const float2 d8p = make_float2(d8, d8), ncp = make_float2(nc, nc);
+                                float2 f0 = tc_ffma2(d8p, make_float2(tc_i2f(sv[i + 0]), tc_i2f(sv[i + 1])), ncp);
+                                float2 f1 = tc_ffma2(d8p, make_float2(tc_i2f(sv[i + 2]), tc_i2f(sv[i + 3])), ncp);
+                                f0 = tc_ffma2(make_float2(dd[i / 4].x, dd[i / 4].y), f0, make_float2(acc[o + 0], acc[o + 1]));
+                                f1 = tc_ffma2(make_float2(dd[i / 4].z, dd[i / 4].w), f1, make_float2(acc[o + 2], acc[o + 3]));
+                                acc[o + 0] = f0.x; acc[o + 1] = f0.y; acc[o + 2] = f1.x; acc[o + 3] = f1.y;
+                            }
 #else
 #pragma unroll
                             for (int i = 0; i < 16; i += 4) {
@@ -474,7 +575,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
                                 acc[o + 3] = fmaf(dd[i / 4].w, fmaf(d8, tc_i2f(sv[i + 3]), nc), acc[o + 3]);
                             }
 #endif
+#endif
                         }
+#endif
                     } else {
                         tc_fence_before();
                         __syncwarp();
@@ -556,7 +659,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
             }
             pw_tail += TC_CLK() - tt0_;
         }
-        if (blockIdx.x == 0 && tid == TC_LOADERS) { g_tc_prof[8] = pw_full; g_tc_prof[9] = pw_tf; g_tc_prof[10] = clock64() - pt0; g_tc_prof[11] = pw_ld; g_tc_prof[12] = pw_tail; }
+        if (blockIdx.x == 0 && tid == TC_LOADERS) { g_tc_prof[8] = pw_full; g_tc_prof[9] = pw_tf; g_tc_prof[10] = clock64() - pt0; g_tc_prof[11] = pw_ld; g_tc_prof[12] = pw_tail; g_tc_prof[21] = pw_math; g_tc_prof[22] = pw_rel; }
+        if (blockIdx.x == 0 && tid == 128) { g_tc_prof[16] = pw_full; g_tc_prof[17] = pw_tf; g_tc_prof[18] = clock64() - pt0; g_tc_prof[19] = pw_ld; g_tc_prof[20] = pw_tail; g_tc_prof[23] = pw_math; g_tc_prof[24] = pw_rel; }
     }
 
     // ---- teardown: everyone meets, then the allocating warp frees TMEM ------------
@@ -600,8 +704,14 @@ extern "C" {
 // Tuning hook (not in the public header): copies the 16 profiling counters of the last launch.
 __attribute__((visibility("default"))) int lkb_debug_gemm_prof(unsigned long long * out16) {
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-    return cudaMemcpyFromSymbol(out16, g_tc_prof, 16 * sizeof(unsigned long long)) == cudaSuccess ? 0 : -1;
+    return cudaMemcpyFromSymbol(out16, g_tc_prof, 32 * sizeof(unsigned long long)) == cudaSuccess ? 0 : -1;
 }
+#if TC_PROF
+__attribute__((visibility("default"))) int lkb_debug_gemm_timeline(long long * out) {      // [8][TC_TL_N]
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    return cudaMemcpyFromSymbol(out, g_tc_tl, sizeof(long long) * 8 * TC_TL_N) == cudaSuccess ? 0 : -1;
+}
+#endif
 int lkb_pf_gemm_status(void) {
     unsigned v = 0, z = 0;
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
