@@ -16,7 +16,7 @@
 //     shuffle at all (in the standard butterfly order: bit-identical to the unfused path);
 //   * two loader warps (cp.async, two stages ahead): activations are gathered through `perm`
 //     straight into the canonical K-major core-matrix layout (8 rows x 16 B), nibbles are staged
-//     raw and expanded to int8 from shared memory; one thread of the last warp issues the MMAs;
+//     raw and expanded to int8 from shared memory; one thread of a warp of its own issues the MMAs;
 //     sixteen epilogue warps (four per TMEM lane quadrant, 32 columns each);
 //   * four TMEM buffers of 128 columns: MMAs run up to four blocks ahead of the epilogue;
 //   * persistent: one CTA per SM walks (row tile, 128-token tile) work items built from
@@ -29,10 +29,27 @@
 #define TC_LW        2              // loader warps; each loader thread serves TC_RPT tokens and TC_RPT weight rows
 #endif
 #define TC_RPT       (128 / (32 * TC_LW))
+#ifndef TC_LAYOUT
+#define TC_LAYOUT 1                   // measured: 65.1 ms per 40-layer 4k-token step with layout 0, 63.0 ms with layout 1
+#endif
+// Which warp plays which role.  A warp's scheduler is warp % 4, and that is also the TMEM lane quadrant an epilogue
+// warp may read, so every scheduler carries four epilogue warps whatever the layout; the layouts differ in which
+// schedulers ALSO carry a loader warp.  0: loaders are warps 0, 1 (schedulers 0, 1), epilogue 2..17, issuer 18.
+// 1: epilogue 0..15, issuer 16, warp 17 idle, loaders 18, 19 (schedulers 2, 3: the quadrants that hold the
+//    padding rows of a partly filled token tile, whose epilogue warps have the least to do).
+#if TC_LAYOUT == 1
+#define TC_THREADS   (20 * 32)
+#define TC_LOADER_W0 (20 - TC_LW)
+#define TC_EPI_W0    0
+#define TC_MMA_WARP  16
+#else
 #define TC_THREADS   ((TC_LW + 16 + 1) * 32)   // loaders, 16 epilogue warps, 1 MMA-issuing warp
+#define TC_LOADER_W0 0
+#define TC_EPI_W0    TC_LW
+#define TC_MMA_WARP  (TC_LW + 16)
+#endif
 #define TC_LOADERS   (32 * TC_LW)
 #define TC_EPI_WARPS 16
-#define TC_MMA_WARP  (TC_LW + 16)
 #define TC_KB        4              // blocks per pipeline stage
 #define TC_STAGES    3
 #define TC_TBUF      4              // TMEM buffers (128 columns each)
@@ -218,10 +235,11 @@ template <int EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm g, const int max_tiles) {
     extern __shared__ __align__(128) unsigned char tc_smem_raw[];
     TcSmem & S = *reinterpret_cast<TcSmem *>(tc_smem_raw);
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int ptid = threadIdx.x, warp = ptid >> 5, lane = ptid & 31;
+    const int tid = ptid - TC_LOADER_W0 * 32;          // index among the loader threads (meaningful in the loader warps only)
 
     // ---- set-up: barriers, TMEM, work list -------------------------------------
-    if (tid == 0) {
+    if (ptid == 0) {
         S.abort = 0;
         for (int i = 0; i < TC_STAGES; ++i) { tc_mbar_init(&S.full[i], TC_LOADERS / 32); tc_mbar_init(&S.empty[i], 1 + TC_EPI_WARPS); }
         for (int i = 0; i < TC_TBUF; ++i) { tc_mbar_init(&S.tfull[i], 1); tc_mbar_init(&S.tempty[i], TC_EPI_WARPS); }
@@ -283,7 +301,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
     // traffic is cp.async (16 B), issued TC_AHEAD stages ahead: activations and their scales land
     // directly in the canonical operand layout, nibbles land in a raw staging row and are expanded
     // to int8 from shared memory when their stage comes up.
-    if (warp < TC_LW) {
+    if (warp >= TC_LOADER_W0 && warp < TC_LOADER_W0 + TC_LW) {
         struct Cur { int item, ks; int ar[TC_RPT]; const int8_t * aq[TC_RPT]; const float2 * as[TC_RPT];
                      const uint4 * wq[TC_RPT]; const __half * wd[TC_RPT]; };
         auto setup = [&](Cur & c) {
@@ -436,11 +454,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
             if (blockIdx.x == 0) { g_tc_prof[4] = pw_full; g_tc_prof[5] = pw_te; g_tc_prof[6] = clock64() - pt0; g_tc_prof[7] = blk; }
         }
     }
-    // ============================ epilogue (warps 4-19) ==========================
+    // ============================ epilogue (sixteen warps) ========================
     // Four warps per TMEM lane quadrant, each folding 32 of the 128 columns: 32 accumulators
     // per thread, four warps per scheduler to hide the TMEM read latency.
-    else {
-        const int ew = warp - TC_LW;                // 0..15
+    else if (warp >= TC_EPI_W0 && warp < TC_EPI_W0 + TC_EPI_WARPS) {
+        const int ew = warp - TC_EPI_W0;             // 0..15
         const int quad = warp & 3;                  // TMEM lane quadrant this warp may access
         const int sub = ew >> 2;                    // which 32 columns
         const int tok = quad * 32 + lane;           // token (TMEM lane) of this thread
@@ -659,8 +677,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
             }
             pw_tail += TC_CLK() - tt0_;
         }
-        if (blockIdx.x == 0 && tid == TC_LOADERS) { g_tc_prof[8] = pw_full; g_tc_prof[9] = pw_tf; g_tc_prof[10] = clock64() - pt0; g_tc_prof[11] = pw_ld; g_tc_prof[12] = pw_tail; g_tc_prof[21] = pw_math; g_tc_prof[22] = pw_rel; }
-        if (blockIdx.x == 0 && tid == 128) { g_tc_prof[16] = pw_full; g_tc_prof[17] = pw_tf; g_tc_prof[18] = clock64() - pt0; g_tc_prof[19] = pw_ld; g_tc_prof[20] = pw_tail; g_tc_prof[23] = pw_math; g_tc_prof[24] = pw_rel; }
+        if (blockIdx.x == 0 && ptid == (TC_EPI_W0 + 0) * 32) { g_tc_prof[8] = pw_full; g_tc_prof[9] = pw_tf; g_tc_prof[10] = clock64() - pt0; g_tc_prof[11] = pw_ld; g_tc_prof[12] = pw_tail; g_tc_prof[21] = pw_math; g_tc_prof[22] = pw_rel; }
+        if (blockIdx.x == 0 && ptid == (TC_EPI_W0 + 2) * 32) { g_tc_prof[16] = pw_full; g_tc_prof[17] = pw_tf; g_tc_prof[18] = clock64() - pt0; g_tc_prof[19] = pw_ld; g_tc_prof[20] = pw_tail; g_tc_prof[23] = pw_math; g_tc_prof[24] = pw_rel; }
     }
 
     // ---- teardown: everyone meets, then the allocating warp frees TMEM ------------
