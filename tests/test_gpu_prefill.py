@@ -133,6 +133,25 @@ def test_pf_swiglu_matches_decode(L, orc):
         assert np.array_equal(host(sc)[r, :, 1], 8.0 * orc.f16_bits_to_f32(os_))
 
 
+def test_router_token_tile_forms_agree(L):
+    """The tiled router has an 8-token and a 32-token form (picked by how many CTAs the chunk gives); both evaluate
+    the same ascending-k chains, so a long chunk (32-token form) equals its pieces (8-token form) bit for bit."""
+    rng = np.random.default_rng(77)
+    m = 32 * L.lib.lkb_sm_count() + 40
+    H = dev(rng.uniform(-1, 1, size=(m, 2048)).astype(np.float32))
+    W = dev(rng.normal(0, 0.05, size=(64, 2048)).astype(np.float32))
+    bias = dev(rng.normal(0, 0.1, size=64).astype(np.float32))
+    inv = dev(rng.uniform(0.5, 2.0, size=m).astype(np.float32))
+    sel, sig = nan_f32(m, 64), nan_f32(m, 64)
+    L.k_pf_router_tiled(H, m, W, bias, inv, sel, sig)
+    sel2, sig2 = nan_f32(m, 64), nan_f32(m, 64)
+    step = 8 * L.lib.lkb_sm_count() - 5                       # ragged pieces, each within one 8-token CTA per SM
+    for a in range(0, m, step):
+        n = min(step, m - a)
+        L.k_pf_router_tiled(H[a:a + n], n, W, bias, inv[a:a + n], sel2[a:a + n], sig2[a:a + n])
+    assert torch.equal(sel, sel2) and torch.equal(sig, sig2) and bool(torch.isfinite(sel).all())
+
+
 @pytest.mark.parametrize("m", [70, 300])
 def test_router_and_select(L, orc, golden_dir, m):
     g = np.load(golden_dir / "router_fixture.npz")
