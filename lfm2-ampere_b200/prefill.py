@@ -208,6 +208,12 @@ class PrefillStackEP:
         self.nrecv = torch.zeros(max(1, len(self.layers)), **i32)
         self.ep_epoch = torch.zeros(1, **i32)                      # advanced on the device, once per layer
 
+    def prepare(self):
+        """Allocate the exchange buffers now (peer dispatch: the symmetric-memory rendezvous, a collective) instead
+        of at the first layer call."""
+        if not hasattr(self, "send_order"):
+            self._alloc_ep(self.X.device)
+
     def status(self):
         """0, or the code of the exchange wait that ran out (peer dispatch)."""
         return int(self.ep_status.item()) if hasattr(self, "ep_status") else 0
