@@ -183,7 +183,9 @@ def numpy_vectors(ref):
 
 
 if __name__ == "__main__":
-    ref = pathlib.Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <checkout of the reference project>")
+    ref = pathlib.Path(sys.argv[1])
     quant_cases(ref)
     router_fixture(ref)
     numpy_vectors(ref)
