@@ -119,6 +119,18 @@ __global__ void __launch_bounds__(32) k_pf_router_small(const float * __restrict
 // staged 32 at a time.  Each (token, expert) logit is one FMA chain over
 // k = 0..2047 ascending.  ref: src/prefill.cu:1606-1666 (same per-logit order)
 #define LKB_RT_K 32
+#ifndef LKB_RT_FFMA2
+#define LKB_RT_FFMA2 1
+#endif
+// (c0, c1) = (a0 * b0 + c0, a1 * b1 + c1), each an IEEE fma, in one fma.rn.f32x2
+__device__ __forceinline__ void pf_ffma2(float a0, float a1, float b0, float b1, float & c0, float & c1) {
+    unsigned long long ra, rb, rc;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a0), "f"(a1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b0), "f"(b1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c0), "f"(c1));
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(rc) : "l"(ra), "l"(rb));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(c0), "=f"(c1) : "l"(rc));
+}
 __global__ void __launch_bounds__(256) k_pf_router(const float * __restrict__ H, int m, const float * __restrict__ Wr,
                                                    const float * __restrict__ bias, const float * __restrict__ inv,
                                                    float * __restrict__ sel, float * __restrict__ sig) {
@@ -134,7 +146,7 @@ __global__ void __launch_bounds__(256) k_pf_router(const float * __restrict__ H,
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
     // The next k-tile travels global -> registers while the current one is multiplied out of shared memory:
     // without the prefetch every one of the 2048 / LKB_RT_K tiles exposed a full global-memory round trip
-    // (112 us for 4096 tokens; 72 us with it.  A 4 x 4-outputs-per-thread variant with 128 threads measured 89 us:
+    // (112 us for 4096 tokens; 72 us with it, 68 us with the FMAs packed two per instruction.  A 4 x 4-outputs-per-thread variant with 128 threads measured 89 us:
     // one warp per scheduler does not cover the shared-memory latency).
     constexpr int NH = (32 * LKB_RT_K) / 256, NW = (64 * LKB_RT_K) / 256;
     float rh[NH], rw[NW];
@@ -162,10 +174,16 @@ __global__ void __launch_bounds__(256) k_pf_router(const float * __restrict__ H,
         for (int c = 0; c < LKB_RT_K; ++c) {
             const float2 h = *reinterpret_cast<const float2 *>(&sH[c][tt * 2]);
             const float4 wv = *reinterpret_cast<const float4 *>(&sW[c][te * 4]);
+#if LKB_RT_FFMA2
+            // the same eight IEEE fused multiply-adds, two per instruction
+            pf_ffma2(h.x, h.x, wv.x, wv.y, acc[0][0], acc[0][1]); pf_ffma2(h.x, h.x, wv.z, wv.w, acc[0][2], acc[0][3]);
+            pf_ffma2(h.y, h.y, wv.x, wv.y, acc[1][0], acc[1][1]); pf_ffma2(h.y, h.y, wv.z, wv.w, acc[1][2], acc[1][3]);
+#else
             acc[0][0] = fmaf(h.x, wv.x, acc[0][0]); acc[0][1] = fmaf(h.x, wv.y, acc[0][1]);
             acc[0][2] = fmaf(h.x, wv.z, acc[0][2]); acc[0][3] = fmaf(h.x, wv.w, acc[0][3]);
             acc[1][0] = fmaf(h.y, wv.x, acc[1][0]); acc[1][1] = fmaf(h.y, wv.y, acc[1][1]);
             acc[1][2] = fmaf(h.y, wv.z, acc[1][2]); acc[1][3] = fmaf(h.y, wv.w, acc[1][3]);
+#endif
         }
         __syncthreads();
     }
@@ -220,8 +238,12 @@ __global__ void __launch_bounds__(256) k_pf_router_t8(const float * __restrict__
         for (int c = 0; c < LKB_RT_K; ++c) {
             const float h = sH[c][tt];
             const float2 wv = *reinterpret_cast<const float2 *>(&sW[c][lane * 2]);
+#if LKB_RT_FFMA2
+            pf_ffma2(h, h, wv.x, wv.y, acc0, acc1);
+#else
             acc0 = fmaf(h, wv.x, acc0);
             acc1 = fmaf(h, wv.y, acc1);
+#endif
         }
         __syncthreads();
     }
