@@ -208,34 +208,41 @@ __global__ void __launch_bounds__(256) k_pf_router(const float * __restrict__ H,
 // chunk share of a few hundred tokens still fills the GPU -- the 32-token form gives a 512-token share 16 CTAs, and
 // its duration does not depend on the token count up to one CTA per SM (the k loop is its critical path).  Every (token, expert) sum is
 // the same ascending-k chain of fused multiply-adds: results are bit-identical to k_pf_router.
+#ifndef LKB_RT8_K
+#define LKB_RT8_K 32                 // k-tile of the 8-token form (64 measured slower: 50 us against 43 us at 512 tokens)
+#endif
 __global__ void __launch_bounds__(256) k_pf_router_t8(const float * __restrict__ H, int m, const float * __restrict__ Wr,
                                                       const float * __restrict__ bias, const float * __restrict__ inv,
                                                       float * __restrict__ sel, float * __restrict__ sig) {
-    __shared__ __align__(16) float sH[LKB_RT_K][8];       // [k][token]
-    __shared__ __align__(16) float sW[LKB_RT_K][66];      // [k][expert]
+    __shared__ __align__(16) float sH[LKB_RT8_K][8];      // [k][token]
+    __shared__ __align__(16) float sW[LKB_RT8_K][66];     // [k][expert]
     const int tid = threadIdx.x, lane = tid & 31, tt = tid >> 5;
     const int t0 = blockIdx.x * 8;
     float acc0 = 0.0f, acc1 = 0.0f;
-    constexpr int NW = (64 * LKB_RT_K) / 256;
-    float rh, rw[NW];
+    constexpr int NH = (8 * LKB_RT8_K) / 256, NW = (64 * LKB_RT8_K) / 256;
+    float rh[NH], rw[NW];
     auto fetch = [&](int k0) {
-        const int tk = t0 + tid / LKB_RT_K;
-        rh = (tk < m) ? H[(size_t) tk * LKB_HIDDEN + k0 + tid % LKB_RT_K] : 0.0f;
+#pragma unroll
+        for (int q = 0; q < NH; ++q) {
+            const int i = tid + q * 256, tk = t0 + i / LKB_RT8_K;
+            rh[q] = (tk < m) ? H[(size_t) tk * LKB_HIDDEN + k0 + i % LKB_RT8_K] : 0.0f;
+        }
 #pragma unroll
         for (int q = 0; q < NW; ++q) {
             const int i = tid + q * 256;
-            rw[q] = Wr[(size_t) (i / LKB_RT_K) * LKB_HIDDEN + k0 + i % LKB_RT_K];
+            rw[q] = Wr[(size_t) (i / LKB_RT8_K) * LKB_HIDDEN + k0 + i % LKB_RT8_K];
         }
     };
     fetch(0);
-    for (int k0 = 0; k0 < LKB_HIDDEN; k0 += LKB_RT_K) {
-        sH[tid % LKB_RT_K][tid / LKB_RT_K] = rh;
+    for (int k0 = 0; k0 < LKB_HIDDEN; k0 += LKB_RT8_K) {
 #pragma unroll
-        for (int q = 0; q < NW; ++q) { const int i = tid + q * 256; sW[i % LKB_RT_K][i / LKB_RT_K] = rw[q]; }
+        for (int q = 0; q < NH; ++q) { const int i = tid + q * 256; sH[i % LKB_RT8_K][i / LKB_RT8_K] = rh[q]; }
+#pragma unroll
+        for (int q = 0; q < NW; ++q) { const int i = tid + q * 256; sW[i % LKB_RT8_K][i / LKB_RT8_K] = rw[q]; }
         __syncthreads();
-        if (k0 + LKB_RT_K < LKB_HIDDEN) fetch(k0 + LKB_RT_K);
+        if (k0 + LKB_RT8_K < LKB_HIDDEN) fetch(k0 + LKB_RT8_K);
 #pragma unroll 8
-        for (int c = 0; c < LKB_RT_K; ++c) {
+        for (int c = 0; c < LKB_RT8_K; ++c) {
             const float h = sH[c][tt];
             const float2 wv = *reinterpret_cast<const float2 *>(&sW[c][lane * 2]);
 #if LKB_RT_FFMA2
