@@ -311,6 +311,14 @@ int lkb_pf_gemm_swiglu(const lkb_pf_gemm * g, int max_tiles, lkb_stream_t st);
  * tensor-core form or an error.  Also read once from the environment variable
  * LKB_PF_CFG by lkb_init().  ref: src/prefill.cu:813-848 (LK_PF_CFG_DENSE/MOE/SWIGLU) */
 int lkb_pf_gemm_config(int cfg);
+/* Per-block term of the three launchers above.  1 (default): the reference's shipped form -- the block sum
+ * arrives as the float 12582912 + S_b and the offset is folded into c = fma(d8, 12582912, 8sum):
+ * acc = fma(d4, fma(d8, 12582912 + S_b, -c), acc); fp32 results are bit-identical to the reference's kernel and
+ * within its own gate of float64 (half an ulp of c per block).  0: the exact term of the decode kernels,
+ * acc = fma(d4, fma(d8, float(S_b), -8sum), acc), within 1e-5 of float64 at one more packed add per value pair.
+ * The int32 block sums S_b are exact either way.  Also read once from LKB_PF_ARITH by lkb_init().
+ * ref: src/prefill.cu:131-139 (PF_EPI2), 341-342, 381-399 */
+int lkb_pf_gemm_arith(int fold);
 /* Every device-side wait of the tensor-core form is bounded; this SYNCHRONISES the device and
  * returns 0, or the code of the first wait that expired since the last call (10 loader,
  * 20/21 MMA issuer, 30/31 epilogue) and clears it.  No counterpart in the reference. */

@@ -20,7 +20,7 @@ __all__ = [
     "k_pf_router", "k_pf_router_small", "k_pf_router_tiled", "k_pf_select", "k_pf_moe_count", "k_pf_moe_plan", "k_pf_moe_scatter",
     "pf_gemm_dense", "pf_gemm_moe", "pf_gemm_swiglu", "k_pf_moe_combine", "k_pf_moe_combine_norm",
     "k_pf_pack_q8_1", "zero_i32", "moe_layer_desc", "moe_scratch", "moe_ffn_decode", "moe_ffn_decode_stack",
-    "layer_descs_to_device", "ep_pack_rows", "ep_unpack_rows", "k_pf_moe_combine_norm_gather", "moe_ffn_decode_stack_static", "set_pdl", "pf_gemm_config", "sm_count",
+    "layer_descs_to_device", "ep_pack_rows", "ep_unpack_rows", "k_pf_moe_combine_norm_gather", "moe_ffn_decode_stack_static", "set_pdl", "pf_gemm_config", "pf_gemm_arith", "sm_count",
     "k_gemv_q6_K", "k_argmax_part", "k_argmax_final", "k_embed_q6_K", "gemv_q6_K_status",
     "k_attn_split", "k_attn_combine", "k_qk_norm_rope", "k_shortconv", "ATTN_SPLIT", "ATTN_PARTW",
     "mixer_layer_desc", "step_scratch", "decode_layers",
@@ -60,6 +60,10 @@ def set_pdl(on):
 
 def pf_gemm_config(cfg):
     check(lib.lkb_pf_gemm_config(int(cfg)))
+
+
+def pf_gemm_arith(fold):
+    check(lib.lkb_pf_gemm_arith(int(fold)))
 
 
 def sm_count():

@@ -95,6 +95,15 @@ __device__ __forceinline__ float lkb_block_acc(float d4, float d8, int sumi, flo
     return fmaf(d4, fmaf(d8, (float) sumi, -sum8), acc);
 }
 
+// The batched-prefill GEMM's form of the same term, as the reference ships it: the integer block sum
+// arrives as the fp32 F whose bit pattern is 0x4B400000 + sumi (= 12582912 + sumi, exact for |sumi| < 2^22)
+// and the offset is folded into c = fma(d8, 12582912, 8sum): acc' = fma(d4, fma(d8, F, -c), acc).
+// ref: src/prefill.cu:32-39,131-139,341-342,381-384
+__device__ __forceinline__ float lkb_block_acc_pf(float d4, float d8, int sumi, float sum8, float acc) {
+    const float c = fmaf(d8, 12582912.0f, sum8);
+    return fmaf(d4, fmaf(d8, __int_as_float(0x4B400000 + sumi), -c), acc);
+}
+
 // Streaming 128-bit load that does not allocate in L1 (weights are read once).
 __device__ __forceinline__ uint4 lkb_ldg_stream(const uint4 * p) {
     uint4 v;

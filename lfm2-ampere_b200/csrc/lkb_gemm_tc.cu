@@ -1,111 +1,94 @@
 // lkb_gemm_tc.cu - tensor-core form of the Q4_0 x Q8_1 grouped GEMM for sm_100a:
-// tcgen05.mma.kind::i8 with accumulators in tensor memory (TMEM).
+// tcgen05.mma.kind::i8 with accumulators in tensor memory (TMEM), operands delivered by the
+// tensor memory accelerator (cp.async.bulk.tensor: a row gather for the activations, tiles
+// of the raw nibble plane for the weights).
 //
-//   out[slot][n] (+)= scale[arow] * sum_{b ascending} fma(d4[n][b], fma(d8[arow][b], float(S_b), -8sum[arow][b]), .)
+//   out[slot][n] (+)= scale[arow] * sum_{b ascending} fma(d4[n][b], fma(d8[arow][b], F_b, -c[arow][b]), .)
 //   S_b = sum_{i<32} nibble[n][b][i] * q8[arow][b][i]                     (int32, exact)
+//   F_b = the fp32 whose bit pattern is 0x4B400000 + S_b  (= 12582912 + S_b, exact: |S_b| < 2^22)
+//   c   = fma(d8, 12582912, 8sum)
+// This (FOLD = 1) is the arithmetic of the reference's shipped GEMM (its accumulator is seeded with the
+// bit pattern of 1.5 * 2^23 and the offset is folded into a per-(token, block) constant), so fp32
+// results are bit-identical to that kernel's.  ref: src/prefill.cu:32-50,131-139,341-342,381-384
+// FOLD = 0 spends one more packed add per value pair to recover float(S_b) = F_b - 12582912 exactly and
+// evaluates the decode kernels' term fma(d4, fma(d8, float(S_b), -8sum), .) -- ref: src/quant.cuh:154-157,
+// src/prefill.cu:391-399 (the reference's PF_EPI2 = 0 build) -- which stays within 1e-5 of float64.
 //
-// One MMA per 32-element block: K = 32 int8 is exactly one Q4_0/Q8_1 block, and the
-// per-block scales forbid accumulating across blocks inside the tensor core, so every
-// block's 128x128 int32 result is read back from TMEM and folded into fp32 register
-// accumulators by the CUDA cores (2 FMA + 1 convert per value).  That epilogue, not
-// the MMA, bounds the kernel (MMA ~64 clk per block per SM, epilogue >= 256), so the
-// design spends the SM on it:
+// One MMA per 32-element block: K = 32 int8 is exactly one Q4_0/Q8_1 block, and the per-block
+// scales forbid accumulating across blocks inside the tensor core, so every block's 128x128
+// int32 result is read back from TMEM and folded into fp32 register accumulators by the CUDA
+// cores: two FMAs per value, no conversion -- the TMEM buffer is PRESET to 0x4B400000 by the
+// epilogue warp that drained it and the MMA accumulates onto it, so what comes back already
+// is F_b.  That epilogue (256 FMA-pipe cycles per block and SM), not the MMA (64), bounds the
+// kernel; everything else is kept out of its issue slots:
 //   * M (TMEM lanes) = 128 tokens, N (TMEM columns) = 128 weight rows.  A thread owns one
-//     token: d8 / 8sum are per-thread scalars, the 32 intermediate rows of a Q8_1 output
-//     block sit in 32 registers of one thread, so the SwiGLU epilogue quantises with no
-//     shuffle at all (in the standard butterfly order: bit-identical to the unfused path);
-//   * two loader warps (cp.async, two stages ahead): activations are gathered through `perm`
-//     straight into the canonical K-major core-matrix layout (8 rows x 16 B), nibbles are staged
-//     raw and expanded to int8 from shared memory; one thread of a warp of its own issues the MMAs;
-//     sixteen epilogue warps (four per TMEM lane quadrant, 32 columns each);
-//   * four TMEM buffers of 128 columns: MMAs run up to four blocks ahead of the epilogue;
-//   * persistent: one CTA per SM walks (row tile, 128-token tile) work items built from
-//     the device-side tile list, expert by expert, so an expert's weights stay in L2.
-// Every wait is bounded; on expiry a status word is set and all roles drain and exit,
-// freeing TMEM.
+//     token: d8 / c are per-thread scalars, the 32 intermediate rows of a Q8_1 output block
+//     sit in 32 registers of one thread, so the SwiGLU epilogue quantises with no shuffle
+//     (in the standard butterfly order: bit-identical to the unfused path);
+//   * one producer warp: per stage of four blocks lane l gathers tokens 4l..4l+3 (one
+//     tile::gather4 copy of 4 x 128 bytes through `perm`, 128-byte swizzle = the MMA's K-major
+//     operand layout), one lane fetches the 128 weight rows' nibbles as two tiles of the raw
+//     plane, and the small per-token / per-row scale vectors follow by cp.async; everything
+//     completes on mbarriers (transaction bytes + cp.async arrivals);
+//   * two expansion warps turn the staged nibbles into the int8 B operand (swizzled stores)
+//     and the fp16 block scales into fp32; they issue no global traffic;
+//   * one thread issues the MMAs; sixteen epilogue warps (four per TMEM lane quadrant, 32
+//     columns each); four TMEM buffers of 128 columns: MMAs run up to four blocks ahead;
+//   * persistent: one CTA per SM walks (128-token tile, row tile) work items built from the
+//     device-side tile list, expert by expert, so an expert's weights stay in L2.
+// No copy in this file is a multicast one; every tensor map covers memory of the GPU the
+// kernel runs on.  Every wait is bounded; on expiry a status word is set and all roles drain
+// and exit, freeing TMEM.
 #include "lkb_device.cuh"
+#include <cuda.h>
 
-#ifndef TC_LW
-#define TC_LW        2              // loader warps; each loader thread serves TC_RPT tokens and TC_RPT weight rows
-#endif
-#define TC_RPT       (128 / (32 * TC_LW))
-#ifndef TC_SUSPEND_NS
-#define TC_SUSPEND_NS 0             // > 0: suspend-time hint (ns) on every mbarrier wait; 2000 measured 4% slower (65.6 against 63.3 ms)
-#endif
-#ifndef TC_LAYOUT
-#define TC_LAYOUT 1                   // measured: 65.1 ms per 40-layer 4k-token step with layout 0, 63.0 ms with layout 1
-#endif
-// Which warp plays which role.  A warp's scheduler is warp % 4, and that is also the TMEM lane quadrant an epilogue
-// warp may read, so every scheduler carries four epilogue warps whatever the layout; the layouts differ in which
-// schedulers ALSO carry a loader warp.  0: loaders are warps 0, 1 (schedulers 0, 1), epilogue 2..17, issuer 18.
-// 1: epilogue 0..15, issuer 16, warp 17 idle, loaders 18, 19 (schedulers 2, 3: the quadrants that hold the
-//    padding rows of a partly filled token tile, whose epilogue warps have the least to do).
-#if TC_LAYOUT == 1
-#define TC_THREADS   (20 * 32)
-#define TC_LOADER_W0 (20 - TC_LW)
-#define TC_EPI_W0    0
+#define TC_M         128            // tokens per tile (TMEM lanes)
+#define TC_N         128            // weight rows per tile (TMEM columns of one buffer)
+#define TC_KB        4              // blocks per pipeline stage = 128 bytes of K per operand row
+#define TC_TBUF      4              // TMEM buffers
+#define TC_EPI_WARPS 16             // warps 0..15
 #define TC_MMA_WARP  16
-#else
-#define TC_THREADS   ((TC_LW + 16 + 1) * 32)   // loaders, 16 epilogue warps, 1 MMA-issuing warp
-#define TC_LOADER_W0 0
-#define TC_EPI_W0    TC_LW
-#define TC_MMA_WARP  (TC_LW + 16)
-#endif
-#define TC_LOADERS   (32 * TC_LW)
-#define TC_EPI_WARPS 16
-#define TC_KB        4              // blocks per pipeline stage
-#define TC_STAGES    3
-#define TC_TBUF      4              // TMEM buffers (128 columns each)
-#define TC_M         128            // tokens per tile
-#define TC_N         128            // weight rows (columns of D) per MMA
-#define TC_AHEAD     2              // stages of cp.async lookahead in the loaders
+#define TC_PROD_WARP 17
+#define TC_EXP_W0    18             // expansion warps 18, 19: thread e serves weight rows e and e + 64
+#define TC_EXP_WARPS 2
+#define TC_THREADS   ((TC_EXP_W0 + TC_EXP_WARPS) * 32)
 #define TC_SPIN      (1u << 24)
 #define TC_MAX_TILES 1024           // 64-token plan tiles the work list can hold
-// Epilogue shape switches (defaults = the fastest measured on B200; the others are kept for ablation):
-#ifndef TC_LD8
-#define TC_LD8 1                     // 1: TMEM is read 8 columns at a time (four reads per block); 0: 16 columns (two reads)
-#endif
-#ifndef TC_FFMA2
-#define TC_FFMA2 1                   // 1: both FMAs of a value pair as fma.rn.f32x2 (same IEEE roundings, half the issue slots):
-                                     //    72.0 -> 65.8 ms per 40-layer step; with TC_LD8 0: 67.4 ms
-#endif
-#ifndef TC_UNROLLJ
-#define TC_UNROLLJ 1                 // 1: the four blocks of a stage unrolled, TMEM buffer index and parity static: 65.8 -> 65.1 ms
-#endif
-#ifndef TC_MAGIC
-#define TC_MAGIC 0                   // 1: int32 -> fp32 by the 1.5*2^23 bit trick (integer add + fp add) instead of
-                                     //    cvt.rn.f32.s32; measured 8% slower than the convert on B200, kept as a switch
-#endif
+#define TC_MAGIC_I   0x4B400000
+#define TC_MAGIC_F   12582912.0f
 
 struct TcStage {
-    alignas(128) unsigned char A[TC_KB][TC_M * 32];      // activations, canonical layout, 4 KB per block
-    alignas(128) unsigned char B[TC_KB][TC_N * 32];      // weights expanded to int8, 4 KB per block
-    alignas(16)  float  d4[TC_KB][TC_N];                 // weight block scales as fp32
-    alignas(16)  float2 sc[TC_M][TC_KB];                 // (d8, 8*sum) per token
-    alignas(16)  unsigned char rawq[TC_N][TC_KB * 16 + 16];   // nibbles as they lie in the pack (+16: bank spread)
-    alignas(8)   __half rawd[TC_N][TC_KB];
+    alignas(1024) unsigned char A[TC_M * 128];          // activations: row r at r*128, 16-byte chunk c at c ^ (r & 7)
+    alignas(1024) unsigned char B[TC_N * 128];          // weights as int8, same layout
+    alignas(1024) unsigned char rawq[TC_N * 64];        // nibbles as in the pack: row r at r*64, chunk c at c ^ ((r >> 1) & 3)
+    alignas(128)  float2 sc[TC_M][TC_KB];               // (d8, 8*sum) per token and block, as the gather lands it
+    alignas(16)   float  d4[TC_KB][TC_N];               // weight block scales as fp32
 };
+static_assert(sizeof(TcStage) % 1024 == 0, "stages keep the 1024-byte alignment of the swizzled operands");
 
+template <int NS, int EPI>
 struct TcSmem {
-    TcStage st[TC_STAGES];
-    alignas(8) unsigned long long full[TC_STAGES], empty[TC_STAGES], tfull[TC_TBUF], tempty[TC_TBUF], qbar[4];
+    TcStage st[NS];
+    alignas(8) unsigned long long rawfull[NS], full[NS], empty[NS], tfull[TC_TBUF], tempty[TC_TBUF], qbar[4];
     unsigned tmem_base;
     int      abort;
     int      n_mtiles;
     // work list: M tiles of up to 128 slots: {expert, start in perm, count}
     int      mt_expert[TC_MAX_TILES], mt_start[TC_MAX_TILES], mt_count[TC_MAX_TILES];
-    float    vbuf[TC_M][65];        // SwiGLU epilogue: v = silu(g)*u of 64 intermediate rows per token (+1: bank spread)
+    float    vbuf[EPI ? TC_M : 1][65];   // SwiGLU epilogue: v = silu(g)*u of 64 intermediate rows per token (+1: bank spread)
 };
 
-__device__ unsigned long long g_tc_prof[32];   // tuning: cycles spent per wait class (CTA 0)
-#if TC_PROF
-#define TC_TL_N 2048
-__device__ long long g_tc_tl[8][TC_TL_N];   // tuning: per-block timestamps of CTA 0 (MMA thread: 0-2, epilogue warps: 3-5, 6-7)
-#define TC_TL(row, b, v) do { if (blockIdx.x == 0 && (b) < TC_TL_N) g_tc_tl[row][b] = (v); } while (0)
-#else
-#define TC_TL(row, b, v) do { } while (0)
-#endif
 __device__ unsigned g_tc_status;     // 0, or the code of the first bounded wait that expired
+
+#ifdef LKB_TUNING
+// Tuning builds only (-DLKB_TUNING; the default build has none of this): clock64 stamps of CTA 0, one row per
+// role, four stamps per block or stage.
+#define TC_TL_N 1024
+__device__ long long g_tc_tl[6][TC_TL_N][4];
+#define TC_TL(row, i, k) do { if (blockIdx.x == 0 && (i) < TC_TL_N) g_tc_tl[row][i][k] = clock64(); } while (0)
+#else
+#define TC_TL(row, i, k) do { } while (0)
+#endif
 
 // ---- PTX -------------------------------------------------------------------
 __device__ __forceinline__ unsigned tc_smem_u32(const void * p) { return (unsigned) __cvta_generic_to_shared(p); }
@@ -115,38 +98,34 @@ __device__ __forceinline__ void tc_mbar_init(unsigned long long * b, unsigned co
 __device__ __forceinline__ void tc_mbar_arrive(unsigned long long * b) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(tc_smem_u32(b)) : "memory");
 }
+__device__ __forceinline__ void tc_mbar_arrive_tx(unsigned long long * b, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(tc_smem_u32(b)), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ bool tc_mbar_try(unsigned long long * b, unsigned parity) {
     unsigned ok;
-#if TC_SUSPEND_NS
-    // with a time hint the thread may stay suspended in hardware until the phase completes (or the hint runs out)
-    // instead of coming back to spin through the issue slots its scheduler's epilogue warps need
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(tc_smem_u32(b)), "r"(parity), "r"((unsigned) TC_SUSPEND_NS) : "memory");
-#else
     asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
                  : "=r"(ok) : "r"(tc_smem_u32(b)), "r"(parity) : "memory");
-#endif
     return ok != 0;
 }
-// Bounded wait.  Returns false when it expired or another role already aborted.
-__device__ __forceinline__ bool tc_wait(TcSmem & S, unsigned long long * b, unsigned parity, unsigned code) {
+// Bounded wait.  Returns false when it expired or another role already aborted.  SLEEP_NS > 0: the roles with slack
+// (producer, expansion, issuer) sleep between polls instead of spinning through the issue slots of their scheduler's
+// epilogue warps.
+template <int SLEEP_NS = 0, class SM>
+__device__ __forceinline__ bool tc_wait(SM & S, unsigned long long * b, unsigned parity, unsigned code) {
     for (unsigned i = 0; i < TC_SPIN; ++i) {
         if (tc_mbar_try(b, parity)) return true;
+        if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if ((i & 255u) == 255u && *(volatile int *) &S.abort) return false;
     }
     atomicCAS(&g_tc_status, 0u, code);
     *(volatile int *) &S.abort = 1;
     return false;
 }
-#ifndef TC_PROF
-#define TC_PROF 0                    // 1: accumulate cycles per wait class (tuning builds only)
+#ifndef TC_SLEEP_PROD
+#define TC_SLEEP_PROD 200
 #endif
-#if TC_PROF
-#define TC_TWAIT(acc, ...) ([&]() { const long long t0_ = TC_CLK(); const bool r_ = tc_wait(__VA_ARGS__); acc += TC_CLK() - t0_; return r_; })()
-#define TC_CLK() clock64()
-#else
-#define TC_TWAIT(acc, ...) tc_wait(__VA_ARGS__)
-#define TC_CLK() 0ll
+#ifndef TC_SLEEP_MMA
+#define TC_SLEEP_MMA 0
 #endif
 __device__ __forceinline__ void tc_fence_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -154,22 +133,25 @@ __device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_commit(unsigned long long * b) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(tc_smem_u32(b)) : "memory");
 }
+// D += A*B (the accumulator holds the preset offset)
 __device__ __forceinline__ void tc_mma_i8(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned idesc) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, 0, 0;\n"          // enable_input_d = 0: D = A*B (no accumulate)
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, 1, 0;\n"
                  " tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}"
                  :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc) : "memory");
 }
-// K-major, no swizzle: core matrix = 8 rows x 16 B contiguous; K-adjacent core matrix at
-// +128 B (leading byte offset), next 8-row group at +256 B (stride byte offset).
-__device__ __forceinline__ unsigned long long tc_desc(const void * smem) {
-    const unsigned a = tc_smem_u32(smem);
-    return (unsigned long long) ((a >> 4) & 0x3FFFu) | ((unsigned long long) (128u >> 4) << 16)
-         | ((unsigned long long) (256u >> 4) << 32) | (1ull << 46);
+// K-major operand with the 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
+// (stride byte offset); a K step of 32 bytes inside the swizzle span moves the start address.
+__device__ __forceinline__ unsigned long long tc_desc(unsigned smem_addr) {
+    return (unsigned long long) ((smem_addr >> 4) & 0x3FFFu) | (1ull << 16)
+         | ((unsigned long long) (1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 // s8 x s8 -> s32, M = 128, N = 128, both operands K-major.
 #define TC_IDESC (0x20u | (1u << 7) | (1u << 10) | ((TC_N >> 3) << 17) | ((TC_M >> 4) << 24))
 
-__device__ __forceinline__ void tc_ld32(unsigned taddr, int (&r)[32]) {
+// One TMEM access instruction costs the same ~26 cycles of a scheduler's TMEM port whether it moves 8, 16 or 32 columns
+// (measured on B200: four x8 reads per warp and block keep the port busy 444 cycles per block, one x32 read 104), so
+// a warp reads its 32 columns of a block with ONE load and presets them with ONE store.
+__device__ __forceinline__ void tc_ld32(unsigned taddr, unsigned (&r)[32]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
                  "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
@@ -178,80 +160,79 @@ __device__ __forceinline__ void tc_ld32(unsigned taddr, int (&r)[32]) {
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr) : "memory");
 }
-__device__ __forceinline__ void tc_ld16(unsigned taddr, int * r) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_ld8(unsigned taddr, int * r) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr) : "memory");
-}
-// Two independent IEEE fused multiply-adds in one instruction (halves the issue slots of the epilogue).
-__device__ __forceinline__ float2 tc_ffma2(float2 a, float2 b, float2 c) {
-    unsigned long long ra, rb, rc, rd;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
-    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
-    asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
-    float2 d;
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
-    return d;
-}
-__device__ __forceinline__ float tc_i2f(int s) {
-#if TC_MAGIC
-    return __fsub_rn(__int_as_float(s + 0x4B400000), 12582912.0f);      // exact for |s| < 2^22
-#else
-    return (float) s;
-#endif
-}
-// Two int32 block sums -> fp32, exactly.  |s| <= 32*15*127 < 2^22, so the integer s + 0x4B400000 read as a
-// float is 12582912 + s with no rounding, and subtracting 12582912 (one packed add) recovers float(s).
-__device__ __forceinline__ float2 tc_i2f2(int a, int b) {
-#if TC_MAGIC
-    unsigned long long r, m, o;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(a + 0x4B400000), "r"(b + 0x4B400000));
-    asm("mov.b64 %0, {%1, %1};" : "=l"(m) : "f"(-12582912.0f));
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(o) : "l"(r), "l"(m));
-    float2 d;
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(o));
-    return d;
-#else
-    return make_float2((float) a, (float) b);
-#endif
+// 32 columns of this warp's 32 lanes <- v, as two stores of 16 (a store's source is a run of distinct registers:
+// one 32-column store would pin 32 registers on the constant)
+__device__ __forceinline__ void tc_st32(unsigned taddr, unsigned v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
+                 :: "r"(taddr), "r"(v) : "memory");
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
+                 :: "r"(taddr + 16u), "r"(v) : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ void tc_cp16(void * dst, const void * src, bool valid) {
-    const unsigned n = valid ? 16u : 0u;                       // 0: the 16 bytes are zero-filled
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(tc_smem_u32(dst)), "l"(src), "r"(n) : "memory");
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// Two independent IEEE fused multiply-adds in one instruction (half the issue slots of the epilogue).
+__device__ __forceinline__ unsigned long long tc_pack(float x, float y) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(x), "f"(y));
+    return r;
 }
-__device__ __forceinline__ void tc_cp8(void * dst, const void * src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" :: "r"(tc_smem_u32(dst)), "l"(src) : "memory");
+__device__ __forceinline__ unsigned long long tc_pack_u(unsigned x, unsigned y) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(x), "r"(y));
+    return r;
 }
-__device__ __forceinline__ void tc_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void tc_cp_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
+__device__ __forceinline__ unsigned long long tc_ffma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long tc_fadd2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ void tc_unpack(unsigned long long v, float & x, float & y) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(x), "=f"(y) : "l"(v));
+}
 
-// Offset of (row r, 16-byte K chunk kc) inside one 4 KB canonical operand block.
-__device__ __forceinline__ int tc_canon(int r, int kc) { return (r >> 3) * 256 + kc * 128 + (r & 7) * 16; }
+// one tile of a 2-D tensor: box at (x, y) -> shared memory, bytes counted on the mbarrier
+__device__ __forceinline__ void tc_tma_tile(void * dst, const CUtensorMap * map, int x, int y, unsigned long long * bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 :: "r"(tc_smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(tc_smem_u32(bar)) : "memory");
+}
+// four rows y0..y3 of a 2-D tensor, columns from x on, one box width each -> four consecutive rows in shared memory
+__device__ __forceinline__ void tc_tma_gather4(void * dst, const CUtensorMap * map, int x, int y0, int y1, int y2, int y3,
+                                               unsigned long long * bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+                 :: "r"(tc_smem_u32(dst)), "l"(map), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3), "r"(tc_smem_u32(bar)) : "memory");
+}
 
 // ---------------------------------------------------------------------------
 // EPI 0: out (+)= scale * acc           (N tile = 128 rows of one weight segment)
 // EPI 1: SwiGLU + Q8_1                  (N tile = 64 gate rows | the same 64 up rows)
+// rpe = weight rows per expert (exp_stride / bpr).
 // ---------------------------------------------------------------------------
-template <int EPI>
-__global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm g, const int max_tiles) {
-    extern __shared__ __align__(128) unsigned char tc_smem_raw[];
-    TcSmem & S = *reinterpret_cast<TcSmem *>(tc_smem_raw);
+template <int EPI, int NS, int FOLD>
+__global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm g, const int max_tiles, const int rpe,
+                                                              const __grid_constant__ CUtensorMap map_a,
+                                                              const __grid_constant__ CUtensorMap map_s,
+                                                              const __grid_constant__ CUtensorMap map_w0,
+                                                              const __grid_constant__ CUtensorMap map_w1,
+                                                              const __grid_constant__ CUtensorMap map_w2) {
+    typedef TcSmem<NS, EPI> Smem;
+    extern __shared__ unsigned char tc_smem_raw[];
+    // the swizzle patterns are functions of the shared-memory address: stages start on 1024-byte boundaries
+    Smem & S = *reinterpret_cast<Smem *>(tc_smem_raw + ((1024u - (tc_smem_u32(tc_smem_raw) & 1023u)) & 1023u));
     const int ptid = threadIdx.x, warp = ptid >> 5, lane = ptid & 31;
-    const int tid = ptid - TC_LOADER_W0 * 32;          // index among the loader threads (meaningful in the loader warps only)
 
     // ---- set-up: barriers, TMEM, work list -------------------------------------
     if (ptid == 0) {
         S.abort = 0;
-        for (int i = 0; i < TC_STAGES; ++i) { tc_mbar_init(&S.full[i], TC_LOADERS / 32); tc_mbar_init(&S.empty[i], 1 + TC_EPI_WARPS); }
+        for (int i = 0; i < NS; ++i) {
+            tc_mbar_init(&S.rawfull[i], 1);                           // the lane that posts the tile bytes
+            tc_mbar_init(&S.full[i], 1 + TC_EXP_WARPS);               // the lane that posts the gather bytes + the expansion warps
+            tc_mbar_init(&S.empty[i], 1 + TC_EPI_WARPS);              // MMA commit + epilogue warps
+        }
         for (int i = 0; i < TC_TBUF; ++i) { tc_mbar_init(&S.tfull[i], 1); tc_mbar_init(&S.tempty[i], TC_EPI_WARPS); }
         for (int i = 0; i < 4; ++i) tc_mbar_init(&S.qbar[i], 4);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -305,179 +286,204 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
     const int n_rt = EPI ? g.N / 64 : g.N / TC_N;
     const int n_items = n_mt * n_rt;
     const int nstage_per_item = g.bpr / TC_KB;
+    // Registers follow the work: the warpgroup of the issuer, producer and expansion warps gives up a third of its
+    // allocation, the four epilogue warpgroups (32 + 32 live accumulator / block-sum registers per thread) take it.
+    // (setmaxnreg sits inside the branch it governs: after a join the compiler must assume the smaller limit)
 
-    // ============================ loaders (warps 0-3) ============================
-    // Thread tid owns token tid of the M tile and weight row tid of the N tile.  All global
-    // traffic is cp.async (16 B), issued TC_AHEAD stages ahead: activations and their scales land
-    // directly in the canonical operand layout, nibbles land in a raw staging row and are expanded
-    // to int8 from shared memory when their stage comes up.
-    if (warp >= TC_LOADER_W0 && warp < TC_LOADER_W0 + TC_LW) {
-        struct Cur { int item, ks; int ar[TC_RPT]; const int8_t * aq[TC_RPT]; const float2 * as[TC_RPT];
-                     const uint4 * wq[TC_RPT]; const __half * wd[TC_RPT]; };
-        auto setup = [&](Cur & c) {
-            if (c.item >= n_items) return;
-            const int mt = c.item / n_rt, rt = c.item % n_rt;
+    if (warp >= TC_EPI_WARPS) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    // ============================ producer (one warp) ============================
+    // Everything a stage needs from memory is four kinds of bulk tensor copies, all completing on mbarriers: lane l
+    // gathers the quants and the (d8, 8sum) rows of tokens 4l..4l+3 (two tile::gather4 copies), lane 0 fetches the two
+    // 64-row tiles of the nibble plane.  The warp issues no other memory instruction.
+    if (warp == TC_PROD_WARP) {
+        unsigned it = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const int mt = item / n_rt, rt = item % n_rt;
             const int expert = S.mt_expert[mt], tstart = S.mt_start[mt], tcnt = S.mt_count[mt];
-            const size_t eo = (size_t) expert * g.exp_stride;
+            int crd[4];                       // activation rows to gather (a dead token repeats a live one: never read back)
+            int last = 0;
 #pragma unroll
-            for (int q = 0; q < TC_RPT; ++q) {
-                const int rr = tid + q * TC_LOADERS;                // token of the M tile == weight row of the N tile
+            for (int q = 0; q < 4; ++q) {
+                const int rr = 4 * lane + q;
                 int slot = -1;
                 if (rr < tcnt) slot = g.perm ? g.perm[tstart + rr] : tstart + rr;
-                c.ar[q] = (slot >= 0) ? (slot >> g.a_shift) : -1;
-                if (EPI) {
-                    const int r = rt * 64 + (rr & 63);
-                    const int sg = rr >> 6;                         // 0: gate, 1: up
-                    c.wq[q] = (const uint4 *) g.qs[sg] + eo + (size_t) r * g.bpr;
-                    c.wd[q] = (const __half *) g.d[sg] + eo + (size_t) r * g.bpr;
-                } else {
-                    const int r = rt * TC_N + rr;
-                    const int seg = (r < g.seg_end[0]) ? 0 : (r < g.seg_end[1]) ? 1 : 2;
-                    const int sbase = seg ? g.seg_end[seg - 1] : 0;
-                    c.wq[q] = (const uint4 *) g.qs[seg] + eo + (size_t) (r - sbase) * g.bpr;
-                    c.wd[q] = (const __half *) g.d[seg] + eo + (size_t) (r - sbase) * g.bpr;
+                if (slot >= 0) last = slot >> g.a_shift;
+                crd[q] = last;
+            }
+            const bool glive = 4 * lane < tcnt;
+            const unsigned a_bytes = (512u + 128u) * (unsigned) ((tcnt + 3) >> 2);
+            const CUtensorMap * mw0 = &map_w0, * mw1 = &map_w1;
+            int wrow0, wrow1;
+            if (EPI) {
+                wrow0 = wrow1 = expert * rpe + rt * 64;
+            } else {
+                const int r = rt * TC_N;
+                const int seg = (r < g.seg_end[0]) ? 0 : (r < g.seg_end[1]) ? 1 : 2;
+                const int sbase = seg ? g.seg_end[seg - 1] : 0;
+                mw0 = mw1 = (seg == 0) ? &map_w0 : (seg == 1) ? &map_w1 : &map_w2;
+                wrow0 = expert * rpe + (r - sbase); wrow1 = wrow0 + 64;
+            }
+            for (int ks = 0; ks < nstage_per_item; ++ks, ++it) {
+                const int stg = it % NS;
+                if (lane == 0) TC_TL(0, it, 0);
+                if (!tc_wait<TC_SLEEP_PROD>(S, &S.empty[stg], ((it / NS) & 1u) ^ 1u, 10u)) { ok = false; break; }
+                if (lane == 0) TC_TL(0, it, 1);
+                TcStage & T = S.st[stg];
+                const int kb0 = ks * TC_KB;
+                if (lane == 0) {
+                    tc_mbar_arrive_tx(&S.rawfull[stg], 2u * 64u * 64u);
+                    tc_tma_tile(T.rawq, mw0, kb0 * 16, wrow0, &S.rawfull[stg]);
+                    tc_tma_tile(T.rawq + 64 * 64, mw1, kb0 * 16, wrow1, &S.rawfull[stg]);
+                    tc_mbar_arrive_tx(&S.full[stg], a_bytes);
                 }
-                c.aq[q] = g.aqs + (size_t) (c.ar[q] < 0 ? 0 : c.ar[q]) * g.bpr * 32;
-                c.as[q] = reinterpret_cast<const float2 *>(g.asc) + (size_t) (c.ar[q] < 0 ? 0 : c.ar[q]) * g.bpr;
-            }
-        };
-        auto advance = [&](Cur & c) { if (++c.ks == nstage_per_item) { c.ks = 0; c.item += gridDim.x; setup(c); } };
-        int my_items = 0;
-        if ((int) blockIdx.x < n_items) my_items = (n_items - 1 - (int) blockIdx.x) / (int) gridDim.x + 1;
-        const unsigned total = (unsigned) my_items * (unsigned) nstage_per_item;
-        Cur ci;
-        ci.item = blockIdx.x; ci.ks = 0;
-#pragma unroll
-        for (int q = 0; q < TC_RPT; ++q) ci.ar[q] = -1;
-        setup(ci);
-        unsigned it_issue = 0;
-        bool ok = true;
-        long long pw_empty = 0, pw_cp = 0, pw_fence = 0, pw_unpack = 0; const long long pt0 = clock64();
-        auto issue = [&]() {
-            // stage it_issue: wait for its buffer, then fire the copies
-            if (ok && it_issue < total) {
-                const int stg = it_issue % TC_STAGES;
-                if (!TC_TWAIT(pw_empty, S, &S.empty[stg], ((it_issue / TC_STAGES) & 1u) ^ 1u, 10u)) ok = false;
-                else {
-                    TcStage & T = S.st[stg];
-                    const int kb0 = ci.ks * TC_KB;
-#pragma unroll
-                    for (int q = 0; q < TC_RPT; ++q) {
-                        const int rr = tid + q * TC_LOADERS;
-                        const bool live = ci.ar[q] >= 0;
-#pragma unroll
-                        for (int j = 0; j < TC_KB; ++j) {
-                            tc_cp16(T.A[j] + tc_canon(rr, 0), ci.aq[q] + (size_t) (kb0 + j) * 32, live);
-                            tc_cp16(T.A[j] + tc_canon(rr, 1), ci.aq[q] + (size_t) (kb0 + j) * 32 + 16, live);
-                            tc_cp16(T.rawq[rr] + j * 16, ci.wq[q] + kb0 + j, true);
-                        }
-                        tc_cp16(&T.sc[rr][0], ci.as[q] + kb0, live);
-                        tc_cp16(&T.sc[rr][2], ci.as[q] + kb0 + 2, live);
-                        tc_cp8(T.rawd[rr], ci.wd[q] + kb0);
-                    }
-                    advance(ci);
+                __syncwarp();
+                if (glive) {
+                    tc_tma_gather4(T.A + lane * 512, &map_a, kb0 * 32, crd[0], crd[1], crd[2], crd[3], &S.full[stg]);
+                    tc_tma_gather4(&T.sc[4 * lane][0], &map_s, kb0 * 8, crd[0], crd[1], crd[2], crd[3], &S.full[stg]);
                 }
+                if (lane == 0) TC_TL(0, it, 2);
             }
-            tc_cp_commit();                                         // one group per call, possibly empty
-            ++it_issue;
-        };
-        // Expansion and publication of one landed stage.
-        auto publish = [&](unsigned it) {
-            TcStage & T = S.st[it % TC_STAGES];
-            const long long tu0_ = TC_CLK();
-            // every raw read of the stage first, then the expansion: a store between two loads would order them
-            // (the compiler cannot tell the staging arrays apart through the computed offsets)
-            uint4 wv[TC_RPT][TC_KB];
-            uint2 dv[TC_RPT];
-#pragma unroll
-            for (int q = 0; q < TC_RPT; ++q) {
-                const int rr = tid + q * TC_LOADERS;
-#pragma unroll
-                for (int j = 0; j < TC_KB; ++j) wv[q][j] = *reinterpret_cast<const uint4 *>(T.rawq[rr] + j * 16);
-                dv[q] = *reinterpret_cast<const uint2 *>(T.rawd[rr]);               // the row's four fp16 block scales
-            }
-#pragma unroll
-            for (int q = 0; q < TC_RPT; ++q) {
-                const int rr = tid + q * TC_LOADERS;
-                const __half2 d01 = *reinterpret_cast<const __half2 *>(&dv[q].x), d23 = *reinterpret_cast<const __half2 *>(&dv[q].y);
-                const float df[4] = {__low2float(d01), __high2float(d01), __low2float(d23), __high2float(d23)};
-#pragma unroll
-                for (int j = 0; j < TC_KB; ++j) {
-                    // byte i of the 16: element i (low nibble) | element i+16 (high nibble)
-                    const uint4 w = wv[q][j];
-                    *reinterpret_cast<uint4 *>(T.B[j] + tc_canon(rr, 0)) =
-                        make_uint4(w.x & 0x0F0F0F0Fu, w.y & 0x0F0F0F0Fu, w.z & 0x0F0F0F0Fu, w.w & 0x0F0F0F0Fu);
-                    *reinterpret_cast<uint4 *>(T.B[j] + tc_canon(rr, 1)) =
-                        make_uint4((w.x >> 4) & 0x0F0F0F0Fu, (w.y >> 4) & 0x0F0F0F0Fu, (w.z >> 4) & 0x0F0F0F0Fu, (w.w >> 4) & 0x0F0F0F0Fu);
-                    T.d4[j][rr] = df[j];
-                }
-            }
-            const long long tf0_ = TC_CLK(); pw_unpack += tf0_ - tu0_;
-            tc_fence_async();                                       // generic-proxy writes -> visible to the MMA
-            pw_fence += TC_CLK() - tf0_;
-            __syncwarp();
-            if (lane == 0) tc_mbar_arrive(&S.full[it % TC_STAGES]);
-        };
-        // Publishing runs as far ahead as the copies: a stage is expanded and published as soon as its copies have
-        // landed, BEFORE the loader blocks on the buffer of the next stage to request.  (Blocking first delayed the
-        // publication of a stage that had landed long ago until the epilogue released an older buffer, and the MMA
-        // issuer starved for the length of one expansion per stage.)
-        for (int p = 0; p < TC_AHEAD; ++p) issue();                 // stages 0 .. TC_AHEAD-1 requested
-        unsigned pub = 0;                                           // stages [0, pub) are published
-        while (pub < total && ok) {
-            // everything requested so far must land; then publish all of it, then request one more stage
-            { const long long t0_ = TC_CLK(); tc_cp_wait<0>(); pw_cp += TC_CLK() - t0_; }
-            const unsigned have = it_issue < total ? it_issue : total;
-            for (; pub < have; ++pub) publish(pub);
-            issue();                                                // blocks until the epilogue has released the buffer
         }
-        tc_cp_wait<0>();
-        if (blockIdx.x == 0 && tid == 0) { g_tc_prof[0] = pw_empty; g_tc_prof[1] = pw_cp; g_tc_prof[2] = clock64() - pt0; g_tc_prof[13] = pw_fence; g_tc_prof[14] = pw_unpack; }
     }
-    // ============================ MMA issuer (last warp) =========================
+    // ============================ expansion (two warps) ==========================
+    // Thread e turns the staged nibbles of weight rows e and e + 64 into int8 (byte i of a block's 16:
+    // element i in the low nibble, element i + 16 in the high one) and their fp16 scales into fp32.  The scales
+    // (8 bytes per row and stage: below the copy engine's 16-byte minimum) come straight from global memory, requested
+    // one stage ahead.
+    else if (warp >= TC_EXP_W0) {
+        const int e = ptid - TC_EXP_W0 * 32;
+        unsigned it = 0;
+        bool ok = true;
+        // scale rows of the two weight rows of item `item`
+        auto scale_rows = [&](int item, const __half * (&dp)[2]) {
+            const int mt = item / n_rt, rt = item % n_rt;
+            const size_t eo = (size_t) S.mt_expert[mt] * g.exp_stride;
+            if (EPI) {
+                dp[0] = (const __half *) g.d[0] + eo + (size_t) (rt * 64 + e) * g.bpr;
+                dp[1] = (const __half *) g.d[1] + eo + (size_t) (rt * 64 + e) * g.bpr;
+            } else {
+                const int r = rt * TC_N;
+                const int seg = (r < g.seg_end[0]) ? 0 : (r < g.seg_end[1]) ? 1 : 2;
+                const int sbase = seg ? g.seg_end[seg - 1] : 0;
+                dp[0] = (const __half *) g.d[seg] + eo + (size_t) (r - sbase + e) * g.bpr;
+                dp[1] = dp[0] + (size_t) 64 * g.bpr;
+            }
+        };
+        const __half * dp[2] = {nullptr, nullptr};
+        uint2 dnext[2] = {make_uint2(0, 0), make_uint2(0, 0)};
+        if ((int) blockIdx.x < n_items) {
+            scale_rows(blockIdx.x, dp);
+            dnext[0] = __ldg(reinterpret_cast<const uint2 *>(dp[0]));
+            dnext[1] = __ldg(reinterpret_cast<const uint2 *>(dp[1]));
+        }
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            for (int ks = 0; ks < nstage_per_item; ++ks, ++it) {
+                const uint2 dcur[2] = {dnext[0], dnext[1]};
+                {   // request the next stage's scales before waiting for this stage's nibbles
+                    int nks = ks + 1, nitem = item;
+                    if (nks == nstage_per_item) { nks = 0; nitem += gridDim.x; if (nitem < n_items) scale_rows(nitem, dp); }
+                    if (nitem < n_items) {
+                        dnext[0] = __ldg(reinterpret_cast<const uint2 *>(dp[0] + nks * TC_KB));
+                        dnext[1] = __ldg(reinterpret_cast<const uint2 *>(dp[1] + nks * TC_KB));
+                    }
+                }
+                const int stg = it % NS;
+                if (e == 0) TC_TL(1, it, 0);
+                if (!tc_wait<TC_SLEEP_PROD>(S, &S.rawfull[stg], (it / NS) & 1u, 15u)) { ok = false; break; }
+                if (e == 0) TC_TL(1, it, 1);
+                TcStage & T = S.st[stg];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int rr = e + 64 * h;                         // staged row
+                    const unsigned char * rq = T.rawq + rr * 64;
+                    const int xs = (rr >> 1) & 3;
+                    uint4 wv[TC_KB];
+#pragma unroll
+                    for (int j = 0; j < TC_KB; ++j) wv[j] = *reinterpret_cast<const uint4 *>(rq + ((j ^ xs) << 4));
+                    // staged row -> operand row r (= TMEM column).  EPI 1: the staged rows are 64 gate rows then the
+                    // same 64 up rows; 16 gate rows and their 16 up rows share a 32-column group (one epilogue warp)
+                    const int r = EPI ? 32 * (e >> 4) + 16 * h + (e & 15) : rr;
+                    unsigned char * rb = T.B + (r >> 3) * 1024 + (r & 7) * 128;
+                    const int x = r & 7;
+                    const uint2 dv = dcur[h];
+                    const __half2 d01 = *reinterpret_cast<const __half2 *>(&dv.x), d23 = *reinterpret_cast<const __half2 *>(&dv.y);
+                    const float df[4] = {__low2float(d01), __high2float(d01), __low2float(d23), __high2float(d23)};
+#pragma unroll
+                    for (int j = 0; j < TC_KB; ++j) {
+                        const uint4 w = wv[j];
+                        *reinterpret_cast<uint4 *>(rb + (((2 * j) ^ x) << 4)) =
+                            make_uint4(w.x & 0x0F0F0F0Fu, w.y & 0x0F0F0F0Fu, w.z & 0x0F0F0F0Fu, w.w & 0x0F0F0F0Fu);
+                        *reinterpret_cast<uint4 *>(rb + (((2 * j + 1) ^ x) << 4)) =
+                            make_uint4((w.x >> 4) & 0x0F0F0F0Fu, (w.y >> 4) & 0x0F0F0F0Fu, (w.z >> 4) & 0x0F0F0F0Fu, (w.w >> 4) & 0x0F0F0F0Fu);
+                        T.d4[j][r] = df[j];
+                    }
+                }
+                tc_fence_async();                                       // generic-proxy writes -> visible to the MMA
+                __syncwarp();
+                if (lane == 0) tc_mbar_arrive(&S.full[stg]);
+                if (e == 0) TC_TL(1, it, 2);
+            }
+        }
+    }
+    // ============================ MMA issuer =====================================
     else if (warp == TC_MMA_WARP) {
         if (lane == 0) {
             unsigned it = 0, blk = 0;
-            long long pw_full = 0, pw_te = 0; const long long pt0 = clock64();
             for (int item = blockIdx.x; item < n_items && !*(volatile int *) &S.abort; item += gridDim.x) {
                 bool ok = true;
                 for (int ks = 0; ks < nstage_per_item && ok; ++ks, ++it) {
-                    const int stg = it % TC_STAGES;
-                    if (!TC_TWAIT(pw_full, S, &S.full[stg], (it / TC_STAGES) & 1u, 20u)) { ok = false; break; }
+                    const int stg = it % NS;
+                    TC_TL(2, it, 0);
+                    if (!tc_wait<TC_SLEEP_MMA>(S, &S.full[stg], (it / NS) & 1u, 20u)) { ok = false; break; }
+                    TC_TL(2, it, 1);
                     tc_fence_after();
-                    TcStage & T = S.st[stg];
+                    const unsigned a0 = tc_smem_u32(S.st[stg].A), b0 = tc_smem_u32(S.st[stg].B);
 #pragma unroll
                     for (int j = 0; j < TC_KB; ++j, ++blk) {
                         const int tb = blk % TC_TBUF;
-                        TC_TL(0, blk, TC_CLK());
-                        if (!TC_TWAIT(pw_te, S, &S.tempty[tb], ((blk / TC_TBUF) & 1u) ^ 1u, 21u)) { ok = false; break; }
-                        TC_TL(1, blk, TC_CLK());
+                        // use k of a buffer waits for phase k: the epilogue presets and releases it once up front,
+                        // then after every read
+                        TC_TL(3, blk, 0);
+                        if (!tc_wait<TC_SLEEP_MMA>(S, &S.tempty[tb], (blk / TC_TBUF) & 1u, 21u)) { ok = false; break; }
+                        TC_TL(3, blk, 1);
                         tc_fence_after();
-                        tc_mma_i8(tmem + tb * TC_N, tc_desc(T.A[j]), tc_desc(T.B[j]), TC_IDESC);
+                        tc_mma_i8(tmem + tb * TC_N, tc_desc(a0 + j * 32), tc_desc(b0 + j * 32), TC_IDESC);
                         tc_commit(&S.tfull[tb]);                    // this block's result is ready
-                        TC_TL(2, blk, TC_CLK());
+                        TC_TL(3, blk, 2);
                     }
                     if (ok) tc_commit(&S.empty[stg]);               // the MMAs have finished reading the stage
                 }
                 if (!ok) break;
             }
-            if (blockIdx.x == 0) { g_tc_prof[4] = pw_full; g_tc_prof[5] = pw_te; g_tc_prof[6] = clock64() - pt0; g_tc_prof[7] = blk; }
         }
+    }
     }
     // ============================ epilogue (sixteen warps) ========================
     // Four warps per TMEM lane quadrant, each folding 32 of the 128 columns: 32 accumulators
     // per thread, four warps per scheduler to hide the TMEM read latency.
-    else if (warp >= TC_EPI_W0 && warp < TC_EPI_W0 + TC_EPI_WARPS) {
-        const int ew = warp - TC_EPI_W0;             // 0..15
+    else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
         const int quad = warp & 3;                  // TMEM lane quadrant this warp may access
-        const int sub = ew >> 2;                    // which 32 columns
+        const int sub = warp >> 2;                  // which 32 columns
         const int tok = quad * 32 + lane;           // token (TMEM lane) of this thread
         const unsigned tlane = (unsigned) (quad * 32) << 16;
-        // EPI 0: columns [32 sub, +32).  EPI 1: gate [16 sub, +16) -> acc[0..15], up [64 + 16 sub, +16) -> acc[16..31].
-        const int c0 = EPI ? 16 * sub : 32 * sub;
-        const int c1 = EPI ? 64 + 16 * sub : 32 * sub + 16;
+        // This warp folds columns [32 sub, +32) of every block.  EPI 1: the expansion warps place gate rows
+        // [16 sub, +16) of the item in columns [32 sub, +16) and the same up rows in [32 sub + 16, +16), so
+        // acc[0..15] are gate values and acc[16..31] the matching up values.
+        const int c0 = 32 * sub;
+        // preset this warp's part of every buffer, then hand them to the MMA issuer
+#pragma unroll
+        for (int tb = 0; tb < TC_TBUF; ++tb) tc_st32(tmem + tlane + tb * TC_N + c0, TC_MAGIC_I);
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+#pragma unroll
+            for (int tb = 0; tb < TC_TBUF; ++tb) tc_mbar_arrive(&S.tempty[tb]);
+        }
         unsigned it = 0, blk = 0, nitem = 0;
-        long long pw_full = 0, pw_tf = 0, pw_ld = 0, pw_tail = 0, pw_math = 0, pw_rel = 0; const long long pt0 = clock64();
         for (int item = blockIdx.x; item < n_items && !*(volatile int *) &S.abort; item += gridDim.x, ++nitem) {
             const int mt = item / n_rt, rt = item % n_rt;
             const int tstart = S.mt_start[mt], tcnt = S.mt_count[mt];
@@ -486,127 +492,67 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
             if (tok < tcnt) slot = g.perm ? g.perm[tstart + tok] : tstart + tok;
             const int ar = (slot >= 0) ? (slot >> g.a_shift) : -1;
             const float scl = (ar >= 0 && g.scale) ? g.scale[ar] : 1.0f;
-            float acc[32];
+            unsigned long long acc[16];                        // 32 fp32 accumulators as 16 pairs
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
+            for (int i = 0; i < 16; ++i) acc[i] = 0ull;
             bool ok = true;
             for (int ks = 0; ks < nstage_per_item && ok; ++ks, ++it) {
-                const int stg = it % TC_STAGES;
-                if (!TC_TWAIT(pw_full, S, &S.full[stg], (it / TC_STAGES) & 1u, 30u)) { ok = false; break; }   // d4 / sc are in place
+                const int stg = it % NS;
+                if (!tc_wait(S, &S.full[stg], (it / NS) & 1u, 30u)) { ok = false; break; }   // d4 / sc are in place
                 TcStage & T = S.st[stg];
-#if TC_UNROLLJ
                 static_assert(TC_KB == TC_TBUF, "block j of a stage lands in TMEM buffer j");
                 const unsigned tpar = it & 1u;                     // == (blk / TC_TBUF) & 1 for every block of the stage
 #pragma unroll
-#else
-#pragma unroll 1
-#endif
                 for (int j = 0; j < TC_KB; ++j, ++blk) {
-#if TC_UNROLLJ
                     const int tb = j;
-#else
-                    const int tb = blk % TC_TBUF;
-                    const unsigned tpar = (blk / TC_TBUF) & 1u;
-#endif
-                    if (lane == 0 && warp == TC_LW) TC_TL(3, blk, TC_CLK());
-                    if (lane == 0 && warp == TC_LW + 15) TC_TL(6, blk, TC_CLK());
-                    if (!TC_TWAIT(pw_tf, S, &S.tfull[tb], tpar, 31u)) { ok = false; break; }
-                    if (lane == 0 && warp == TC_LW) TC_TL(4, blk, TC_CLK());
-                    if (lane == 0 && warp == TC_LW + 15) TC_TL(7, blk, TC_CLK());
+                    if (lane == 0 && (warp == 0 || warp == 7)) TC_TL(warp ? 5 : 4, blk, 0);
+                    if (!tc_wait(S, &S.tfull[tb], tpar, 31u)) { ok = false; break; }
+                    if (lane == 0 && (warp == 0 || warp == 7)) TC_TL(warp ? 5 : 4, blk, 1);
                     tc_fence_after();
                     if (warp_live) {
+                        // a padding token of a live warp reads whatever the stage held before: finite or not,
+                        // the value stays in this thread's registers and is never stored
+                        unsigned sv[32];
+                        tc_ld32(tmem + tlane + tb * TC_N + c0, sv);
                         const float2 sc = T.sc[tok][j];
-                        const float d8 = sc.x, nc = -sc.y;
-#if TC_LD8
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            // 8 columns at a time: few enough live registers that the three passes below stay
-                            // separate (eight independent converts, then eight inner, then eight outer FMAs)
-                            const int col = ((q & 2) ? c1 : c0) + 8 * (q & 1);
-                            int sv[8];
-                            const long long tl0_ = TC_CLK();
-                            tc_ld8(tmem + tlane + tb * TC_N + col, sv);
-                            const float4 da = *reinterpret_cast<const float4 *>(&T.d4[j][col]);
-                            const float4 db = *reinterpret_cast<const float4 *>(&T.d4[j][col + 4]);
-                            tc_wait_ld();
-                            const long long tl1_ = TC_CLK(); pw_ld += tl1_ - tl0_;
-                            if (q == 3) {
-                                tc_fence_before();
-                                __syncwarp();
-                                if (lane == 0) tc_mbar_arrive(&S.tempty[tb]);      // TMEM buffer is free again
-                            }
-                            const long long tl2_ = TC_CLK(); pw_rel += tl2_ - tl1_;
-#if TC_FFMA2
-                            // two IEEE FMAs per issue slot: same roundings, half the FMA instructions
-                            const float2 d8p = make_float2(d8, d8), ncp = make_float2(nc, nc);
-                            const float2 ddp[4] = {make_float2(da.x, da.y), make_float2(da.z, da.w), make_float2(db.x, db.y), make_float2(db.z, db.w)};
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                float2 f = make_float2(tc_i2f(sv[2 * i]), tc_i2f(sv[2 * i + 1]));
-                                f = tc_ffma2(d8p, f, ncp);
-                                const float2 r = tc_ffma2(ddp[i], f, make_float2(acc[8 * q + 2 * i], acc[8 * q + 2 * i + 1]));
-                                acc[8 * q + 2 * i] = r.x; acc[8 * q + 2 * i + 1] = r.y;
-                            }
-#if TC_PROF
-                            pw_math += TC_CLK() - tl2_ + (__float_as_int(acc[8 * q]) == 0x7fc12345 ? 1 : 0);   // keeps the clock read after the math
+                        const float d8 = sc.x, nc = FOLD ? -fmaf(sc.x, TC_MAGIC_F, sc.y) : -sc.y;
+                        const unsigned long long d8p = tc_pack(d8, d8), ncp = tc_pack(nc, nc);
+                        const unsigned long long nmag = tc_pack(-TC_MAGIC_F, -TC_MAGIC_F);
+                        tc_wait_ld();
+#ifndef TC_ABL_NOST
+                        tc_st32(tmem + tlane + tb * TC_N + c0, TC_MAGIC_I);     // the next block of this buffer starts from the offset
+                        tc_wait_st();
 #endif
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) tc_mbar_arrive(&S.tempty[tb]);           // TMEM buffer is free again
+                        if (lane == 0 && (warp == 0 || warp == 7)) TC_TL(warp ? 5 : 4, blk, 2);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+#ifdef TC_ABL_NOD4
+                            const float4 dd = make_float4(d8, nc, d8, nc);
 #else
-                            float f[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) f[i] = tc_i2f(sv[i]);
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) f[i] = fmaf(d8, f[i], nc);
-                            const float dd8[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) acc[8 * q + i] = fmaf(dd8[i], f[i], acc[8 * q + i]);
+                            const float4 dd = *reinterpret_cast<const float4 *>(&T.d4[j][c0 + 4 * i]);
 #endif
+#ifdef TC_ABL_NOMATH
+                            acc[2 * i] ^= tc_pack_u(sv[4 * i] ^ sv[4 * i + 1], __float_as_uint(dd.x)); acc[2 * i + 1] ^= tc_pack_u(sv[4 * i + 2] ^ sv[4 * i + 3], __float_as_uint(dd.z));
+                            continue;
+#endif
+                            unsigned long long f0 = tc_pack_u(sv[4 * i], sv[4 * i + 1]);         // (F, F) of two columns
+                            unsigned long long f1 = tc_pack_u(sv[4 * i + 2], sv[4 * i + 3]);
+                            if (!FOLD) { f0 = tc_fadd2(f0, nmag); f1 = tc_fadd2(f1, nmag); }       // float(S), exact
+                            f0 = tc_ffma2(d8p, f0, ncp);
+                            f1 = tc_ffma2(d8p, f1, ncp);
+                            acc[2 * i] = tc_ffma2(tc_pack(dd.x, dd.y), f0, acc[2 * i]);
+                            acc[2 * i + 1] = tc_ffma2(tc_pack(dd.z, dd.w), f1, acc[2 * i + 1]);
                         }
-#else
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            // 16 columns at a time keeps the live registers under the 96-register budget (no spills)
-                            int sv[16];
-                            tc_ld16(tmem + tlane + tb * TC_N + (h ? c1 : c0), sv);
-                            // the weight scales of these 16 columns come from shared memory while the TMEM read is in flight
-                            const float * dp = &T.d4[j][h ? c1 : c0];
-                            float4 dd[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) dd[i] = *reinterpret_cast<const float4 *>(dp + 4 * i);
-                            { const long long t0_ = TC_CLK(); tc_wait_ld(); pw_ld += TC_CLK() - t0_; }
-                            if (h == 1) {
-                                tc_fence_before();
-                                __syncwarp();
-                                if (lane == 0) tc_mbar_arrive(&S.tempty[tb]);      // TMEM buffer is free again
-                                if (lane == 0 && warp == TC_LW) TC_TL(5, blk, TC_CLK());
-                            }
-#ifdef TC_ABLATE_MATH
-                            acc[h] += __int_as_float(sv[0] ^ sv[15]);
-#else
-#if TC_FFMA2
-#pragma unroll
-                            for (int i = 0; i < 16; i += 4) {
-                                const int o = h * 16 + i;
-                                const float2 d8p = make_float2(d8, d8), ncp = make_float2(nc, nc);
-                                float2 f0 = tc_ffma2(d8p, make_float2(tc_i2f(sv[i + 0]), tc_i2f(sv[i + 1])), ncp);
-                                float2 f1 = tc_ffma2(d8p, make_float2(tc_i2f(sv[i + 2]), tc_i2f(sv[i + 3])), ncp);
-                                f0 = tc_ffma2(make_float2(dd[i / 4].x, dd[i / 4].y), f0, make_float2(acc[o + 0], acc[o + 1]));
-                                f1 = tc_ffma2(make_float2(dd[i / 4].z, dd[i / 4].w), f1, make_float2(acc[o + 2], acc[o + 3]));
-                                acc[o + 0] = f0.x; acc[o + 1] = f0.y; acc[o + 2] = f1.x; acc[o + 3] = f1.y;
-                            }
-#else
-#pragma unroll
-                            for (int i = 0; i < 16; i += 4) {
-                                const int o = h * 16 + i;
-                                acc[o + 0] = fmaf(dd[i / 4].x, fmaf(d8, tc_i2f(sv[i + 0]), nc), acc[o + 0]);
-                                acc[o + 1] = fmaf(dd[i / 4].y, fmaf(d8, tc_i2f(sv[i + 1]), nc), acc[o + 1]);
-                                acc[o + 2] = fmaf(dd[i / 4].z, fmaf(d8, tc_i2f(sv[i + 2]), nc), acc[o + 2]);
-                                acc[o + 3] = fmaf(dd[i / 4].w, fmaf(d8, tc_i2f(sv[i + 3]), nc), acc[o + 3]);
-                            }
-#endif
-#endif
-                        }
+#ifdef LKB_TUNING
+                        if (lane == 0 && (warp == 0 || warp == 7) && blockIdx.x == 0 && blk < TC_TL_N)
+                            g_tc_tl[warp ? 5 : 4][blk][3] = clock64() + (long long) (acc[15] == 0x7fc123457fc12345ull);   // read the clock after the math
 #endif
                     } else {
+                        tc_st32(tmem + tlane + tb * TC_N + c0, TC_MAGIC_I);
+                        tc_wait_st();
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) tc_mbar_arrive(&S.tempty[tb]);
@@ -618,15 +564,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
             }
             if (!ok) break;
             // ---- tile epilogue -----------------------------------------------------
-            const long long tt0_ = TC_CLK();
+            float a[32];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) tc_unpack(acc[i], a[2 * i], a[2 * i + 1]);
             if (EPI) {
-                // acc[0..7] = 16 gate rows, acc[8..15] = the same 16 up rows.  v goes through shared memory so
+                // a[0..15] = 16 gate rows, a[16..31] = the same 16 up rows.  v goes through shared memory so
                 // that one thread sees the 32 rows of a Q8_1 block: subs (0,1) form block 0, (2,3) block 1.
                 if (slot >= 0) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        const float g0 = __fmul_rn(acc[2 * i], scl), g1 = __fmul_rn(acc[2 * i + 1], scl);
-                        const float u0 = __fmul_rn(acc[16 + 2 * i], scl), u1 = __fmul_rn(acc[16 + 2 * i + 1], scl);
+                        const float g0 = __fmul_rn(a[2 * i], scl), g1 = __fmul_rn(a[2 * i + 1], scl);
+                        const float u0 = __fmul_rn(a[16 + 2 * i], scl), u1 = __fmul_rn(a[16 + 2 * i + 1], scl);
                         S.vbuf[tok][16 * sub + 2 * i]     = __fmul_rn(lkb_silu(g0), u0);
                         S.vbuf[tok][16 * sub + 2 * i + 1] = __fmul_rn(lkb_silu(g1), u1);
                     }
@@ -634,7 +582,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
                 // the four warps of this quadrant meet (bounded, like every other wait)
                 __syncwarp();
                 if (lane == 0) tc_mbar_arrive(&S.qbar[quad]);
-                if (!tc_wait(S, &S.qbar[quad], nitem & 1u, 32u)) break;
+                if (!tc_wait(S, &S.qbar[quad], 0u, 32u)) break;
                 if ((sub & 1) == 0 && slot >= 0) {
                     const int b = sub >> 1;
                     float v[32];
@@ -672,23 +620,27 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
                     reinterpret_cast<float2 *>(g.osc)[(size_t) slot * g.okb + orow0 / 32] =
                         make_float2(__low2float(ds), __fmul_rn(8.0f, __high2float(ds)));
                 }
+                // the readers of vbuf are done before any warp of the quadrant writes the next item's values
+                __syncwarp();
+                if (lane == 0) tc_mbar_arrive(&S.qbar[quad]);
+                if (!tc_wait(S, &S.qbar[quad], 1u, 33u)) break;
             } else if (slot >= 0) {
                 float * p0 = g.out + (size_t) slot * g.out_ld + rt * TC_N + c0;
 #pragma unroll
                 for (int i = 0; i < 32; i += 4) {
-                    float4 o0 = make_float4(__fmul_rn(acc[i], scl), __fmul_rn(acc[i + 1], scl),
-                                            __fmul_rn(acc[i + 2], scl), __fmul_rn(acc[i + 3], scl));
+                    float4 o0;
                     if (g.add) {
+                        // the residual add as the reference's build evaluates it: one fused multiply-add
+                        // (nvcc contracts its `*p + acc * scale`, src/prefill.cu:484-486)
                         const float4 a0 = *reinterpret_cast<const float4 *>(p0 + i);
-                        o0 = make_float4(__fadd_rn(a0.x, o0.x), __fadd_rn(a0.y, o0.y), __fadd_rn(a0.z, o0.z), __fadd_rn(a0.w, o0.w));
+                        o0 = make_float4(fmaf(a[i], scl, a0.x), fmaf(a[i + 1], scl, a0.y), fmaf(a[i + 2], scl, a0.z), fmaf(a[i + 3], scl, a0.w));
+                    } else {
+                        o0 = make_float4(__fmul_rn(a[i], scl), __fmul_rn(a[i + 1], scl), __fmul_rn(a[i + 2], scl), __fmul_rn(a[i + 3], scl));
                     }
                     *reinterpret_cast<float4 *>(p0 + i) = o0;
                 }
             }
-            pw_tail += TC_CLK() - tt0_;
         }
-        if (blockIdx.x == 0 && ptid == (TC_EPI_W0 + 0) * 32) { g_tc_prof[8] = pw_full; g_tc_prof[9] = pw_tf; g_tc_prof[10] = clock64() - pt0; g_tc_prof[11] = pw_ld; g_tc_prof[12] = pw_tail; g_tc_prof[21] = pw_math; g_tc_prof[22] = pw_rel; }
-        if (blockIdx.x == 0 && ptid == (TC_EPI_W0 + 2) * 32) { g_tc_prof[16] = pw_full; g_tc_prof[17] = pw_tf; g_tc_prof[18] = clock64() - pt0; g_tc_prof[19] = pw_ld; g_tc_prof[20] = pw_tail; g_tc_prof[23] = pw_math; g_tc_prof[24] = pw_rel; }
     }
 
     // ---- teardown: everyone meets, then the allocating warp frees TMEM ------------
@@ -701,43 +653,86 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_pf_gemm_tc(const lkb_pf_gemm 
 }
 
 // ---------------------------------------------------------------------------
+#define TC_NS_DENSE 4               // stages of the plain form (no SwiGLU staging buffer in shared memory)
+#define TC_NS_EPI   3
 static int g_tc_ready = 0;
+typedef CUresult (*tc_encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static tc_encode_fn g_tc_encode = nullptr;
 
 int lkb_gemm_tc_init() {
-    cudaError_t e = cudaFuncSetAttribute(k_pf_gemm_tc<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sizeof(TcSmem));
+    cudaError_t e = cudaSuccess;
+    const int s0 = (int) sizeof(TcSmem<TC_NS_DENSE, 0>) + 1024, s1 = (int) sizeof(TcSmem<TC_NS_EPI, 1>) + 1024;
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_pf_gemm_tc<0, TC_NS_DENSE, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, s0);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_pf_gemm_tc<0, TC_NS_DENSE, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, s0);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_pf_gemm_tc<1, TC_NS_EPI, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, s1);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_pf_gemm_tc<1, TC_NS_EPI, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, s1);
     if (e != cudaSuccess) return -(int) e;
-    e = cudaFuncSetAttribute(k_pf_gemm_tc<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sizeof(TcSmem));
+    // the tensor-map encoder is a driver entry point; it is looked up through the runtime so that the
+    // library carries no link-time dependency on the driver
+    void * fn = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr);
     if (e != cudaSuccess) return -(int) e;
+    if (!fn || qr != cudaDriverEntryPointSuccess) return LKB_ERR_UNSUPPORTED;
+    g_tc_encode = (tc_encode_fn) fn;
     g_tc_ready = 1;
     return LKB_OK;
 }
 
+// A byte matrix [rows][row_bytes] as a 2-D tensor; box = box_bytes x box_rows.
+static int tc_make_map(CUtensorMap * m, const void * base, unsigned row_bytes, unsigned box_bytes, unsigned box_rows,
+                       CUtensorMapSwizzle sw) {
+    const cuuint64_t dims[2] = {row_bytes, 1ull << 30};          // the row bound only clips; every coordinate used is in range
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {box_bytes, box_rows};
+    const cuuint32_t es[2] = {1, 1};
+    const CUresult r = g_tc_encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, es,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? LKB_OK : LKB_ERR_UNSUPPORTED;
+}
+
 // Shapes the tensor-core form covers; otherwise LKB_ERR_UNSUPPORTED (the caller falls back
-// to the CUDA-core form): out_ld / okb rows must allow 16-byte vector stores.
-int lkb_gemm_tc_launch(const lkb_pf_gemm * g, int epi, int max_tiles, cudaStream_t st) {
+// to the CUDA-core form): out_ld / okb rows must allow 16-byte vector stores, the planes the
+// alignment the copy engine asks for.
+int lkb_gemm_tc_launch(const lkb_pf_gemm * g, int epi, int fold, int max_tiles, cudaStream_t st) {
     if (!g_tc_ready) return LKB_ERR_NOT_INIT;
     if (g->bpr % TC_KB) return LKB_ERR_UNSUPPORTED;
-    if (epi) { if (g->N % 64 || (g->okb * 32) % 16) return LKB_ERR_UNSUPPORTED; }
+    if (epi) { if (g->N % 64 || (g->okb * 32) % 16 || g->bpr < 2 * TC_KB) return LKB_ERR_UNSUPPORTED; }
     else if (g->N % TC_N || g->out_ld % 4 || ((size_t) g->out & 15)) return LKB_ERR_UNSUPPORTED;
     if (g->perm && max_tiles > TC_MAX_TILES) return LKB_ERR_UNSUPPORTED;
     if (!g->perm && (g->ntok + TC_M - 1) / TC_M > TC_MAX_TILES) return LKB_ERR_UNSUPPORTED;
     if (((size_t) g->aqs & 15) || ((size_t) g->asc & 15)) return LKB_ERR_UNSUPPORTED;
+    if (g->exp_stride % g->bpr) return LKB_ERR_UNSUPPORTED;
+    const int nseg = epi ? 2 : (g->seg_end[0] >= g->N ? 1 : g->seg_end[1] >= g->N ? 2 : 3);
+    CUtensorMap ma, ms, mw[3];
+    int r = tc_make_map(&ma, g->aqs, (unsigned) g->bpr * 32u, 128u, 1u, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r != LKB_OK) return r;
+    r = tc_make_map(&ms, g->asc, (unsigned) g->bpr * 8u, 32u, 1u, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (r != LKB_OK) return r;
+    for (int s = 0; s < 3; ++s) {
+        const int src = s < nseg ? s : 0;
+        if (((size_t) g->qs[src] & 15) || ((size_t) g->d[src] & 7)) return LKB_ERR_UNSUPPORTED;
+        r = tc_make_map(&mw[s], g->qs[src], (unsigned) g->bpr * 16u, 64u, 64u, CU_TENSOR_MAP_SWIZZLE_64B);
+        if (r != LKB_OK) return r;
+    }
+    const int rpe = (int) (g->exp_stride / g->bpr);
     const int grid = lkb_context().sm_count;
-    if (epi) k_pf_gemm_tc<1><<<grid, TC_THREADS, sizeof(TcSmem), st>>>(*g, max_tiles);
-    else     k_pf_gemm_tc<0><<<grid, TC_THREADS, sizeof(TcSmem), st>>>(*g, max_tiles);
+    const size_t s0 = sizeof(TcSmem<TC_NS_DENSE, 0>) + 1024, s1 = sizeof(TcSmem<TC_NS_EPI, 1>) + 1024;
+    if (epi && fold)       k_pf_gemm_tc<1, TC_NS_EPI, 1><<<grid, TC_THREADS, s1, st>>>(*g, max_tiles, rpe, ma, ms, mw[0], mw[1], mw[2]);
+    else if (epi)          k_pf_gemm_tc<1, TC_NS_EPI, 0><<<grid, TC_THREADS, s1, st>>>(*g, max_tiles, rpe, ma, ms, mw[0], mw[1], mw[2]);
+    else if (fold)         k_pf_gemm_tc<0, TC_NS_DENSE, 1><<<grid, TC_THREADS, s0, st>>>(*g, max_tiles, rpe, ma, ms, mw[0], mw[1], mw[2]);
+    else                   k_pf_gemm_tc<0, TC_NS_DENSE, 0><<<grid, TC_THREADS, s0, st>>>(*g, max_tiles, rpe, ma, ms, mw[0], mw[1], mw[2]);
     return lkb_check_launch();
 }
 
 extern "C" {
-// Tuning hook (not in the public header): copies the 16 profiling counters of the last launch.
-__attribute__((visibility("default"))) int lkb_debug_gemm_prof(unsigned long long * out16) {
+#ifdef LKB_TUNING
+__attribute__((visibility("default"))) int lkb_debug_gemm_timeline(long long * out) {      // [6][TC_TL_N][4]
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-    return cudaMemcpyFromSymbol(out16, g_tc_prof, 32 * sizeof(unsigned long long)) == cudaSuccess ? 0 : -1;
-}
-#if TC_PROF
-__attribute__((visibility("default"))) int lkb_debug_gemm_timeline(long long * out) {      // [8][TC_TL_N]
-    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-    return cudaMemcpyFromSymbol(out, g_tc_tl, sizeof(long long) * 8 * TC_TL_N) == cudaSuccess ? 0 : -1;
+    return cudaMemcpyFromSymbol(out, g_tc_tl, sizeof(long long) * 6 * TC_TL_N * 4) == cudaSuccess ? 0 : -1;
 }
 #endif
 int lkb_pf_gemm_status(void) {

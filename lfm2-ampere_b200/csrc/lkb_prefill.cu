@@ -489,14 +489,16 @@ __global__ void __launch_bounds__(256) k_pf_moe_combine_norm_gather(float * __re
 // tile; thread = rows (lane, lane+32) x 8 tokens, so a warp holds 32 consecutive
 // rows of a token and the SwiGLU epilogue quantises with the standard warp
 // quantiser: fused output == unfused output bit for bit.
-// Per (row, token): acc = fma(d4, fma(d8, float(S_b), -8sum), acc) for b ascending,
-// then * scale, then (+ out).  ref: src/prefill.cu:172-491 (semantics), 391-399
+// Per (row, token), b ascending: fold = 1: acc = fma(d4, fma(d8, F_b, -c), acc) with F_b = 12582912 + S_b and
+// c = fma(d8, 12582912, 8sum) (the reference's shipped form, src/prefill.cu:131-139,341-342,381-384);
+// fold = 0: acc = fma(d4, fma(d8, float(S_b), -8sum), acc) (src/prefill.cu:391-399); then * scale, then (+ out).
+// ref: src/prefill.cu:172-491 (semantics)
 // ---------------------------------------------------------------------------
 #define SG_KB 8
 #define SG_WP (SG_KB * 16 + 16)        // weight row pitch in smem (bytes), +16 against bank conflicts
 
 template <int EPI>
-__global__ void __launch_bounds__(256) k_pf_gemm_simple(const lkb_pf_gemm g) {
+__global__ void __launch_bounds__(256) k_pf_gemm_simple(const lkb_pf_gemm g, const int fold) {
     __shared__ __align__(16) unsigned char s_w[64 * SG_WP];
     __shared__ __align__(16) __half        s_d[64 * SG_KB];
     __shared__ __align__(16) int8_t        s_a[64 * SG_KB * 32];
@@ -583,7 +585,10 @@ __global__ void __launch_bounds__(256) k_pf_gemm_simple(const lkb_pf_gemm g) {
                 const float2 sc = s_s[tk * SG_KB + kk];
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
-                    acc[h][j] = lkb_block_acc(d4[h], sc.x, lkb_sumi(wv[h], xv), sc.y, acc[h][j]);
+                    {
+                        const int si = lkb_sumi(wv[h], xv);
+                        acc[h][j] = fold ? lkb_block_acc_pf(d4[h], sc.x, si, sc.y, acc[h][j]) : lkb_block_acc(d4[h], sc.x, si, sc.y, acc[h][j]);
+                    }
             }
         }
         __syncthreads();
@@ -604,9 +609,9 @@ __global__ void __launch_bounds__(256) k_pf_gemm_simple(const lkb_pf_gemm g) {
         } else {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const float a = __fmul_rn(acc[h][j], scl);
+                // the residual add is one fused multiply-add, as the reference's build contracts it (src/prefill.cu:484-486)
                 float * p = g.out + (size_t) orow * g.out_ld + row0 + 32 * h + lane;
-                *p = g.add ? __fadd_rn(*p, a) : a;
+                *p = g.add ? fmaf(acc[h][j], scl, *p) : __fmul_rn(acc[h][j], scl);
             }
         }
     }
@@ -616,13 +621,16 @@ __global__ void __launch_bounds__(256) k_pf_gemm_simple(const lkb_pf_gemm g) {
 // C ABI
 // ---------------------------------------------------------------------------
 int lkb_gemm_tc_init();                                      // lkb_gemm_tc.cu
-int lkb_gemm_tc_launch(const lkb_pf_gemm * g, int epi, int max_tiles, cudaStream_t st);   // LKB_ERR_UNSUPPORTED if shape not covered
+int lkb_gemm_tc_launch(const lkb_pf_gemm * g, int epi, int fold, int max_tiles, cudaStream_t st);   // LKB_ERR_UNSUPPORTED if shape not covered
 
 static int g_gemm_cfg = -1;        // -1: tensor-core form when it covers the shape; 0: CUDA-core form
+static int g_gemm_fold = 1;        // 1: the reference's shipped per-block term (folded offset); 0: the exact term
 
 int lkb_prefill_init() {
     const char * v = getenv("LKB_PF_CFG");
     if (v) g_gemm_cfg = atoi(v);
+    v = getenv("LKB_PF_ARITH");
+    if (v) g_gemm_fold = atoi(v) ? 1 : 0;
     return lkb_gemm_tc_init();
 }
 
@@ -645,18 +653,19 @@ static int gemm_dispatch(const lkb_pf_gemm * g, int epi, int max_tiles, cudaStre
     const int ty = g->perm ? max_tiles : (g->ntok + 63) / 64;
     if (ty <= 0) return g->perm ? LKB_ERR_SHAPE : LKB_OK;
     if (g_gemm_cfg != 0) {
-        const int t = lkb_gemm_tc_launch(g, epi, max_tiles, st);
+        const int t = lkb_gemm_tc_launch(g, epi, g_gemm_fold, max_tiles, st);
         if (t != LKB_ERR_UNSUPPORTED) return t;
         if (g_gemm_cfg > 0) return t;
     }
-    if (epi) k_pf_gemm_simple<1><<<dim3(g->N / 32, ty), 256, 0, st>>>(*g);
-    else     k_pf_gemm_simple<0><<<dim3(g->N / 64, ty), 256, 0, st>>>(*g);
+    if (epi) k_pf_gemm_simple<1><<<dim3(g->N / 32, ty), 256, 0, st>>>(*g, g_gemm_fold);
+    else     k_pf_gemm_simple<0><<<dim3(g->N / 64, ty), 256, 0, st>>>(*g, g_gemm_fold);
     return lkb_check_launch();
 }
 
 extern "C" {
 
 int lkb_pf_gemm_config(int cfg) { g_gemm_cfg = cfg; return LKB_OK; }
+int lkb_pf_gemm_arith(int fold) { g_gemm_fold = fold ? 1 : 0; return LKB_OK; }
 
 int lkb_pf_norm(const float * X, const float * w, int plain, lkb_pf_act a, float * inv_out, float * h32,
                 int m, lkb_stream_t st) {

@@ -123,6 +123,15 @@ ORC_API void orc_block_sumi(const uint8_t * qs, const int8_t * aq, int rows, int
 static inline float block_term_acc(float d4, float d8, int32_t sumi, float sum8, float acc) {
     return fmaf(d4, fmaf(d8, (float) sumi, -sum8), acc);
 }
+/* The batched-prefill GEMM's form of the same term, as the reference ships it (PF_EPI2 = 1,
+ * src/prefill.cu:32-39,131-139,341-342,381-384): the tensor-core accumulator is seeded with the bit
+ * pattern of 1.5 * 2^23, so the block sum arrives as the float 12582912 + sumi (exact), and the offset
+ * is folded into the per-(token, block) constant c = fma(d8, 12582912, 8sum). */
+static inline float block_term_acc_pf(float d4, float d8, int32_t sumi, float sum8, float acc) {
+    const float c = fmaf(d8, 12582912.0f, sum8);
+    const float F = (float) (12582912 + sumi);          /* exact: |sumi| < 2^22 */
+    return fmaf(d4, fmaf(d8, F, -c), acc);
+}
 
 /* One GEMV row in the reference's order: lane l accumulates blocks l, l+32, ...
  * then the butterfly.  src/kernels.cu:214-223 + warp_sum. */
@@ -491,12 +500,14 @@ ORC_API void orc_moe_scatter(const int * idx, int n, int n_exp, const int * off,
 
 /* a13. The grouped / dense Q4_0 x Q8_1 GEMM.  src/prefill.cuh:45-66,
  * src/prefill.cu:186-233, 391-399, 474-490.
- *   out[orow][n] = (add ? out : 0) + scale[arow] * sum_{b ascending} fma(d4, fma(d8, S_b, -8sum), .)
+ *   out[orow][n] = (add ? out : 0) + scale[arow] * sum_{b ascending} fma(d4, fma(d8, 12582912 + S_b, -c), .)
+ *   with c = fma(d8, 12582912, 8sum), the reference's shipped form (block_term_acc_pf above)
  * Weight row n of the stacked tensor lives in segment seg (rows [seg_end[seg-1],
  * seg_end[seg])) at qs[seg] + expert*exp_stride + (n - seg_start)*bpr.
  * Tokens: dense rows [0, ntok) or, with perm != NULL, every slot perm[i]
  * (expert = idx_of_slot from the tile that covers i), arow = slot >> a_shift.
- * out64/mag (optional) receive the float64 value before scale/add and sum|terms|.
+ * out64/mag/slack (optional) receive the float64 value before scale/add, sum|terms| and the folded
+ * form's allowed rounding.
  */
 typedef struct {
     const uint8_t *  qs[3];
@@ -525,16 +536,20 @@ static void gemm_locate(const orc_gemm_t * g, int n, int expert, const uint8_t *
     *d = g->d[seg] + blk;
 }
 
+static int g_gemm_fold = 1;      /* 1: the reference's shipped (folded) term; 0: the exact term */
+ORC_API void orc_set_gemm_fold(int fold) { g_gemm_fold = fold ? 1 : 0; }
+
 static float gemm_dot32(const orc_gemm_t * g, const uint8_t * q, const uint16_t * d, int arow) {
     const int8_t * aq = g->aqs + (size_t) arow * g->bpr * 32;
     const float * as = g->asc + (size_t) arow * g->bpr * 2;
     float acc = 0.0f;
     for (int b = 0; b < g->bpr; ++b)
-        acc = block_term_acc(orc_f16_to_f32(d[b]), as[2 * b], block_sumi(q + (size_t) b * 16, aq + b * 32), as[2 * b + 1], acc);
+        acc = g_gemm_fold ? block_term_acc_pf(orc_f16_to_f32(d[b]), as[2 * b], block_sumi(q + (size_t) b * 16, aq + b * 32), as[2 * b + 1], acc)
+                          : block_term_acc(orc_f16_to_f32(d[b]), as[2 * b], block_sumi(q + (size_t) b * 16, aq + b * 32), as[2 * b + 1], acc);
     return acc;
 }
 
-ORC_API void orc_pf_gemm(const orc_gemm_t * g, double * out64, double * mag) {
+ORC_API void orc_pf_gemm(const orc_gemm_t * g, double * out64, double * mag, double * slack) {
     const int nrows = g->perm ? 0 : g->ntok;
     /* flatten (slot, expert) pairs */
     int total = nrows;
@@ -556,20 +571,26 @@ ORC_API void orc_pf_gemm(const orc_gemm_t * g, double * out64, double * mag) {
         for (int n = 0; n < g->N; ++n) {
             const uint8_t * q; const uint16_t * d;
             gemm_locate(g, n, expt[i], &q, &d);
-            const float a = gemm_dot32(g, q, d, arow) * scl;
+            /* the residual add is ONE fused multiply-add: nvcc contracts the reference's `*p + acc * scale`
+             * (src/prefill.cu:484-486), confirmed by byte comparison with the reference's kernel on a B200 */
+            const float acc = gemm_dot32(g, q, d, arow);
             float * p = g->out + (size_t) orow * g->out_ld + n;
-            *p = g->add ? (*p + a) : a;
+            *p = g->add ? fmaf(acc, scl, *p) : acc * scl;
             if (out64) {
                 const int8_t * aq = g->aqs + (size_t) arow * g->bpr * 32;
                 const float * as = g->asc + (size_t) arow * g->bpr * 2;
-                double acc = 0.0, am = 0.0;
+                double acc = 0.0, am = 0.0, sl = 0.0;
                 for (int b = 0; b < g->bpr; ++b) {
-                    const double t = (double) orc_f16_to_f32(d[b]) *
-                        ((double) as[2 * b] * (double) block_sumi(q + (size_t) b * 16, aq + b * 32) - (double) as[2 * b + 1]);
+                    const double d4 = (double) orc_f16_to_f32(d[b]);
+                    const double t = d4 * ((double) as[2 * b] * (double) block_sumi(q + (size_t) b * 16, aq + b * 32) - (double) as[2 * b + 1]);
                     acc += t; am += fabs(t);
+                    /* the rounding the folded form is allowed: |d4| * half an ulp of c (tests/test_prefill.cu:78-79) */
+                    const float c = fabsf(fmaf(as[2 * b], 12582912.0f, as[2 * b + 1]));
+                    sl += fabs(d4) * 0.5 * (double) (nextafterf(c, INFINITY) - c);
                 }
                 out64[(size_t) orow * g->out_ld + n] = acc;
                 if (mag) mag[(size_t) orow * g->out_ld + n] = am;
+                if (slack) slack[(size_t) orow * g->out_ld + n] = sl;
             }
         }
     }

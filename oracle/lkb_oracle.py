@@ -359,17 +359,26 @@ def _mk_gemm(segs, seg_end, N, bpr, exp_stride, aqs, asc, ntok, perm, tiles, a_s
     return g
 
 
+def set_gemm_fold(fold):
+    """Per-block term of pf_gemm / pf_gemm_swiglu: True (default) the reference's shipped folded form,
+    False the exact term of the decode kernels."""
+    _lib.orc_set_gemm_fold(1 if fold else 0)
+
+
 def pf_gemm(segs, seg_end, N, bpr, aqs, asc, *, ntok=0, exp_stride=0, perm=None, tiles=None, a_shift=0,
-            scale=None, out_rows=None, out_init=None, add=0, want_f64=False):
+            scale=None, out_rows=None, out_init=None, add=0, want_f64=False, want_slack=False):
     """The grouped / dense GEMM.  segs = [(qs, d), ...] up to three stacked tensors.
-    Returns out (fp32, block-order accumulation) and, with want_f64, (out, out64, mag)."""
+    Returns out (fp32, block-order accumulation) and, with want_f64, (out, out64, mag[, slack])."""
     rows = out_rows if out_rows is not None else ntok
     out = np.full((rows, N), np.nan, np.float32) if out_init is None else _c(out_init, np.float32).copy()
     keep = []
     g = _mk_gemm(segs, seg_end, N, bpr, exp_stride, aqs, asc, ntok, perm, tiles, a_shift, scale, out, N, add, keep)
     o64 = np.zeros((rows, N), np.float64) if want_f64 else None
     mag = np.zeros((rows, N), np.float64) if want_f64 else None
-    _lib.orc_pf_gemm(C.byref(g), _p(o64, _f64p), _p(mag, _f64p))
+    slack = np.zeros((rows, N), np.float64) if (want_f64 and want_slack) else None
+    _lib.orc_pf_gemm(C.byref(g), _p(o64, _f64p), _p(mag, _f64p), _p(slack, _f64p))
+    if want_f64 and want_slack:
+        return out, o64, mag, slack
     return (out, o64, mag) if want_f64 else out
 
 
