@@ -319,9 +319,18 @@ int lkb_pf_gemm_config(int cfg);
  * The int32 block sums S_b are exact either way.  Also read once from LKB_PF_ARITH by lkb_init().
  * ref: src/prefill.cu:131-139 (PF_EPI2), 341-342, 381-399 */
 int lkb_pf_gemm_arith(int fold);
+/* Optional workspace of the grouped (perm != NULL) tensor-core form.  With a workspace registered, lkb_pf_gemm_moe /
+ * lkb_pf_gemm_swiglu first copy the activation rows into token-tile order (one small kernel) and the GEMM then fetches
+ * every 128-token tile with one bulk tensor copy; without one the rows are gathered through perm inside the GEMM, four
+ * per copy, which is slower.  Results are identical.  The buffer is the caller's (this library allocates nothing):
+ * 256-byte aligned device memory of at least lkb_pf_gemm_workspace_bytes(max_tiles, K of the widest activation)
+ * bytes; it is read and written by every grouped GEMM launched afterwards, so calls that share it must be ordered on
+ * one stream.  ptr = NULL unregisters.  No counterpart in the reference (its kernel gathers rows with cp.async). */
+int lkb_pf_gemm_workspace_bytes(int max_tiles, int k_max, size_t * bytes_out);
+int lkb_pf_gemm_set_workspace(void * ptr, size_t bytes);
 /* Every device-side wait of the tensor-core form is bounded; this SYNCHRONISES the device and
- * returns 0, or the code of the first wait that expired since the last call (10 loader,
- * 20/21 MMA issuer, 30/31 epilogue) and clears it.  No counterpart in the reference. */
+ * returns 0, or the code of the first wait that expired since the last call (10 producer,
+ * 15 expansion, 20/21 MMA issuer, 30/31 epilogue) and clears it.  No counterpart in the reference. */
 int lkb_pf_gemm_status(void);
 /* ref: src/prefill.cuh:123-127  k_pf_moe_combine / k_pf_moe_combine_norm / k_pf_pack_q8_1 */
 int lkb_pf_moe_combine(float * X, const float * D, const float * w, int m, lkb_stream_t st);

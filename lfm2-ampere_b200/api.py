@@ -20,7 +20,7 @@ __all__ = [
     "k_pf_router", "k_pf_router_small", "k_pf_router_tiled", "k_pf_select", "k_pf_moe_count", "k_pf_moe_plan", "k_pf_moe_scatter",
     "pf_gemm_dense", "pf_gemm_moe", "pf_gemm_swiglu", "k_pf_moe_combine", "k_pf_moe_combine_norm",
     "k_pf_pack_q8_1", "zero_i32", "moe_layer_desc", "moe_scratch", "moe_ffn_decode", "moe_ffn_decode_stack",
-    "layer_descs_to_device", "ep_pack_rows", "ep_unpack_rows", "k_pf_moe_combine_norm_gather", "moe_ffn_decode_stack_static", "set_pdl", "pf_gemm_config", "pf_gemm_arith", "sm_count",
+    "layer_descs_to_device", "ep_pack_rows", "ep_unpack_rows", "k_pf_moe_combine_norm_gather", "moe_ffn_decode_stack_static", "set_pdl", "pf_gemm_config", "pf_gemm_arith", "pf_gemm_workspace_bytes", "pf_gemm_set_workspace", "sm_count",
     "k_gemv_q6_K", "k_argmax_part", "k_argmax_final", "k_embed_q6_K", "gemv_q6_K_status",
     "k_attn_split", "k_attn_combine", "k_qk_norm_rope", "k_shortconv", "ATTN_SPLIT", "ATTN_PARTW",
     "mixer_layer_desc", "step_scratch", "decode_layers",
@@ -64,6 +64,20 @@ def pf_gemm_config(cfg):
 
 def pf_gemm_arith(fold):
     check(lib.lkb_pf_gemm_arith(int(fold)))
+
+
+def pf_gemm_workspace_bytes(max_tiles, k_max):
+    n = C.c_size_t(0)
+    check(lib.lkb_pf_gemm_workspace_bytes(int(max_tiles), int(k_max), C.byref(n)))
+    return n.value
+
+
+def pf_gemm_set_workspace(buf):
+    """Register (or with None unregister) the caller-owned workspace of the grouped tensor-core GEMM."""
+    if buf is None:
+        check(lib.lkb_pf_gemm_set_workspace(None, 0))
+    else:
+        check(lib.lkb_pf_gemm_set_workspace(ptr(buf), buf.numel() * buf.element_size()))
 
 
 def sm_count():

@@ -44,13 +44,16 @@ class PrefillStack:
         self.a = api.pf_act(self.a_qs, self.a_sc)
         self.a2 = api.pf_act(self.a2_qs, self.a2_sc)
         self.an = api.pf_act(self.n_qs, self.n_sc)
-        self.launches_per_step = 9 * len(layers)        # kernels per layer (the memset is not a kernel)
+        # caller-owned workspace of the grouped GEMM: activation rows in token-tile order (widest: the gate|up input)
+        self.gemm_ws = torch.zeros(api.pf_gemm_workspace_bytes(self.max_tiles, H), dtype=torch.uint8, device=device)
+        self.launches_per_step = 11 * len(layers)       # kernels per layer (the memset is not a kernel)
 
     def layer(self, i, next_norm_w=None, next_act=None):
         """One MoE FFN layer over the chunk.  next_norm_w / next_act = (PfAct, inv): where the fused combine + norm
         puts the next consumer's quantised activation (the full model: the next mixer's attn_norm, into the live
         activation buffers); by default the next layer's ffn_norm into scratch."""
         l, m = self.layers[i], self.m
+        api.pf_gemm_set_workspace(self.gemm_ws)
         api.k_pf_norm(self.X, l.norm_w, 0, self.a, self.inv, self.h32, m)
         api.k_pf_router(self.h32, m, l.router, l.rbias, self.inv, self.sel, self.sig)
         api.k_pf_select(self.sel, self.sig, m, self.idx, self.w)

@@ -33,6 +33,18 @@ def fold(request, L, orc):
     orc.set_gemm_fold(1)
 
 
+@pytest.fixture(params=["gather", "tiles"])
+def ws(request, L):
+    """Both activation paths of the grouped tensor-core GEMM: rows gathered through perm inside the kernel (no
+    workspace), or copied into token-tile order first (caller-owned workspace registered)."""
+    buf = None
+    if request.param == "tiles":
+        buf = torch.full((L.pf_gemm_workspace_bytes(4 * 700 // 64 + 64, 2048),), 0x5A, dtype=torch.uint8, device="cuda")
+    L.pf_gemm_set_workspace(buf)
+    yield request.param
+    L.pf_gemm_set_workspace(None)
+
+
 def _f64_gate(got, full, mag, slack, s, bpr, fold):
     """fp32 result against float64 (see the module docstring)."""
     if fold:
@@ -249,7 +261,7 @@ def test_gemm_dense(L, orc, fold, cfg, N, bpr, M, add, scale, three):
 
 @pytest.mark.parametrize("cfg", [0, 1])
 @pytest.mark.parametrize("E,rows,bpr,M,a_shift", [(8, 256, 64, 130, 2), (8, 384, 48, 257, 0), (64, 128, 8, 700, 2)])
-def test_gemm_moe(L, orc, fold, cfg, E, rows, bpr, M, a_shift):
+def test_gemm_moe(L, orc, fold, ws, cfg, E, rows, bpr, M, a_shift):
     L.pf_gemm_config(cfg)
     rng = np.random.default_rng(E * rows + bpr + M)
     NS = M * 4
@@ -287,7 +299,7 @@ def test_gemm_moe(L, orc, fold, cfg, E, rows, bpr, M, a_shift):
 
 
 @pytest.mark.parametrize("cfg", [0, 1])
-def test_gemm_swiglu_fused_equals_unfused(L, orc, fold, cfg):
+def test_gemm_swiglu_fused_equals_unfused(L, orc, fold, ws, cfg):
     L.pf_gemm_config(cfg)
     rng = np.random.default_rng(31)
     E, I, bpr, M = 8, 256, 64, 150

@@ -197,10 +197,16 @@ def _routing(rng, M, E):
     return idx
 
 
-@pytest.mark.parametrize("cfg", [0, 1])
+@pytest.mark.parametrize("cfg", [0, 1, 2])
 @pytest.mark.parametrize("E,rows,bpr,M,a_shift", [(8, 256, 64, 130, 2), (8, 384, 48, 257, 0), (64, 128, 8, 700, 2)])
 def test_gemm_moe_memcmp_reference_kernel(L, R, orc, cfg, E, rows, bpr, M, a_shift):
-    """pf_gemm_moe: the default (folded) per-block term is the reference kernel's own arithmetic -> identical bytes."""
+    """pf_gemm_moe: the default (folded) per-block term is the reference kernel's own arithmetic -> identical bytes.
+    cfg 0: CUDA-core form; 1: tensor-core form, rows gathered in the kernel; 2: tensor-core form with a workspace."""
+    wsbuf = None
+    if cfg == 2:
+        wsbuf = torch.zeros(L.pf_gemm_workspace_bytes(M * 4 // 64 + 64, bpr * 32), dtype=torch.uint8, device="cuda")
+        cfg = 1
+    L.pf_gemm_set_workspace(wsbuf)
     L.pf_gemm_config(cfg)
     L.pf_gemm_arith(1)
     rng = np.random.default_rng(E * rows + bpr + M + 7)
@@ -232,6 +238,7 @@ def test_gemm_moe_memcmp_reference_kernel(L, R, orc, cfg, E, rows, bpr, M, a_shi
     assert _same(o0, o1)
     assert L.lib.lkb_pf_gemm_status() == 0
     L.pf_gemm_config(-1)
+    L.pf_gemm_set_workspace(None)
 
 
 @pytest.mark.parametrize("cfg", [0, 1])
