@@ -3,21 +3,25 @@
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Headline (one JSON line on stdout, rank 0):
-  metric  "bs1 decode tok/s": one step = ONE token through the 40-layer MoE-FFN stack of
-          the synthetic model (benchmark configuration 1 repeated over 40 distinct layers:
-          router -> top-4 -> gate|up GEMV of the 4 chosen experts -> SwiGLU/Q8_1 -> down
-          GEMV + weighted sum + residual + next layer's norm quantiser).  13.6 GB of expert
-          weights are resident; a step streams 871 MB of them (which experts depends on the
-          token), so nothing is served from the 126 MB L2 twice.
-  value   tokens/s with inputs resident in HBM (CUDA-event time, max over ranks).
-  e2e     the same steps driven through the public API with the token's hidden state
-          copied host->device from pinned memory and the result copied back every step.
-  roofline  the dominant kernel (MoE gate|up GEMV): algorithmic bytes / its CUDA-event time.
-  prefill   4096-token batched prefill through the same 40 layers (configuration 3, Zipf-
-          skewed routing): tok/s, grouped-GEMM TMAC/s and tensor-pipe roofline; expert-
-          parallel over N GPUs when N > 1.
-Decode does not shard (batch 1): with --gpus N each rank runs an independent replica.
+One JSON line on stdout (rank 0).  The same metric at every N:
+  metric  "4k prefill tok/s": one step = a 4096-token chunk through the 40 MoE-FFN layers of the synthetic model
+          (benchmark configuration 3, Zipf(1.1)-skewed routing): per layer norm -> batched router -> top-4 -> count /
+          plan / scatter -> grouped gate|up GEMM with the SwiGLU + Q8_1 epilogue -> grouped down GEMM -> rank-order
+          combine + next norm.  13.6 GB of expert weights are streamed per step (inputs larger than L2).
+          N > 1: expert-parallel (64/N experts and 4096/N tokens per GPU, token exchange over NVLink), strong scaling;
+          before timing every rank compares a 2-layer 512-token expert-parallel run with the single-GPU path bit for
+          bit (config.ep_parity) and the run exits non-zero on a mismatch.
+  value   tokens/s with the chunk's hidden states resident in HBM (CUDA-event time over exactly K steps, max over ranks).
+  e2e     the same steps through the public API with the hidden states copied host->device from pinned memory and
+          the result copied back inside the timed region.
+  roofline  the dominant kernel (the tcgen05 grouped GEMM): int8 operations of the useful slots per launch / its
+          CUDA-event duration, against the int8 tensor peak measured on the spot with a library GEMM; under
+          roofline.decode the batch-1 decode step (configuration 2) against the measured HBM peak.
+  config.decode  the other half of the metric, measured at N = 1 (batch-1 decode does not shard): the full-model
+          step (configuration 2), the 40-layer MoE stack (configuration 1 x 40), the single GEMV (configuration 0),
+          the lm_head, and the long-context figures (configuration 4).
+  cpu_baseline  the CPU checker's restatement of the reference formulas on a 256-token slice of one layer of
+          configuration 3, all host cores, extrapolated linearly in tokens and layers.
 Data are seeded synthetic tensors with the configurations' shapes and value distributions.
 """
 import argparse
@@ -38,12 +42,9 @@ sys.path.insert(0, str(ROOT))
 N_LAYERS = 40
 H, E, TOPK, I = 2048, 64, 4, 1536
 LAYER_BYTES = E * H * 4 + 2 * TOPK * I * (H // 32) * 18 + TOPK * H * (I // 32) * 18 + 3 * H * 4   # 21,782,528
-GATEUP_BYTES = 2 * TOPK * I * (H // 32) * 18 + 64 * 36 + 2 * TOPK * I * 4                          # per launch
-# DRAM traffic of the fused decode kernel per MoE layer, from one ncu capture of a 4-layer launch
-# (dram__bytes_read.sum + dram__bytes_write.sum = 87,141,120 + 2,562,816 B; it grows in proportion to the layers)
-FUSED_TRAFFIC_PER_LAYER = (87141120 + 2562816) / 4
-METRIC = "bs1 decode tok/s"
+METRIC = "4k prefill tok/s"
 UNIT = "tok/s"
+DTYPE = "int4 x int8 -> int32 block sums (exact), fp32 accumulate"
 
 
 def peaks():
@@ -131,8 +132,19 @@ def cpu_layer_token(orc, L, x):
     return xo
 
 
-def cpu_baseline(target_s=12.0, max_tokens=None):
+def host_threads():
+    """Host cores this process may use (its CPU affinity): the CPU legs pin their OpenMP team to it, so that a
+    launcher's OMP_NUM_THREADS=1 does not decide the baseline."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def cpu_decode_baseline(target_s=4.0):
+    """Batch-1 MoE layer passes on the host (the CPU side of the decode figures under config.decode)."""
     orc = importlib.import_module("oracle.lkb_oracle")
+    orc.set_num_threads(host_threads())
     L = host_layer()
     rng = np.random.default_rng(1)
     x = rng.standard_normal(H).astype(np.float32)
@@ -140,48 +152,107 @@ def cpu_baseline(target_s=12.0, max_tokens=None):
     x1 = cpu_layer_token(orc, L, x)
     t1 = time.perf_counter() - t0
     n = max(2, int(target_s / max(t1, 1e-4)))
-    if max_tokens:
-        n = min(n, max_tokens)
     t0 = time.perf_counter()
     for i in range(n):
         x1 = cpu_layer_token(orc, L, x if i % 2 else x1 * 0.5)
-    dt = time.perf_counter() - t0
-    per_layer = dt / n
+    per_layer = (time.perf_counter() - t0) / n
     return {"value": 1.0 / (per_layer * N_LAYERS), "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
-            "sample": f"{n} MoE-layer passes of one token on the host (the CPU checker's restatement of the "
-                      f"reference formulas, OpenMP over rows); {per_layer * 1e3:.2f} ms per layer, x{N_LAYERS} layers per token"}, per_layer
+            "sample": f"{n} batch-1 MoE-layer passes on the host, {per_layer * 1e3:.2f} ms per layer, x{N_LAYERS} layers per token"}
+
+
+PF_SLICE = 256           # tokens of the CPU leg's slice of configuration 3
+
+
+def cpu_prefill_layer(orc, L, X):
+    """The checker's statement of one prefill MoE layer over the rows of X (the reference's CPU-side formulas)."""
+    m = X.shape[0]
+    aq, asc, inv, h32 = orc.pf_norm(X, L["nw"], plain=False, want_h32=True)
+    logits = orc.pf_router_logits(h32, L["router"], inv, 0 if m <= 256 else 1)
+    sel, sig = orc.pf_gate(logits, L["bias"])
+    idx, w = orc.pf_select(sel, sig)
+    cnt, off, tiles, perm = orc.moe_plan(idx.reshape(-1))
+    a2q, a2s, _ = orc.pf_gemm_swiglu(L["gate"], L["up"], I, H // 32, aq, asc, exp_stride=I * (H // 32), perm=perm, tiles=tiles,
+                                     a_shift=2, scale=inv, out_rows=m * TOPK)
+    D = orc.pf_gemm([L["down"]], [H, H, H], H, I // 32, a2q, a2s, exp_stride=H * (I // 32), perm=perm, tiles=tiles, a_shift=0,
+                    out_rows=m * TOPK)
+    return orc.pf_combine(X, D, w)
+
+
+def cpu_baseline(target_s=12.0):
+    """Configuration 3 on the host: a PF_SLICE-token slice of one layer (router, plan, both grouped GEMMs in the
+    reference's arithmetic, combine), repeated for about target_s seconds, extrapolated linearly in tokens and layers
+    (the work is linear in both: 9.4 MMAC per token and layer)."""
+    orc = importlib.import_module("oracle.lkb_oracle")
+    orc.set_num_threads(host_threads())
+    L = host_layer()
+    rng = np.random.default_rng(2)
+    X = rng.standard_normal((PF_SLICE, H)).astype(np.float32)
+    t0 = time.perf_counter()
+    Y = cpu_prefill_layer(orc, L, X)
+    t1 = time.perf_counter() - t0
+    n = max(1, int(target_s / max(t1, 1e-3)))
+    t0 = time.perf_counter()
+    for i in range(n):
+        Y = cpu_prefill_layer(orc, L, X if i % 2 == 0 else (Y * 0.5).astype(np.float32))
+    per_slice = (time.perf_counter() - t0) / n
+    tok_s = PF_SLICE / (per_slice * N_LAYERS)
+    return {"value": tok_s, "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
+            "sample": f"{n} passes of one MoE layer over a {PF_SLICE}-token slice of configuration 3 (the CPU checker's restatement "
+                      f"of the reference formulas, OpenMP over slots): {per_slice * 1e3:.0f} ms per slice and layer; extrapolated "
+                      f"linearly to {N_LAYERS} layers ({4096 // PF_SLICE} slices per 4096-token chunk)"}, per_slice
 
 
 def run_reference(args):
+    """The reference's CPU implementation of the path = the CPU checker (the reference has no CPU inference path; its CPU
+    code for this path is its test oracles), all host cores, on a bounded sample of the same workload."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    per = []
-    for _ in range(args.warmup):
+    for _ in range(min(args.warmup, 2)):
         cpu_baseline(target_s=0.5)
+    per = []
     t0 = time.perf_counter()
-    for _ in range(max(1, args.steps)):
-        cb, per_layer = cpu_baseline(target_s=min(20.0, 60.0 / max(1, args.steps)))
-        per.append(per_layer)
+    steps = max(1, args.steps)
+    for _ in range(steps):
+        cb, per_slice = cpu_baseline(target_s=min(15.0, 60.0 / steps))
+        per.append(per_slice)
     wall = time.perf_counter() - t0
-    per_layer = float(np.mean(per))
-    val = 1.0 / (per_layer * N_LAYERS)
+    per_slice = float(np.mean(per))
+    val = PF_SLICE / (per_slice * N_LAYERS)
     cb["value"] = val
     out = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
-           "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_layer * N_LAYERS * 1e3,
-           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8xint4->int32, fp32 accumulate",
+           "steps": args.steps, "warmup": args.warmup, "ms_per_step": 4096 / val * 1e3,
+           "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DTYPE,
            "data": "synthetic (seeded; shapes and distributions of the benchmark configuration)",
-           "config": {"workload": f"config 1 x {N_LAYERS} layers: batch-1 MoE FFN stack (64 experts, top-4, "
-                                  "hidden 2048, inter 1536, Q4_0 weights x Q8_1 activations); each step here is a "
-                                  "bounded sample of MoE-layer passes on the host cores",
-                      "wall_s": wall},
+           "config": {"workload": WORKLOAD, "tokens": 4096, "layers": N_LAYERS, "cpu_threads": cb["cores"], "wall_s": wall,
+                      "note": "each step is a bounded sample of the workload on the host cores (see cpu_baseline.sample)"},
            "cpu_baseline": cb,
            "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
            "gpu_launches": 0}
     print(json.dumps(out), flush=True)
 
 
+WORKLOAD = ("config 3: 4096-token batched prefill through the 40 MoE-FFN layers (64 experts, top-4, hidden 2048, inter 1536, "
+            "Q4_0 weights x Q8_1 activations, sigmoid + Zipf(1.1) bias router; per-expert counts, 64-slot tile plan, "
+            "fixed-order scatter, grouped int8 GEMMs)")
+
+
 # --------------------------------------------------------------------------- GPU arm
+def profile_traffic(name):
+    """DRAM bytes per launch recorded in a profiles/ summary (a line `traffic_bytes_per_launch: N`), or None when the
+    summary is missing: the figure belongs to the kernel build it was captured from, so it is read, never hard-coded."""
+    p = ROOT / "profiles" / name
+    if not p.exists():
+        return None
+    for ln in p.read_text().splitlines():
+        if ln.strip().startswith("traffic_bytes_per_launch:"):
+            try:
+                return float(ln.split(":", 1)[1].split()[0])
+            except ValueError:
+                return None
+    return None
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -200,8 +271,13 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     lkb.init(local)
-    lkb.set_pdl(not args.no_pdl)
+    lkb.set_pdl(False)
     hbm_peak, peak_kind, _ = peaks()
+    st = torch.cuda.current_stream()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    decode_sections = world == 1                # batch-1 decode does not shard: measured once, at N = 1
+    dsteps = max(200, args.decode_steps)        # timed decode steps
+    fsteps = 3                                  # timed full-model prefill chunks
 
     def barrier():
         if world > 1:
@@ -216,247 +292,235 @@ def run_ours(args):
         return float(t.item())
 
     layers = synth.make_model(args.layers, seed=1234, zipf_s=1.1)       # the same model on every rank
-    stack = decode.DecodeStack(layers)
-    rng = np.random.default_rng(99 + rank)
-    n_in = 64
-    x_host = torch.from_numpy(rng.standard_normal((n_in, H)).astype(np.float32)).pin_memory()
-    y_host = torch.empty(H, dtype=torch.float32).pin_memory()
-    x_pool = x_host.cuda()
-    st = torch.cuda.current_stream()
-
-    # one CUDA graph per step shape: copy-in of a resident input, then the 201 kernels
-    fused = args.decode_impl == "fused"
-    use_graph = (not args.no_graph) and not fused
-    graph = None
-    x_in = torch.zeros(H, device="cuda")
-    if use_graph:
-        stack.x.copy_(x_pool[0])
-        stack.step()                                  # warm the launch path before capture
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            stack.x.copy_(x_in)
-            stack.step()
-
-    def one_step(i, e2e=False):
-        if e2e:
-            x_in.copy_(x_host[i % n_in], non_blocking=True)
-        else:
-            x_in.copy_(x_pool[i % n_in])
-        if graph is not None:
-            graph.replay()
-        elif fused:
-            stack.x.copy_(x_in)
-            stack.step_fused()
-        else:
-            stack.x.copy_(x_in)
-            stack.step()
-        if e2e:
-            y_host.copy_(stack.x, non_blocking=True)
-            st.synchronize()
-
-    for i in range(max(3, args.warmup)):
-        one_step(i)
-    barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for i in range(args.steps):
-        one_step(i)
-    ev1.record()
-    barrier()
-    ms = max_over_ranks(ev0.elapsed_time(ev1))
-    clocks = None
-    tok_s = world * args.steps / (ms * 1e-3)
 
-    # end to end: host buffers, copies inside the timed region
-    for i in range(3):
-        one_step(i, e2e=True)
-    barrier()
-    ev0.record()
-    for i in range(args.steps):
-        one_step(i, e2e=True)
-    ev1.record()
-    barrier()
-    ms_e2e = max_over_ranks(ev0.elapsed_time(ev1))
-    e2e_tok_s = world * args.steps / (ms_e2e * 1e-3)
-
-    if fused and stack.status() != 0:
-        raise SystemExit(f"fused decode kernel reported status {stack.status()} (a bounded wait expired)")
-    if fused:
-        # the dominant kernel IS the step: one launch of k_moe_ffn_stack per token; its CUDA-event
-        # duration over the timed region is ms / steps
-        k_ms = ms / args.steps
-        ach = args.layers * LAYER_BYTES / (k_ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "kernel": f"k_moe_ffn_stack (persistent, {args.layers} MoE layers per launch)",
-                    "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
-                    "peak_kind": f"of {peak_kind}", "traffic": args.layers * FUSED_TRAFFIC_PER_LAYER,
-                    "algorithmic_bytes_per_launch": args.layers * LAYER_BYTES, "avg_launch_ms": k_ms}
-        n_launch = args.steps
-    else:
-        # dominant kernel: MoE gate|up GEMV, CUDA events around every launch of it while the
-        # same steps run un-graphed (the graph hides individual launches from events)
-        evs = []
-        lkb.set_pdl(False)
-        for i in range(min(args.steps, 10)):
-            stack.x.copy_(x_pool[i % n_in])
-            lkb.norm_produce(stack.x, H, stack._np[0])
-            for li, l in enumerate(layers):
-                lkb.k_router_dot(stack.h32, l.router, stack.logits, l.rbias, None, None, stack.ssq, 1e-5)
-                lkb.k_router_top4(stack.logits, l.rbias, stack.idx, stack.w)
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-                lkb.k_gemv_q4_0_exp2(l.gate_qs, l.gate_d, l.up_qs, l.up_d, stack.xq, I, H // 32, I, 0, stack.idx,
-                                     stack.gu[:TOPK * I], stack.gu[TOPK * I:], stack.ssq, 1e-5)
-                b.record()
-                evs.append((a, b))
-                lkb.k_swiglu(stack.gu[:TOPK * I], stack.gu[TOPK * I:], TOPK * I, None, stack.xq2, l.down_qs, stack.idx,
-                             H, I // 32, stack.pf_bytes)
-                nxt = stack._np[li + 1] if li + 1 < len(layers) else None
-                lkb.k_moe_down_accum(l.down_qs, l.down_d, stack.xq2, H, I // 32, H, I // 32, stack.idx, stack.w, stack.x, nxt)
+    # ================================================================ prefill, configuration 3 (the headline)
+    m = args.pf_tokens
+    ep = world > 1
+    ep_note, ep_parity = None, None
+    if ep:
+        # ---- parity first: 2 layers, 512 tokens, expert-parallel against the single-GPU path, bit for bit
+        mp_, lp_ = 512, layers[:2]
+        gen = torch.Generator(device="cuda").manual_seed(9)
+        Xp = torch.randn(mp_, H, device="cuda", generator=gen)
+        disp = args.ep_dispatch
+        good = torch.ones(1, device="cuda")
+        epp = None
+        if disp == "peer":
+            try:
+                epp = prefill.PrefillStackEP(lp_, mp_, rank, world, dispatch="peer")
+                epp.prepare()
+            except Exception as exc:                                         # noqa: BLE001 - reported in the JSON line
+                good.zero_()
+                ep_note = f"peer exchange unavailable ({type(exc).__name__}: {exc}); NCCL exchange used"
+            dist.all_reduce(good, op=dist.ReduceOp.MIN)
+            if float(good.item()) == 0.0:
+                epp, disp = None, "nccl"
+                ep_note = ep_note or "peer exchange unavailable on another rank; NCCL exchange used"
+        args.ep_dispatch = disp
+        if epp is None:
+            epp = prefill.PrefillStackEP(lp_, mp_, rank, world, dispatch="nccl")
+        mlp = mp_ // world
+        epp.X.copy_(Xp[rank * mlp:(rank + 1) * mlp])
+        epp.step()
+        refp = prefill.PrefillStack(lp_, mp_)
+        refp.X.copy_(Xp)
+        refp.step()
         torch.cuda.synchronize()
-        k_ms = float(np.mean([a.elapsed_time(b) for a, b in evs]))
-        lkb.set_pdl(not args.no_pdl)
-        ach = GATEUP_BYTES / (k_ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "kernel": "k_gemv_multi<2,6> (MoE gate|up GEMV, 8 x 1536 rows x K2048)",
-                    "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
-                    "peak_kind": f"of {peak_kind}", "traffic": None,
-                    "algorithmic_bytes_per_launch": GATEUP_BYTES, "avg_launch_ms": k_ms,
-                    "whole_step": {"bytes_per_step": args.layers * LAYER_BYTES,
-                                   "achieved_GBs": args.layers * LAYER_BYTES / (ms / args.steps * 1e-3) / 1e9,
-                                   "frac": args.layers * LAYER_BYTES / (ms / args.steps * 1e-3) / 1e9 / hbm_peak}}
-        n_launch = args.steps * stack.launches_per_step
+        same = torch.equal(epp.X, refp.X[rank * mlp:(rank + 1) * mlp]) and bool(torch.isfinite(epp.X).all())
+        okp = torch.tensor([1 if (same and epp.status() == 0) else 0], device="cuda")
+        dist.all_reduce(okp, op=dist.ReduceOp.MIN)
+        ep_parity = {"bitwise_equal_to_1gpu": bool(int(okp.item())), "dispatch": disp, "tokens": mp_, "layers": 2,
+                     "checked_on": f"{world} ranks, every rank's token slice, all_reduce(MIN)"}
+        del epp, refp
+        if not ep_parity["bitwise_equal_to_1gpu"]:
+            if rank == 0:
+                print(json.dumps({"metric": METRIC, "error": "expert-parallel prefill differs from the single-GPU path",
+                                  "config": {"ep_parity": ep_parity}}), flush=True)
+            dist.destroy_process_group()
+            raise SystemExit(3)
+        ps = prefill.PrefillStackEP(layers, m, rank, world, dispatch=disp)
+        ps.prepare()
+    else:
+        ps = prefill.PrefillStack(layers, m)
+    ml = m // world
+    Xall = np.random.default_rng(5).standard_normal((m, H)).astype(np.float32)
+    Xh = torch.from_numpy(Xall[rank * ml:(rank + 1) * ml].copy()).pin_memory()       # this rank's tokens
+    Xd = Xh.cuda()
+    Yh = torch.empty(ml, H, dtype=torch.float32).pin_memory()
+    pf_graph = None
 
-    # ---------------------------------------------------------------- prefill (configuration 3)
-    pf = None
-    if not args.no_prefill:
-        m = args.pf_tokens
-        del graph
-        ep = world > 1
-        ep_note = None
-        if ep:
-            ps = None
-            if args.ep_dispatch == "peer":
-                # the peer exchange needs symmetric memory across the ranks; where the platform refuses it, every rank
-                # falls back to the NCCL exchange together (both are this library's GPU paths; the line says which ran)
-                good = torch.ones(1, device="cuda")
-                try:
-                    ps = prefill.PrefillStackEP(layers, m, rank, world, dispatch="peer")
-                    ps.prepare()
-                except Exception as exc:                                     # noqa: BLE001 - reported in the JSON line
-                    good.zero_()
-                    ep_note = f"peer exchange unavailable ({type(exc).__name__}: {exc}); NCCL exchange used"
-                dist.all_reduce(good, op=dist.ReduceOp.MIN)
-                if float(good.item()) == 0.0:
-                    ps = None
-                    args.ep_dispatch = "nccl"
-                    ep_note = ep_note or "peer exchange unavailable on another rank; NCCL exchange used"
-            if ps is None:
-                ps = prefill.PrefillStackEP(layers, m, rank, world, dispatch="nccl")
+    def pf_step(e2e=False):
+        ps.X.copy_(Xh if e2e else Xd, non_blocking=True)
+        if pf_graph is not None:
+            pf_graph.replay()
         else:
-            ps = prefill.PrefillStack(layers, m)
-        ml = m // world
-        Xall = np.random.default_rng(5).standard_normal((m, H)).astype(np.float32)
-        Xh = torch.from_numpy(Xall[rank * ml:(rank + 1) * ml].copy()).pin_memory()       # this rank's tokens
-        Xd = Xh.cuda()
-        Yh = torch.empty(ml, H, dtype=torch.float32).pin_memory()
-
-        pf_graph = None
-
-        def pf_step(e2e=False):
-            ps.X.copy_(Xh if e2e else Xd, non_blocking=True)
-            if pf_graph is not None:
-                pf_graph.replay()
-            else:
-                ps.step()
-            if e2e:
-                Yh.copy_(ps.X, non_blocking=True)
-                st.synchronize()
+            ps.step()
+        if e2e:
+            Yh.copy_(ps.X, non_blocking=True)
+            st.synchronize()
+    pf_step()
+    # per-launch durations of the dominant kernel: one eager step with CUDA events around every grouped-GEMM launch
+    # (a graph replay hides individual launches from events); the timed region below replays the graph
+    ps.gemm_events = []
+    ps.step()
+    torch.cuda.synchronize()
+    gemm_ms = [a.elapsed_time(b) for a, b in ps.gemm_events]
+    ps.gemm_events = None
+    if (not ep or args.ep_dispatch == "peer") and not args.no_graph:
+        # one CUDA graph for the step's launches (the NCCL exchange has a host sync per layer and cannot be captured)
+        barrier()
+        pf_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(pf_graph, capture_error_mode="thread_local"):
+            ps.step()
+    for _ in range(max(3, args.warmup)):
         pf_step()
-        if (not ep or args.ep_dispatch == "peer") and not args.no_graph:
-            # one CUDA graph for the step's launches (the NCCL exchange has a host sync per layer and cannot be captured)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        pf_step()
+    ev1.record()
+    barrier()
+    pms = max_over_ranks(ev0.elapsed_time(ev1)) / args.steps
+    for _ in range(2):
+        pf_step(e2e=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        pf_step(e2e=True)
+    ev1.record()
+    barrier()
+    pms_e2e = max_over_ranks(ev0.elapsed_time(ev1)) / args.steps
+    gstat = lkb.lib.lkb_pf_gemm_status()
+    if gstat != 0:
+        raise SystemExit(f"tensor-core GEMM reported status {gstat} (a bounded wait expired)")
+    # int8 tensor peak of this GPU, measured with a library GEMM (timing only): MEASURED_PEAKS.json has no int8 figure
+    int8_peak = None
+    try:
+        A8 = torch.randint(-8, 8, (8192, 8192), dtype=torch.int8, device="cuda")
+        B8 = torch.randint(-8, 8, (8192, 8192), dtype=torch.int8, device="cuda")
+        for _ in range(3):
+            torch._int_mm(A8, B8)
+        torch.cuda.synchronize()
+        best = 1e9
+        for _ in range(5):
+            ev0.record()
+            torch._int_mm(A8, B8)
+            ev1.record()
             torch.cuda.synchronize()
-            barrier()
-            pf_graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(pf_graph, capture_error_mode="thread_local"):
-                ps.step()
-            pf_step()
-        barrier()
-        ev0.record()
-        for _ in range(args.pf_steps):
-            pf_step()
-        ev1.record()
-        barrier()
-        pms = max_over_ranks(ev0.elapsed_time(ev1)) / args.pf_steps
-        ev0.record()
-        for _ in range(args.pf_steps):
-            pf_step(e2e=True)
-        ev1.record()
-        barrier()
-        pms_e2e = max_over_ranks(ev0.elapsed_time(ev1)) / args.pf_steps
-        gstat = lkb.lib.lkb_pf_gemm_status()
-        if gstat != 0:
-            raise SystemExit(f"tensor-core GEMM reported status {gstat} (a bounded wait expired)")
-        # int8 tensor peak of this GPU, measured with a library GEMM (timing only): MEASURED_PEAKS.json has no int8 figure
+            best = min(best, ev0.elapsed_time(ev1))
+        int8_peak = 2 * 8192 ** 3 / (best * 1e-3) / 1e12
+        del A8, B8
+    except Exception:
         int8_peak = None
-        try:
-            A8 = torch.randint(-8, 8, (8192, 8192), dtype=torch.int8, device="cuda")
-            B8 = torch.randint(-8, 8, (8192, 8192), dtype=torch.int8, device="cuda")
-            for _ in range(3):
-                torch._int_mm(A8, B8)
-            torch.cuda.synchronize()
-            best = 1e9
-            for _ in range(5):
-                ev0.record()
-                torch._int_mm(A8, B8)
-                ev1.record()
-                torch.cuda.synchronize()
-                best = min(best, ev0.elapsed_time(ev1))
-            int8_peak = 2 * 8192 ** 3 / (best * 1e-3) / 1e12
-            del A8, B8
-        except Exception:
-            int8_peak = None
-        macs = args.layers * m * TOPK * (2 * I * H + H * I)
-        tmacs = macs / (pms * 1e-3) / 1e12
-        if ep:
-            est = torch.tensor([ps.status()], device="cuda")
-            dist.all_reduce(est, op=dist.ReduceOp.MAX)                       # every rank leaves together
-            if int(est.item()) != 0:
-                raise SystemExit(f"expert-parallel exchange reported status {int(est.item())} (a bounded wait expired)")
-            mine = torch.as_tensor(ps.recv_slots).sum().to("cuda", torch.float64).reshape(1)
-            mx, sm = mine.clone(), mine.clone()
-            dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-            dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-            imbalance = float(mx.item() / (sm.item() / world))
-            launches = args.pf_steps * ps.launches_per_step * world
-        else:
-            cnt = ps.cnt.cpu().numpy()
-            imbalance = float(cnt.max() / max(1.0, cnt.mean()))
-            launches = args.pf_steps * ps.launches_per_step
-        pf = {"metric": "4k prefill tok/s (40-layer MoE-FFN stack)", "tokens": m, "value": m / (pms * 1e-3), "unit": UNIT,
-              "ms_per_step": pms, "scaling": "strong", "cuda_graph": pf_graph is not None,
-              "parallelism": (f"expert-parallel x{world}: {E // world} experts and {ml} tokens per GPU, token all-to-all "
-                              "before and after the grouped GEMMs, " + ("NCCL all_to_all_single with one host sync per layer"
-                                                                        if args.ep_dispatch == "nccl" else
-                                                                        "peer-memory stores over NVLink with device-side flags, no host sync"))
-              if ep else "single GPU",
-              "e2e": {"value": m / (pms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": m * H * 4,
-                      "d2h_bytes_per_step": m * H * 4},
-              "gemm_tmacs": tmacs, "note": ep_note,
+    macs = args.layers * m * TOPK * (2 * I * H + H * I)
+    if ep:
+        est = torch.tensor([ps.status()], device="cuda")
+        dist.all_reduce(est, op=dist.ReduceOp.MAX)                       # every rank leaves together
+        if int(est.item()) != 0:
+            raise SystemExit(f"expert-parallel exchange reported status {int(est.item())} (a bounded wait expired)")
+        mine = torch.as_tensor(ps.recv_slots).sum().to("cuda", torch.float64).reshape(1)
+        mx, sm = mine.clone(), mine.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        imbalance = float(mx.item() / (sm.item() / world))
+        my_macs = float(mine.item()) * (2 * I * H + H * I)               # slots this rank's experts received, all layers
+        launches = args.steps * ps.launches_per_step * world
+    else:
+        cnt = ps.cnt.cpu().numpy()
+        imbalance = float(cnt.max() / max(1.0, cnt.mean()))
+        my_macs = float(macs)
+        launches = args.steps * ps.launches_per_step
+    # dominant kernel: k_pf_gemm_tc (two launches per layer).  Algorithmic int8 operations of this rank's useful slots per
+    # launch / the launches' average CUDA-event duration (the row-gather kernel of the workspace path runs inside the entry
+    # point and is inside that duration).
+    n_gemm = max(1, len(gemm_ms))
+    avg_launch_ms = float(np.mean(gemm_ms)) if gemm_ms else None
+    ops_per_launch = 2.0 * my_macs / n_gemm
+    ach = ops_per_launch / (avg_launch_ms * 1e-3) / 1e12 if avg_launch_ms else None
+    peak8 = int8_peak or 4500.0
+    roofline = {"bound": "tensor", "kernel": "k_pf_gemm_tc (tcgen05.mma.kind::i8, TMEM accumulators, operands by bulk tensor copies)",
+                "achieved": ach, "peak": peak8, "unit": "TOP/s", "frac": (ach / peak8) if ach else None,
+                "peak_kind": ("of measured here: torch._int_mm 8192^3, best of 5 (MEASURED_PEAKS.json records no int8 figure)"
+                              if int8_peak else "of nominal dense int8 (MEASURED_PEAKS.json records no int8 figure)"),
+                "nominal_int8_tops": 4500.0, "launches_per_step": n_gemm, "avg_launch_ms": avg_launch_ms,
+                "algorithmic_ops_per_launch": ops_per_launch,
+                "gemm_share_of_step": (float(np.sum(gemm_ms)) / pms) if gemm_ms else None,
+                "traffic": profile_traffic("k_pf_gemm_tc_prefill_4096tok.txt"),
+                "co_bound": "the exact per-block scale arithmetic (2 fp32 FMAs per int32 block sum on the CUDA cores) costs 256 "
+                            "FMA-pipe cycles per 128x128x32 block against 64 tensor-pipe cycles: the tensor pipe cannot exceed 25% busy",
+                "whole_step_TMACs": macs / (pms * 1e-3) / 1e12}
+    pf_cfg = {"workload": WORKLOAD, "tokens": m, "layers": args.layers, "resident_weight_bytes": args.layers * 339738624,
+              "cold_cache": "each step streams the whole 13.6 GB expert set (inputs larger than L2)",
+              "parallelism": (f"expert-parallel x{world}: {E // world} experts and {ml} tokens per GPU, token exchange before and after "
+                              "the grouped GEMMs, " + ("NCCL all_to_all_single with one host sync per layer" if args.ep_dispatch == "nccl"
+                                                       else "peer-memory stores over NVLink with device-side flags, no host sync")) if ep else "single GPU",
+              "cuda_graph": pf_graph is not None, "gemm_arith": "reference's shipped per-block term (folded offset): bit-identical to the reference kernel",
               ("slots_per_gpu_max_over_mean" if ep else "last_layer_max_over_mean_slots_per_expert"): imbalance,
-              "gpu_launches": launches,
-              "roofline": {"bound": "tensor", "achieved": 2 * tmacs, "unit": "TOP/s (int8)",
-                           "peak": (int8_peak or 4500.0) * world, "frac": 2 * tmacs / ((int8_peak or 4500.0) * world),
-                           "peak_kind": (f"of measured here: torch._int_mm 8192^3, best of 5, on rank 0's GPU, x {world} GPUs" if int8_peak else
-                                         "of nominal dense int8 (MEASURED_PEAKS.json records no int8 figure)"),
-                           "nominal_int8_tops": 4500.0,
-                           "note": "the per-block fp32 scale epilogue on the CUDA cores, not the MMA, bounds this kernel"}}
+              "gemm_TMACs": macs / (pms * 1e-3) / 1e12, "note": ep_note, "ep_parity": ep_parity,
+              "published_reference": {"value": 21188.0, "unit": UNIT, "hardware": "RTX 3090 Ti, real weights, full model incl. attention, 4096 tokens",
+                                      "note": "not this metric (full model): see config.full_prefill for the like-for-like chunk"}}
+    del pf_graph
+
+    # ================================================================ decode (N = 1 only): configurations 0, 1, 2, 4
+    dec = None
+    if decode_sections:
+        stack = decode.DecodeStack(layers)
+        rng = np.random.default_rng(99 + rank)
+        n_in = 64
+        x_host = torch.from_numpy(rng.standard_normal((n_in, H)).astype(np.float32)).pin_memory()
+        y_host = torch.empty(H, dtype=torch.float32).pin_memory()
+        x_pool = x_host.cuda()
+        x_in = torch.zeros(H, device="cuda")
+        # parity inside the bench: the fused persistent kernel against the five-kernel sequence on one seeded token
+        stack.x.copy_(x_pool[0]); stack.step(); torch.cuda.synchronize(); xa = stack.x.clone()
+        stack.x.copy_(x_pool[0]); stack.step_fused(); torch.cuda.synchronize()
+        dec_parity = bool(torch.equal(xa, stack.x))
+
+        def one_step(i, e2e=False):
+            if e2e:
+                x_in.copy_(x_host[i % n_in], non_blocking=True)
+            else:
+                x_in.copy_(x_pool[i % n_in])
+            stack.x.copy_(x_in)
+            stack.step_fused()
+            if e2e:
+                y_host.copy_(stack.x, non_blocking=True)
+                st.synchronize()
+        for i in range(5):
+            one_step(i)
+        torch.cuda.synchronize()
+        ev0.record()
+        for i in range(dsteps):
+            one_step(i)
+        ev1.record()
+        torch.cuda.synchronize()
+        ms = ev0.elapsed_time(ev1)
+        ev0.record()
+        for i in range(dsteps):
+            one_step(i, e2e=True)
+        ev1.record()
+        torch.cuda.synchronize()
+        ms_e2e = ev0.elapsed_time(ev1)
+        if stack.status() != 0:
+            raise SystemExit(f"fused decode kernel reported status {stack.status()} (a bounded wait expired)")
+        k_ms = ms / dsteps
+        ach_d = args.layers * LAYER_BYTES / (k_ms * 1e-3) / 1e9
+        dec = {"moe_stack": {"metric": "bs1 decode tok/s, 40-layer MoE-FFN stack (configuration 1 x 40)", "value": dsteps / (ms * 1e-3),
+                             "unit": UNIT, "ms_per_step": k_ms, "steps": dsteps, "parity_fused_equals_kernel_sequence": dec_parity,
+                             "e2e": {"value": dsteps / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": H * 4, "d2h_bytes_per_step": H * 4},
+                             "roofline": {"bound": "hbm", "kernel": f"k_moe_ffn_stack (persistent, {args.layers} MoE layers per launch)",
+                                          "achieved": ach_d, "peak": hbm_peak, "unit": "GB/s", "frac": ach_d / hbm_peak,
+                                          "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": args.layers * LAYER_BYTES,
+                                          "traffic": (lambda t: t * args.layers / 4 if t else None)(profile_traffic("k_moe_ffn_stack_decode_4layers.txt")),
+                                          "traffic_note": "ncu capture of a 4-layer launch, scaled by layers (traffic grows in proportion)"}}}
+        del stack
 
     # ---------------------------------------------------------------- output projection + argmax (decode tail)
     lm = None
-    if not args.no_lmhead:
+    if decode_sections and not args.no_lmhead:
         V, SB, NCOPY = 65536, 8, 3                      # three weight copies in rotation: 330 MB > L2
         gen = torch.Generator(device="cuda").manual_seed(77)
         copies = []
@@ -509,12 +573,12 @@ def run_ours(args):
               "gemv_argmax_us": res[1] * 1e3, "launches_per_token": 3, "cold_cache": f"{NCOPY} weight copies in rotation (330 MB > L2)",
               "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
                            "peak_kind": f"of {peak_kind}", "algorithmic_bytes": lm_bytes,
-                           "traffic": 114323968 if V == 65536 else None}}   # ncu dram read + write of one launch (profiles/)
+                           "traffic": profile_traffic("k_gemv_q6_K_stream_lmhead_65536rows.txt") if V == 65536 else None}}
         del copies
 
     # ---------------------------------------------------------------- Q4_0 x Q8_1 GEMV size sweep (configuration 0 and up)
     sweep = None
-    if not args.no_sweep:
+    if decode_sections and not args.no_sweep:
         gen2 = torch.Generator(device="cuda").manual_seed(9)
         xq_s = torch.empty(H // 32 * 36, dtype=torch.uint8, device="cuda")
         lkb.k_quantize_q8_1(torch.randn(H, device="cuda", generator=gen2), xq_s, H // 32)
@@ -546,7 +610,7 @@ def run_ours(args):
 
     # ---------------------------------------------------------------- full decode step (configuration 2)
     full = None
-    if not args.no_full:
+    if decode_sections and not args.no_full:
         model_mod = importlib.import_module("lfm2-ampere_b200.model")
         ctx = args.ctx
         fm = model_mod.make_full_model(n_layers=args.layers, seed=4321, moe_layers=layers)
@@ -554,7 +618,7 @@ def run_ours(args):
         out_h = torch.zeros(1, dtype=torch.int32).pin_memory()
         res = {}
         for impl in ("mega", "kernels"):
-            ds = model_mod.DecodeStep(fm, max_seq=ctx + 2 * (args.steps + 8) + 8, moe_impl=impl)
+            ds = model_mod.DecodeStep(fm, max_seq=ctx + 2 * (dsteps + 8) + 8, moe_impl=impl)
             ds.fill_kv(ctx)
             ds.d_token.fill_(11)
             lkb.set_pdl(impl == "kernels" and not args.no_pdl)
@@ -568,14 +632,14 @@ def run_ours(args):
                 gf.replay()
             barrier()
             ev0.record()
-            for _ in range(args.steps):
+            for _ in range(dsteps):
                 gf.replay()
             ev1.record()
             barrier()
-            t_dev = max_over_ranks(ev0.elapsed_time(ev1)) / args.steps
+            t_dev = max_over_ranks(ev0.elapsed_time(ev1)) / dsteps
             # end to end: the token id arrives from pinned host memory, the chosen token goes back, every step
             ev0.record()
-            for i in range(args.steps):
+            for i in range(dsteps):
                 tok_h[0] = 11 + i
                 ds.d_token.copy_(tok_h, non_blocking=True)
                 gf.replay()
@@ -583,7 +647,7 @@ def run_ours(args):
                 st.synchronize()
             ev1.record()
             barrier()
-            t_e2e = max_over_ranks(ev0.elapsed_time(ev1)) / args.steps
+            t_e2e = max_over_ranks(ev0.elapsed_time(ev1)) / dsteps
             if ds.status() != 0 or lkb.gemv_q6_K_status() != 0:
                 raise SystemExit("full decode step: a bounded device-side wait expired")
             res[impl] = (t_dev, t_e2e, ds.launches_per_step, ds.bytes_per_step(ctx))
@@ -611,7 +675,7 @@ def run_ours(args):
 
     # ---------------------------------------------------------------- full-model prefill chunk
     fpf = None
-    if not args.no_full and not args.no_prefill and world == 1:
+    if decode_sections and not args.no_full:
         model_mod = importlib.import_module("lfm2-ampere_b200.model")
         m = args.pf_tokens
         fm = model_mod.make_full_model(n_layers=args.layers, seed=4321, moe_layers=layers)
@@ -632,17 +696,17 @@ def run_ours(args):
         fpf_step()
         torch.cuda.synchronize()
         ev0.record()
-        for _ in range(args.pf_steps):
+        for _ in range(fsteps):
             fpf_step()
         ev1.record()
         torch.cuda.synchronize()
-        t_pf = ev0.elapsed_time(ev1) / args.pf_steps
+        t_pf = ev0.elapsed_time(ev1) / fsteps
         ev0.record()
-        for _ in range(args.pf_steps):
+        for _ in range(fsteps):
             fpf_step(e2e=True)
         ev1.record()
         torch.cuda.synchronize()
-        t_pf_e2e = ev0.elapsed_time(ev1) / args.pf_steps
+        t_pf_e2e = ev0.elapsed_time(ev1) / fsteps
         if lkb.lib.lkb_pf_gemm_status() != 0:
             raise SystemExit("full-model prefill: a bounded wait of the tensor-core GEMM expired")
         attn_macs = sum(mx.is_attn for mx in fm.mixers) * 32 * 64 * 2 * (m * (m + 1) // 2)
@@ -659,7 +723,7 @@ def run_ours(args):
 
     # ---------------------------------------------------------------- long context (configuration 4)
     longc = None
-    if args.long_ctx and world == 1 and not args.no_full:
+    if decode_sections and not args.no_long_ctx and not args.no_full:
         model_mod = importlib.import_module("lfm2-ampere_b200.model")
         fm = model_mod.make_full_model(n_layers=args.layers, seed=4321, moe_layers=layers)
         LC = 131072
@@ -696,7 +760,7 @@ def run_ours(args):
         for _ in range(3):
             gL.replay()
         torch.cuda.synchronize()
-        nst = min(args.steps, 20)
+        nst = 40
         ev0.record()
         for _ in range(nst):
             gL.replay()
@@ -715,22 +779,30 @@ def run_ours(args):
         del gL, ds, fm
 
     if rank == 0:
-        clocks = sampler.stop()          # sampled over every timed region above (decode, e2e, prefill, lm_head, full step)
-        cb, _ = cpu_baseline() if world == 1 and not args.no_cpu else (None, None)
-        out = {"metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-               "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
-               "scaling": "weak", "vs_baseline": None, "dtype": "int8xint4->int32, fp32 accumulate",
+        clocks = sampler.stop()          # sampled over every timed region above
+        cb = None
+        if world == 1 and not args.no_cpu:
+            cb, _ = cpu_baseline()
+        if dec is not None:
+            dec["full_step"] = full
+            dec["lm_head"] = lm
+            dec["gemv_sweep_config0"] = sweep
+            dec["long_context"] = longc
+            dec["cpu_baseline_decode"] = cpu_decode_baseline() if not args.no_cpu else None
+            pf_cfg["decode"] = dec
+            pf_cfg["full_prefill"] = fpf
+            if full is not None:
+                roofline["decode"] = dict(full["roofline"], kernel="full-model batch-1 decode step (configuration 2), one CUDA graph per token",
+                                          tok_s=full["value"], ms_per_step=full["ms_per_step"], e2e_tok_s=full["e2e"]["value"])
+        else:
+            pf_cfg["decode"] = "measured at N = 1: batch-1 decode does not shard (replicas only)"
+        out = {"metric": METRIC, "value": m / (pms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+               "warmup": max(3, args.warmup), "ms_per_step": pms, "higher_is_better": True,
+               "scaling": "strong", "vs_baseline": None, "dtype": DTYPE,
                "data": "synthetic (seeded; shapes and distributions of the benchmark configurations)",
-               "config": {"workload": f"config 1 x {args.layers} layers: batch-1 MoE FFN stack (64 experts, top-4, hidden "
-                                      "2048, inter 1536, Q4_0 weights x Q8_1 activations, sigmoid+bias router)",
-                          "layers": args.layers, "resident_weight_bytes": args.layers * 339738624,
-                          "bytes_per_token": args.layers * LAYER_BYTES,
-                          "cold_cache": "each step streams 871 MB of a 13.6 GB weight set (inputs larger than L2)",
-                          "parallelism": "replicas" if world > 1 else "single GPU",
-                          "decode_impl": args.decode_impl, "cuda_graph": use_graph, "pdl": (not args.no_pdl) and not fused},
-               "e2e": {"value": e2e_tok_s, "unit": UNIT, "h2d_bytes_per_step": H * 4, "d2h_bytes_per_step": H * 4},
-               "gpu_launches": n_launch,
-               "roofline": roofline, "cpu_baseline": cb, "clocks": clocks, "prefill": pf, "lm_head": lm, "gemv_sweep": sweep, "full_step": full, "full_prefill": fpf, "long_context": longc}
+               "config": pf_cfg,
+               "e2e": {"value": m / (pms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": m * H * 4, "d2h_bytes_per_step": m * H * 4},
+               "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cb, "clocks": clocks}
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -739,27 +811,23 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=10, help="timed prefill steps (one step = one 4096-token chunk through 40 layers)")
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--decode-steps", type=int, default=200, help="timed steps of the batch-1 decode sections (at least 200)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=N_LAYERS)
     ap.add_argument("--pf-tokens", type=int, default=4096)
-    ap.add_argument("--pf-steps", type=int, default=3)
     ap.add_argument("--ep-dispatch", choices=["nccl", "peer"], default="peer",
                     help="token exchange of the expert-parallel prefill (N > 1): NCCL all-to-all, or this library's peer-memory kernels")
-    ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-lmhead", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the GEMV size sweep")
-    ap.add_argument("--long-ctx", action="store_true", help="also time decode at 131072 positions of context and a chunked 32768-token prefill")
+    ap.add_argument("--no-long-ctx", action="store_true", help="skip decode at 131072 positions of context and the chunked 32768-token prefill")
     ap.add_argument("--no-full", action="store_true", help="skip the full-model decode step (configuration 2)")
     ap.add_argument("--ctx", type=int, default=4096, help="KV positions pre-filled for the full decode step")
     ap.add_argument("--lm-steps", type=int, default=90)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--decode-impl", default="fused", choices=["fused", "kernels"],
-                    help="fused: one persistent launch per token (lkb_moe_ffn_decode_stack); "
-                         "kernels: the reference's five launches per layer, graph + PDL")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -255,6 +255,11 @@ int lkb_decode_layers(const lkb_moe_layer * moe_dev, const lkb_mixer_layer * mix
 int lkb_moe_ffn_decode_stack_static(const lkb_moe_layer * layers_dev, int n_layers, int hidden, int inter,
                                     int n_experts, int top_k, int softmax, float * x, int * idx_out, float * w_out,
                                     const lkb_norm_prod_t * next, lkb_stream_t st);
+/* The bounded-wait status of the last lkb_moe_ffn_decode_stack_static call on the current device: 0, or the code of
+ * the device-side wait that gave up (what a caller of the allocating form reads from scratch->sync[1] itself; here
+ * the word lives in the library's array).  SYNCHRONISES the device, copies four bytes, allocates nothing.
+ * No counterpart in the reference. */
+int lkb_moe_ffn_decode_stack_static_status(void);
 
 /* ------------------------------------------------------------------ router */
 /* ref: src/kernels.cuh:543-547  k_router_dot<<<64,32>>> (sel/sig may be null) */

@@ -936,4 +936,15 @@ int lkb_moe_ffn_decode_stack_static(const lkb_moe_layer * layers_dev, int n_laye
     return fused_launch(a, (cudaStream_t) st);
 }
 
+// The status word of the built-in scratch: what `scratch->sync[1]` is for the allocating entry point.  Copies four bytes
+// out of the library's array with cudaMemcpyFromSymbol; allocates nothing.
+int lkb_moe_ffn_decode_stack_static_status(void) {
+    const size_t logits_b = (((size_t) LKB_N_EXPERTS * 4) + 255) & ~(size_t) 255;
+    const size_t gu_b = (((size_t) 2 * LKB_TOP_K * LKB_MOE_INTER * 4) + 255) & ~(size_t) 255;
+    unsigned v = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(&v, g_static_scratch, sizeof v, logits_b + gu_b + sizeof(unsigned)) != cudaSuccess) return -1;
+    return (int) v;
+}
+
 }  // extern "C"

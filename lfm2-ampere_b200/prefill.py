@@ -12,9 +12,22 @@ from . import api
 from .synth import E, H, I, TOPK
 
 
+def _timed(owner, fn, *args):
+    """Run one GEMM entry point; when owner.gemm_events is a list, bracket it with CUDA events on the current stream."""
+    ev = getattr(owner, "gemm_events", None)
+    if ev is None:
+        return fn(*args)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    fn(*args)
+    e1.record()
+    ev.append((e0, e1))
+
+
 class PrefillStack:
     def __init__(self, layers, m, device="cuda"):
         self.layers, self.m = layers, m
+        self.gemm_events = None                              # set to a list to time every grouped-GEMM launch
         ns = m * TOPK
         self.ns = ns
         self.max_tiles = ns // 64 + E                       # ref: src/engine.cu:1007
@@ -64,11 +77,11 @@ class PrefillStack:
         g = api.make_pf_gemm([(l.gate_qs, l.gate_d), (l.up_qs, l.up_d)], [I, I, I], I, H // 32, self.a_qs, self.a_sc,
                              exp_stride=I * (H // 32), perm=self.perm, tiles=self.tiles, ntiles=self.ntiles,
                              a_shift=2, scale=self.inv, oqs=self.a2_qs, osc=self.a2_sc, okb=I // 32)
-        api.pf_gemm_swiglu(g, self.max_tiles)
+        _timed(self, api.pf_gemm_swiglu, g, self.max_tiles)
         dn = api.make_pf_gemm([(l.down_qs, l.down_d)], [H, H, H], H, I // 32, self.a2_qs, self.a2_sc,
                               exp_stride=H * (I // 32), perm=self.perm, tiles=self.tiles, ntiles=self.ntiles,
                               a_shift=0, out=self.D, out_ld=H)
-        api.pf_gemm_moe(dn, self.max_tiles)
+        _timed(self, api.pf_gemm_moe, dn, self.max_tiles)
         if next_norm_w is None:
             next_norm_w, next_act = self.layers[(i + 1) % len(self.layers)].norm_w, (self.an, self.n_inv)
         api.k_pf_moe_combine_norm(self.X, self.D, self.w, next_norm_w, next_act[0], next_act[1], m)
@@ -119,7 +132,7 @@ class PrefillStackEP:
         self.dispatch = dispatch
         self.rank, self.world, self.group = rank, world, group
         # this library's kernels per layer (memsets, the torch division and NCCL's own kernels not counted)
-        self.launches_per_step = (18 if dispatch == "peer" else 14) * len(layers)
+        self.launches_per_step = (20 if dispatch == "peer" else 16) * len(layers)
         self.layers = layers
         self.shards = [shard_layer(l, rank, world) for l in layers]
         self.m = m_total // world
@@ -152,6 +165,8 @@ class PrefillStackEP:
         self.a = api.pf_act(self.a_qs, self.a_sc)
         self.an = api.pf_act(self.n_qs, self.n_sc)
         self.recv_slots = []                                     # per layer: slots this rank computed (load balance)
+        self.gemm_events = None
+        self.gemm_ws = torch.zeros(api.pf_gemm_workspace_bytes(self.max_tiles, H), dtype=torch.uint8, device=device)
 
     def _alloc_ep(self, device):
         """Buffers of the device-side dispatch (called once)."""
@@ -231,11 +246,11 @@ class PrefillStackEP:
         g = api.make_pf_gemm([(sh.gate_qs, sh.gate_d), (sh.up_qs, sh.up_d)], [I, I, I], I, H // 32, self.r_qs, self.r_sc,
                              exp_stride=I * (H // 32), perm=self.perm, tiles=self.tiles, ntiles=self.ntiles,
                              a_shift=0, scale=self.r_inv, oqs=self.a2_qs, osc=self.a2_sc, okb=I // 32)
-        api.pf_gemm_swiglu(g, self.max_tiles)
+        _timed(self, api.pf_gemm_swiglu, g, self.max_tiles)
         dn = api.make_pf_gemm([(sh.down_qs, sh.down_d)], [H, H, H], H, I // 32, self.a2_qs, self.a2_sc,
                               exp_stride=H * (I // 32), perm=self.perm, tiles=self.tiles, ntiles=self.ntiles,
                               a_shift=0, out=self.D, out_ld=H)
-        api.pf_gemm_moe(dn, self.max_tiles)
+        _timed(self, api.pf_gemm_moe, dn, self.max_tiles)
 
     def _exchange_peer(self, i):
         """counts -> rows to their owners -> experts -> D rows home, all on the stream."""
@@ -264,11 +279,11 @@ class PrefillStackEP:
         g = api.make_pf_gemm([(sh.gate_qs, sh.gate_d), (sh.up_qs, sh.up_d)], [I, I, I], I, H // 32, self.r_qs, self.r_sc,
                              exp_stride=I * (H // 32), perm=self.perm, tiles=self.tiles, ntiles=self.ntiles,
                              a_shift=0, scale=self.r_inv, oqs=self.a2_qs, osc=self.a2_sc, okb=I // 32)
-        api.pf_gemm_swiglu(g, mt)
+        _timed(self, api.pf_gemm_swiglu, g, mt)
         dn = api.make_pf_gemm([(sh.down_qs, sh.down_d)], [H, H, H], H, I // 32, self.a2_qs, self.a2_sc,
                               exp_stride=H * (I // 32), perm=self.perm, tiles=self.tiles, ntiles=self.ntiles,
                               a_shift=0, out=self.D, out_ld=H)
-        api.pf_gemm_moe(dn, mt)
+        _timed(self, api.pf_gemm_moe, dn, mt)
 
     def layer(self, i):
         import torch.distributed as dist
@@ -276,6 +291,7 @@ class PrefillStackEP:
         ns, per = m * TOPK, E // G
         if not hasattr(self, "send_order"):
             self._alloc_ep(self.X.device)
+        api.pf_gemm_set_workspace(self.gemm_ws)
         api.k_pf_norm(self.X, l.norm_w, 0, self.a, self.inv, self.h32, m)
         # the router form follows the CHUNK size, as on one GPU (ref: src/engine.cu:1170-1176)
         router = api.k_pf_router_small if self.m_total <= 256 else api.k_pf_router_tiled

@@ -675,6 +675,16 @@ ORC_API void orc_pf_pack_q8_1(const int8_t * qs, const float * sc, int t, int kb
 /* contraction of a block of GEMM work, all host threads.  Returns the number */
 /* of (row, token) dot products evaluated.                                    */
 /* ------------------------------------------------------------------------- */
+/* Pin the OpenMP team size (the benchmark sets it from the process's CPU affinity, so that a launcher's
+ * OMP_NUM_THREADS=1 does not decide the baseline). */
+ORC_API void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void) n;
+#endif
+}
+
 ORC_API int orc_num_threads(void) {
     int n = 1;
 #ifdef _OPENMP

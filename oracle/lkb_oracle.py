@@ -432,6 +432,10 @@ def num_threads():
     return int(_lib.orc_num_threads())
 
 
+def set_num_threads(n):
+    _lib.orc_set_num_threads(int(n))
+
+
 # ------------------------------------------------------------ Q6_K lm_head --
 def gemv_q6_K(ql, qh, sc, d, act, rows, sbpr=8, ninv=1.0):
     """act = (q, d16, s16) of the activation; shipped (dp4a) summation order."""

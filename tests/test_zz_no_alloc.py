@@ -41,6 +41,7 @@ def test_static_scratch_entry_matches_the_allocating_one_twice(lkb):
         lkb.moe_ffn_decode_stack_static(st.layers_dev, 3, x, idx, w, None)
         torch.cuda.synchronize()
         assert torch.equal(x, ref[0]) and torch.equal(idx, ref[1]) and torch.equal(w, ref[2])
+        assert lkb.lib.lkb_moe_ffn_decode_stack_static_status() == 0      # no bounded wait gave up (the word lives in the library)
     # a shape whose scratch does not fit the built-in array is refused, as is a shape the kernel is not built for
     x = x0.clone()
     rc = lkb.lib.lkb_moe_ffn_decode_stack_static(st.layers_dev.data_ptr(), 3, 2048, 1 << 20, 64, 4, 0, x.data_ptr(),
