@@ -62,6 +62,41 @@ __device__ __forceinline__ void lkb_quant_store_planar(float xi, int8_t * __rest
     }
 }
 
+// ---------------------------------------------------------------------------
+// Four elements per lane.  A 32-element block lives in 8 adjacent lanes, lane l holding elements 4(l&7) .. +3
+// (one 128-bit load), so a warp covers four blocks = 512 contiguous bytes per step.  The xor-butterfly of the
+// one-element-per-lane form pairs element i with i^16, i^8, i^4, i^2, i^1: here the first three levels are lane
+// exchanges (xor 4, 2, 1, one per held element) and the last two are adds inside the thread, so every partial
+// sum is the same pair of operands as there (fp32 addition is commutative) and the result has the same bits.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float lkb_quad_sum(float a0, float a1, float a2, float a3) {
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) {
+        a0 = __fadd_rn(a0, __shfl_xor_sync(LKB_FULL, a0, o));
+        a1 = __fadd_rn(a1, __shfl_xor_sync(LKB_FULL, a1, o));
+        a2 = __fadd_rn(a2, __shfl_xor_sync(LKB_FULL, a2, o));
+        a3 = __fadd_rn(a3, __shfl_xor_sync(LKB_FULL, a3, o));
+    }
+    return __fadd_rn(__fadd_rn(a0, a2), __fadd_rn(a1, a3));
+}
+
+// Q8_1 of the block this lane's group of 8 holds: returns the lane's four quants packed low byte first;
+// (d, 8 * sum) after the fp16 round trip of the planar layout in sc_out (same in all 8 lanes).
+__device__ __forceinline__ unsigned lkb_quad_quant(const float4 v, int lane, float2 & sc_out) {
+    const unsigned gm = 0xFFu << (lane & 24);
+    const unsigned m01 = max(__float_as_uint(fabsf(v.x)), __float_as_uint(fabsf(v.y)));
+    const unsigned m23 = max(__float_as_uint(fabsf(v.z)), __float_as_uint(fabsf(v.w)));
+    const unsigned am = __reduce_max_sync(gm, max(m01, m23));
+    const float sum = lkb_quad_sum(v.x, v.y, v.z, v.w);
+    const float d = __fdiv_rn(__uint_as_float(am), 127.0f);
+    const __half2 ds = __floats2half2_rn(d, sum);
+    sc_out = make_float2(__low2float(ds), __fmul_rn(8.0f, __high2float(ds)));
+    if (am == 0u) return 0u;
+    const int q0 = (int) roundf(__fdiv_rn(v.x, d)), q1 = (int) roundf(__fdiv_rn(v.y, d));
+    const int q2 = (int) roundf(__fdiv_rn(v.z, d)), q3 = (int) roundf(__fdiv_rn(v.w, d));
+    return (unsigned) (q0 & 255) | ((unsigned) (q1 & 255) << 8) | ((unsigned) (q2 & 255) << 16) | ((unsigned) q3 << 24);
+}
+
 // Producer of the scale-carrying norm split: quantise RAW u = x*w, emit the
 // block's sum of squares of x.  ref: src/kernels.cuh:421-431
 __device__ __forceinline__ void lkb_norm_prod_warp(float xv, float uv, int lane,

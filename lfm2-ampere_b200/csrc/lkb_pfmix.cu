@@ -23,38 +23,74 @@ __global__ void __launch_bounds__(256) k_pf_embed(const unsigned char * __restri
     x[(size_t) t * n + i] = __fmul_rn(__fmul_rn(__half2float(d[blk]), (float) sc[blk * 16 + e / 16]), (float) (q6 - 32));
 }
 
-// Short gated convolution over a chunk: token t sees bx of tokens t-2, t-1 (from the chunk, or from the
-// two-tap history for the first two tokens).  Y = in_proj output [m][6144] = B | C | X.  Output: planar Q8_1
-// rows of v = C * conv.  grid (m, 8) x 256: warp = one 32-channel block.  ref: src/prefill.cu:937-957
-__global__ void __launch_bounds__(256) k_pf_conv(const float * __restrict__ Y, const float * __restrict__ cw,
-                                                 const float * __restrict__ hist, lkb_pf_act a) {
-    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.y * 8 + warp, ch = b * 32 + lane;
-    const float * yt = Y + (size_t) t * (3 * LKB_HIDDEN);
-    const float bx = __fmul_rn(yt[ch], yt[2 * LKB_HIDDEN + ch]);
-    float h0, h1;
-    if (t >= 2)      { const float * y2 = yt - 2 * (3 * LKB_HIDDEN); h0 = __fmul_rn(y2[ch], y2[2 * LKB_HIDDEN + ch]); }
-    else if (t == 1) { h0 = hist[ch * 2 + 1]; }
-    else             { h0 = hist[ch * 2]; }
-    if (t >= 1)      { const float * y1 = yt - (3 * LKB_HIDDEN); h1 = __fmul_rn(y1[ch], y1[2 * LKB_HIDDEN + ch]); }
-    else             { h1 = hist[ch * 2 + 1]; }
-    const float conv = fmaf(bx, cw[3 * ch + 2], fmaf(h1, cw[3 * ch + 1], __fmul_rn(h0, cw[3 * ch])));
-    const float v = __fmul_rn(yt[LKB_HIDDEN + ch], conv);
-    lkb_quant_store_planar(v, reinterpret_cast<int8_t *>(a.qs) + (size_t) t * LKB_HIDDEN + b * 32,
-                           reinterpret_cast<float2 *>(a.sc) + (size_t) t * (LKB_HIDDEN / 32) + b, lane);
+// Short gated convolution over a chunk.  Y = in_proj output [m][6144] = B | C | X; token t sees bx = B * X of
+// tokens t-2 and t-1 (from the chunk, or from the two-tap history for the first two tokens); the output is the
+// planar Q8_1 row of v = C * conv.  A warp owns 128 channels (four per lane, 128-bit loads) over a run of
+// PF_CONV_RUN consecutive tokens and slides bx of the previous two tokens through registers, so Y is read once
+// instead of three times; taps and the fused multiply-add nesting are the decode kernel's, per channel.
+// ref semantics: src/prefill.cu:937-957
+#define PF_CONV_RUN 16
+__device__ __forceinline__ float4 pf_mul4(const float4 a, const float4 b) {
+    return make_float4(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y), __fmul_rn(a.z, b.z), __fmul_rn(a.w, b.w));
+}
+__global__ void __launch_bounds__(128) k_pf_conv_run(const float * __restrict__ Y, const float * __restrict__ cw,
+                                                     const float * __restrict__ hist, lkb_pf_act a, int m) {
+    const int lane = threadIdx.x & 31;
+    const int wid = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int cg = wid & 15, t0 = (wid >> 4) * PF_CONV_RUN;
+    if (t0 >= m) return;                                   // warp-uniform
+    const int ch = cg * 128 + lane * 4;
+    const float4 * c4 = reinterpret_cast<const float4 *>(cw + 3 * ch);
+    const float4 f0 = __ldg(c4), f1 = __ldg(c4 + 1), f2 = __ldg(c4 + 2);
+    const float tap[12] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w, f2.x, f2.y, f2.z, f2.w};    // [channel][3]
+    float4 h0, h1;
+    if (t0 == 0) {
+        const float4 g0 = *reinterpret_cast<const float4 *>(hist + 2 * ch), g1 = *reinterpret_cast<const float4 *>(hist + 2 * ch + 4);
+        h0 = make_float4(g0.x, g0.z, g1.x, g1.z);
+        h1 = make_float4(g0.y, g0.w, g1.y, g1.w);
+    } else {
+        const float * y2 = Y + (size_t) (t0 - 2) * (3 * LKB_HIDDEN) + ch;
+        h0 = pf_mul4(*reinterpret_cast<const float4 *>(y2), *reinterpret_cast<const float4 *>(y2 + 2 * LKB_HIDDEN));
+        h1 = pf_mul4(*reinterpret_cast<const float4 *>(y2 + 3 * LKB_HIDDEN), *reinterpret_cast<const float4 *>(y2 + 5 * LKB_HIDDEN));
+    }
+    const int t1 = min(t0 + PF_CONV_RUN, m);
+#pragma unroll 4
+    for (int t = t0; t < t1; ++t) {
+        const float * yt = Y + (size_t) t * (3 * LKB_HIDDEN) + ch;
+        const float4 bx = pf_mul4(*reinterpret_cast<const float4 *>(yt), *reinterpret_cast<const float4 *>(yt + 2 * LKB_HIDDEN));
+        const float4 cv = *reinterpret_cast<const float4 *>(yt + LKB_HIDDEN);
+        float4 v;
+        v.x = __fmul_rn(cv.x, fmaf(bx.x, tap[2],  fmaf(h1.x, tap[1],  __fmul_rn(h0.x, tap[0]))));
+        v.y = __fmul_rn(cv.y, fmaf(bx.y, tap[5],  fmaf(h1.y, tap[4],  __fmul_rn(h0.y, tap[3]))));
+        v.z = __fmul_rn(cv.z, fmaf(bx.z, tap[8],  fmaf(h1.z, tap[7],  __fmul_rn(h0.z, tap[6]))));
+        v.w = __fmul_rn(cv.w, fmaf(bx.w, tap[11], fmaf(h1.w, tap[10], __fmul_rn(h0.w, tap[9]))));
+        float2 s2;
+        const unsigned pk = lkb_quad_quant(v, lane, s2);
+        reinterpret_cast<unsigned *>(reinterpret_cast<int8_t *>(a.qs) + (size_t) t * LKB_HIDDEN + ch)[0] = pk;
+        if ((lane & 7) == 0) reinterpret_cast<float2 *>(a.sc)[(size_t) t * (LKB_HIDDEN / 32) + (ch >> 5)] = s2;
+        h0 = h1; h1 = bx;
+    }
 }
 
-// The history after the chunk: bx of its last two tokens.  Runs after k_pf_conv.  ref: src/prefill.cu:960-970
+// The history after the chunk: bx of its last two tokens (of the last one and the old second tap when m = 1).
+// Runs after the convolution, which reads the old history.  Four channels per thread.
+// ref semantics: src/prefill.cu:960-970
 __global__ void __launch_bounds__(256) k_pf_conv_hist(const float * __restrict__ Y, int m, float * __restrict__ hist) {
-    const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+    const int ch = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (ch >= LKB_HIDDEN) return;
-    const float * yl = Y + (size_t) (m - 1) * (3 * LKB_HIDDEN);
-    const float b1 = __fmul_rn(yl[ch], yl[2 * LKB_HIDDEN + ch]);
-    float b0;
-    if (m >= 2) { const float * yp = yl - (3 * LKB_HIDDEN); b0 = __fmul_rn(yp[ch], yp[2 * LKB_HIDDEN + ch]); }
-    else        { b0 = hist[ch * 2 + 1]; }
-    hist[ch * 2] = b0;
-    hist[ch * 2 + 1] = b1;
+    const float * yl = Y + (size_t) (m - 1) * (3 * LKB_HIDDEN) + ch;
+    const float4 b1 = pf_mul4(*reinterpret_cast<const float4 *>(yl), *reinterpret_cast<const float4 *>(yl + 2 * LKB_HIDDEN));
+    float4 * hp = reinterpret_cast<float4 *>(hist + 2 * ch);
+    float4 b0;
+    if (m >= 2) {
+        const float * yp = yl - 3 * LKB_HIDDEN;
+        b0 = pf_mul4(*reinterpret_cast<const float4 *>(yp), *reinterpret_cast<const float4 *>(yp + 2 * LKB_HIDDEN));
+    } else {
+        const float4 g0 = hp[0], g1 = hp[1];
+        b0 = make_float4(g0.y, g0.w, g1.y, g1.w);
+    }
+    hp[0] = make_float4(b0.x, b1.x, b0.y, b1.y);
+    hp[1] = make_float4(b0.z, b1.z, b0.w, b1.w);
 }
 
 // Per-head RMSNorm + RoPE of token t at position P + t.  Y = q|k|v GEMM output [m][3072].  Q leaves as fp16
@@ -252,14 +288,15 @@ int lkb_pf_conv(const float * Y, const float * cw, const float * hist, lkb_pf_ac
     if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
     if (!Y || !cw || !hist || !a.qs || !a.sc) return LKB_ERR_NULL;
     if (m <= 0) return LKB_ERR_SHAPE;
-    return lkb_launch(k_pf_conv, dim3(m, LKB_HIDDEN / 256), dim3(256), 0, (cudaStream_t) st, Y, cw, hist, a);
+    const int runs = (m + PF_CONV_RUN - 1) / PF_CONV_RUN;      // 16 warps (channel groups) per run, 4 warps per CTA
+    return lkb_launch(k_pf_conv_run, dim3(runs * 4), dim3(128), 0, (cudaStream_t) st, Y, cw, hist, a, m);
 }
 
 int lkb_pf_conv_hist(const float * Y, int m, float * hist, lkb_stream_t st) {
     if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
     if (!Y || !hist) return LKB_ERR_NULL;
     if (m <= 0) return LKB_ERR_SHAPE;
-    return lkb_launch(k_pf_conv_hist, dim3(LKB_HIDDEN / 256), dim3(256), 0, (cudaStream_t) st, Y, m, hist);
+    return lkb_launch(k_pf_conv_hist, dim3(LKB_HIDDEN / 1024), dim3(256), 0, (cudaStream_t) st, Y, m, hist);
 }
 
 int lkb_pf_qknr(const float * Y, const float * qn, const float * kn, int P, void * qh, void * kc, void * vc, int m, float theta,

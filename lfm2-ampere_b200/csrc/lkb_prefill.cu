@@ -11,104 +11,165 @@
 #define LKB_REQUIRE_INIT() do { if (!lkb_context().inited) return LKB_ERR_NOT_INIT; } while (0)
 
 // ---------------------------------------------------------------------------
-// Per-token norm.  grid m x 256.  ref: src/prefill.cu:871-932
+// Per-token kernels.  One WARP owns one token (or one 512-byte run of a row): four elements per lane through
+// 128-bit loads, four 32-element blocks per step (lkb_quad_quant), no shared memory and no block barrier, several
+// tokens per CTA.  The arithmetic per element, per block and per token is that of the decode kernels
+// (reference semantics: src/prefill.cu:871-932 norm, :1574-1594 row quantisers), so outputs compare byte for byte.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) k_pf_norm(const float * __restrict__ X, const float * __restrict__ w, int plain,
-                                                 int8_t * __restrict__ aqs, float2 * __restrict__ asc,
-                                                 float * __restrict__ inv_out, float * __restrict__ h32) {
-    const int t = blockIdx.x;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#define PF_TOK_WARPS 4                   // tokens per CTA of the per-token kernels
+
+// MODE 0: norm of X.  MODE 1: X += sum_k w[4t+k] * D[4t+k] first (rank-order chain), then the norm.
+// MODE 2: as 1 with the row of slot 4t+k found through pos[].  Quantises u = x * nw per block, keeps each block's
+// sum of squares of x in the two lanes that need it, and ends with 1/rms from the 64 partials in the decode
+// kernels' order ((ssq[l] + ssq[l+32]) butterflied over l).
+template <int MODE>
+__global__ void __launch_bounds__(PF_TOK_WARPS * 32) k_pf_token_norm(float * __restrict__ X, const float * __restrict__ D,
+                                                                      const int * __restrict__ pos, const float * __restrict__ wts,
+                                                                      const float * __restrict__ nw, int8_t * __restrict__ aqs,
+                                                                      float2 * __restrict__ asc, float * __restrict__ inv_out,
+                                                                      float * __restrict__ h32, int m) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * PF_TOK_WARPS + (threadIdx.x >> 5);
+    if (t >= m) return;                                   // warp-uniform
+    float4 * x4 = reinterpret_cast<float4 *>(X + (size_t) t * LKB_HIDDEN);
+    const float4 * w4 = reinterpret_cast<const float4 *>(nw);
+    unsigned * q4 = reinterpret_cast<unsigned *>(aqs + (size_t) t * LKB_HIDDEN);
+    float2 * sc = asc + (size_t) t * (LKB_HIDDEN / 32);
+    float4 * h4 = (MODE == 0 && h32) ? reinterpret_cast<float4 *>(h32 + (size_t) t * LKB_HIDDEN) : nullptr;
+    const float4 * d4[LKB_TOP_K]; float wk[LKB_TOP_K];
+    if (MODE) {
+#pragma unroll
+        for (int k = 0; k < LKB_TOP_K; ++k) {
+            wk[k] = wts[t * 4 + k];
+            const int row = (MODE == 2) ? pos[t * 4 + k] : t * 4 + k;
+            d4[k] = reinterpret_cast<const float4 *>(D + (size_t) row * LKB_HIDDEN);
+        }
+    }
+    float lo = 0.0f, hi = 0.0f;                           // ssq of blocks `lane` and `lane + 32`
+#pragma unroll 4
+    for (int s = 0; s < LKB_HIDDEN / 128; ++s) {
+        const int i4 = s * 32 + lane;
+        float4 xv = x4[i4];
+        if (MODE) {
+            float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (int k = 0; k < LKB_TOP_K; ++k) {
+                const float4 dv = d4[k][i4];
+                a.x = fmaf(wk[k], dv.x, a.x); a.y = fmaf(wk[k], dv.y, a.y);
+                a.z = fmaf(wk[k], dv.z, a.z); a.w = fmaf(wk[k], dv.w, a.w);
+            }
+            xv = make_float4(__fadd_rn(xv.x, a.x), __fadd_rn(xv.y, a.y), __fadd_rn(xv.z, a.z), __fadd_rn(xv.w, a.w));
+            x4[i4] = xv;
+        }
+        const float4 wv = __ldg(w4 + i4);
+        const float4 u = make_float4(__fmul_rn(xv.x, wv.x), __fmul_rn(xv.y, wv.y), __fmul_rn(xv.z, wv.z), __fmul_rn(xv.w, wv.w));
+        if (h4) h4[i4] = u;
+        float2 s2;
+        q4[i4] = lkb_quad_quant(u, lane, s2);
+        if ((lane & 7) == 0) sc[s * 4 + (lane >> 3)] = s2;
+        const float sq = lkb_quad_sum(__fmul_rn(xv.x, xv.x), __fmul_rn(xv.y, xv.y), __fmul_rn(xv.z, xv.z), __fmul_rn(xv.w, xv.w));
+        // block 4s + g sits in lane group g; lane l keeps blocks l and l + 32, i.e. group l & 3 of steps l >> 2 and 8 + (l >> 2)
+        const float tq = __shfl_sync(LKB_FULL, sq, (lane & 3) * 8);
+        if ((lane >> 2) == (s & 7)) { if (s < 8) lo = tq; else hi = tq; }
+    }
+    const float sv = lkb_warp_sum(__fadd_rn(lo, hi));
+    if (lane == 0) inv_out[t] = rsqrtf(fmaf(sv, 1.0f / (float) LKB_HIDDEN, LKB_EPS));
+}
+
+// Layer-0 form: normalise first (x * inv) * w, quantise that, report scale 1.  The sum of squares keeps the
+// order of a 256-wide reduction (element i in chain i mod 256, chains folded 128 / 64 / 32 apart, then the
+// butterfly): lane l runs the eight chains l + 32g and folds them in registers.
+__global__ void __launch_bounds__(PF_TOK_WARPS * 32) k_pf_token_norm_plain(const float * __restrict__ X, const float * __restrict__ nw,
+                                                                            int8_t * __restrict__ aqs, float2 * __restrict__ asc,
+                                                                            float * __restrict__ inv_out, int m) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * PF_TOK_WARPS + (threadIdx.x >> 5);
+    if (t >= m) return;
     const float * x = X + (size_t) t * LKB_HIDDEN;
-    int8_t * q = aqs + (size_t) t * LKB_HIDDEN;
-    float2 * s = asc + (size_t) t * (LKB_HIDDEN / 32);
-    __shared__ float s_sq[256];
-    if (plain) {
-        float xv[8], wv[8];
+    float S[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { xv[j] = x[tid + j * 256]; wv[j] = w[tid + j * 256]; }
-        float sq = 0.0f;
+    for (int g = 0; g < 8; ++g) {
+        S[g] = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) sq = fmaf(xv[j], xv[j], sq);
-        s_sq[tid] = sq;
-        __syncthreads();
-#pragma unroll
-        for (int o = 128; o > 16; o >>= 1) {
-            if (tid < o) s_sq[tid] = __fadd_rn(s_sq[tid], s_sq[tid + o]);
-            __syncthreads();
-        }
-        if (tid < 32) {
-            const float v = lkb_warp_sum(s_sq[tid]);
-            if (tid == 0) s_sq[0] = v;
-        }
-        __syncthreads();
-        const float inv = rsqrtf(fmaf(s_sq[0], 1.0f / 2048.0f, LKB_EPS));
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float tv = __fmul_rn(__fmul_rn(xv[j], inv), wv[j]);
-            const int b = warp + 8 * j;
-            lkb_quant_store_planar(tv, q + b * 32, s + b, lane);
-        }
-        if (tid == 0) inv_out[t] = 1.0f;
-        return;
+        for (int j = 0; j < 8; ++j) { const float xv = x[lane + 32 * g + 256 * j]; S[g] = fmaf(xv, xv, S[g]); }
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const int b = warp + 8 * j;
-        const int i = b * 32 + lane;
-        const float xv = x[i];
-        const float uv = __fmul_rn(xv, w[i]);
-        if (h32) h32[(size_t) t * LKB_HIDDEN + i] = uv;
-        lkb_quant_store_planar(uv, q + b * 32, s + b, lane);
-        const float sq = lkb_warp_sum(__fmul_rn(xv, xv));
-        if (lane == 0) s_sq[b] = sq;
+    for (int g = 0; g < 4; ++g) S[g] = __fadd_rn(S[g], S[g + 4]);
+    S[0] = __fadd_rn(S[0], S[2]); S[1] = __fadd_rn(S[1], S[3]);
+    const float ss = lkb_warp_sum(__fadd_rn(S[0], S[1]));
+    const float inv = rsqrtf(fmaf(ss, 1.0f / (float) LKB_HIDDEN, LKB_EPS));
+    const float4 * x4 = reinterpret_cast<const float4 *>(x);
+    const float4 * w4 = reinterpret_cast<const float4 *>(nw);
+    unsigned * q4 = reinterpret_cast<unsigned *>(aqs + (size_t) t * LKB_HIDDEN);
+    float2 * sc = asc + (size_t) t * (LKB_HIDDEN / 32);
+#pragma unroll 4
+    for (int s = 0; s < LKB_HIDDEN / 128; ++s) {
+        const int i4 = s * 32 + lane;
+        const float4 xv = x4[i4], wv = __ldg(w4 + i4);
+        const float4 u = make_float4(__fmul_rn(__fmul_rn(xv.x, inv), wv.x), __fmul_rn(__fmul_rn(xv.y, inv), wv.y),
+                                     __fmul_rn(__fmul_rn(xv.z, inv), wv.z), __fmul_rn(__fmul_rn(xv.w, inv), wv.w));
+        float2 s2;
+        q4[i4] = lkb_quad_quant(u, lane, s2);
+        if ((lane & 7) == 0) sc[s * 4 + (lane >> 3)] = s2;
     }
-    __syncthreads();
-    if (warp == 0) {
-        const float sv = lkb_warp_sum(__fadd_rn(s_sq[lane], s_sq[lane + 32]));
-        if (lane == 0) inv_out[t] = rsqrtf(fmaf(sv, 1.0f / (float) LKB_HIDDEN, LKB_EPS));
-    }
+    if (lane == 0) inv_out[t] = 1.0f;
 }
 
-// grid (rows, ceil(kb/8)) x 256.  ref: src/prefill.cu:1574-1581
-__global__ void __launch_bounds__(256) k_pf_quant_rows(const float * __restrict__ X, int ld, int kb,
-                                                       int8_t * __restrict__ aqs, float2 * __restrict__ asc) {
-    const int r = blockIdx.x;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.y * 8 + warp;
-    if (b >= kb) return;
-    const float v = X[(size_t) r * ld + b * 32 + lane];
-    lkb_quant_store_planar(v, aqs + (size_t) r * kb * 32 + b * 32, asc + (size_t) r * kb + b, lane);
-}
-
-// ref: src/prefill.cu:1584-1594
-__global__ void __launch_bounds__(256) k_pf_swiglu(const float * __restrict__ Y, int ld, int up_off, int kb,
-                                                   int8_t * __restrict__ aqs, float2 * __restrict__ asc) {
-    const int r = blockIdx.x;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.y * 8 + warp;
-    if (b >= kb) return;
-    const int i = b * 32 + lane;
-    const float * y = Y + (size_t) r * ld;
-    const float v = __fmul_rn(lkb_silu(y[i]), y[up_off + i]);
-    lkb_quant_store_planar(v, aqs + (size_t) r * kb * 32 + b * 32, asc + (size_t) r * kb + b, lane);
+// Row quantisers: a warp takes four adjacent blocks of one row (SWIGLU: of silu(gate) * up, the two halves of a
+// row up_off apart).  Rows x ceil(kb / 4) warps, 8 per CTA.
+template <int SWIGLU>
+__global__ void __launch_bounds__(256) k_pf_rows_q8(const float * __restrict__ Y, int ld, int up_off, int kb, int rows,
+                                                    int8_t * __restrict__ aqs, float2 * __restrict__ asc) {
+    const int lane = threadIdx.x & 31;
+    const int gpr = (kb + 3) >> 2;
+    const long long wid = (long long) blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (wid >= (long long) rows * gpr) return;
+    const int r = (int) (wid / gpr), g = (int) (wid - (long long) r * gpr);
+    const int b = g * 4 + (lane >> 3);
+    const bool live = b < kb;
+    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (live) {
+        const float * y = Y + (size_t) r * ld + b * 32 + (lane & 7) * 4;
+        v = *reinterpret_cast<const float4 *>(y);
+        if (SWIGLU) {
+            const float4 up = *reinterpret_cast<const float4 *>(y + up_off);
+            v = make_float4(__fmul_rn(lkb_silu(v.x), up.x), __fmul_rn(lkb_silu(v.y), up.y),
+                            __fmul_rn(lkb_silu(v.z), up.z), __fmul_rn(lkb_silu(v.w), up.w));
+        }
+    }
+    float2 s2;
+    const unsigned pk = lkb_quad_quant(v, lane, s2);
+    if (live) {
+        reinterpret_cast<unsigned *>(aqs + (size_t) r * kb * 32 + b * 32)[lane & 7] = pk;
+        if ((lane & 7) == 0) asc[(size_t) r * kb + b] = s2;
+    }
 }
 
 // ---------------------------------------------------------------------------
-// Router.  Small form: one warp per (expert, token), the decode router's
-// arithmetic verbatim.  ref: src/prefill.cu:1668-1693
+// Router.  Short form for a few tokens: a CTA per token keeps the token's activation in registers (64 per lane)
+// and each warp walks eight expert rows over it; a logit is the decode router's sum (lane l chains elements
+// l, l+32, ... ascending, then the butterfly), so it is bit-identical to it.  ref semantics: src/prefill.cu:1668-1693
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(32) k_pf_router_small(const float * __restrict__ H, const float * __restrict__ Wr,
-                                                        const float * __restrict__ bias, const float * __restrict__ inv,
-                                                        float * __restrict__ sel, float * __restrict__ sig) {
-    const int e = blockIdx.x, t = blockIdx.y, lane = threadIdx.x;
+__global__ void __launch_bounds__(256) k_pf_router_token(const float * __restrict__ H, const float * __restrict__ Wr,
+                                                         const float * __restrict__ bias, const float * __restrict__ inv,
+                                                         float * __restrict__ sel, float * __restrict__ sig) {
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float * h = H + (size_t) t * LKB_HIDDEN;
-    const float * row = Wr + (size_t) e * LKB_HIDDEN;
-    float acc = 0.0f;
-#pragma unroll 16
-    for (int j = 0; j < LKB_HIDDEN / 32; ++j) acc = fmaf(row[j * 32 + lane], h[j * 32 + lane], acc);
-    acc = lkb_warp_sum(acc);
-    if (lane == 0) {
-        const float l = __fmul_rn(acc, inv[t]);
+    float hv[LKB_HIDDEN / 32];
+#pragma unroll
+    for (int j = 0; j < LKB_HIDDEN / 32; ++j) hv[j] = h[j * 32 + lane];
+    float mine = 0.0f;
+    for (int q = 0; q < 8; ++q) {
+        const float * row = Wr + (size_t) (warp * 8 + q) * LKB_HIDDEN;
+        float acc = 0.0f;
+#pragma unroll
+        for (int j = 0; j < LKB_HIDDEN / 32; ++j) acc = fmaf(__ldg(row + j * 32 + lane), hv[j], acc);
+        acc = lkb_warp_sum(acc);
+        if (lane == q) mine = acc;
+    }
+    if (lane < 8) {
+        const int e = warp * 8 + lane;
+        const float l = __fmul_rn(mine, inv[t]);
         const float gv = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-l)));
         sig[(size_t) t * 64 + e] = gv;
         sel[(size_t) t * 64 + e] = __fadd_rn(gv, bias[e]);
@@ -263,17 +324,19 @@ __global__ void __launch_bounds__(256) k_pf_router_t8(const float * __restrict__
         make_float2(__fadd_rn(g0, bias[lane * 2]), __fadd_rn(g1, bias[lane * 2 + 1]));
 }
 
-// One warp per token.  ref: src/prefill.cu:1696-1708
+// Top-4 of 64 per token: warps stride over the tokens (any grid); the selection itself is the redux-based
+// lkb_router_select shared with the decode router.  ref semantics: src/prefill.cu:1696-1708
 __global__ void __launch_bounds__(256) k_pf_select(const float * __restrict__ sel, const float * __restrict__ sig, int m,
-                                                   int * __restrict__ idx, float * __restrict__ w) {
-    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+                                                   int4 * __restrict__ idx, float4 * __restrict__ w) {
     const int lane = threadIdx.x & 31;
-    if (t >= m) return;
-    int ord[LKB_TOP_K]; float wv[LKB_TOP_K];
-    lkb_router_select(sel + (size_t) t * 64, sig + (size_t) t * 64, lane, ord, wv);
-    if (lane == 0) {
-        *reinterpret_cast<int4 *>(idx + t * 4) = make_int4(ord[0], ord[1], ord[2], ord[3]);
-        *reinterpret_cast<float4 *>(w + t * 4) = make_float4(wv[0], wv[1], wv[2], wv[3]);
+    const int nw = gridDim.x * (blockDim.x >> 5);
+    for (int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < m; t += nw) {
+        int ord[LKB_TOP_K]; float wv[LKB_TOP_K];
+        lkb_router_select(sel + (size_t) t * 64, sig + (size_t) t * 64, lane, ord, wv);
+        if (lane == 0) {
+            idx[t] = make_int4(ord[0], ord[1], ord[2], ord[3]);
+            w[t] = make_float4(wv[0], wv[1], wv[2], wv[3]);
+        }
     }
 }
 
@@ -353,64 +416,37 @@ __global__ void __launch_bounds__(1024) k_pf_moe_scatter(const int * __restrict_
 }
 
 // ---------------------------------------------------------------------------
-// combine.  ref: src/prefill.cu:1804-1814 and 1764-1800
+// combine: x[t] += sum over the token's four slots in rank order (one fused multiply-add chain from zero, then
+// one add), four channels per thread.  The combine that feeds the next layer's norm is k_pf_token_norm<1>.
+// ref semantics: src/prefill.cu:1804-1814 and 1764-1800
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) k_pf_moe_combine(float * __restrict__ X, const float * __restrict__ D,
-                                                        const float * __restrict__ w) {
-    const int t = blockIdx.x;
-    const int n = blockIdx.y * blockDim.x + threadIdx.x;
-    float a = 0.0f;
+__global__ void __launch_bounds__(256) k_pf_moe_combine(float4 * __restrict__ X, const float4 * __restrict__ D,
+                                                        const float * __restrict__ w, int m) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;          // float4 index into X
+    if (i >= m * (LKB_HIDDEN / 4)) return;
+    const int t = i / (LKB_HIDDEN / 4), c = i - t * (LKB_HIDDEN / 4);
+    const float4 wk = *reinterpret_cast<const float4 *>(w + t * 4);
+    const float wv[4] = {wk.x, wk.y, wk.z, wk.w};
+    float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-    for (int k = 0; k < LKB_TOP_K; ++k) a = fmaf(w[t * 4 + k], D[(size_t) (t * 4 + k) * LKB_HIDDEN + n], a);
-    float * xp = X + (size_t) t * LKB_HIDDEN + n;
-    *xp = __fadd_rn(*xp, a);
+    for (int k = 0; k < LKB_TOP_K; ++k) {
+        const float4 dv = D[(size_t) (t * 4 + k) * (LKB_HIDDEN / 4) + c];
+        a.x = fmaf(wv[k], dv.x, a.x); a.y = fmaf(wv[k], dv.y, a.y); a.z = fmaf(wv[k], dv.z, a.z); a.w = fmaf(wv[k], dv.w, a.w);
+    }
+    const float4 xv = X[i];
+    X[i] = make_float4(__fadd_rn(xv.x, a.x), __fadd_rn(xv.y, a.y), __fadd_rn(xv.z, a.z), __fadd_rn(xv.w, a.w));
 }
 
-__global__ void __launch_bounds__(256) k_pf_moe_combine_norm(float * __restrict__ X, const float * __restrict__ D,
-                                                             const float * __restrict__ w, const float * __restrict__ nw,
-                                                             int8_t * __restrict__ aqs, float2 * __restrict__ asc,
-                                                             float * __restrict__ inv_out) {
-    const int t = blockIdx.x;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    __shared__ float s_sq[64];
-    float wk[LKB_TOP_K];
-#pragma unroll
-    for (int k = 0; k < LKB_TOP_K; ++k) wk[k] = w[t * 4 + k];
-    float * x = X + (size_t) t * LKB_HIDDEN;
-    int8_t * q = aqs + (size_t) t * LKB_HIDDEN;
-    float2 * sc = asc + (size_t) t * (LKB_HIDDEN / 32);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const int i = tid + 256 * j;
-        float acc = 0.0f;
-#pragma unroll
-        for (int k = 0; k < LKB_TOP_K; ++k) acc = fmaf(wk[k], D[(size_t) (t * 4 + k) * LKB_HIDDEN + i], acc);
-        const float xv = __fadd_rn(x[i], acc);
-        x[i] = xv;
-        const int b = warp + 8 * j;
-        const float uv = __fmul_rn(xv, nw[i]);
-        lkb_quant_store_planar(uv, q + b * 32, sc + b, lane);
-        const float sq = lkb_warp_sum(__fmul_rn(xv, xv));
-        if (lane == 0) s_sq[b] = sq;
+// planar row -> 36-byte blocks (exact: 8 sum is a power-of-two multiple).  Eight lanes per block, one word each.
+// ref semantics: src/prefill.cu:1819-1828
+__global__ void __launch_bounds__(512) k_pf_pack_q8_1(const int8_t * __restrict__ aqs, const float2 * __restrict__ asc, int t,
+                                                      lkb_q8blk * __restrict__ y) {
+    const int b = threadIdx.x >> 3, wd = threadIdx.x & 7;
+    reinterpret_cast<int *>(y[b].qs)[wd] = reinterpret_cast<const int *>(aqs + (size_t) t * LKB_HIDDEN + b * 32)[wd];
+    if (wd == 0) {
+        const float2 s = asc[(size_t) t * 64 + b];
+        y[b].ds = __floats2half2_rn(s.x, __fmul_rn(s.y, 0.125f));
     }
-    __syncthreads();
-    if (warp == 0) {
-        const float sv = lkb_warp_sum(__fadd_rn(s_sq[lane], s_sq[lane + 32]));
-        if (lane == 0) inv_out[t] = rsqrtf(fmaf(sv, 1.0f / (float) LKB_HIDDEN, LKB_EPS));
-    }
-}
-
-// planar row -> 36-byte blocks (exact).  ref: src/prefill.cu:1819-1828
-__global__ void __launch_bounds__(64) k_pf_pack_q8_1(const int8_t * __restrict__ aqs, const float2 * __restrict__ asc, int t,
-                                                     lkb_q8blk * __restrict__ y) {
-    const int b = threadIdx.x;
-    const float2 s = asc[(size_t) t * 64 + b];
-    y[b].ds = __floats2half2_rn(s.x, __fmul_rn(s.y, 0.125f));
-    const int4 * src = reinterpret_cast<const int4 *>(aqs + (size_t) t * LKB_HIDDEN + b * 32);
-    const int4 v0 = src[0], v1 = src[1];
-    int * dq = reinterpret_cast<int *>(y[b].qs);
-    dq[0] = v0.x; dq[1] = v0.y; dq[2] = v0.z; dq[3] = v0.w;
-    dq[4] = v1.x; dq[5] = v1.y; dq[6] = v1.z; dq[7] = v1.w;
 }
 
 // ---------------------------------------------------------------------------
@@ -448,40 +484,6 @@ __global__ void __launch_bounds__(192) k_ep_unpack(const unsigned char * __restr
     else if (i == 160) { const uint4 v = row[160]; inv[p] = __uint_as_float(v.x); le[p] = (int) v.y; }
 }
 
-// combine + next norm with the four D rows of a token found through pos[] (their places in the returned buffer)
-__global__ void __launch_bounds__(256) k_pf_moe_combine_norm_gather(float * __restrict__ X, const float * __restrict__ D,
-                                                                    const int * __restrict__ pos, const float * __restrict__ w,
-                                                                    const float * __restrict__ nw, int8_t * __restrict__ aqs,
-                                                                    float2 * __restrict__ asc, float * __restrict__ inv_out) {
-    const int t = blockIdx.x;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    __shared__ float s_sq[64];
-    float wk[LKB_TOP_K]; const float * dr[LKB_TOP_K];
-#pragma unroll
-    for (int k = 0; k < LKB_TOP_K; ++k) { wk[k] = w[t * 4 + k]; dr[k] = D + (size_t) pos[t * 4 + k] * LKB_HIDDEN; }
-    float * x = X + (size_t) t * LKB_HIDDEN;
-    int8_t * q = aqs + (size_t) t * LKB_HIDDEN;
-    float2 * sc = asc + (size_t) t * (LKB_HIDDEN / 32);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const int i = tid + 256 * j;
-        float acc = 0.0f;
-#pragma unroll
-        for (int k = 0; k < LKB_TOP_K; ++k) acc = fmaf(wk[k], dr[k][i], acc);
-        const float xv = __fadd_rn(x[i], acc);
-        x[i] = xv;
-        const int b = warp + 8 * j;
-        const float uv = __fmul_rn(xv, nw[i]);
-        lkb_quant_store_planar(uv, q + b * 32, sc + b, lane);
-        const float sq = lkb_warp_sum(__fmul_rn(xv, xv));
-        if (lane == 0) s_sq[b] = sq;
-    }
-    __syncthreads();
-    if (warp == 0) {
-        const float sv = lkb_warp_sum(__fadd_rn(s_sq[lane], s_sq[lane + 32]));
-        if (lane == 0) inv_out[t] = rsqrtf(fmaf(sv, 1.0f / (float) LKB_HIDDEN, LKB_EPS));
-    }
-}
 
 // ---------------------------------------------------------------------------
 // CUDA-core form of the Q4_0 x Q8_1 GEMM (dense, grouped, SwiGLU epilogue).
@@ -672,7 +674,10 @@ int lkb_pf_norm(const float * X, const float * w, int plain, lkb_pf_act a, float
     LKB_REQUIRE_INIT();
     if (!X || !w || !a.qs || !a.sc || !inv_out) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    k_pf_norm<<<m, 256, 0, (cudaStream_t) st>>>(X, w, plain, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out, h32);
+    const int grid = (m + PF_TOK_WARPS - 1) / PF_TOK_WARPS;
+    if (plain) k_pf_token_norm_plain<<<grid, PF_TOK_WARPS * 32, 0, (cudaStream_t) st>>>(X, w, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out, m);
+    else       k_pf_token_norm<0><<<grid, PF_TOK_WARPS * 32, 0, (cudaStream_t) st>>>(const_cast<float *>(X), nullptr, nullptr, nullptr, w, a.qs,
+                                                                                  reinterpret_cast<float2 *>(a.sc), inv_out, h32, m);
     return lkb_check_launch();
 }
 
@@ -680,7 +685,9 @@ int lkb_pf_quant_rows(const float * X, int ld, int kb, lkb_pf_act a, int rows, l
     LKB_REQUIRE_INIT();
     if (!X || !a.qs || !a.sc) return LKB_ERR_NULL;
     if (rows <= 0 || kb <= 0) return (rows == 0) ? LKB_OK : LKB_ERR_SHAPE;
-    k_pf_quant_rows<<<dim3(rows, (kb + 7) / 8), 256, 0, (cudaStream_t) st>>>(X, ld, kb, a.qs, reinterpret_cast<float2 *>(a.sc));
+    if ((ld & 3) || (reinterpret_cast<uintptr_t>(X) & 15)) return LKB_ERR_SHAPE;      // 128-bit loads
+    const long long warps = (long long) rows * ((kb + 3) / 4);
+    k_pf_rows_q8<0><<<(unsigned) ((warps + 7) / 8), 256, 0, (cudaStream_t) st>>>(X, ld, 0, kb, rows, a.qs, reinterpret_cast<float2 *>(a.sc));
     return lkb_check_launch();
 }
 
@@ -688,7 +695,9 @@ int lkb_pf_swiglu(const float * Y, int ld, int up_off, int kb, lkb_pf_act a, int
     LKB_REQUIRE_INIT();
     if (!Y || !a.qs || !a.sc) return LKB_ERR_NULL;
     if (rows <= 0 || kb <= 0) return (rows == 0) ? LKB_OK : LKB_ERR_SHAPE;
-    k_pf_swiglu<<<dim3(rows, (kb + 7) / 8), 256, 0, (cudaStream_t) st>>>(Y, ld, up_off, kb, a.qs, reinterpret_cast<float2 *>(a.sc));
+    if ((ld & 3) || (up_off & 3) || (reinterpret_cast<uintptr_t>(Y) & 15)) return LKB_ERR_SHAPE;
+    const long long warps = (long long) rows * ((kb + 3) / 4);
+    k_pf_rows_q8<1><<<(unsigned) ((warps + 7) / 8), 256, 0, (cudaStream_t) st>>>(Y, ld, up_off, kb, rows, a.qs, reinterpret_cast<float2 *>(a.sc));
     return lkb_check_launch();
 }
 
@@ -698,7 +707,7 @@ int lkb_pf_router_small(const float * H, int m, const float * Wr, const float * 
     if (!H || !Wr || !bias || !inv || !sel || !sig) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
     if (m > 65535) return LKB_ERR_SHAPE;
-    k_pf_router_small<<<dim3(LKB_N_EXPERTS, m), 32, 0, (cudaStream_t) st>>>(H, Wr, bias, inv, sel, sig);
+    k_pf_router_token<<<m, 256, 0, (cudaStream_t) st>>>(H, Wr, bias, inv, sel, sig);
     return lkb_check_launch();
 }
 
@@ -725,7 +734,7 @@ int lkb_pf_select(const float * sel, const float * sig, int m, int * idx, float 
     LKB_REQUIRE_INIT();
     if (!sel || !sig || !idx || !w) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    k_pf_select<<<(m + 7) / 8, 256, 0, (cudaStream_t) st>>>(sel, sig, m, idx, w);
+    k_pf_select<<<min((m + 7) / 8, 148 * 8), 256, 0, (cudaStream_t) st>>>(sel, sig, m, reinterpret_cast<int4 *>(idx), reinterpret_cast<float4 *>(w));
     return lkb_check_launch();
 }
 
@@ -776,7 +785,7 @@ int lkb_pf_moe_combine(float * X, const float * D, const float * w, int m, lkb_s
     LKB_REQUIRE_INIT();
     if (!X || !D || !w) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    k_pf_moe_combine<<<dim3(m, LKB_HIDDEN / 256), 256, 0, (cudaStream_t) st>>>(X, D, w);
+    k_pf_moe_combine<<<m * (LKB_HIDDEN / 4 / 256), 256, 0, (cudaStream_t) st>>>(reinterpret_cast<float4 *>(X), reinterpret_cast<const float4 *>(D), w, m);
     return lkb_check_launch();
 }
 
@@ -785,7 +794,8 @@ int lkb_pf_moe_combine_norm(float * X, const float * D, const float * w, const f
     LKB_REQUIRE_INIT();
     if (!X || !D || !w || !nw || !a.qs || !a.sc || !inv_out) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    k_pf_moe_combine_norm<<<m, 256, 0, (cudaStream_t) st>>>(X, D, w, nw, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out);
+    k_pf_token_norm<1><<<(m + PF_TOK_WARPS - 1) / PF_TOK_WARPS, PF_TOK_WARPS * 32, 0, (cudaStream_t) st>>>(
+        X, D, nullptr, w, nw, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out, nullptr, m);
     return lkb_check_launch();
 }
 
@@ -838,7 +848,8 @@ int lkb_pf_moe_combine_norm_gather(float * X, const float * D, const int * pos, 
     LKB_REQUIRE_INIT();
     if (!X || !D || !pos || !w || !nw || !a.qs || !a.sc || !inv_out) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    k_pf_moe_combine_norm_gather<<<m, 256, 0, (cudaStream_t) st>>>(X, D, pos, w, nw, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out);
+    k_pf_token_norm<2><<<(m + PF_TOK_WARPS - 1) / PF_TOK_WARPS, PF_TOK_WARPS * 32, 0, (cudaStream_t) st>>>(
+        X, D, pos, w, nw, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out, nullptr, m);
     return lkb_check_launch();
 }
 
@@ -846,7 +857,7 @@ int lkb_pf_pack_q8_1(lkb_pf_act a, int t, lkb_block_q8_1 * y, lkb_stream_t st) {
     LKB_REQUIRE_INIT();
     if (!a.qs || !a.sc || !y) return LKB_ERR_NULL;
     if (t < 0) return LKB_ERR_SHAPE;
-    k_pf_pack_q8_1<<<1, 64, 0, (cudaStream_t) st>>>(a.qs, reinterpret_cast<const float2 *>(a.sc), t, reinterpret_cast<lkb_q8blk *>(y));
+    k_pf_pack_q8_1<<<1, 512, 0, (cudaStream_t) st>>>(a.qs, reinterpret_cast<const float2 *>(a.sc), t, reinterpret_cast<lkb_q8blk *>(y));
     return lkb_check_launch();
 }
 

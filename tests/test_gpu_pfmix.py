@@ -85,9 +85,11 @@ def test_pf_qknr_equals_decode_kernel(L, orc, m, P):
     assert float(kc[P + m].float().min().item()) == 7.0 and (P == 0 or float(kc[P - 1].float().min().item()) == 7.0)
 
 
-@pytest.mark.parametrize("m,P", [(64, 0), (100, 150), (37, 1000), (1, 0), (33, 31), (512, 0), (256, 3840)])
+@pytest.mark.parametrize("m,P", [(64, 0), (100, 150), (37, 1000), (1, 0), (33, 31), (512, 0), (256, 3840),
+                                 (64, 32704), (32, 131040)])
 def test_pf_attn_vs_float64(L, orc, m, P):
-    """The reference's three cases plus tile-boundary and long-prefix cases."""
+    """The reference's three cases plus tile-boundary and long-prefix cases, and the last chunk rows of the long-context
+    configuration's 32768- and 131072-token prompts (every query attends over the whole cache)."""
     rng = np.random.default_rng(m + P)
     S = P + m
     K = (rng.standard_normal((S + 2, 8, 64)) * 1.5).astype(np.float16)

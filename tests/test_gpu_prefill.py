@@ -409,3 +409,76 @@ def test_prefill_moe_layer_small_config3(L, orc):
                                   a_shift=2, scale=host(inv), out_rows=m * 4, v=v)
     dq8 = host(a2q).astype(np.int32) - tq
     assert np.max(np.abs(dq8)) <= 1 and np.count_nonzero(dq8) <= 2e-4 * tq.size   # __expf vs libm exp near ties
+
+
+def _sub_plan(operm, otiles, rng, per_tile=9):
+    """A sub-plan for the checker: from every tile of the device's plan its first and last rows (the ragged tails) plus a
+    few random ones, regrouped into tiles of the same experts.  A slot's GEMM row depends only on its own activation row
+    and its expert's weights, so the checker's rows on the sub-plan must equal the device's rows on the full plan."""
+    perm_sub, tiles_sub = [], []
+    for e, start, count, _ in otiles:
+        pick = {0, count - 1, count // 2}
+        pick.update(int(v) for v in rng.integers(0, count, size=per_tile))
+        rows = sorted(pick)
+        tiles_sub.append((e, len(perm_sub), len(rows), 0))
+        perm_sub.extend(int(operm[start + r]) for r in rows)
+    return np.asarray(perm_sub, np.int32), np.asarray(tiles_sub, np.int32).reshape(-1, 4)
+
+
+def test_gemm_moe_full_size_4096_tokens_zipf(L, orc):
+    """The benchmark's configuration at full size: 4096 tokens x top-4 = 16384 slots over 64 experts with Zipf(1.1)-skewed
+    routing, real layer shapes (gate|up 2 x 1536 x 2048 with the fused SwiGLU quantiser, down 2048 x 1536), through the
+    tensor-core kernel on its workspace path.  Every slot row is checked on the device against the unfused form; more than
+    2048 slots (first / middle / last row of every tile and random ones) bit for bit against the CPU checker."""
+    rng = np.random.default_rng(4096)
+    m, H, I, E = 4096, 2048, 1536, 64
+    NS = m * 4
+    gq, gd = rand_q4(rng, E * I, 64)
+    uq, ud = rand_q4(rng, E * I, 64)
+    dq_, dd_ = rand_q4(rng, E * H, 48)
+    # routing: Zipf(1.1) load over the experts, four distinct experts per token
+    p = 1.0 / (rng.permutation(E) + 1.0) ** 1.1
+    p /= p.sum()
+    idx = np.stack([rng.choice(E, size=4, replace=False, p=p) for _ in range(m)]).astype(np.int32)
+    X = act_floats(rng, m * H).reshape(m, H)
+    aq, asc = orc.pf_quant_rows(X, 64)
+    inv = rng.uniform(0.5, 2.0, size=m).astype(np.float32)
+    cnt, off, tiles, ntiles, perm, max_tiles = _plan_dev(L, idx.reshape(-1))
+    ocnt, ooff, otiles, operm = orc.moe_plan(idx.reshape(-1))
+    assert np.array_equal(host(perm), operm) and np.array_equal(host(cnt), ocnt)
+    assert ocnt.max() > 4 * ocnt[ocnt > 0].min()                         # the load really is skewed
+    wsb = torch.zeros(L.pf_gemm_workspace_bytes(max_tiles, H), dtype=torch.uint8, device="cuda")
+    L.pf_gemm_set_workspace(wsb)
+    L.pf_gemm_config(1)
+    dg = [dev(a) for a in (gq, gd, uq, ud, dq_, dd_)]
+    daq, dasc, dinv = dev(aq), dev(asc), dev(inv)
+    a2q, a2s = _act_bufs(NS, I // 32)
+    g = L.make_pf_gemm([(dg[0], dg[1]), (dg[2], dg[3])], [I, I, I], I, 64, daq, dasc, exp_stride=I * 64, perm=perm,
+                       tiles=tiles, ntiles=ntiles, a_shift=2, scale=dinv, oqs=a2q, osc=a2s, okb=I // 32)
+    L.pf_gemm_swiglu(g, max_tiles)
+    Y = nan_f32(NS, 2 * I)
+    g2 = L.make_pf_gemm([(dg[0], dg[1]), (dg[2], dg[3])], [I, 2 * I, 2 * I], 2 * I, 64, daq, dasc, exp_stride=I * 64,
+                        perm=perm, tiles=tiles, ntiles=ntiles, a_shift=2, scale=dinv, out=Y, out_ld=2 * I)
+    L.pf_gemm_moe(g2, max_tiles)
+    uqs, usc = _act_bufs(NS, I // 32)
+    L.k_pf_swiglu(Y, 2 * I, I, I // 32, L.pf_act(uqs, usc), NS)
+    assert torch.equal(a2q, uqs) and torch.equal(a2s, usc)               # all 16384 slots: fused == unfused
+    D = nan_f32(NS, H)
+    gd_ = L.make_pf_gemm([(dg[4], dg[5])], [H, H, H], H, 48, a2q, a2s, exp_stride=H * 48, perm=perm, tiles=tiles,
+                         ntiles=ntiles, a_shift=0, out=D, out_ld=H)
+    L.pf_gemm_moe(gd_, max_tiles)
+    torch.cuda.synchronize()
+    assert L.lib.lkb_pf_gemm_status() == 0
+    gotY, gotD = host(Y), host(D)
+    assert not np.any(np.isnan(gotY)) and not np.any(np.isnan(gotD))
+
+    sperm, stiles = _sub_plan(operm, otiles, rng)
+    assert sperm.size >= 2048 and np.unique(sperm).size == sperm.size
+    oY = orc.pf_gemm([(gq, gd), (uq, ud)], [I, 2 * I, 2 * I], 2 * I, 64, aq, asc, exp_stride=I * 64, perm=sperm, tiles=stiles,
+                     a_shift=2, scale=inv, out_rows=NS)
+    assert np.array_equal(gotY[sperm], oY[sperm])                        # gate|up rows, bit for bit
+    oD = orc.pf_gemm([(dq_, dd_)], [H, H, H], H, 48, host(a2q), host(a2s), exp_stride=H * 48, perm=sperm, tiles=stiles,
+                     a_shift=0, out_rows=NS)
+    assert np.array_equal(gotD[sperm], oD[sperm])                        # down rows, bit for bit
+    L.pf_gemm_set_workspace(None)
+    L.pf_gemm_config(-1)
