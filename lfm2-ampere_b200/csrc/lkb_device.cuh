@@ -82,19 +82,43 @@ __device__ __forceinline__ float lkb_quad_sum(float a0, float a1, float a2, floa
 
 // Q8_1 of the block this lane's group of 8 holds: returns the lane's four quants packed low byte first;
 // (d, 8 * sum) after the fp16 round trip of the planar layout in sc_out (same in all 8 lanes).
+// q = roundf(v / d) without the four IEEE divisions: t = v * rcp(d) is within 3e-5 of the true quotient
+// (|q| <= 127, two ulps of relative error), so wherever t is farther than 1e-4 from a half-integer the nearest
+// integer of t IS roundf of the IEEE quotient; only the rare element inside that band (and any NaN) takes the
+// division (one branch for the lane's four).  The nearest integer comes from the 1.5 * 2^23 trick, whose low mantissa
+// byte is q's two's complement.
 __device__ __forceinline__ unsigned lkb_quad_quant(const float4 v, int lane, float2 & sc_out) {
-    const unsigned gm = 0xFFu << (lane & 24);
+    (void) lane;
     const unsigned m01 = max(__float_as_uint(fabsf(v.x)), __float_as_uint(fabsf(v.y)));
     const unsigned m23 = max(__float_as_uint(fabsf(v.z)), __float_as_uint(fabsf(v.w)));
-    const unsigned am = __reduce_max_sync(gm, max(m01, m23));
+    unsigned am = max(m01, m23);
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) am = max(am, __shfl_xor_sync(LKB_FULL, am, o));      // exact, order-free
     const float sum = lkb_quad_sum(v.x, v.y, v.z, v.w);
     const float d = __fdiv_rn(__uint_as_float(am), 127.0f);
     const __half2 ds = __floats2half2_rn(d, sum);
     sc_out = make_float2(__low2float(ds), __fmul_rn(8.0f, __high2float(ds)));
-    if (am == 0u) return 0u;
-    const int q0 = (int) roundf(__fdiv_rn(v.x, d)), q1 = (int) roundf(__fdiv_rn(v.y, d));
-    const int q2 = (int) roundf(__fdiv_rn(v.z, d)), q3 = (int) roundf(__fdiv_rn(v.w, d));
-    return (unsigned) (q0 & 255) | ((unsigned) (q1 & 255) << 8) | ((unsigned) (q2 & 255) << 16) | ((unsigned) q3 << 24);
+    float rd;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rd) : "f"(d));
+    const float MAGIC = 12582912.0f;                     // 1.5 * 2^23: adding it rounds to the nearest (even) integer
+    const float vv[4] = {v.x, v.y, v.z, v.w};
+    float sft[4];
+    bool sure = true;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        sft[k] = fmaf(vv[k], rd, MAGIC);                                  // nearest integer of v * rd, offset by MAGIC
+        const float diff = fmaf(vv[k], rd, -__fadd_rn(sft[k], -MAGIC));   // v * rd - that integer
+        sure = sure && (fabsf(diff) < 0.4999f);
+    }
+    if (!sure) {                                         // rare: some element within 1e-4 of a tie, a NaN, or an all-zero block
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float r = roundf(__fdiv_rn(vv[k], d));
+            sft[k] = (am != 0u && r == r) ? __fadd_rn(r, MAGIC) : MAGIC;  // (int) NaN is 0; an all-zero block quantises to 0
+        }
+    }
+    return __byte_perm(__byte_perm(__float_as_uint(sft[0]), __float_as_uint(sft[1]), 0x0040),
+                       __byte_perm(__float_as_uint(sft[2]), __float_as_uint(sft[3]), 0x0040), 0x5410);
 }
 
 // Producer of the scale-carrying norm split: quantise RAW u = x*w, emit the

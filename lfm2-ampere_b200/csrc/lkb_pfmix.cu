@@ -29,7 +29,9 @@ __global__ void __launch_bounds__(256) k_pf_embed(const unsigned char * __restri
 // PF_CONV_RUN consecutive tokens and slides bx of the previous two tokens through registers, so Y is read once
 // instead of three times; taps and the fused multiply-add nesting are the decode kernel's, per channel.
 // ref semantics: src/prefill.cu:937-957
-#define PF_CONV_RUN 16
+#ifndef PF_CONV_RUN
+#define PF_CONV_RUN 4
+#endif
 __device__ __forceinline__ float4 pf_mul4(const float4 a, const float4 b) {
     return make_float4(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y), __fmul_rn(a.z, b.z), __fmul_rn(a.w, b.w));
 }
@@ -53,9 +55,10 @@ __global__ void __launch_bounds__(128) k_pf_conv_run(const float * __restrict__ 
         h0 = pf_mul4(*reinterpret_cast<const float4 *>(y2), *reinterpret_cast<const float4 *>(y2 + 2 * LKB_HIDDEN));
         h1 = pf_mul4(*reinterpret_cast<const float4 *>(y2 + 3 * LKB_HIDDEN), *reinterpret_cast<const float4 *>(y2 + 5 * LKB_HIDDEN));
     }
-    const int t1 = min(t0 + PF_CONV_RUN, m);
-#pragma unroll 4
-    for (int t = t0; t < t1; ++t) {
+#pragma unroll
+    for (int j = 0; j < PF_CONV_RUN; ++j) {
+        const int t = t0 + j;
+        if (t >= m) break;
         const float * yt = Y + (size_t) t * (3 * LKB_HIDDEN) + ch;
         const float4 bx = pf_mul4(*reinterpret_cast<const float4 *>(yt), *reinterpret_cast<const float4 *>(yt + 2 * LKB_HIDDEN));
         const float4 cv = *reinterpret_cast<const float4 *>(yt + LKB_HIDDEN);

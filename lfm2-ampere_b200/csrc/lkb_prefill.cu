@@ -11,16 +11,20 @@
 #define LKB_REQUIRE_INIT() do { if (!lkb_context().inited) return LKB_ERR_NOT_INIT; } while (0)
 
 // ---------------------------------------------------------------------------
-// Per-token kernels.  One WARP owns one token (or one 512-byte run of a row): four elements per lane through
-// 128-bit loads, four 32-element blocks per step (lkb_quad_quant), no shared memory and no block barrier, several
-// tokens per CTA.  The arithmetic per element, per block and per token is that of the decode kernels
-// (reference semantics: src/prefill.cu:871-932 norm, :1574-1594 row quantisers), so outputs compare byte for byte.
+// Per-token kernels.  Warps own contiguous 512-byte runs: four elements per lane through 128-bit loads, four
+// 32-element blocks per step (lkb_quad_quant), several tokens per CTA and no CTA-wide barrier.  The arithmetic per
+// element, per block and per token is that of the decode kernels (reference semantics: src/prefill.cu:871-932 norm,
+// :1574-1594 row quantisers), so outputs compare byte for byte.
 // ---------------------------------------------------------------------------
-#define PF_TOK_WARPS 4                   // tokens per CTA of the per-token kernels
+#ifndef PF_TOK_SPLIT
+#define PF_TOK_SPLIT 4                   // warps sharing one token in k_pf_token_norm
+#endif
+#define PF_TOK_WARPS (PF_TOK_SPLIT > 4 ? PF_TOK_SPLIT : 4)        // warps per CTA of the per-token kernels
+#define PF_TOK_PER_CTA (PF_TOK_WARPS / PF_TOK_SPLIT)
 
 // MODE 0: norm of X.  MODE 1: X += sum_k w[4t+k] * D[4t+k] first (rank-order chain), then the norm.
-// MODE 2: as 1 with the row of slot 4t+k found through pos[].  Quantises u = x * nw per block, keeps each block's
-// sum of squares of x in the two lanes that need it, and ends with 1/rms from the 64 partials in the decode
+// MODE 2: as 1 with the row of slot 4t+k found through pos[].  PF_TOK_SPLIT warps share a token (consecutive runs of blocks): each quantises u = x * nw per block and leaves each block's sum of squares of x in shared memory;
+// after a named barrier over the token's warps the first warp of the token ends with 1/rms from the 64 partials in the decode
 // kernels' order ((ssq[l] + ssq[l+32]) butterflied over l).
 template <int MODE>
 __global__ void __launch_bounds__(PF_TOK_WARPS * 32) k_pf_token_norm(float * __restrict__ X, const float * __restrict__ D,
@@ -28,9 +32,11 @@ __global__ void __launch_bounds__(PF_TOK_WARPS * 32) k_pf_token_norm(float * __r
                                                                       const float * __restrict__ nw, int8_t * __restrict__ aqs,
                                                                       float2 * __restrict__ asc, float * __restrict__ inv_out,
                                                                       float * __restrict__ h32, int m) {
-    const int lane = threadIdx.x & 31;
-    const int t = blockIdx.x * PF_TOK_WARPS + (threadIdx.x >> 5);
-    if (t >= m) return;                                   // warp-uniform
+    __shared__ float s_sq[PF_TOK_PER_CTA][64];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tl = warp / PF_TOK_SPLIT, part = warp % PF_TOK_SPLIT;
+    const int t = blockIdx.x * PF_TOK_PER_CTA + tl;
+    if (t >= m) return;                                   // all warps of the token leave together
     float4 * x4 = reinterpret_cast<float4 *>(X + (size_t) t * LKB_HIDDEN);
     const float4 * w4 = reinterpret_cast<const float4 *>(nw);
     unsigned * q4 = reinterpret_cast<unsigned *>(aqs + (size_t) t * LKB_HIDDEN);
@@ -45,9 +51,9 @@ __global__ void __launch_bounds__(PF_TOK_WARPS * 32) k_pf_token_norm(float * __r
             d4[k] = reinterpret_cast<const float4 *>(D + (size_t) row * LKB_HIDDEN);
         }
     }
-    float lo = 0.0f, hi = 0.0f;                           // ssq of blocks `lane` and `lane + 32`
 #pragma unroll 4
-    for (int s = 0; s < LKB_HIDDEN / 128; ++s) {
+    constexpr int STEPS = LKB_HIDDEN / 128 / PF_TOK_SPLIT;
+    for (int s = part * STEPS; s < part * STEPS + STEPS; ++s) {
         const int i4 = s * 32 + lane;
         float4 xv = x4[i4];
         if (MODE) {
@@ -66,14 +72,14 @@ __global__ void __launch_bounds__(PF_TOK_WARPS * 32) k_pf_token_norm(float * __r
         if (h4) h4[i4] = u;
         float2 s2;
         q4[i4] = lkb_quad_quant(u, lane, s2);
-        if ((lane & 7) == 0) sc[s * 4 + (lane >> 3)] = s2;
         const float sq = lkb_quad_sum(__fmul_rn(xv.x, xv.x), __fmul_rn(xv.y, xv.y), __fmul_rn(xv.z, xv.z), __fmul_rn(xv.w, xv.w));
-        // block 4s + g sits in lane group g; lane l keeps blocks l and l + 32, i.e. group l & 3 of steps l >> 2 and 8 + (l >> 2)
-        const float tq = __shfl_sync(LKB_FULL, sq, (lane & 3) * 8);
-        if ((lane >> 2) == (s & 7)) { if (s < 8) lo = tq; else hi = tq; }
+        if ((lane & 7) == 0) { sc[s * 4 + (lane >> 3)] = s2; s_sq[tl][s * 4 + (lane >> 3)] = sq; }
     }
-    const float sv = lkb_warp_sum(__fadd_rn(lo, hi));
-    if (lane == 0) inv_out[t] = rsqrtf(fmaf(sv, 1.0f / (float) LKB_HIDDEN, LKB_EPS));
+    asm volatile("bar.sync %0, %1;" :: "r"(1 + tl), "n"(32 * PF_TOK_SPLIT) : "memory");
+    if (part == 0) {
+        const float sv = lkb_warp_sum(__fadd_rn(s_sq[tl][lane], s_sq[tl][lane + 32]));
+        if (lane == 0) inv_out[t] = rsqrtf(fmaf(sv, 1.0f / (float) LKB_HIDDEN, LKB_EPS));
+    }
 }
 
 // Layer-0 form: normalise first (x * inv) * w, quantise that, report scale 1.  The sum of squares keeps the
@@ -674,9 +680,8 @@ int lkb_pf_norm(const float * X, const float * w, int plain, lkb_pf_act a, float
     LKB_REQUIRE_INIT();
     if (!X || !w || !a.qs || !a.sc || !inv_out) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    const int grid = (m + PF_TOK_WARPS - 1) / PF_TOK_WARPS;
-    if (plain) k_pf_token_norm_plain<<<grid, PF_TOK_WARPS * 32, 0, (cudaStream_t) st>>>(X, w, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out, m);
-    else       k_pf_token_norm<0><<<grid, PF_TOK_WARPS * 32, 0, (cudaStream_t) st>>>(const_cast<float *>(X), nullptr, nullptr, nullptr, w, a.qs,
+    if (plain) k_pf_token_norm_plain<<<(m + PF_TOK_WARPS - 1) / PF_TOK_WARPS, PF_TOK_WARPS * 32, 0, (cudaStream_t) st>>>(X, w, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out, m);
+    else       k_pf_token_norm<0><<<(m + PF_TOK_PER_CTA - 1) / PF_TOK_PER_CTA, PF_TOK_WARPS * 32, 0, (cudaStream_t) st>>>(const_cast<float *>(X), nullptr, nullptr, nullptr, w, a.qs,
                                                                                   reinterpret_cast<float2 *>(a.sc), inv_out, h32, m);
     return lkb_check_launch();
 }
@@ -794,7 +799,7 @@ int lkb_pf_moe_combine_norm(float * X, const float * D, const float * w, const f
     LKB_REQUIRE_INIT();
     if (!X || !D || !w || !nw || !a.qs || !a.sc || !inv_out) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    k_pf_token_norm<1><<<(m + PF_TOK_WARPS - 1) / PF_TOK_WARPS, PF_TOK_WARPS * 32, 0, (cudaStream_t) st>>>(
+    k_pf_token_norm<1><<<(m + PF_TOK_PER_CTA - 1) / PF_TOK_PER_CTA, PF_TOK_WARPS * 32, 0, (cudaStream_t) st>>>(
         X, D, nullptr, w, nw, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out, nullptr, m);
     return lkb_check_launch();
 }
@@ -848,7 +853,7 @@ int lkb_pf_moe_combine_norm_gather(float * X, const float * D, const int * pos, 
     LKB_REQUIRE_INIT();
     if (!X || !D || !pos || !w || !nw || !a.qs || !a.sc || !inv_out) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    k_pf_token_norm<2><<<(m + PF_TOK_WARPS - 1) / PF_TOK_WARPS, PF_TOK_WARPS * 32, 0, (cudaStream_t) st>>>(
+    k_pf_token_norm<2><<<(m + PF_TOK_PER_CTA - 1) / PF_TOK_PER_CTA, PF_TOK_WARPS * 32, 0, (cudaStream_t) st>>>(
         X, D, pos, w, nw, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out, nullptr, m);
     return lkb_check_launch();
 }
