@@ -238,6 +238,81 @@ WORKLOAD = ("config 3: 4096-token batched prefill through the 40 MoE-FFN layers 
 
 
 # --------------------------------------------------------------------------- GPU arm
+def ab_reference_kernels(ps, layers, api, rounds=5):
+    """A/B on this GPU against the kernels to beat: the reference's own grouped-GEMM kernels, compiled unchanged for
+    sm_100a (oracle/_ref/libref_kernels.so; absent where the reference checkout was not at hand when the tree was
+    built -> null).  Same plan, same activations, same weights; the two layers' weight sets alternate so that neither
+    side finds its weights in L2; ours and theirs interleaved, medians over `rounds`.  Outputs are compared byte for byte."""
+    import torch
+    try:
+        rk = importlib.import_module("oracle.ref_kernels")
+        if not rk.available():
+            return None
+    except Exception:
+        return None
+    from importlib import import_module
+    synth = import_module("lfm2-ampere_b200.synth")
+    Hh, Ii = synth.H, synth.I
+
+    def descs(li):
+        l = layers[li]
+        g = api.make_pf_gemm([(l.gate_qs, l.gate_d), (l.up_qs, l.up_d)], [Ii, Ii, Ii], Ii, Hh // 32, ps.a_qs, ps.a_sc,
+                             exp_stride=Ii * (Hh // 32), perm=ps.perm, tiles=ps.tiles, ntiles=ps.ntiles,
+                             a_shift=2, scale=ps.inv, oqs=ps.a2_qs, osc=ps.a2_sc, okb=Ii // 32)
+        dn = api.make_pf_gemm([(l.down_qs, l.down_d)], [Hh, Hh, Hh], Hh, Ii // 32, ps.a2_qs, ps.a2_sc,
+                              exp_stride=Hh * (Ii // 32), perm=ps.perm, tiles=ps.tiles, ntiles=ps.ntiles,
+                              a_shift=0, out=ps.D, out_ld=Hh)
+        return g, dn
+
+    def timed(fn):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3
+
+    api.pf_gemm_set_workspace(ps.gemm_ws)
+    ours, theirs = {"swiglu": [], "down": []}, {"swiglu": [], "down": []}
+    # parity first (untimed): same plan and inputs through both, outputs byte for byte
+    g, dn = descs(0)
+    api.pf_gemm_swiglu(g, ps.max_tiles)
+    q_ours, s_ours = ps.a2_qs.clone(), ps.a2_sc.clone()
+    rk.pf_gemm_swiglu(g, ps.max_tiles)
+    beq = lambda a, b: bool(torch.equal(a.view(torch.uint8), b.view(torch.uint8)))      # bytes: NaN-safe
+    same = beq(q_ours, ps.a2_qs) and beq(s_ours, ps.a2_sc)
+    api.pf_gemm_moe(dn, ps.max_tiles)
+    d_ours = ps.D.clone()
+    rk.pf_gemm_moe(dn, ps.max_tiles)
+    same = same and beq(d_ours, ps.D)
+    del q_ours, s_ours, d_ours
+    nl = min(2, len(layers))
+    for r in range(rounds):
+        # each call's weights were last read two calls earlier (a layer's gate|up planes alone are 226 MB: L2 is cold for both)
+        for k, li in enumerate((r % nl, (r + 1) % nl)):
+            g, dn = descs(li)
+            mine = (k == 0)
+            (ours if mine else theirs)["swiglu"].append(timed(lambda: (api if mine else rk).pf_gemm_swiglu(g, ps.max_tiles)))
+        for k, li in enumerate(((r + 1) % nl, r % nl)):
+            g, dn = descs(li)
+            mine = (k == 0)
+            (ours if mine else theirs)["swiglu"].append(timed(lambda: (api if mine else rk).pf_gemm_swiglu(g, ps.max_tiles)))
+        for k, li in enumerate((r % nl, (r + 1) % nl)):
+            g, dn = descs(li)
+            mine = (k == 0)
+            (ours if mine else theirs)["down"].append(timed(lambda: (api if mine else rk).pf_gemm_moe(dn, ps.max_tiles)))
+        for k, li in enumerate(((r + 1) % nl, r % nl)):
+            g, dn = descs(li)
+            mine = (k == 0)
+            (ours if mine else theirs)["down"].append(timed(lambda: (api if mine else rk).pf_gemm_moe(dn, ps.max_tiles)))
+    med = lambda v: float(np.median(v))
+    o, t = med(ours["swiglu"]) + med(ours["down"]), med(theirs["swiglu"]) + med(theirs["down"])
+    return {"what": "one layer's two grouped GEMMs on the same plan: this library vs the reference's kernels compiled unchanged for sm_100a",
+            "ours_us": {"swiglu": med(ours["swiglu"]), "down": med(ours["down"])},
+            "reference_kernel_us": {"swiglu": med(theirs["swiglu"]), "down": med(theirs["down"])},
+            "speedup": t / o, "outputs_identical": bool(same), "timed_calls_each": 2 * rounds}
+
+
 def profile_traffic(name):
     """DRAM bytes per launch recorded in a profiles/ summary (a line `traffic_bytes_per_launch: N`), or None when the
     summary is missing: the figure belongs to the kernel build it was captured from, so it is read, never hard-coded."""
@@ -369,6 +444,7 @@ def run_ours(args):
     torch.cuda.synchronize()
     gemm_ms = [a.elapsed_time(b) for a, b in ps.gemm_events]
     ps.gemm_events = None
+    vs_ref_kernel = ab_reference_kernels(ps, layers, lkb) if not ep else None
     if (not ep or args.ep_dispatch == "peer") and not args.no_graph:
         # one CUDA graph for the step's launches (the NCCL exchange has a host sync per layer and cannot be captured)
         barrier()
@@ -449,6 +525,7 @@ def run_ours(args):
                 "algorithmic_ops_per_launch": ops_per_launch,
                 "gemm_share_of_step": (float(np.sum(gemm_ms)) / pms) if gemm_ms else None,
                 "traffic": profile_traffic("k_pf_gemm_tc_prefill_4096tok.txt"),
+                "vs_ref_kernel": vs_ref_kernel,
                 "co_bound": "the exact per-block scale arithmetic (2 fp32 FMAs per int32 block sum on the CUDA cores) costs 256 "
                             "FMA-pipe cycles per 128x128x32 block against 64 tensor-pipe cycles: the tensor pipe cannot exceed 25% busy",
                 "whole_step_TMACs": macs / (pms * 1e-3) / 1e12}

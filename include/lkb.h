@@ -453,6 +453,18 @@ int lkb_ep_pack_push(lkb_pf_act a, const float * inv, const int * idx, const int
                      int n, int experts_per_rank, const lkb_ep_peers * peers, int me, int G, const int * epoch, int * pos, unsigned * done,
                      lkb_stream_t st);
 int lkb_ep_wait(const int * flags, int phase, int G, const int * epoch, int * status, lkb_stream_t st);
+/* No counterpart in the reference: the home side's routing and count exchange in ONE launch -- slots grouped by the
+ * rank owning their expert (send_order[n], doff[64]: first position of each destination; stable, the order of
+ * lkb_pf_moe_count / _plan / _scatter keyed by owner rank), then everything lkb_ep_counts_exchange does with those
+ * counts.  One CTA; n is a rank's slots of a chunk (a few thousand). */
+int lkb_ep_route_exchange(const int * idx, int n, int experts_per_rank, const lkb_ep_peers * peers, int me, int G, int * epoch,
+                          int * send_order, int * doff, int * offs, int * status, lkb_stream_t st);
+/* No counterpart in the reference: the owner side's wait for the dispatched rows (lkb_ep_wait phase 1) and the grouped
+ * GEMM's plan over them (cnt[64], off[64], tiles, ntiles, perm: the results of lkb_pf_moe_count_dev / _plan /
+ * _scatter_dev keyed by the local expert id each received row carries) in ONE launch.  nrecv_out (optional) receives
+ * the row count.  When the wait gives up, *ntiles = 0 and the status word holds the code. */
+int lkb_ep_route_experts(const void * recv, int cap, const int * flags, int G, const int * epoch, const int * offs, int * cnt, int * off,
+                         int * tiles, int * ntiles, int * perm, int * nrecv_out, int * status, lkb_stream_t st);
 int lkb_ep_push_back(const float * D, const int * offs, int max_rows, const lkb_ep_peers * peers, int me, int G,
                      const int * epoch, unsigned * done, lkb_stream_t st);
 /* No counterpart in the reference: the unpack / count / scatter kernels with the live row count on the device. */

@@ -154,6 +154,119 @@ __global__ void __launch_bounds__(256) k_ep_push_back(const float * __restrict__
     (void) me;
 }
 
+// ---------------------------------------------------------------------------
+// One-CTA routing: histogram of n keys in [0, 64), exclusive offsets, optional 64-row tiles in key order (the
+// grouped GEMM's plan), and the stable scatter perm (key-major, index-ascending inside a key) -- the results of the
+// count / plan / scatter kernels of the single-GPU path in ONE launch of 1024 threads.  A rank's share of a chunk is a
+// few thousand slots, for which four launches cost more than the work; chunks of 1024 keys are ranked with match_any
+// and a per-warp count table, with a running offset per key carried from chunk to chunk.
+// ---------------------------------------------------------------------------
+struct EpRouteSmem { int wc[32][LKB_N_EXPERTS]; int cnt[LKB_N_EXPERTS]; int run[LKB_N_EXPERTS]; int ok; };
+
+template <class KeyFn>
+__device__ __forceinline__ void ep_route_cta(EpRouteSmem & R, KeyFn key, int n, int * __restrict__ cnt_out, int * __restrict__ off,
+                                             int4 * __restrict__ tiles, int * __restrict__ ntiles, int * __restrict__ perm) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < LKB_N_EXPERTS) R.cnt[tid] = 0;
+    __syncthreads();
+    for (int s = tid; s < n; s += 1024) atomicAdd(&R.cnt[key(s)], 1);
+    __syncthreads();
+    if (warp == 0) {
+        const int c0 = R.cnt[lane], c1 = R.cnt[lane + 32];
+        const int n0 = (c0 + LKB_MOE_BN - 1) / LKB_MOE_BN, n1 = (c1 + LKB_MOE_BN - 1) / LKB_MOE_BN;
+        int so = c0, st = n0, so1 = c1, st1 = n1;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int a = __shfl_up_sync(LKB_FULL, so, o), b = __shfl_up_sync(LKB_FULL, st, o);
+            const int c = __shfl_up_sync(LKB_FULL, so1, o), d = __shfl_up_sync(LKB_FULL, st1, o);
+            if (lane >= o) { so += a; st += b; so1 += c; st1 += d; }
+        }
+        const int tot_o = __shfl_sync(LKB_FULL, so, 31), tot_t = __shfl_sync(LKB_FULL, st, 31);
+        const int off0 = so - c0, off1 = tot_o + so1 - c1;
+        R.run[lane] = off0; R.run[lane + 32] = off1;
+        off[lane] = off0; off[lane + 32] = off1;
+        if (cnt_out) { cnt_out[lane] = c0; cnt_out[lane + 32] = c1; }
+        if (tiles) {
+            const int tb0 = st - n0, tb1 = tot_t + st1 - n1;
+            for (int i = 0; i < n0; ++i) tiles[tb0 + i] = make_int4(lane, off0 + i * LKB_MOE_BN, min(LKB_MOE_BN, c0 - i * LKB_MOE_BN), 0);
+            for (int i = 0; i < n1; ++i) tiles[tb1 + i] = make_int4(lane + 32, off1 + i * LKB_MOE_BN, min(LKB_MOE_BN, c1 - i * LKB_MOE_BN), 0);
+            if (lane == 31) *ntiles = tot_t + st1;
+        }
+    }
+    for (int c0 = 0; c0 < n; c0 += 1024) {
+        for (int i = tid; i < 32 * LKB_N_EXPERTS; i += 1024) (&R.wc[0][0])[i] = 0;
+        __syncthreads();
+        const int s = c0 + tid;
+        const bool live = s < n;
+        const int e = live ? key(s) : -1 - lane;               // dead lanes match nobody
+        const unsigned same = __match_any_sync(LKB_FULL, e);
+        const int rank_w = __popc(same & ((1u << lane) - 1u));
+        if (live && rank_w == 0) R.wc[warp][e] = __popc(same);
+        __syncthreads();
+        if (tid < LKB_N_EXPERTS) {                             // exclusive scan over the 32 warps, per key, from the running offset
+            int run = R.run[tid];
+            for (int wv = 0; wv < 32; ++wv) { const int c = R.wc[wv][tid]; R.wc[wv][tid] = run; run += c; }
+            R.run[tid] = run;
+        }
+        __syncthreads();
+        if (live) perm[R.wc[warp][e] + rank_w] = s;
+        __syncthreads();
+    }
+}
+
+// Home side of a layer's exchange in one launch: slots grouped by the rank that owns their expert (send_order, doff),
+// then the count exchange of k_ep_counts_exchange with the counts taken from shared memory.
+__global__ void __launch_bounds__(1024) k_ep_route_exchange(const int * __restrict__ idx, int ns, int experts_per_rank, EpPeers P, int me, int G,
+                                                            int * __restrict__ epoch_dev, int * __restrict__ send_order, int * __restrict__ doff,
+                                                            int * __restrict__ offs, int * __restrict__ status, unsigned long long limit_ns) {
+    __shared__ EpRouteSmem R;
+    const int t = threadIdx.x;
+    ep_route_cta(R, [&](int s) { return idx[s] / experts_per_rank; }, ns, nullptr, doff, nullptr, nullptr, send_order);
+    const int epoch = *epoch_dev + 1;                                    // this layer's epoch; stored back at the end
+    if (t < G * G) P.cmat[t / G][me * G + (t % G)] = R.cnt[t % G];      // my row, into every rank's matrix
+    __threadfence_system();
+    if (t == 0) R.ok = 1;
+    __syncthreads();
+    if (t < G) ep_st_release(P.flags[t] + 0 * EP_MAX_RANKS + me, epoch);
+    if (t < G && !ep_wait_flag(P.flags[me], 0, t, epoch, status, 1, limit_ns)) R.ok = 0;
+    __syncthreads();
+    if (!R.ok) return;
+    const int * C = P.cmat[me];                                          // my copy: C[s*G + g] = rows s sends to g
+    if (t < G) {
+        int sb = 0, ro = 0, bb = 0;
+        for (int s = 0; s < me; ++s) sb += __ldcg(C + s * G + t);
+        for (int s = 0; s < t; ++s) ro += __ldcg(C + s * G + me);
+        for (int g = 0; g < me; ++g) bb += __ldcg(C + t * G + g);
+        offs[t] = sb; offs[G + t] = ro; offs[2 * G + t] = bb;
+    }
+    if (t == 0) {
+        int n = 0;
+        for (int s = 0; s < G; ++s) n += __ldcg(C + s * G + me);
+        offs[3 * G] = n;
+        *epoch_dev = epoch;
+    }
+}
+
+// Owner side in one launch: wait until every source has published its rows, then the grouped GEMM's plan over the
+// received rows (key = the local expert id each row carries).
+__global__ void __launch_bounds__(1024) k_ep_route_experts(const unsigned char * __restrict__ recv, int cap, const int * __restrict__ flags, int G,
+                                                           const int * __restrict__ epoch_dev, const int * __restrict__ offs,
+                                                           int * __restrict__ cnt, int * __restrict__ off, int4 * __restrict__ tiles,
+                                                           int * __restrict__ ntiles, int * __restrict__ perm, int * __restrict__ nrecv_out,
+                                                           int * __restrict__ status, unsigned long long limit_ns) {
+    __shared__ EpRouteSmem R;
+    const int t = threadIdx.x;
+    if (t == 0) R.ok = 1;
+    __syncthreads();
+    if (t < G && !ep_wait_flag(flags, 1, t, *epoch_dev, status, 3, limit_ns)) R.ok = 0;
+    __syncthreads();
+    if (!R.ok) { if (t == 0) *ntiles = 0; return; }          // nothing for the GEMMs to do
+    int n = offs[3 * G]; if (n > cap) n = cap;
+    ep_route_cta(R, [&](int s) { return (int) __ldcg(reinterpret_cast<const unsigned *>(recv + (size_t) s * EP_ROW_BYTES) + 641); },
+                 n, cnt, off, tiles, ntiles, perm);
+    if (t == 0 && nrecv_out) *nrecv_out = n;
+}
+
 static int ep_peers(EpPeers & P, const void * const * cmat, const void * const * flags, const void * const * recv,
                     const void * const * dback, int G) {
     if (!cmat || !flags || !recv || !dback) return LKB_ERR_NULL;
@@ -184,6 +297,28 @@ int lkb_ep_counts_exchange(const int * dcnt, const lkb_ep_peers * peers, int me,
     if (r != LKB_OK) return r;
     if (me < 0 || me >= G) return LKB_ERR_SHAPE;
     k_ep_counts_exchange<<<1, 64, 0, (cudaStream_t) st>>>(dcnt, P, me, G, epoch, offs, status, g_ep_limit_ns);
+    return lkb_check_launch();
+}
+
+int lkb_ep_route_exchange(const int * idx, int n, int experts_per_rank, const lkb_ep_peers * peers, int me, int G, int * epoch,
+                          int * send_order, int * doff, int * offs, int * status, lkb_stream_t st) {
+    if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
+    if (!idx || !peers || !epoch || !send_order || !doff || !offs || !status) return LKB_ERR_NULL;
+    EpPeers P = {};
+    const int r = ep_peers(P, peers->cmat, peers->flags, peers->recv, peers->dback, G);
+    if (r != LKB_OK) return r;
+    if (n <= 0 || experts_per_rank <= 0 || me < 0 || me >= G) return LKB_ERR_SHAPE;
+    k_ep_route_exchange<<<1, 1024, 0, (cudaStream_t) st>>>(idx, n, experts_per_rank, P, me, G, epoch, send_order, doff, offs, status, g_ep_limit_ns);
+    return lkb_check_launch();
+}
+
+int lkb_ep_route_experts(const void * recv, int cap, const int * flags, int G, const int * epoch, const int * offs, int * cnt, int * off,
+                         int * tiles, int * ntiles, int * perm, int * nrecv_out, int * status, lkb_stream_t st) {
+    if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
+    if (!recv || !flags || !epoch || !offs || !cnt || !off || !tiles || !ntiles || !perm || !status) return LKB_ERR_NULL;
+    if (cap <= 0 || G < 1 || G > EP_MAX_RANKS) return LKB_ERR_SHAPE;
+    k_ep_route_experts<<<1, 1024, 0, (cudaStream_t) st>>>(reinterpret_cast<const unsigned char *>(recv), cap, flags, G, epoch, offs, cnt, off,
+                                                          reinterpret_cast<int4 *>(tiles), ntiles, perm, nrecv_out, status, g_ep_limit_ns);
     return lkb_check_launch();
 }
 

@@ -51,8 +51,8 @@ __global__ void __launch_bounds__(PF_TOK_WARPS * 32) k_pf_token_norm(float * __r
             d4[k] = reinterpret_cast<const float4 *>(D + (size_t) row * LKB_HIDDEN);
         }
     }
-#pragma unroll 4
     constexpr int STEPS = LKB_HIDDEN / 128 / PF_TOK_SPLIT;
+#pragma unroll
     for (int s = part * STEPS; s < part * STEPS + STEPS; ++s) {
         const int i4 = s * 32 + lane;
         float4 xv = x4[i4];
@@ -182,152 +182,126 @@ __global__ void __launch_bounds__(256) k_pf_router_token(const float * __restric
     }
 }
 
-// Tiled form: CTA = 32 tokens x 64 experts, thread = 2 tokens x 4 experts, K
-// staged 32 at a time.  Each (token, expert) logit is one FMA chain over
-// k = 0..2047 ascending.  ref: src/prefill.cu:1606-1666 (same per-logit order)
-#define LKB_RT_K 32
-#ifndef LKB_RT_FFMA2
-#define LKB_RT_FFMA2 1
+// Tiled form.  Each (token, expert) logit is one FMA chain over k = 0..2047 ascending (reference semantics:
+// src/prefill.cu:1606-1666, same per-logit order), so a CTA runs a long sequential k loop and the kernel is bound by
+// (a) how well the loads of the next k-tiles hide behind the FMAs of the current one and (b) how many FMAs each
+// shared-memory wavefront feeds.  CTA = NW warps = 2 NW token groups x 16 expert lanes; a thread owns TPT tokens x the
+// four experts (lane, lane + 16, + 32, + 48): 4 * TPT independent chains.  Tiles of 32 k-values of the CTA's token
+// rows and of all 64 router rows travel global -> shared by 16-byte asynchronous copies through a ring of RT_STAGES
+// buffers (rows keep their [row][k] layout, pitch 36 floats: nothing is transposed and 128-bit loads of 16 different
+// rows are conflict-free); the multiply loop reads four k-values per load.  With TPT = 4 a warp spends 16 wavefronts
+// (4 loads of router rows, 4 of token rows shared by half a warp) on 64 FMA instructions: the ratio at which the FMA
+// pipes rather than shared memory set the pace.  One CTA barrier per tile.
+#define RT_KT     32
+#define RT_PITCH  36
+#ifndef RT_STAGES
+#define RT_STAGES 6
 #endif
-// (c0, c1) = (a0 * b0 + c0, a1 * b1 + c1), each an IEEE fma, in one fma.rn.f32x2
-__device__ __forceinline__ void pf_ffma2(float a0, float a1, float b0, float b1, float & c0, float & c1) {
-    unsigned long long ra, rb, rc;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a0), "f"(a1));
-    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b0), "f"(b1));
-    asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c0), "f"(c1));
-    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(rc) : "l"(ra), "l"(rb));
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(c0), "=f"(c1) : "l"(rc));
+#ifndef RT_L_TPT
+#define RT_L_TPT 4          // long form: 4 warps, 32 tokens per CTA (measured on B200 at 4096 tokens: 66 us; 8 warps x 2 tokens 74 us,
+#define RT_L_NW  4          // 8 warps x 4 tokens 94 us, 4 warps x 2 tokens 76 us; the k loop of one CTA is the critical path)
+#endif
+#ifndef RT_S_TPT
+#define RT_S_TPT 2          // short form (a chunk share of expert-parallel prefill): 4 warps, 16 tokens per CTA (55 us up to 2048 tokens)
+#define RT_S_NW  4
+#endif
+__device__ __forceinline__ void rt_cp16(float * dst, const float * src, bool live) {
+    const unsigned d = (unsigned) __cvta_generic_to_shared(dst);
+    const int n = live ? 16 : 0;                          // 0: the 16 bytes are zero-filled, nothing is read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(d), "l"(src), "r"(n) : "memory");
 }
-__global__ void __launch_bounds__(256) k_pf_router(const float * __restrict__ H, int m, const float * __restrict__ Wr,
-                                                   const float * __restrict__ bias, const float * __restrict__ inv,
-                                                   float * __restrict__ sel, float * __restrict__ sig) {
-    __shared__ __align__(16) float sH[LKB_RT_K][34];      // [k][token]
-    __shared__ __align__(16) float sW[LKB_RT_K][68];      // [k][expert]
-    const int tid = threadIdx.x;
-    const int te = tid & 15, tt = tid >> 4;               // experts 4te.., tokens 2tt..
-    const int t0 = blockIdx.x * 32;
-    float acc[2][4];
-#pragma unroll
-    for (int i = 0; i < 2; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
-    // The next k-tile travels global -> registers while the current one is multiplied out of shared memory:
-    // without the prefetch every one of the 2048 / LKB_RT_K tiles exposed a full global-memory round trip
-    // (112 us for 4096 tokens; 72 us with it, 68 us with the FMAs packed two per instruction.  A 4 x 4-outputs-per-thread variant with 128 threads measured 89 us:
-    // one warp per scheduler does not cover the shared-memory latency).
-    constexpr int NH = (32 * LKB_RT_K) / 256, NW = (64 * LKB_RT_K) / 256;
-    float rh[NH], rw[NW];
-    auto fetch = [&](int k0) {
-#pragma unroll
-        for (int q = 0; q < NH; ++q) {
-            const int i = tid + q * 256, r = i / LKB_RT_K, c = i % LKB_RT_K, tk = t0 + r;
-            rh[q] = (tk < m) ? H[(size_t) tk * LKB_HIDDEN + k0 + c] : 0.0f;
+template <int TPT, int NW>
+__global__ void __launch_bounds__(32 * NW) k_pf_router_pipe(const float * __restrict__ H, int m, const float * __restrict__ Wr,
+                                                        const float * __restrict__ bias, const float * __restrict__ inv,
+                                                        float * __restrict__ sel, float * __restrict__ sig) {
+    constexpr int TT = 2 * NW * TPT, ROWS = TT + LKB_N_EXPERTS, NTILES = LKB_HIDDEN / RT_KT;
+    extern __shared__ __align__(16) float rt_ring[];                   // [RT_STAGES][ROWS][RT_PITCH]
+    const int tid = threadIdx.x, te = tid & 15, tg = tid >> 4;
+    const int t0 = blockIdx.x * TT;
+    auto issue = [&](int tile) {
+        if (tile < NTILES) {
+            float * st = rt_ring + (size_t) (tile % RT_STAGES) * ROWS * RT_PITCH;
+            const int k0 = tile * RT_KT;
+            for (int ch = tid; ch < ROWS * 8; ch += 32 * NW) {
+                const int row = ch >> 3, part = (ch & 7) * 4;
+                if (row < TT) {
+                    const int tk = t0 + row;
+                    rt_cp16(st + row * RT_PITCH + part, H + (size_t) (tk < m ? tk : 0) * LKB_HIDDEN + k0 + part, tk < m);
+                } else {
+                    rt_cp16(st + row * RT_PITCH + part, Wr + (size_t) (row - TT) * LKB_HIDDEN + k0 + part, true);
+                }
+            }
         }
-#pragma unroll
-        for (int q = 0; q < NW; ++q) {
-            const int i = tid + q * 256, r = i / LKB_RT_K, c = i % LKB_RT_K;
-            rw[q] = Wr[(size_t) r * LKB_HIDDEN + k0 + c];
-        }
+        asm volatile("cp.async.commit_group;" ::: "memory");      // (an empty group keeps the count uniform)
     };
-    fetch(0);
-    for (int k0 = 0; k0 < LKB_HIDDEN; k0 += LKB_RT_K) {
+    float acc[TPT][4];
 #pragma unroll
-        for (int q = 0; q < NH; ++q) { const int i = tid + q * 256; sH[i % LKB_RT_K][i / LKB_RT_K] = rh[q]; }
+    for (int i = 0; i < TPT; ++i)
 #pragma unroll
-        for (int q = 0; q < NW; ++q) { const int i = tid + q * 256; sW[i % LKB_RT_K][i / LKB_RT_K] = rw[q]; }
-        __syncthreads();
-        if (k0 + LKB_RT_K < LKB_HIDDEN) fetch(k0 + LKB_RT_K);
-#pragma unroll 8
-        for (int c = 0; c < LKB_RT_K; ++c) {
-            const float2 h = *reinterpret_cast<const float2 *>(&sH[c][tt * 2]);
-            const float4 wv = *reinterpret_cast<const float4 *>(&sW[c][te * 4]);
-#if LKB_RT_FFMA2
-            // the same eight IEEE fused multiply-adds, two per instruction
-            pf_ffma2(h.x, h.x, wv.x, wv.y, acc[0][0], acc[0][1]); pf_ffma2(h.x, h.x, wv.z, wv.w, acc[0][2], acc[0][3]);
-            pf_ffma2(h.y, h.y, wv.x, wv.y, acc[1][0], acc[1][1]); pf_ffma2(h.y, h.y, wv.z, wv.w, acc[1][2], acc[1][3]);
-#else
-            acc[0][0] = fmaf(h.x, wv.x, acc[0][0]); acc[0][1] = fmaf(h.x, wv.y, acc[0][1]);
-            acc[0][2] = fmaf(h.x, wv.z, acc[0][2]); acc[0][3] = fmaf(h.x, wv.w, acc[0][3]);
-            acc[1][0] = fmaf(h.y, wv.x, acc[1][0]); acc[1][1] = fmaf(h.y, wv.y, acc[1][1]);
-            acc[1][2] = fmaf(h.y, wv.z, acc[1][2]); acc[1][3] = fmaf(h.y, wv.w, acc[1][3]);
-#endif
+        for (int q = 0; q < 4; ++q) acc[i][q] = 0.0f;
+#pragma unroll
+    for (int s = 0; s < RT_STAGES - 1; ++s) issue(s);
+    for (int tile = 0; tile < NTILES; ++tile) {
+        asm volatile("cp.async.wait_group %0;" :: "n"(RT_STAGES - 2) : "memory");
+        __syncthreads();                   // this tile has landed for everyone; the stage refilled below is no longer read
+        issue(tile + RT_STAGES - 1);
+        const float * st = rt_ring + (size_t) (tile % RT_STAGES) * ROWS * RT_PITCH;
+        const float * sh = st + (tg * TPT) * RT_PITCH, * sw = st + (TT + te) * RT_PITCH;
+#pragma unroll
+        for (int c = 0; c < RT_KT; c += 4) {
+            float4 w[4], h[TPT];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) w[q] = *reinterpret_cast<const float4 *>(sw + 16 * q * RT_PITCH + c);
+#pragma unroll
+            for (int i = 0; i < TPT; ++i) h[i] = *reinterpret_cast<const float4 *>(sh + i * RT_PITCH + c);
+            // k-major order: consecutive FMAs belong to different chains, so none waits for its predecessor
+#pragma unroll
+            for (int i = 0; i < TPT; ++i)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) acc[i][q] = fmaf(h[i].x, w[q].x, acc[i][q]);
+#pragma unroll
+            for (int i = 0; i < TPT; ++i)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) acc[i][q] = fmaf(h[i].y, w[q].y, acc[i][q]);
+#pragma unroll
+            for (int i = 0; i < TPT; ++i)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) acc[i][q] = fmaf(h[i].z, w[q].z, acc[i][q]);
+#pragma unroll
+            for (int i = 0; i < TPT; ++i)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) acc[i][q] = fmaf(h[i].w, w[q].w, acc[i][q]);
         }
-        __syncthreads();
     }
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int tk = t0 + tt * 2 + i;
+    for (int i = 0; i < TPT; ++i) {
+        const int tk = t0 + tg * TPT + i;
         if (tk >= m) continue;
-        float sg[4], sl[4];
+        const float iv = inv[tk];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float l = __fmul_rn(acc[i][j], inv[tk]);
+        for (int q = 0; q < 4; ++q) {
+            const int e = te + 16 * q;
+            const float l = __fmul_rn(acc[i][q], iv);
             const float gv = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-l)));
-            sg[j] = gv;
-            sl[j] = __fadd_rn(gv, bias[te * 4 + j]);
+            sig[(size_t) tk * 64 + e] = gv;
+            sel[(size_t) tk * 64 + e] = __fadd_rn(gv, bias[e]);
         }
-        *reinterpret_cast<float4 *>(sig + (size_t) tk * 64 + te * 4) = make_float4(sg[0], sg[1], sg[2], sg[3]);
-        *reinterpret_cast<float4 *>(sel + (size_t) tk * 64 + te * 4) = make_float4(sl[0], sl[1], sl[2], sl[3]);
     }
 }
-
-// The same logits for a short token range: 8 tokens per CTA (a warp per token, a lane per expert pair), so that a
-// chunk share of a few hundred tokens still fills the GPU -- the 32-token form gives a 512-token share 16 CTAs, and
-// its duration does not depend on the token count up to one CTA per SM (the k loop is its critical path).  Every (token, expert) sum is
-// the same ascending-k chain of fused multiply-adds: results are bit-identical to k_pf_router.
-#ifndef LKB_RT8_K
-#define LKB_RT8_K 32                 // k-tile of the 8-token form (64 measured slower: 50 us against 43 us at 512 tokens)
-#endif
-__global__ void __launch_bounds__(256) k_pf_router_t8(const float * __restrict__ H, int m, const float * __restrict__ Wr,
-                                                      const float * __restrict__ bias, const float * __restrict__ inv,
-                                                      float * __restrict__ sel, float * __restrict__ sig) {
-    __shared__ __align__(16) float sH[LKB_RT8_K][8];      // [k][token]
-    __shared__ __align__(16) float sW[LKB_RT8_K][66];     // [k][expert]
-    const int tid = threadIdx.x, lane = tid & 31, tt = tid >> 5;
-    const int t0 = blockIdx.x * 8;
-    float acc0 = 0.0f, acc1 = 0.0f;
-    constexpr int NH = (8 * LKB_RT8_K) / 256, NW = (64 * LKB_RT8_K) / 256;
-    float rh[NH], rw[NW];
-    auto fetch = [&](int k0) {
-#pragma unroll
-        for (int q = 0; q < NH; ++q) {
-            const int i = tid + q * 256, tk = t0 + i / LKB_RT8_K;
-            rh[q] = (tk < m) ? H[(size_t) tk * LKB_HIDDEN + k0 + i % LKB_RT8_K] : 0.0f;
-        }
-#pragma unroll
-        for (int q = 0; q < NW; ++q) {
-            const int i = tid + q * 256;
-            rw[q] = Wr[(size_t) (i / LKB_RT8_K) * LKB_HIDDEN + k0 + i % LKB_RT8_K];
-        }
-    };
-    fetch(0);
-    for (int k0 = 0; k0 < LKB_HIDDEN; k0 += LKB_RT8_K) {
-#pragma unroll
-        for (int q = 0; q < NH; ++q) { const int i = tid + q * 256; sH[i % LKB_RT8_K][i / LKB_RT8_K] = rh[q]; }
-#pragma unroll
-        for (int q = 0; q < NW; ++q) { const int i = tid + q * 256; sW[i % LKB_RT8_K][i / LKB_RT8_K] = rw[q]; }
-        __syncthreads();
-        if (k0 + LKB_RT8_K < LKB_HIDDEN) fetch(k0 + LKB_RT8_K);
-#pragma unroll 8
-        for (int c = 0; c < LKB_RT8_K; ++c) {
-            const float h = sH[c][tt];
-            const float2 wv = *reinterpret_cast<const float2 *>(&sW[c][lane * 2]);
-#if LKB_RT_FFMA2
-            pf_ffma2(h, h, wv.x, wv.y, acc0, acc1);
-#else
-            acc0 = fmaf(h, wv.x, acc0);
-            acc1 = fmaf(h, wv.y, acc1);
-#endif
-        }
-        __syncthreads();
+template <int TPT, int NW>
+static int rt_launch(const float * H, int m, const float * Wr, const float * bias, const float * inv, float * sel, float * sig,
+                     cudaStream_t st) {
+    constexpr int TT = 2 * NW * TPT;
+    constexpr size_t smem = (size_t) RT_STAGES * (TT + LKB_N_EXPERTS) * RT_PITCH * sizeof(float);
+    static int ready[LKB_STATIC_MAX_DEVICES] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < LKB_STATIC_MAX_DEVICES && !ready[dev]) {
+        if (cudaFuncSetAttribute(k_pf_router_pipe<TPT, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess) return -(int) cudaGetLastError();
+        ready[dev] = 1;
     }
-    const int tk = t0 + tt;
-    if (tk >= m) return;
-    const float l0 = __fmul_rn(acc0, inv[tk]), l1 = __fmul_rn(acc1, inv[tk]);
-    const float g0 = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-l0))), g1 = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-l1)));
-    *reinterpret_cast<float2 *>(sig + (size_t) tk * 64 + lane * 2) = make_float2(g0, g1);
-    *reinterpret_cast<float2 *>(sel + (size_t) tk * 64 + lane * 2) =
-        make_float2(__fadd_rn(g0, bias[lane * 2]), __fadd_rn(g1, bias[lane * 2 + 1]));
+    k_pf_router_pipe<TPT, NW><<<(m + TT - 1) / TT, 32 * NW, smem, st>>>(H, m, Wr, bias, inv, sel, sig);
+    return lkb_check_launch();
 }
 
 // Top-4 of 64 per token: warps stride over the tokens (any grid); the selection itself is the redux-based
@@ -721,12 +695,10 @@ int lkb_pf_router_tiled(const float * H, int m, const float * Wr, const float * 
     LKB_REQUIRE_INIT();
     if (!H || !Wr || !bias || !inv || !sel || !sig) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    // at most one 8-token CTA per SM: the 8-token form (same arithmetic; measured on B200 43 us against 71 us up to
-    // 1024 tokens, 75 against 71 at 2048, 147 against 71 at 4096)
-    static const int form = [] { const char * e = getenv("LKB_ROUTER_FORM"); return e ? atoi(e) : 0; }();   // 8 / 32 force a form (tuning)
-    if (form == 8 || (form != 32 && (m + 7) / 8 <= lkb_context().sm_count)) k_pf_router_t8<<<(m + 7) / 8, 256, 0, (cudaStream_t) st>>>(H, m, Wr, bias, inv, sel, sig);
-    else k_pf_router<<<(m + 31) / 32, 256, 0, (cudaStream_t) st>>>(H, m, Wr, bias, inv, sel, sig);
-    return lkb_check_launch();
+    // short token ranges (a chunk share of expert-parallel prefill) run 16 tokens per CTA so that more SMs take part
+    static const int form = [] { const char * e = getenv("LKB_ROUTER_FORM"); return e ? atoi(e) : 0; }();   // 16 / 32 force a form (tuning)
+    if (form == 16 || (form != 32 && m <= 16 * lkb_context().sm_count)) return rt_launch<RT_S_TPT, RT_S_NW>(H, m, Wr, bias, inv, sel, sig, (cudaStream_t) st);
+    return rt_launch<RT_L_TPT, RT_L_NW>(H, m, Wr, bias, inv, sel, sig, (cudaStream_t) st);
 }
 
 int lkb_pf_router(const float * H, int m, const float * Wr, const float * bias, const float * inv,

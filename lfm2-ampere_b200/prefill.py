@@ -132,7 +132,7 @@ class PrefillStackEP:
         self.dispatch = dispatch
         self.rank, self.world, self.group = rank, world, group
         # this library's kernels per layer (memsets, the torch division and NCCL's own kernels not counted)
-        self.launches_per_step = (20 if dispatch == "peer" else 16) * len(layers)
+        self.launches_per_step = (14 if dispatch == "peer" else 16) * len(layers)
         self.layers = layers
         self.shards = [shard_layer(l, rank, world) for l in layers]
         self.m = m_total // world
@@ -237,12 +237,8 @@ class PrefillStackEP:
         return int(self.ep_status.item()) if hasattr(self, "ep_status") else 0
 
     def _experts_dev(self, li):
-        """_experts with the received-row count left on the device (peer dispatch)."""
-        sh, n_dev, cap = self.shards[li], self.ep_offs[3 * self.world:], self.cap
-        api.zero_i32(self.cnt, E)
-        api.k_pf_moe_count_dev(self.r_le, cap, n_dev, self.cnt)
-        api.k_pf_moe_plan(self.cnt, self.off, self.tiles, self.ntiles)
-        api.k_pf_moe_scatter_dev(self.r_le, cap, n_dev, self.off, self.perm)
+        """The two grouped GEMMs over the received rows; the plan (tiles, perm) is already on the device."""
+        sh = self.shards[li]
         g = api.make_pf_gemm([(sh.gate_qs, sh.gate_d), (sh.up_qs, sh.up_d)], [I, I, I], I, H // 32, self.r_qs, self.r_sc,
                              exp_stride=I * (H // 32), perm=self.perm, tiles=self.tiles, ntiles=self.ntiles,
                              a_shift=0, scale=self.r_inv, oqs=self.a2_qs, osc=self.a2_sc, okb=I // 32)
@@ -253,18 +249,18 @@ class PrefillStackEP:
         _timed(self, api.pf_gemm_moe, dn, self.max_tiles)
 
     def _exchange_peer(self, i):
-        """counts -> rows to their owners -> experts -> D rows home, all on the stream."""
+        """route + counts -> rows to their owners -> plan + experts -> D rows home, all on the stream: 9 launches."""
         G, ns, per, me = self.world, self.m * TOPK, E // self.world, self.rank
         ep = self.ep_epoch
-        api.ep_counts_exchange(self.dcnt, self.peers, me, G, ep, self.ep_offs, self.ep_status)
+        api.ep_route_exchange(self.idx, ns, per, self.peers, me, G, ep, self.send_order, self.doff, self.ep_offs, self.ep_status)
         api.ep_pack_push(self.a, self.inv, self.idx, self.send_order, self.doff, self.ep_offs, ns, per, self.peers, me, G, ep,
                          self.pos, self.ep_done[0:])
-        api.ep_wait(self.flags, 1, G, ep, self.ep_status)
+        api.ep_route_experts(self.recv_buf, self.cap, self.flags, G, ep, self.ep_offs, self.cnt, self.off, self.tiles, self.ntiles,
+                             self.perm, self.nrecv[i:i + 1], self.ep_status)
         api.ep_unpack_rows_dev(self.recv_buf, self.cap, self.ep_offs[3 * G:], self.r_act, self.r_inv, self.r_le)
         self._experts_dev(i)
         api.ep_push_back(self.D, self.ep_offs, self.cap, self.peers, me, G, ep, self.ep_done[1:])
         api.ep_wait(self.flags, 2, G, ep, self.ep_status)
-        self.nrecv[i:i + 1].copy_(self.ep_offs[3 * G:3 * G + 1])
 
     def _experts(self, li, n):
         """count / plan / scatter + the two grouped GEMMs over the n slots received for this rank's experts."""
@@ -297,6 +293,11 @@ class PrefillStackEP:
         router = api.k_pf_router_small if self.m_total <= 256 else api.k_pf_router_tiled
         router(self.h32, m, l.router, l.rbias, self.inv, self.sel, self.sig)
         api.k_pf_select(self.sel, self.sig, m, self.idx, self.w)
+        nxt = self.layers[(i + 1) % len(self.layers)]
+        if self.dispatch == "peer":
+            self._exchange_peer(i)
+            api.k_pf_moe_combine_norm_gather(self.X, self.d_back, self.pos, self.w, nxt.norm_w, self.an, self.n_inv, m)
+            return
         # slots grouped by destination rank, ascending slot order inside a destination: the same stable
         # count / plan / scatter kernels, keyed by owner rank instead of expert
         torch.div(self.idx.view(-1), per, rounding_mode="floor", out=self.dest)
@@ -304,11 +305,6 @@ class PrefillStackEP:
         api.k_pf_moe_count(self.dest, ns, self.dcnt)
         api.k_pf_moe_plan(self.dcnt, self.doff, self.dtiles, self.dnt)
         api.k_pf_moe_scatter(self.dest, ns, self.doff, self.send_order)
-        nxt = self.layers[(i + 1) % len(self.layers)]
-        if self.dispatch == "peer":
-            self._exchange_peer(i)
-            api.k_pf_moe_combine_norm_gather(self.X, self.d_back, self.pos, self.w, nxt.norm_w, self.an, self.n_inv, m)
-            return
         self.counts[0].copy_(self.dcnt[:G])
         dist.all_to_all_single(self.counts[1], self.counts[0], group=self.group)
         api.ep_pack_rows(self.a, self.inv, self.idx, self.send_order, ns, per, self.send_buf, self.pos)
