@@ -464,7 +464,16 @@ int lkb_ep_route_exchange(const int * idx, int n, int experts_per_rank, const lk
  * _scatter_dev keyed by the local expert id each received row carries) in ONE launch.  nrecv_out (optional) receives
  * the row count.  When the wait gives up, *ntiles = 0 and the status word holds the code. */
 int lkb_ep_route_experts(const void * recv, int cap, const int * flags, int G, const int * epoch, const int * offs, int * cnt, int * off,
-                         int * tiles, int * ntiles, int * perm, int * nrecv_out, int * status, lkb_stream_t st);
+                         int * tiles, int * ntiles, int * perm, int * nrecv_out, const lkb_ep_peers * peers, float ** home_rows,
+                         int * status, lkb_stream_t st);
+/* No counterpart in the reference.  home_rows (optional, with peers) of lkb_ep_route_experts receives, per received
+ * row, the address its result row has in its home rank's return buffer; lkb_pf_gemm_moe_rows is lkb_pf_gemm_moe
+ * writing the output row of slot s to out_rows[s] instead of out + s * out_ld (plain stores, peer memory included;
+ * add must be 0; tensor-core form only, else LKB_ERR_UNSUPPORTED), so the down projection's rows travel home while
+ * the GEMM still computes; lkb_ep_publish then announces `phase` of the epoch to every rank (the role of the flag
+ * store at the end of lkb_ep_push_back, which this pair replaces). */
+int lkb_pf_gemm_moe_rows(const lkb_pf_gemm * g, int max_tiles, float * const * out_rows, lkb_stream_t st);
+int lkb_ep_publish(const lkb_ep_peers * peers, int me, int G, int phase, const int * epoch, lkb_stream_t st);
 int lkb_ep_push_back(const float * D, const int * offs, int max_rows, const lkb_ep_peers * peers, int me, int G,
                      const int * epoch, unsigned * done, lkb_stream_t st);
 /* No counterpart in the reference: the unpack / count / scatter kernels with the live row count on the device. */

@@ -95,26 +95,32 @@ __global__ void __launch_bounds__(64) k_ep_counts_exchange(const int * __restric
 }
 
 // Row p of my send order (slot send_order[p], destination rank = its expert's owner) -> the owner's receive buffer.
-// doff[g] = first position of destination g in my send order.  The last CTA to finish publishes the rows.
-__global__ void __launch_bounds__(192) k_ep_pack_push(const int8_t * __restrict__ aqs, const float2 * __restrict__ asc,
+// doff[g] = first position of destination g in my send order.  A warp per row, rows walked with a grid stride by a grid
+// of a few CTAs per SM, ONE system-scope fence per CTA at the end (a fence per row made the kernel wait for the NVLink
+// round trip 2048 times); the last CTA to finish publishes the rows.
+__global__ void __launch_bounds__(256) k_ep_pack_push(const int8_t * __restrict__ aqs, const float2 * __restrict__ asc,
                                                       const float * __restrict__ inv, const int * __restrict__ idx,
                                                       const int * __restrict__ send_order, const int * __restrict__ doff,
-                                                      const int * __restrict__ offs, int experts_per_rank, EpPeers P, int me, int G,
+                                                      const int * __restrict__ offs, int n, int experts_per_rank, EpPeers P, int me, int G,
                                                       const int * __restrict__ epoch_dev, int * __restrict__ pos,
                                                       unsigned * __restrict__ done) {
-    const int p = blockIdx.x, i = threadIdx.x;
-    const int slot = send_order[p], t = slot >> 2;
-    const int e = idx[slot], dest = e / experts_per_rank;
-    uint4 * row = reinterpret_cast<uint4 *>(P.recv[dest] + (size_t) (offs[dest] + p - doff[dest]) * EP_ROW_BYTES);
-    if (i < 128) row[i] = reinterpret_cast<const uint4 *>(aqs + (size_t) t * LKB_HIDDEN)[i];
-    else if (i < 160) row[i] = reinterpret_cast<const uint4 *>(asc + (size_t) t * (LKB_HIDDEN / 32))[i - 128];
-    else if (i == 160) {
-        row[160] = make_uint4(__float_as_uint(inv[t]), (unsigned) (e % experts_per_rank), 0u, 0u);
-        pos[slot] = p;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int p = blockIdx.x * 8 + warp; p < n; p += gridDim.x * 8) {
+        const int slot = send_order[p], t = slot >> 2;
+        const int e = idx[slot], dest = e / experts_per_rank;
+        uint4 * row = reinterpret_cast<uint4 *>(P.recv[dest] + (size_t) (offs[dest] + p - doff[dest]) * EP_ROW_BYTES);
+        const uint4 * q = reinterpret_cast<const uint4 *>(aqs + (size_t) t * LKB_HIDDEN);
+        const uint4 * sc = reinterpret_cast<const uint4 *>(asc + (size_t) t * (LKB_HIDDEN / 32));
+        const uint4 v0 = q[lane], v1 = q[lane + 32], v2 = q[lane + 64], v3 = q[lane + 96], v4 = sc[lane];
+        row[lane] = v0; row[lane + 32] = v1; row[lane + 64] = v2; row[lane + 96] = v3; row[lane + 128] = v4;
+        if (lane == 0) {
+            row[160] = make_uint4(__float_as_uint(inv[t]), (unsigned) (e % experts_per_rank), 0u, 0u);
+            pos[slot] = p;
+        }
     }
     __threadfence_system();
     __syncthreads();
-    if (i == 0 && atomicAdd(done, 1u) == gridDim.x - 1) {
+    if (threadIdx.x == 0 && atomicAdd(done, 1u) == gridDim.x - 1) {
         *done = 0u;
         __threadfence_system();
         const int epoch = *epoch_dev;
@@ -253,6 +259,7 @@ __global__ void __launch_bounds__(1024) k_ep_route_experts(const unsigned char *
                                                            const int * __restrict__ epoch_dev, const int * __restrict__ offs,
                                                            int * __restrict__ cnt, int * __restrict__ off, int4 * __restrict__ tiles,
                                                            int * __restrict__ ntiles, int * __restrict__ perm, int * __restrict__ nrecv_out,
+                                                           EpPeers P, float ** __restrict__ home_rows,
                                                            int * __restrict__ status, unsigned long long limit_ns) {
     __shared__ EpRouteSmem R;
     const int t = threadIdx.x;
@@ -265,6 +272,21 @@ __global__ void __launch_bounds__(1024) k_ep_route_experts(const unsigned char *
     ep_route_cta(R, [&](int s) { return (int) __ldcg(reinterpret_cast<const unsigned *>(recv + (size_t) s * EP_ROW_BYTES) + 641); },
                  n, cnt, off, tiles, ntiles, perm);
     if (t == 0 && nrecv_out) *nrecv_out = n;
+    // where each received row's result goes home to: row (back_base[s] + j) of source s's return buffer (its send order)
+    if (home_rows) {
+        for (int r = t; r < n; r += 1024) {
+            int s = 0;
+            while (s + 1 < G && r >= offs[G + s + 1]) ++s;
+            home_rows[r] = P.dback[s] + (size_t) (offs[2 * G + s] + (r - offs[G + s])) * LKB_HIDDEN;
+        }
+    }
+}
+
+// Publish `phase` of this epoch to every rank: the stores of the kernels before this one on the stream (the grouped
+// GEMM writing result rows straight into their home ranks' buffers) are complete when this kernel starts.
+__global__ void __launch_bounds__(32) k_ep_publish(EpPeers P, int me, int G, int phase, const int * __restrict__ epoch_dev) {
+    __threadfence_system();
+    if ((int) threadIdx.x < G) ep_st_release(P.flags[threadIdx.x] + phase * EP_MAX_RANKS + me, *epoch_dev);
 }
 
 static int ep_peers(EpPeers & P, const void * const * cmat, const void * const * flags, const void * const * recv,
@@ -313,12 +335,31 @@ int lkb_ep_route_exchange(const int * idx, int n, int experts_per_rank, const lk
 }
 
 int lkb_ep_route_experts(const void * recv, int cap, const int * flags, int G, const int * epoch, const int * offs, int * cnt, int * off,
-                         int * tiles, int * ntiles, int * perm, int * nrecv_out, int * status, lkb_stream_t st) {
+                         int * tiles, int * ntiles, int * perm, int * nrecv_out, const lkb_ep_peers * peers, float ** home_rows,
+                         int * status, lkb_stream_t st) {
     if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
     if (!recv || !flags || !epoch || !offs || !cnt || !off || !tiles || !ntiles || !perm || !status) return LKB_ERR_NULL;
     if (cap <= 0 || G < 1 || G > EP_MAX_RANKS) return LKB_ERR_SHAPE;
+    EpPeers P = {};
+    if (home_rows) {
+        if (!peers) return LKB_ERR_NULL;
+        const int r = ep_peers(P, peers->cmat, peers->flags, peers->recv, peers->dback, G);
+        if (r != LKB_OK) return r;
+    }
     k_ep_route_experts<<<1, 1024, 0, (cudaStream_t) st>>>(reinterpret_cast<const unsigned char *>(recv), cap, flags, G, epoch, offs, cnt, off,
-                                                          reinterpret_cast<int4 *>(tiles), ntiles, perm, nrecv_out, status, g_ep_limit_ns);
+                                                          reinterpret_cast<int4 *>(tiles), ntiles, perm, nrecv_out, P, home_rows, status,
+                                                          g_ep_limit_ns);
+    return lkb_check_launch();
+}
+
+int lkb_ep_publish(const lkb_ep_peers * peers, int me, int G, int phase, const int * epoch, lkb_stream_t st) {
+    if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
+    if (!peers || !epoch) return LKB_ERR_NULL;
+    EpPeers P = {};
+    const int r = ep_peers(P, peers->cmat, peers->flags, peers->recv, peers->dback, G);
+    if (r != LKB_OK) return r;
+    if (me < 0 || me >= G || phase < 0 || phase > 2) return LKB_ERR_SHAPE;
+    k_ep_publish<<<1, 32, 0, (cudaStream_t) st>>>(P, me, G, phase, epoch);
     return lkb_check_launch();
 }
 
@@ -331,8 +372,10 @@ int lkb_ep_pack_push(lkb_pf_act a, const float * inv, const int * idx, const int
     const int r = ep_peers(P, peers->cmat, peers->flags, peers->recv, peers->dback, G);
     if (r != LKB_OK) return r;
     if (n <= 0 || experts_per_rank <= 0 || me < 0 || me >= G) return LKB_ERR_SHAPE;
-    k_ep_pack_push<<<n, 192, 0, (cudaStream_t) st>>>(reinterpret_cast<const int8_t *>(a.qs), reinterpret_cast<const float2 *>(a.sc), inv,
-                                                     idx, send_order, doff, offs, experts_per_rank, P, me, G, epoch, pos, done);
+    int grid = lkb_context().sm_count * 4;
+    if (grid > (n + 7) / 8) grid = (n + 7) / 8;
+    k_ep_pack_push<<<grid, 256, 0, (cudaStream_t) st>>>(reinterpret_cast<const int8_t *>(a.qs), reinterpret_cast<const float2 *>(a.sc), inv,
+                                                        idx, send_order, doff, offs, n, experts_per_rank, P, me, G, epoch, pos, done);
     return lkb_check_launch();
 }
 

@@ -277,7 +277,8 @@ __global__ void __launch_bounds__(TcCfg<EPI>::THREADS, 1) k_pf_gemm_tc(const lkb
                                                               const __grid_constant__ CUtensorMap map_s,
                                                               const __grid_constant__ CUtensorMap map_w0,
                                                               const __grid_constant__ CUtensorMap map_w1,
-                                                              const __grid_constant__ CUtensorMap map_w2) {
+                                                              const __grid_constant__ CUtensorMap map_w2,
+                                                              float * const * __restrict__ out_rows) {
     extern __shared__ unsigned char tc_smem_raw[];
     // the swizzle patterns are functions of the shared-memory address: stages start on 1024-byte boundaries
     typedef TcSmem<EPI> Smem;
@@ -369,6 +370,10 @@ __global__ void __launch_bounds__(TcCfg<EPI>::THREADS, 1) k_pf_gemm_tc(const lkb
             int slot_l = -1;
             if (tokl < tcnt) slot_l = g.perm ? g.perm[tstart + tokl] : tstart + tokl;
             const float scl_l = (slot_l >= 0 && g.scale) ? g.scale[slot_l >> g.a_shift] : 1.0f;
+            // where the slot's output row starts: the caller's matrix, or a row address of its own (the expert-parallel
+            // form: the row goes straight into its home rank's buffer, a peer's memory included -- plain stores)
+            unsigned long long rowp_l = 0ull;
+            if (slot_l >= 0) rowp_l = (unsigned long long) (EPI == 0 && out_rows ? out_rows[slot_l] : g.out + (size_t) slot_l * g.out_ld);
             if (!tc_wait<TC_HINT_PROD>(S, &S.tailfull, k & 1u, 40u)) break;
 #ifdef TC_ABL_TAILSKIP
             const int nrows = 0;
@@ -377,11 +382,12 @@ __global__ void __launch_bounds__(TcCfg<EPI>::THREADS, 1) k_pf_gemm_tc(const lkb
 #endif
             // four rows per iteration: their dependent chains (shuffles, divisions) interleave
             for (int i0 = 0; i0 < nrows; i0 += 4) {
-                int slot[4]; float scl[4];
+                int slot[4]; float scl[4]; unsigned long long rowp[4];
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     slot[u] = __shfl_sync(LKB_FULL, slot_l, (i0 + u) & 31);
                     scl[u] = __shfl_sync(LKB_FULL, scl_l, (i0 + u) & 31);
+                    rowp[u] = __shfl_sync(LKB_FULL, rowp_l, (i0 + u) & 31);
                     if (i0 + u >= nrows) slot[u] = -1;
                 }
                 {
@@ -390,7 +396,7 @@ __global__ void __launch_bounds__(TcCfg<EPI>::THREADS, 1) k_pf_gemm_tc(const lkb
                         if (slot[u] < 0) continue;
                         const int t = 32 * tw + i0 + u;
                         const float4 a = S.tile_out[lane * TC_OUT_PITCH + t];
-                        float4 * p = reinterpret_cast<float4 *>(g.out + (size_t) slot[u] * g.out_ld + rt * TC_N) + lane;
+                        float4 * p = reinterpret_cast<float4 *>(reinterpret_cast<float *>(rowp[u]) + rt * TC_N) + lane;
                         float4 o;
                         if (g.add) {
                             // the residual add as the reference's build evaluates it: one fused multiply-add
@@ -796,7 +802,8 @@ static int tc_make_map(CUtensorMap * m, const void * base, unsigned row_bytes, u
 // Shapes the tensor-core form covers; otherwise LKB_ERR_UNSUPPORTED (the caller falls back
 // to the CUDA-core form): out_ld / okb rows must allow 16-byte vector stores, the planes the
 // alignment the copy engine asks for.
-int lkb_gemm_tc_launch(const lkb_pf_gemm * g, int epi, int fold, int max_tiles, cudaStream_t st) {
+int lkb_gemm_tc_launch(const lkb_pf_gemm * g, int epi, int fold, int max_tiles, cudaStream_t st, float * const * out_rows) {
+    if (out_rows && (epi || !g->perm || g->add)) return LKB_ERR_SHAPE;          // row targets: the plain grouped form, no residual add
     if (!g_tc_ready) return LKB_ERR_NOT_INIT;
     if (g->bpr % TC_KB) return LKB_ERR_UNSUPPORTED;
     if (epi) { if (g->N % 64 || (g->okb * 32) % 16) return LKB_ERR_UNSUPPORTED; }
@@ -843,10 +850,10 @@ int lkb_gemm_tc_launch(const lkb_pf_gemm * g, int epi, int fold, int max_tiles, 
     const int rpe = (int) (g->exp_stride / g->bpr);
     const int grid = lkb_context().sm_count;
     const size_t sm0 = sizeof(TcSmem<0>) + 1024, sm1 = sizeof(TcSmem<1>) + 1024;
-    if (epi && fold)       k_pf_gemm_tc<1, 1><<<grid, TcCfg<1>::THREADS, sm1, st>>>(*g, max_tiles, rpe, tiled, ma, ms, mw[0], mw[1], mw[2]);
-    else if (epi)          k_pf_gemm_tc<1, 0><<<grid, TcCfg<1>::THREADS, sm1, st>>>(*g, max_tiles, rpe, tiled, ma, ms, mw[0], mw[1], mw[2]);
-    else if (fold)         k_pf_gemm_tc<0, 1><<<grid, TcCfg<0>::THREADS, sm0, st>>>(*g, max_tiles, rpe, tiled, ma, ms, mw[0], mw[1], mw[2]);
-    else                   k_pf_gemm_tc<0, 0><<<grid, TcCfg<0>::THREADS, sm0, st>>>(*g, max_tiles, rpe, tiled, ma, ms, mw[0], mw[1], mw[2]);
+    if (epi && fold)       k_pf_gemm_tc<1, 1><<<grid, TcCfg<1>::THREADS, sm1, st>>>(*g, max_tiles, rpe, tiled, ma, ms, mw[0], mw[1], mw[2], out_rows);
+    else if (epi)          k_pf_gemm_tc<1, 0><<<grid, TcCfg<1>::THREADS, sm1, st>>>(*g, max_tiles, rpe, tiled, ma, ms, mw[0], mw[1], mw[2], out_rows);
+    else if (fold)         k_pf_gemm_tc<0, 1><<<grid, TcCfg<0>::THREADS, sm0, st>>>(*g, max_tiles, rpe, tiled, ma, ms, mw[0], mw[1], mw[2], out_rows);
+    else                   k_pf_gemm_tc<0, 0><<<grid, TcCfg<0>::THREADS, sm0, st>>>(*g, max_tiles, rpe, tiled, ma, ms, mw[0], mw[1], mw[2], out_rows);
     return lkb_check_launch();
 }
 

@@ -225,6 +225,7 @@ class PrefillStackEP:
         self.ep_done = torch.zeros(2, **i32)
         self.nrecv = torch.zeros(max(1, len(self.layers)), **i32)
         self.ep_epoch = torch.zeros(1, **i32)                      # advanced on the device, once per layer
+        self.home_rows = torch.zeros(self.cap, dtype=torch.int64, device=dev)      # per received row: address of its result row at home
 
     def prepare(self):
         """Allocate the exchange buffers now (peer dispatch: the symmetric-memory rendezvous, a collective) instead
@@ -246,7 +247,8 @@ class PrefillStackEP:
         dn = api.make_pf_gemm([(sh.down_qs, sh.down_d)], [H, H, H], H, I // 32, self.a2_qs, self.a2_sc,
                               exp_stride=H * (I // 32), perm=self.perm, tiles=self.tiles, ntiles=self.ntiles,
                               a_shift=0, out=self.D, out_ld=H)
-        _timed(self, api.pf_gemm_moe, dn, self.max_tiles)
+        # result rows go straight into their home ranks' return buffers (NVLink stores from the GEMM's tail warps)
+        _timed(self, api.pf_gemm_moe_rows, dn, self.max_tiles, self.home_rows)
 
     def _exchange_peer(self, i):
         """route + counts -> rows to their owners -> plan + experts -> D rows home, all on the stream: 9 launches."""
@@ -256,10 +258,10 @@ class PrefillStackEP:
         api.ep_pack_push(self.a, self.inv, self.idx, self.send_order, self.doff, self.ep_offs, ns, per, self.peers, me, G, ep,
                          self.pos, self.ep_done[0:])
         api.ep_route_experts(self.recv_buf, self.cap, self.flags, G, ep, self.ep_offs, self.cnt, self.off, self.tiles, self.ntiles,
-                             self.perm, self.nrecv[i:i + 1], self.ep_status)
+                             self.perm, self.nrecv[i:i + 1], self.ep_status, self.peers, self.home_rows)
         api.ep_unpack_rows_dev(self.recv_buf, self.cap, self.ep_offs[3 * G:], self.r_act, self.r_inv, self.r_le)
         self._experts_dev(i)
-        api.ep_push_back(self.D, self.ep_offs, self.cap, self.peers, me, G, ep, self.ep_done[1:])
+        api.ep_publish(self.peers, me, G, 2, ep)
         api.ep_wait(self.flags, 2, G, ep, self.ep_status)
 
     def _experts(self, li, n):
