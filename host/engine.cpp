@@ -137,7 +137,7 @@ void build(Engine & e, int max_seq, int pf_cap) {
         m.is_attn = p.has(b + "attn_q.qs");
         m.attn_norm = p.f32(b + "attn_norm");
         lkb_mixer_layer d{};
-        d.is_attn = m.is_attn; d.attn_norm = m.attn_norm;
+        d.is_attn = m.is_attn; d.attn_norm = m.attn_norm; d.max_seq = max_seq;
         if (m.is_attn) {
             m.wq = q4(p, b + "attn_q"); m.wk = q4(p, b + "attn_k"); m.wv = q4(p, b + "attn_v"); m.out = q4(p, b + "attn_output");
             m.qnorm = p.f32(b + "attn_q_norm"); m.knorm = p.f32(b + "attn_k_norm");

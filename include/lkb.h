@@ -183,7 +183,8 @@ typedef struct {
  * ref: src/engine.cu:136-145 (struct Layer) */
 typedef struct {
     int           is_attn;
-    int           reserved;
+    int           max_seq;                          /* attention: positions the KV cache holds; 0 = not checked.  A step at
+                                                     * *d_pos >= max_seq writes nothing and sets status 600 + layer */
     const float * attn_norm;                        /* fp32[2048], the norm in front of the mixer */
     const void *  in_qs;  const void * in_d;        /* conv: in_proj */
     const float * conv_w;                           /* conv: fp32[2048*3] */

@@ -50,7 +50,7 @@ class MoeScratch(C.Structure):
 
 class MixerLayer(C.Structure):
     """lkb_mixer_layer"""
-    _fields_ = [("is_attn", C.c_int), ("reserved", C.c_int), ("attn_norm", C.c_void_p),
+    _fields_ = [("is_attn", C.c_int), ("max_seq", C.c_int), ("attn_norm", C.c_void_p),
                 ("in_qs", C.c_void_p), ("in_d", C.c_void_p), ("conv_w", C.c_void_p), ("hist", C.c_void_p),
                 ("wq_qs", C.c_void_p), ("wq_d", C.c_void_p), ("wk_qs", C.c_void_p), ("wk_d", C.c_void_p),
                 ("wv_qs", C.c_void_p), ("wv_d", C.c_void_p), ("qnorm", C.c_void_p), ("knorm", C.c_void_p),

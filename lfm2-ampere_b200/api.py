@@ -344,10 +344,10 @@ def k_shortconv(bcx, conv_w, hist, y, yq8, n, t=0):
 
 
 # ------------------------------------------------------------ whole-step kernel --
-def mixer_layer_desc(mx, hist=None, kc=None, vc=None):
-    """lkb_mixer_layer from a model.Mixer plus this layer's state (conv history or KV cache)."""
+def mixer_layer_desc(mx, hist=None, kc=None, vc=None, max_seq=0):
+    """lkb_mixer_layer from a model.Mixer plus this layer's state (conv history, or KV cache and its capacity in positions)."""
     if mx.is_attn:
-        return MixerLayer(1, 0, ptr(mx.attn_norm), None, None, None, None, ptr(mx.wq[0]), ptr(mx.wq[1]), ptr(mx.wk[0]),
+        return MixerLayer(1, int(max_seq), ptr(mx.attn_norm), None, None, None, None, ptr(mx.wq[0]), ptr(mx.wq[1]), ptr(mx.wk[0]),
                           ptr(mx.wk[1]), ptr(mx.wv[0]), ptr(mx.wv[1]), ptr(mx.qnorm), ptr(mx.knorm), ptr(kc), ptr(vc),
                           ptr(mx.out_qs), ptr(mx.out_d))
     return MixerLayer(0, 0, ptr(mx.attn_norm), ptr(mx.in_qs), ptr(mx.in_d), ptr(mx.conv_w), ptr(hist), None, None, None,

@@ -205,11 +205,18 @@ __device__ __forceinline__ void load_xregs(const lkb_q8blk * xq, int bpr, int la
     }
 }
 
-// Optional phase timestamps (clock64 of thread 0) for tuning: [cta][layer][32].
+// Tuning builds only (-DLKB_TUNING; the default build has none of it): phase timestamps (clock64 of thread 0),
+// [cta][layer][32].
+#ifdef LKB_TUNING
 static unsigned long long * g_fused_timing = nullptr;
+#endif
 static int g_fused_absent_cta = -1;              // test hook, see lkb_debug_fused_absent_cta
 static unsigned g_fused_spin_limit = 0;          // 0: default
+#ifdef LKB_TUNING
 #define FUSED_STAMP(slot) do { if (a.timing && tid == 0 && l < 4) a.timing[((size_t) cta * 4 + l) * 32 + (slot)] = clock64(); } while (0)
+#else
+#define FUSED_STAMP(slot) do { } while (0)
+#endif
 
 
 // Four independent 32-element blocks quantised together: the same operations per block
@@ -400,6 +407,15 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
     }
     __syncthreads();
     if constexpr (MIX) {
+        // KV capacity: an attention layer whose descriptor states max_seq refuses a position past its cache.  Every CTA
+        // evaluates the same test before anything is in flight, so all leave together (status 600 + layer).
+        int over = -1;
+        for (int l = tid; l < a.n_layers; l += blockDim.x)
+            if (a.mixers[l].is_attn && a.mixers[l].max_seq > 0 && pos >= a.mixers[l].max_seq) over = l;
+        if (__syncthreads_or(over >= 0)) {
+            if (over >= 0) atomicCAS(status, 0u, 600u + (unsigned) over);
+            return;
+        }
         if (tid == 0) {
             mix_issue_in(S, S.mx, dn0, n_dn, qa0, qa1);
             if (!S.mx.is_attn) mix_issue_out(S, S.mx, dn0, n_dn);
@@ -832,7 +848,11 @@ static int fused_launch(FusedArgs & a, cudaStream_t st) {
         (LKB_HIDDEN + grid - 1) / grid > MAX_DN_ROWS) return LKB_ERR_DEVICE;
     cudaError_t e = cudaMemsetAsync(a.bar, 0, 2 * sizeof(unsigned), st);
     if (e != cudaSuccess) return -(int) e;
+#ifdef LKB_TUNING
     a.timing = g_fused_timing;
+#else
+    a.timing = nullptr;
+#endif
     a.absent_cta = g_fused_absent_cta;
     a.spin_limit = g_fused_spin_limit ? g_fused_spin_limit : SPIN_LIMIT;
     cudaLaunchConfig_t cfg = {};
@@ -848,8 +868,10 @@ static int fused_launch(FusedArgs & a, cudaStream_t st) {
 
 extern "C" {
 
+#ifdef LKB_TUNING
 // Tuning hook (not part of the public header): device buffer of [#CTAs][4 layers][32] clock64 stamps, or null.
 __attribute__((visibility("default"))) int lkb_debug_fused_timing(unsigned long long * buf) { g_fused_timing = buf; return LKB_OK; }
+#endif
 
 // Test hook (not in the public header): the next launches run WITHOUT CTA `cta` (it returns at once), so every
 // other CTA's first grid-barrier wait runs out after `spin_limit` polls and the kernel ends with a status code

@@ -375,11 +375,7 @@ __global__ void __launch_bounds__(TcCfg<EPI>::THREADS, 1) k_pf_gemm_tc(const lkb
             unsigned long long rowp_l = 0ull;
             if (slot_l >= 0) rowp_l = (unsigned long long) (EPI == 0 && out_rows ? out_rows[slot_l] : g.out + (size_t) slot_l * g.out_ld);
             if (!tc_wait<TC_HINT_PROD>(S, &S.tailfull, k & 1u, 40u)) break;
-#ifdef TC_ABL_TAILSKIP
-            const int nrows = 0;
-#else
             const int nrows = min(32, tcnt - 32 * tw);
-#endif
             // four rows per iteration: their dependent chains (shuffles, divisions) interleave
             for (int i0 = 0; i0 < nrows; i0 += 4) {
                 int slot[4]; float scl[4]; unsigned long long rowp[4];
@@ -521,7 +517,6 @@ __global__ void __launch_bounds__(TcCfg<EPI>::THREADS, 1) k_pf_gemm_tc(const lkb
                 if (!tc_wait<TC_HINT_PROD>(S, &S.rawfull[stg], (it / TC_NS) & 1u, 15u)) { ok = false; break; }
                 if (e == 0) TC_TL(1, it, 1);
                 TcStage & T = S.st[stg];
-#ifndef TC_ABL_NOEXP
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const int rr = e + 64 * h;                         // staged row
@@ -549,7 +544,6 @@ __global__ void __launch_bounds__(TcCfg<EPI>::THREADS, 1) k_pf_gemm_tc(const lkb
                         T.d4[j][r] = df[j];
                     }
                 }
-#endif
                 tc_fence_async();                                       // generic-proxy writes -> visible to the MMA
                 __syncwarp();
                 if (lane == 0) tc_mbar_arrive(&S.full[stg]);

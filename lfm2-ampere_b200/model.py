@@ -131,7 +131,7 @@ class DecodeStep:
             descs = []
             for mx in model.mixers:
                 if mx.is_attn:
-                    descs.append(api.mixer_layer_desc(mx, kc=self.kc[ai], vc=self.vc[ai]))
+                    descs.append(api.mixer_layer_desc(mx, kc=self.kc[ai], vc=self.vc[ai], max_seq=max_seq))
                     ai += 1
                 else:
                     descs.append(api.mixer_layer_desc(mx, hist=self.hist[ci]))
@@ -231,6 +231,8 @@ class PrefillChunk:
 
     def step(self, P=0):
         m, md, st, moe = self.m_, self.model, self.state, self.moe
+        if P < 0 or P + m > st.max_seq:
+            raise ValueError(f"chunk [{P}, {P + m}) does not fit the KV cache of {st.max_seq} positions")
         bpr = H // 32
         api.k_pf_embed(*md.emb, self.toks, self.X, H, m)
         norm_ready = False

@@ -192,3 +192,23 @@ def test_prefill_chunk_agrees_with_token_by_token_decode(M, lkb):
     torch.cuda.synchronize()
     assert int(st.d_pos.item()) == m + 1 and 0 <= int(st.d_token.item()) < 4096 and st.status() == 0
     lkb.pf_gemm_arith(1)
+
+
+def test_kv_capacity_is_checked(M, lkb):
+    """A decode step at a position past the KV cache writes nothing and reports it (status 600 + layer); a prefill chunk
+    that does not fit is refused on the host."""
+    model = M.make_full_model(n_layers=3, seed=2, vocab=2048)
+    ds = M.DecodeStep(model, max_seq=4, moe_impl="mega")
+    ds.d_pos.fill_(3)
+    ds.step()                                                      # position 3: the last one that fits
+    torch.cuda.synchronize()
+    assert ds.status() == 0 and int(ds.d_pos.item()) == 4
+    kc, vc = ds.kc.clone(), ds.vc.clone()
+    ds.step()                                                      # position 4: past the cache
+    torch.cuda.synchronize()
+    assert ds.status() == 602                                      # layer 2 is the attention layer
+    assert torch.equal(kc, ds.kc) and torch.equal(vc, ds.vc)
+    ds.sync.zero_()
+    pc = M.PrefillChunk(model, 8, M.DecodeStep(model, max_seq=8, moe_impl="mega"))
+    with pytest.raises(ValueError):
+        pc.step(P=1)
