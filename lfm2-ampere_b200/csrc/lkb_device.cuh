@@ -62,6 +62,27 @@ __device__ __forceinline__ void lkb_quant_store_planar(float xi, int8_t * __rest
     }
 }
 
+// The planar quantiser with the block sum in the order of the reference's FUSED SwiGLU epilogue, where a lane holds
+// rows g, g+8, g+16, g+24 of the block, adds (v0 + v1) + (v2 + v3) and then exchanges over g ^ 1, 2, 4: in row terms
+// the pairing order 8, 16, 1, 2, 4 (ref: src/prefill.cu:424-448).  Same quants and d as the butterfly form; the sum
+// differs in its last bits, which the fp16 rounding of the field exposes for about one block in a few thousand.
+__device__ __forceinline__ void lkb_quant_store_planar_fused_epilogue(float xi, int8_t * __restrict__ qs,
+                                                                      float2 * __restrict__ sc, int lane) {
+    float d, s;
+    const int q = lkb_quant_lane(xi, d, s);
+    qs[lane] = (int8_t) q;
+    float v = xi;
+    v = __fadd_rn(v, __shfl_xor_sync(LKB_FULL, v, 8));
+    v = __fadd_rn(v, __shfl_xor_sync(LKB_FULL, v, 16));
+    v = __fadd_rn(v, __shfl_xor_sync(LKB_FULL, v, 1));
+    v = __fadd_rn(v, __shfl_xor_sync(LKB_FULL, v, 2));
+    v = __fadd_rn(v, __shfl_xor_sync(LKB_FULL, v, 4));
+    if (lane == 0) {
+        const __half2 ds = __floats2half2_rn(d, v);
+        *sc = make_float2(__low2float(ds), __fmul_rn(8.0f, __high2float(ds)));
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Four elements per lane.  A 32-element block lives in 8 adjacent lanes, lane l holding elements 4(l&7) .. +3
 // (one 128-bit load), so a warp covers four blocks = 512 contiguous bytes per step.  The xor-butterfly of the

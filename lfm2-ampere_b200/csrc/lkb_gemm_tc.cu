@@ -682,15 +682,26 @@ __global__ void __launch_bounds__(TcCfg<EPI>::THREADS, 1) k_pf_gemm_tc(const lkb
                     float am = 0.0f;
 #pragma unroll
                     for (int i = 0; i < 32; ++i) am = fmaxf(am, fabsf(v[i]));
-                    // the sum in xor-butterfly order (16, 8, 4, 2, 1), as the warp quantiser produces it
-                    float t[16];
+                    float sum;
+                    if (FOLD) {
+                        // shipped arithmetic: the block sum in the order of the reference's fused epilogue, where a lane adds
+                        // rows (g, g+8) + (g+16, g+24) and the eight lanes then pair over g ^ 1, 2, 4 (src/prefill.cu:424-448)
+                        float t[8];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) t[i] = __fadd_rn(v[i], v[i + 16]);
+                        for (int i = 0; i < 8; ++i) t[i] = __fadd_rn(__fadd_rn(v[i], v[i + 8]), __fadd_rn(v[i + 16], v[i + 24]));
+                        sum = __fadd_rn(__fadd_rn(__fadd_rn(t[0], t[1]), __fadd_rn(t[2], t[3])),
+                                        __fadd_rn(__fadd_rn(t[4], t[5]), __fadd_rn(t[6], t[7])));
+                    } else {
+                        // exact mode: xor-butterfly order (16, 8, 4, 2, 1), as the warp quantiser of the unfused path produces it
+                        float t[16];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) t[i] = __fadd_rn(t[i], t[i + 8]);
+                        for (int i = 0; i < 16; ++i) t[i] = __fadd_rn(v[i], v[i + 16]);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) t[i] = __fadd_rn(t[i], t[i + 4]);
-                    const float sum = __fadd_rn(__fadd_rn(t[0], t[2]), __fadd_rn(t[1], t[3]));
+                        for (int i = 0; i < 8; ++i) t[i] = __fadd_rn(t[i], t[i + 8]);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) t[i] = __fadd_rn(t[i], t[i + 4]);
+                        sum = __fadd_rn(__fadd_rn(t[0], t[2]), __fadd_rn(t[1], t[3]));
+                    }
                     const float d = __fdiv_rn(am, 127.0f);
                     // q = roundf(v / d), the quotient rounded as IEEE division rounds it.  The product with the
                     // reciprocal is within 2e-5 of that quotient (|q| <= 127), so unless it lies that close to a

@@ -586,8 +586,11 @@ __global__ void __launch_bounds__(256) k_pf_gemm_simple(const lkb_pf_gemm g, con
             const float gt = __fmul_rn(acc[0][j], scl);
             const float up = __fmul_rn(acc[1][j], scl);
             const float v = __fmul_rn(lkb_silu(gt), up);
-            lkb_quant_store_planar(v, g.oqs + (size_t) orow * (g.okb * 32) + row0,
-                                   reinterpret_cast<float2 *>(g.osc) + (size_t) orow * g.okb + row0 / 32, lane);
+            // shipped arithmetic: the block sum in the reference's fused-epilogue order; exact mode: the quantiser's butterfly
+            if (fold) lkb_quant_store_planar_fused_epilogue(v, g.oqs + (size_t) orow * (g.okb * 32) + row0,
+                                                            reinterpret_cast<float2 *>(g.osc) + (size_t) orow * g.okb + row0 / 32, lane);
+            else      lkb_quant_store_planar(v, g.oqs + (size_t) orow * (g.okb * 32) + row0,
+                                             reinterpret_cast<float2 *>(g.osc) + (size_t) orow * g.okb + row0 / 32, lane);
         } else {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {

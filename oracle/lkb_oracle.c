@@ -64,6 +64,21 @@ static float butterfly32(const float v_in[32]) {
     return v[0];
 }
 
+/* The block sum as the reference's FUSED SwiGLU epilogue takes it (src/prefill.cu:424-448): a lane holds rows
+ * g, g+8, g+16, g+24 of the block and adds (v0 + v1) + (v2 + v3), then xor-shuffles over 4, 8, 16 (g ^ 1, 2, 4):
+ * in row terms the pairing order is 8, 16, 1, 2, 4.  Differs from butterfly32 in the last bits only, which the
+ * fp16 rounding of the sum field exposes for about one block in a few thousand. */
+static float butterfly32_fused_epilogue(const float v_in[32]) {
+    static const int order[5] = {8, 16, 1, 2, 4};
+    float v[32], t[32];
+    memcpy(v, v_in, sizeof v);
+    for (int k = 0; k < 5; ++k) {
+        for (int i = 0; i < 32; ++i) t[i] = v[i] + v[i ^ order[k]];
+        memcpy(v, t, sizeof v);
+    }
+    return v[0];
+}
+
 /* ------------------------------------------------------------------------- */
 /* a1. Q8_1 quantiser for one 32-element block.                               */
 /* src/quant.cuh:106-121 (quantize_q8_1_warp), src/prefill.cu:90-103.         */
@@ -93,6 +108,18 @@ static void quant_block_planar(const float x[32], int8_t q[32], float sc[2]) {
     quant_block(x, q, &d16, &s16);
     sc[0] = orc_f16_to_f32(d16);
     sc[1] = 8.0f * orc_f16_to_f32(s16);
+}
+/* the same with the sum in the fused epilogue's order */
+static void quant_block_planar_fused_epilogue(const float x[32], int8_t q[32], float sc[2]) {
+    quant_block_planar(x, q, sc);
+    sc[1] = 8.0f * orc_f16_to_f32(orc_f32_to_f16(butterfly32_fused_epilogue(x)));
+}
+
+/* 8 * fp16(sum) of each 32-element block of v in the fused epilogue's order: the second field of the planar
+ * (d, 8 sum) pair the reference's fused SwiGLU GEMM writes. */
+ORC_API void orc_fused_epilogue_sums(const float * v, long long nblocks, float * out) {
+    for (long long b = 0; b < nblocks; ++b)
+        out[b] = 8.0f * orc_f16_to_f32(orc_f32_to_f16(butterfly32_fused_epilogue(v + b * 32)));
 }
 
 /* ------------------------------------------------------------------------- */
@@ -600,8 +627,8 @@ ORC_API void orc_pf_gemm(const orc_gemm_t * g, double * out64, double * mag, dou
 /* a13 with the fused SwiGLU epilogue.  src/prefill.cu:424-469: g.qs[0] = gate,
  * g.qs[1] = up, N = intermediate width; gate and up values are multiplied by
  * scale[arow], v = silu(g)*u, then Q8_1 over 32 consecutive intermediate rows
- * of one slot -> oqs[orow][okb*32], osc[orow][okb][2].  The block sum is taken
- * with the standard butterfly so that fused == unfused bit for bit.
+ * of one slot -> oqs[orow][okb*32], osc[orow][okb][2].  The block sum follows the
+ * arithmetic mode (orc_set_gemm_fold): the fused epilogue's own order, or the butterfly.
  * vbuf (optional) [nslots][N]: receives v, or when use_v != 0 supplies it. */
 ORC_API void orc_pf_gemm_swiglu(const orc_gemm_t * g, int8_t * oqs, float * osc, int okb,
                                 float * vbuf, int use_v) {
@@ -633,7 +660,9 @@ ORC_API void orc_pf_gemm_swiglu(const orc_gemm_t * g, int8_t * oqs, float * osc,
                 v[r] = (gt / (1.0f + expf(-gt))) * up;
                 if (vbuf) vbuf[(size_t) orow * g->N + n] = v[r];
             }
-            quant_block_planar(v, oqs + (size_t) orow * okb * 32 + b0 * 32, osc + ((size_t) orow * okb + b0) * 2);
+            /* shipped arithmetic: the fused epilogue's own sum order; exact mode: the quantiser's butterfly (fused == unfused) */
+            if (g_gemm_fold) quant_block_planar_fused_epilogue(v, oqs + (size_t) orow * okb * 32 + b0 * 32, osc + ((size_t) orow * okb + b0) * 2);
+            else quant_block_planar(v, oqs + (size_t) orow * okb * 32 + b0 * 32, osc + ((size_t) orow * okb + b0) * 2);
         }
     }
     free(slot); free(expt);

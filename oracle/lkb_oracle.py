@@ -395,6 +395,14 @@ def pf_gemm_swiglu(gate, up, N, bpr, aqs, asc, *, ntok=0, exp_stride=0, perm=Non
     return oqs, osc, vb
 
 
+def fused_epilogue_sums(v):
+    """8 * fp16(block sum) per 32-element block of v, summed in the order of the reference's fused SwiGLU epilogue."""
+    v = _c(v, np.float32)
+    out = np.empty(v.size // 32, np.float32)
+    _lib.orc_fused_epilogue_sums(_p(v, _f32p), C.c_longlong(v.size // 32), _p(out, _f32p))
+    return out.reshape(v.shape[:-1] + (v.shape[-1] // 32,))
+
+
 def pf_combine(X, D, w):
     X = _c(X, np.float32).copy()
     D = _c(D, np.float32)

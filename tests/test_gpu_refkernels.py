@@ -259,9 +259,11 @@ def test_gemm_dense_and_swiglu_against_reference_kernel(L, R, orc, cfg):
     R.pf_gemm_dense(L.make_pf_gemm(segs, [128, 256, 384], N, bpr, daq, dasc, ntok=M, scale=sc, out=o1, out_ld=N, add=1))
     torch.cuda.synchronize()
     assert _same(o0, o1)
-    # fused SwiGLU epilogue: quants and d identical; the block sum within 4 fp16 ulp (the reference sums the 32 values in
-    # another order than its own stand-alone quantiser: its gate, tests/test_prefill.cu:788-800)
-    E, I, M = 8, 256, 150
+    # fused SwiGLU epilogue: quants, d AND the block sum identical -- the reference sums the 32 values of a block in
+    # another order there than in its stand-alone quantiser (rows paired 8, 16, 1, 2, 4 apart; it gates the two against
+    # each other within fp16 steps, tests/test_prefill.cu:788-800), and shipped arithmetic follows the fused order.
+    # 38400 blocks: an order mismatch would show in about twenty of them
+    E, I, M = 8, 512, 600
     NS = M * 4
     gq, gd = rand_q4(rng, E * I, bpr, "ref")
     uq, ud = rand_q4(rng, E * I, bpr, "ref")
@@ -285,12 +287,7 @@ def test_gemm_dense_and_swiglu_against_reference_kernel(L, R, orc, cfg):
     R.pf_gemm_swiglu(L.make_pf_gemm(dw, [I, I, I], I, bpr, daq, dasc, exp_stride=I * bpr, perm=perm, tiles=tiles, ntiles=ntiles,
                                     a_shift=2, scale=inv, oqs=q1, osc=s1, okb=I // 32), max_tiles)
     torch.cuda.synchronize()
-    assert _same(q0, q1)
-    a, b = host(s0), host(s1)
-    assert np.array_equal(a[..., 0], b[..., 0])
-    ha = (a[..., 1] / 8.0).astype(np.float16).view(np.int16).astype(np.int32)
-    hb = (b[..., 1] / 8.0).astype(np.float16).view(np.int16).astype(np.int32)
-    assert np.max(np.abs(ha - hb)) <= 4
+    assert _same(q0, q1) and _same(s0, s1)
     assert L.lib.lkb_pf_gemm_status() == 0
     L.pf_gemm_config(-1)
 
