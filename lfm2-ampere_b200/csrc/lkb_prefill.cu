@@ -186,19 +186,22 @@ __global__ void __launch_bounds__(256) k_pf_router_token(const float * __restric
 // src/prefill.cu:1606-1666, same per-logit order), so a CTA runs a long sequential k loop and the kernel is bound by
 // (a) how well the loads of the next k-tiles hide behind the FMAs of the current one and (b) how many FMAs each
 // shared-memory wavefront feeds.  CTA = NW warps = 2 NW token groups x 16 expert lanes; a thread owns TPT tokens x the
-// four experts (lane, lane + 16, + 32, + 48): 4 * TPT independent chains.  Tiles of 32 k-values of the CTA's token
+// four experts (lane, lane + 16, + 32, + 48): 4 * TPT independent chains.  Tiles of RT_KT k-values of the CTA's token
 // rows and of all 64 router rows travel global -> shared by 16-byte asynchronous copies through a ring of RT_STAGES
-// buffers (rows keep their [row][k] layout, pitch 36 floats: nothing is transposed and 128-bit loads of 16 different
+// buffers (rows keep their [row][k] layout, pitch RT_KT + 4 floats: nothing is transposed and 128-bit loads of 16 different
 // rows are conflict-free); the multiply loop reads four k-values per load.  With TPT = 4 a warp spends 16 wavefronts
 // (4 loads of router rows, 4 of token rows shared by half a warp) on 64 FMA instructions: the ratio at which the FMA
 // pipes rather than shared memory set the pace.  One CTA barrier per tile.
-#define RT_KT     32
-#define RT_PITCH  36
+#ifndef RT_KT
+#define RT_KT     64                          // measured on B200, 4096 tokens: 32 -> 66 us, 64 -> 55 us, 128 (4 stages) -> 72 us
+#endif
+#define RT_PITCH  (RT_KT + 4)
+#define RT_CPR    (RT_KT / 4)                 // 16-byte copies per staged row
 #ifndef RT_STAGES
 #define RT_STAGES 6
 #endif
 #ifndef RT_L_TPT
-#define RT_L_TPT 4          // long form: 4 warps, 32 tokens per CTA (measured on B200 at 4096 tokens: 66 us; 8 warps x 2 tokens 74 us,
+#define RT_L_TPT 4          // long form: 4 warps, 32 tokens per CTA (measured on B200 at 4096 tokens, 32-wide k-tiles: 66 us; 8 warps x 2 tokens 74 us,
 #define RT_L_NW  4          // 8 warps x 4 tokens 94 us, 4 warps x 2 tokens 76 us; the k loop of one CTA is the critical path)
 #endif
 #ifndef RT_S_TPT
@@ -218,19 +221,24 @@ __global__ void __launch_bounds__(32 * NW) k_pf_router_pipe(const float * __rest
     extern __shared__ __align__(16) float rt_ring[];                   // [RT_STAGES][ROWS][RT_PITCH]
     const int tid = threadIdx.x, te = tid & 15, tg = tid >> 4;
     const int t0 = blockIdx.x * TT;
+    // a thread copies the same (row, 16-byte part) set of every tile: sources and ring offsets are computed once
+    constexpr int NCP = (ROWS * RT_CPR + 32 * NW - 1) / (32 * NW);
+    const float * src[NCP]; int dst[NCP]; bool live[NCP];
+#pragma unroll
+    for (int j = 0; j < NCP; ++j) {
+        const int ch = tid + j * 32 * NW;
+        const int row = ch / RT_CPR, part = (ch % RT_CPR) * 4;
+        dst[j] = (ch < ROWS * RT_CPR) ? row * RT_PITCH + part : -1;
+        if (row < TT) { const int tk = t0 + row; live[j] = tk < m; src[j] = H + (size_t) (tk < m ? tk : 0) * LKB_HIDDEN + part; }
+        else          { live[j] = true; src[j] = Wr + (size_t) (row < ROWS ? row - TT : 0) * LKB_HIDDEN + part; }
+    }
     auto issue = [&](int tile) {
         if (tile < NTILES) {
             float * st = rt_ring + (size_t) (tile % RT_STAGES) * ROWS * RT_PITCH;
             const int k0 = tile * RT_KT;
-            for (int ch = tid; ch < ROWS * 8; ch += 32 * NW) {
-                const int row = ch >> 3, part = (ch & 7) * 4;
-                if (row < TT) {
-                    const int tk = t0 + row;
-                    rt_cp16(st + row * RT_PITCH + part, H + (size_t) (tk < m ? tk : 0) * LKB_HIDDEN + k0 + part, tk < m);
-                } else {
-                    rt_cp16(st + row * RT_PITCH + part, Wr + (size_t) (row - TT) * LKB_HIDDEN + k0 + part, true);
-                }
-            }
+#pragma unroll
+            for (int j = 0; j < NCP; ++j)
+                if (dst[j] >= 0) rt_cp16(st + dst[j], src[j] + k0, live[j]);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");      // (an empty group keeps the count uniform)
     };
