@@ -242,7 +242,9 @@ def ab_reference_kernels(ps, layers, api, rounds=5):
     """A/B on this GPU against the kernels to beat: the reference's own grouped-GEMM kernels, compiled unchanged for
     sm_100a (oracle/_ref/libref_kernels.so; absent where the reference checkout was not at hand when the tree was
     built -> null).  Same plan, same activations, same weights; the two layers' weight sets alternate so that neither
-    side finds its weights in L2; ours and theirs interleaved, medians over `rounds`.  Outputs are compared byte for byte."""
+    side finds its weights in L2; ours and theirs interleaved, medians.  Outputs are compared byte for byte.
+    Two routings: the benchmark's own Zipf-skewed plan, and the uniform 4-distinct-experts routing of the reference's
+    own GEMM benchmark (tests/test_prefill.cu:605-638)."""
     import torch
     try:
         rk = importlib.import_module("oracle.ref_kernels")
@@ -252,17 +254,7 @@ def ab_reference_kernels(ps, layers, api, rounds=5):
         return None
     from importlib import import_module
     synth = import_module("lfm2-ampere_b200.synth")
-    Hh, Ii = synth.H, synth.I
-
-    def descs(li):
-        l = layers[li]
-        g = api.make_pf_gemm([(l.gate_qs, l.gate_d), (l.up_qs, l.up_d)], [Ii, Ii, Ii], Ii, Hh // 32, ps.a_qs, ps.a_sc,
-                             exp_stride=Ii * (Hh // 32), perm=ps.perm, tiles=ps.tiles, ntiles=ps.ntiles,
-                             a_shift=2, scale=ps.inv, oqs=ps.a2_qs, osc=ps.a2_sc, okb=Ii // 32)
-        dn = api.make_pf_gemm([(l.down_qs, l.down_d)], [Hh, Hh, Hh], Hh, Ii // 32, ps.a2_qs, ps.a2_sc,
-                              exp_stride=Hh * (Ii // 32), perm=ps.perm, tiles=ps.tiles, ntiles=ps.ntiles,
-                              a_shift=0, out=ps.D, out_ld=Hh)
-        return g, dn
+    Hh, Ii, Ee = synth.H, synth.I, synth.E
 
     def timed(fn):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -272,45 +264,63 @@ def ab_reference_kernels(ps, layers, api, rounds=5):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) * 1e3
 
-    api.pf_gemm_set_workspace(ps.gemm_ws)
-    ours, theirs = {"swiglu": [], "down": []}, {"swiglu": [], "down": []}
-    # parity first (untimed): same plan and inputs through both, outputs byte for byte
-    g, dn = descs(0)
-    api.pf_gemm_swiglu(g, ps.max_tiles)
-    q_ours, s_ours = ps.a2_qs.clone(), ps.a2_sc.clone()
-    rk.pf_gemm_swiglu(g, ps.max_tiles)
     beq = lambda a, b: bool(torch.equal(a.view(torch.uint8), b.view(torch.uint8)))      # bytes: NaN-safe
-    same = beq(q_ours, ps.a2_qs) and beq(s_ours, ps.a2_sc)
-    api.pf_gemm_moe(dn, ps.max_tiles)
-    d_ours = ps.D.clone()
-    rk.pf_gemm_moe(dn, ps.max_tiles)
-    same = same and beq(d_ours, ps.D)
-    del q_ours, s_ours, d_ours
-    nl = min(2, len(layers))
-    for r in range(rounds):
-        # each call's weights were last read two calls earlier (a layer's gate|up planes alone are 226 MB: L2 is cold for both)
-        for k, li in enumerate((r % nl, (r + 1) % nl)):
-            g, dn = descs(li)
-            mine = (k == 0)
-            (ours if mine else theirs)["swiglu"].append(timed(lambda: (api if mine else rk).pf_gemm_swiglu(g, ps.max_tiles)))
-        for k, li in enumerate(((r + 1) % nl, r % nl)):
-            g, dn = descs(li)
-            mine = (k == 0)
-            (ours if mine else theirs)["swiglu"].append(timed(lambda: (api if mine else rk).pf_gemm_swiglu(g, ps.max_tiles)))
-        for k, li in enumerate((r % nl, (r + 1) % nl)):
-            g, dn = descs(li)
-            mine = (k == 0)
-            (ours if mine else theirs)["down"].append(timed(lambda: (api if mine else rk).pf_gemm_moe(dn, ps.max_tiles)))
-        for k, li in enumerate(((r + 1) % nl, r % nl)):
-            g, dn = descs(li)
-            mine = (k == 0)
-            (ours if mine else theirs)["down"].append(timed(lambda: (api if mine else rk).pf_gemm_moe(dn, ps.max_tiles)))
     med = lambda v: float(np.median(v))
-    o, t = med(ours["swiglu"]) + med(ours["down"]), med(theirs["swiglu"]) + med(theirs["down"])
-    return {"what": "one layer's two grouped GEMMs on the same plan: this library vs the reference's kernels compiled unchanged for sm_100a",
-            "ours_us": {"swiglu": med(ours["swiglu"]), "down": med(ours["down"])},
-            "reference_kernel_us": {"swiglu": med(theirs["swiglu"]), "down": med(theirs["down"])},
-            "speedup": t / o, "outputs_identical": bool(same), "timed_calls_each": 2 * rounds}
+    api.pf_gemm_set_workspace(ps.gemm_ws)
+
+    def one_routing(perm, tiles, ntiles):
+        def descs(li):
+            l = layers[li]
+            g = api.make_pf_gemm([(l.gate_qs, l.gate_d), (l.up_qs, l.up_d)], [Ii, Ii, Ii], Ii, Hh // 32, ps.a_qs, ps.a_sc,
+                                 exp_stride=Ii * (Hh // 32), perm=perm, tiles=tiles, ntiles=ntiles,
+                                 a_shift=2, scale=ps.inv, oqs=ps.a2_qs, osc=ps.a2_sc, okb=Ii // 32)
+            dn = api.make_pf_gemm([(l.down_qs, l.down_d)], [Hh, Hh, Hh], Hh, Ii // 32, ps.a2_qs, ps.a2_sc,
+                                  exp_stride=Hh * (Ii // 32), perm=perm, tiles=tiles, ntiles=ntiles,
+                                  a_shift=0, out=ps.D, out_ld=Hh)
+            return g, dn
+        ours, theirs = {"swiglu": [], "down": []}, {"swiglu": [], "down": []}
+        # parity first (untimed): same plan and inputs through both, outputs byte for byte
+        g, dn = descs(0)
+        api.pf_gemm_swiglu(g, ps.max_tiles)
+        q_ours, s_ours = ps.a2_qs.clone(), ps.a2_sc.clone()
+        rk.pf_gemm_swiglu(g, ps.max_tiles)
+        same = beq(q_ours, ps.a2_qs) and beq(s_ours, ps.a2_sc)
+        api.pf_gemm_moe(dn, ps.max_tiles)
+        d_ours = ps.D.clone()
+        rk.pf_gemm_moe(dn, ps.max_tiles)
+        same = same and beq(d_ours, ps.D)
+        del q_ours, s_ours, d_ours
+        nl = min(2, len(layers))
+        for r in range(rounds):
+            # each call's weights were last read two calls earlier (a layer's gate|up planes alone are 226 MB: L2 is cold for both)
+            for which, form in (("swiglu", 0), ("down", 1)):
+                for order in ((r % nl, (r + 1) % nl), ((r + 1) % nl, r % nl)):
+                    for k, li in enumerate(order):
+                        gd = descs(li)
+                        lib_ = api if k == 0 else rk
+                        fn = (lambda: lib_.pf_gemm_swiglu(gd[0], ps.max_tiles)) if form == 0 else (lambda: lib_.pf_gemm_moe(gd[1], ps.max_tiles))
+                        (ours if k == 0 else theirs)[which].append(timed(fn))
+        o, t = med(ours["swiglu"]) + med(ours["down"]), med(theirs["swiglu"]) + med(theirs["down"])
+        return {"ours_us": {"swiglu": med(ours["swiglu"]), "down": med(ours["down"])},
+                "reference_kernel_us": {"swiglu": med(theirs["swiglu"]), "down": med(theirs["down"])},
+                "speedup": t / o, "outputs_identical": bool(same), "timed_calls_each": 2 * rounds}
+
+    out = {"what": "one layer's two grouped GEMMs on the same plan: this library vs the reference's kernels compiled unchanged for sm_100a"}
+    out.update(one_routing(ps.perm, ps.tiles, ps.ntiles))                      # the benchmark's Zipf-skewed routing
+    # uniform routing: four distinct experts per token, uniformly at random (seeded)
+    m = ps.m
+    gen = torch.Generator(device="cuda").manual_seed(4242)
+    idx_u = torch.rand(m, Ee, device="cuda", generator=gen).topk(4, dim=1).indices.to(torch.int32).contiguous()
+    cnt = torch.zeros(Ee, dtype=torch.int32, device="cuda")
+    off = torch.zeros(Ee, dtype=torch.int32, device="cuda")
+    tiles = torch.zeros_like(ps.tiles)
+    ntiles = torch.zeros(1, dtype=torch.int32, device="cuda")
+    perm = torch.zeros_like(ps.perm)
+    api.k_pf_moe_count(idx_u, m * 4, cnt)
+    api.k_pf_moe_plan(cnt, off, tiles, ntiles)
+    api.k_pf_moe_scatter(idx_u, m * 4, off, perm)
+    out["uniform_routing"] = one_routing(perm, tiles, ntiles)
+    return out
 
 
 def profile_traffic(name):
@@ -540,6 +550,41 @@ def run_ours(args):
               "published_reference": {"value": 21188.0, "unit": UNIT, "hardware": "RTX 3090 Ti, real weights, full model incl. attention, 4096 tokens",
                                       "note": "not this metric (full model): see config.full_prefill for the like-for-like chunk"}}
     del pf_graph
+
+    # ---- long prompts through the expert-parallel MoE stack (configuration 4 at N > 1): 8192-token chunks, a 32768-token
+    #      prompt = 4 chunks, a 131072-token prompt = 16 (the MoE stack has no state across chunks: same chunk, repeated)
+    if ep and disp == "peer" and not args.no_long_ctx and not args.no_graph:
+        try:
+            del ps
+            torch.cuda.empty_cache()
+            m8 = 8192
+            ps8 = prefill.PrefillStackEP(layers, m8, rank, world, dispatch="peer")
+            ps8.prepare()
+            ps8.X.copy_(torch.randn(m8 // world, H, device="cuda", generator=torch.Generator(device="cuda").manual_seed(77 + rank)))
+            ps8.step()
+            torch.cuda.synchronize()
+            barrier()
+            g8 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g8, capture_error_mode="thread_local"):
+                ps8.step()
+            for _ in range(3):
+                g8.replay()
+            barrier()
+            ev0.record()
+            for _ in range(16):
+                g8.replay()
+            ev1.record()
+            barrier()
+            ms16 = max_over_ranks(ev0.elapsed_time(ev1))
+            est = torch.tensor([ps8.status()], device="cuda")
+            dist.all_reduce(est, op=dist.ReduceOp.MAX)
+            pf_cfg["long_context_ep"] = {
+                "workload": "configuration 4 through the expert-parallel MoE stack: 8192-token chunks (a 32768-token prompt = 4, a 131072-token prompt = 16)",
+                "chunk_ms": ms16 / 16, "tok_s": 16 * m8 / (ms16 * 1e-3), "prompt_32768_ms": ms16 / 4, "prompt_131072_ms": ms16,
+                "exchange_status": int(est.item())}
+            del g8, ps8
+        except Exception as exc:                       # reported, not fatal: the headline is measured above
+            pf_cfg["long_context_ep"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
 
     # ================================================================ decode (N = 1 only): configurations 0, 1, 2, 4
     dec = None
