@@ -25,7 +25,7 @@ __all__ = [
     "k_attn_split", "k_attn_combine", "k_qk_norm_rope", "k_shortconv", "ATTN_SPLIT", "ATTN_PARTW",
     "mixer_layer_desc", "step_scratch", "decode_layers",
     "k_pf_embed", "k_pf_conv", "k_pf_conv_hist", "k_pf_qknr", "k_pf_attn",
-    "ep_peers", "ep_set_wait_limit_ms", "ep_counts_exchange", "ep_route_exchange", "ep_route_experts", "pf_gemm_moe_rows", "ep_publish", "ep_pack_push", "ep_wait", "ep_push_back", "ep_unpack_rows_dev", "k_pf_moe_count_dev",
+    "ep_peers", "EP_ROW_BYTES", "ep_set_wait_limit_ms", "ep_counts_exchange", "ep_route_exchange", "ep_route_experts", "pf_gemm_moe_rows", "ep_publish", "ep_pack_push", "ep_wait", "ep_push_back", "ep_unpack_rows_dev", "k_pf_moe_count_dev",
     "k_pf_moe_scatter_dev",
 ]
 

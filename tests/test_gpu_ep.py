@@ -1,6 +1,6 @@
-"""Expert-parallel prefill on 2+ GPUs == the single-GPU prefill, bit for bit, through both exchanges: NCCL
-all-to-all and the peer-memory kernels.  Needs >= 2 B200s (skipped on a single-GPU box).  The exchange's bounded
-wait is exercised on one GPU with a flag that nothing sets."""
+"""Expert-parallel prefill on 1, 2, 4 and 8 GPUs == the single-GPU prefill, bit for bit, through both exchanges: NCCL
+all-to-all and the peer-memory kernels (the cases above the box's GPU count are skipped; world 1 runs the same kernels
+against the rank's own buffers).  The exchange's bounded wait is exercised with a flag that nothing sets."""
 import importlib
 import os
 import socket
@@ -67,8 +67,10 @@ def _worker(rank, world, port, m, n_layers, out, dispatch):
 
 
 @pytest.mark.parametrize("dispatch", ["nccl", "peer"])
-@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
 def test_ep_prefill_bitwise_equals_single_gpu(world, dispatch, tmp_path):
+    """world 1 runs the whole exchange chain (routing + count exchange, dispatch rows, plan over received rows, result rows
+    written home by the GEMM, flags) against the rank's own buffers: the kernels are exercised on a single-GPU box too."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
@@ -98,3 +100,35 @@ def test_ep_wait_runs_out_and_reports(lkb):
     finally:
         lkb.ep_set_wait_limit_ms(5000)
     assert float(torch.ones(4, device="cuda").sum().item()) == 4.0
+
+
+def test_one_cta_routing_equals_count_plan_scatter(lkb):
+    """lkb_ep_route_experts' plan over received rows == lkb_pf_moe_count / _plan / _scatter on the same keys (bit for
+    bit, ragged and skewed), and lkb_ep_route_exchange's send order == the same kernels keyed by owner rank."""
+    import numpy as np
+    lkb.init(0)
+    rng = np.random.default_rng(12)
+    i32 = dict(dtype=torch.int32, device="cuda")
+    for n, per in ((1, 8), (700, 8), (2048, 8), (5000, 32), (16384, 64)):
+        keys = np.minimum(rng.geometric(0.08, size=n) - 1, per - 1).astype(np.int32)        # skewed local expert ids
+        # received rows: only the key word (uint4 #160, .y) matters to the routing kernel
+        rows = torch.zeros(n, lkb.EP_ROW_BYTES, dtype=torch.uint8, device="cuda")
+        rows.view(torch.int32).view(n, lkb.EP_ROW_BYTES // 4)[:, 641] = torch.from_numpy(keys).cuda()
+        flags = torch.full((24,), 7, **i32)
+        epoch = torch.tensor([7], **i32)
+        offs = torch.zeros(4, **i32); offs[3] = n                                            # G = 1: [send, recv, back, n]
+        mt = n // 64 + 64
+        cnt, off, tiles, nt, perm = (torch.full((64,), -1, **i32), torch.full((64,), -1, **i32), torch.full((mt, 4), -1, **i32),
+                                     torch.full((1,), -1, **i32), torch.full((n,), -1, **i32))
+        nrecv, status = torch.zeros(1, **i32), torch.zeros(1, **i32)
+        lkb.ep_route_experts(rows, n, flags, 1, epoch, offs, cnt, off, tiles, nt, perm, nrecv, status)
+        k = torch.from_numpy(keys).cuda()
+        c2, o2, t2, n2, p2 = (torch.zeros(64, **i32), torch.full((64,), -1, **i32), torch.full((mt, 4), -1, **i32),
+                              torch.full((1,), -1, **i32), torch.full((n,), -1, **i32))
+        lkb.k_pf_moe_count(k, n, c2)
+        lkb.k_pf_moe_plan(c2, o2, t2, n2)
+        lkb.k_pf_moe_scatter(k, n, o2, p2)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0 and int(nrecv.item()) == n
+        assert torch.equal(cnt, c2) and torch.equal(off, o2) and torch.equal(nt, n2) and torch.equal(perm, p2)
+        assert torch.equal(tiles[:int(nt.item())], t2[:int(n2.item())])
