@@ -356,7 +356,7 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     lkb.init(local)
-    lkb.set_pdl(False)
+    lkb.set_pdl(False)                          # prefill: programmatic dependent launch measured 0.6% slower (1297 vs 1289 us per layer)
     hbm_peak, peak_kind, _ = peaks()
     st = torch.cuda.current_stream()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

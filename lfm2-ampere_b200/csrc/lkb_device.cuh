@@ -270,4 +270,8 @@ static int lkb_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem
     if (e != cudaSuccess) { (void) cudaGetLastError(); return -(int) e; }
     return LKB_OK;
 }
+// The prefill chain's launches: programmatic dependent launch when enabled (lkb_set_pdl), so that a kernel's launch
+// latency hides behind its predecessor; every kernel launched this way starts with lkb_pdl_wait().
+#define LKB_PF_LAUNCH(kern, grid, block, smem, st, ...) \
+    do { const int lkb_r_ = lkb_launch(kern, grid, block, smem, st, __VA_ARGS__); if (lkb_r_ != LKB_OK) return lkb_r_; } while (0)
 

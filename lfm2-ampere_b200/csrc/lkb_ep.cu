@@ -66,6 +66,7 @@ __device__ __forceinline__ bool ep_wait_flag(const int * flags, int phase, int s
 __global__ void __launch_bounds__(64) k_ep_counts_exchange(const int * __restrict__ dcnt, EpPeers P, int me, int G, int * __restrict__ epoch_dev,
                                                            int * __restrict__ offs, int * __restrict__ status,
                                                            unsigned long long limit_ns) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int t = threadIdx.x;
     const int epoch = *epoch_dev + 1;                                    // this layer's epoch; stored back at the end
     if (t < G * G) P.cmat[t / G][me * G + (t % G)] = dcnt[t % G];       // my row, into every rank's matrix
@@ -104,6 +105,7 @@ __global__ void __launch_bounds__(256) k_ep_pack_push(const int8_t * __restrict_
                                                       const int * __restrict__ offs, int n, int experts_per_rank, EpPeers P, int me, int G,
                                                       const int * __restrict__ epoch_dev, int * __restrict__ pos,
                                                       unsigned * __restrict__ done) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int p = blockIdx.x * 8 + warp; p < n; p += gridDim.x * 8) {
         const int slot = send_order[p], t = slot >> 2;
@@ -131,6 +133,7 @@ __global__ void __launch_bounds__(256) k_ep_pack_push(const int8_t * __restrict_
 // Wait until every source has published `phase` for this epoch.
 __global__ void __launch_bounds__(32) k_ep_wait(const int * __restrict__ flags, int phase, int G, const int * __restrict__ epoch_dev,
                                                 int * __restrict__ status, unsigned long long limit_ns) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int epoch = *epoch_dev;
     if ((int) threadIdx.x < G) ep_wait_flag(flags, phase, threadIdx.x, epoch, status, 2 + phase, limit_ns);
 }
@@ -139,6 +142,7 @@ __global__ void __launch_bounds__(32) k_ep_wait(const int * __restrict__ flags, 
 // row back_base[s] + j of ITS send order.  grid = upper bound of rows; rows >= n_recv exit.  One CTA per row.
 __global__ void __launch_bounds__(256) k_ep_push_back(const float * __restrict__ D, const int * __restrict__ offs, EpPeers P, int me, int G,
                                                       const int * __restrict__ epoch_dev, unsigned * __restrict__ done) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int n = offs[3 * G];
     for (int r = blockIdx.x; r < n; r += gridDim.x) {
         int s = 0;
@@ -225,6 +229,7 @@ __device__ __forceinline__ void ep_route_cta(EpRouteSmem & R, KeyFn key, int n, 
 __global__ void __launch_bounds__(1024) k_ep_route_exchange(const int * __restrict__ idx, int ns, int experts_per_rank, EpPeers P, int me, int G,
                                                             int * __restrict__ epoch_dev, int * __restrict__ send_order, int * __restrict__ doff,
                                                             int * __restrict__ offs, int * __restrict__ status, unsigned long long limit_ns) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     __shared__ EpRouteSmem R;
     const int t = threadIdx.x;
     ep_route_cta(R, [&](int s) { return idx[s] / experts_per_rank; }, ns, nullptr, doff, nullptr, nullptr, send_order);
@@ -261,6 +266,7 @@ __global__ void __launch_bounds__(1024) k_ep_route_experts(const unsigned char *
                                                            int * __restrict__ ntiles, int * __restrict__ perm, int * __restrict__ nrecv_out,
                                                            EpPeers P, float ** __restrict__ home_rows,
                                                            int * __restrict__ status, unsigned long long limit_ns) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     __shared__ EpRouteSmem R;
     const int t = threadIdx.x;
     if (t == 0) R.ok = 1;
@@ -285,6 +291,7 @@ __global__ void __launch_bounds__(1024) k_ep_route_experts(const unsigned char *
 // Publish `phase` of this epoch to every rank: the stores of the kernels before this one on the stream (the grouped
 // GEMM writing result rows straight into their home ranks' buffers) are complete when this kernel starts.
 __global__ void __launch_bounds__(32) k_ep_publish(EpPeers P, int me, int G, int phase, const int * __restrict__ epoch_dev) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     __threadfence_system();
     if ((int) threadIdx.x < G) ep_st_release(P.flags[threadIdx.x] + phase * EP_MAX_RANKS + me, *epoch_dev);
 }
@@ -318,7 +325,7 @@ int lkb_ep_counts_exchange(const int * dcnt, const lkb_ep_peers * peers, int me,
     const int r = ep_peers(P, peers->cmat, peers->flags, peers->recv, peers->dback, G);
     if (r != LKB_OK) return r;
     if (me < 0 || me >= G) return LKB_ERR_SHAPE;
-    k_ep_counts_exchange<<<1, 64, 0, (cudaStream_t) st>>>(dcnt, P, me, G, epoch, offs, status, g_ep_limit_ns);
+    LKB_PF_LAUNCH(k_ep_counts_exchange, dim3(1), dim3(64), 0, (cudaStream_t) st, dcnt, P, me, G, epoch, offs, status, g_ep_limit_ns);
     return lkb_check_launch();
 }
 
@@ -330,7 +337,7 @@ int lkb_ep_route_exchange(const int * idx, int n, int experts_per_rank, const lk
     const int r = ep_peers(P, peers->cmat, peers->flags, peers->recv, peers->dback, G);
     if (r != LKB_OK) return r;
     if (n <= 0 || experts_per_rank <= 0 || me < 0 || me >= G) return LKB_ERR_SHAPE;
-    k_ep_route_exchange<<<1, 1024, 0, (cudaStream_t) st>>>(idx, n, experts_per_rank, P, me, G, epoch, send_order, doff, offs, status, g_ep_limit_ns);
+    LKB_PF_LAUNCH(k_ep_route_exchange, dim3(1), dim3(1024), 0, (cudaStream_t) st, idx, n, experts_per_rank, P, me, G, epoch, send_order, doff, offs, status, g_ep_limit_ns);
     return lkb_check_launch();
 }
 
@@ -346,7 +353,7 @@ int lkb_ep_route_experts(const void * recv, int cap, const int * flags, int G, c
         const int r = ep_peers(P, peers->cmat, peers->flags, peers->recv, peers->dback, G);
         if (r != LKB_OK) return r;
     }
-    k_ep_route_experts<<<1, 1024, 0, (cudaStream_t) st>>>(reinterpret_cast<const unsigned char *>(recv), cap, flags, G, epoch, offs, cnt, off,
+    LKB_PF_LAUNCH(k_ep_route_experts, dim3(1), dim3(1024), 0, (cudaStream_t) st, reinterpret_cast<const unsigned char *>(recv), cap, flags, G, epoch, offs, cnt, off,
                                                           reinterpret_cast<int4 *>(tiles), ntiles, perm, nrecv_out, P, home_rows, status,
                                                           g_ep_limit_ns);
     return lkb_check_launch();
@@ -359,7 +366,7 @@ int lkb_ep_publish(const lkb_ep_peers * peers, int me, int G, int phase, const i
     const int r = ep_peers(P, peers->cmat, peers->flags, peers->recv, peers->dback, G);
     if (r != LKB_OK) return r;
     if (me < 0 || me >= G || phase < 0 || phase > 2) return LKB_ERR_SHAPE;
-    k_ep_publish<<<1, 32, 0, (cudaStream_t) st>>>(P, me, G, phase, epoch);
+    LKB_PF_LAUNCH(k_ep_publish, dim3(1), dim3(32), 0, (cudaStream_t) st, P, me, G, phase, epoch);
     return lkb_check_launch();
 }
 
@@ -374,7 +381,7 @@ int lkb_ep_pack_push(lkb_pf_act a, const float * inv, const int * idx, const int
     if (n <= 0 || experts_per_rank <= 0 || me < 0 || me >= G) return LKB_ERR_SHAPE;
     int grid = lkb_context().sm_count * 4;
     if (grid > (n + 7) / 8) grid = (n + 7) / 8;
-    k_ep_pack_push<<<grid, 256, 0, (cudaStream_t) st>>>(reinterpret_cast<const int8_t *>(a.qs), reinterpret_cast<const float2 *>(a.sc), inv,
+    LKB_PF_LAUNCH(k_ep_pack_push, dim3(grid), dim3(256), 0, (cudaStream_t) st, reinterpret_cast<const int8_t *>(a.qs), reinterpret_cast<const float2 *>(a.sc), inv,
                                                         idx, send_order, doff, offs, n, experts_per_rank, P, me, G, epoch, pos, done);
     return lkb_check_launch();
 }
@@ -383,7 +390,7 @@ int lkb_ep_wait(const int * flags, int phase, int G, const int * epoch, int * st
     if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
     if (!flags || !epoch || !status) return LKB_ERR_NULL;
     if (phase < 0 || phase > 2 || G < 1 || G > EP_MAX_RANKS) return LKB_ERR_SHAPE;
-    k_ep_wait<<<1, 32, 0, (cudaStream_t) st>>>(flags, phase, G, epoch, status, g_ep_limit_ns);
+    LKB_PF_LAUNCH(k_ep_wait, dim3(1), dim3(32), 0, (cudaStream_t) st, flags, phase, G, epoch, status, g_ep_limit_ns);
     return lkb_check_launch();
 }
 
@@ -397,7 +404,7 @@ int lkb_ep_push_back(const float * D, const int * offs, int max_rows, const lkb_
     if (max_rows <= 0 || me < 0 || me >= G) return LKB_ERR_SHAPE;
     int grid = lkb_context().sm_count * 8;                   // rows are walked with a grid stride: the live count is on the device
     if (grid > max_rows) grid = max_rows;
-    k_ep_push_back<<<grid, 256, 0, (cudaStream_t) st>>>(D, offs, P, me, G, epoch, done);
+    LKB_PF_LAUNCH(k_ep_push_back, dim3(grid), dim3(256), 0, (cudaStream_t) st, D, offs, P, me, G, epoch, done);
     return lkb_check_launch();
 }
 

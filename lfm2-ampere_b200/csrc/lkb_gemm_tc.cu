@@ -247,6 +247,7 @@ __device__ __forceinline__ void tc_fold32(unsigned long long (&acc)[32], const u
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) k_pf_gather_rows(const lkb_pf_gemm g, const int max_tiles, int8_t * __restrict__ wq,
                                                         float2 * __restrict__ ws, const int cap_rows) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int nt = *g.ntiles; if (nt > max_tiles) nt = max_tiles;
     if (nt <= 0) return;
@@ -279,6 +280,7 @@ __global__ void __launch_bounds__(TcCfg<EPI>::THREADS, 1) k_pf_gemm_tc(const lkb
                                                               const __grid_constant__ CUtensorMap map_w1,
                                                               const __grid_constant__ CUtensorMap map_w2,
                                                               float * const * __restrict__ out_rows) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     extern __shared__ unsigned char tc_smem_raw[];
     // the swizzle patterns are functions of the shared-memory address: stages start on 1024-byte boundaries
     typedef TcSmem<EPI> Smem;
@@ -833,7 +835,7 @@ int lkb_gemm_tc_launch(const lkb_pf_gemm * g, int epi, int fold, int max_tiles, 
             int8_t * wq = (int8_t *) g_tc_ws;
             float2 * ws = (float2 *) ((char *) g_tc_ws + cap * qrow);
             const int grid = lkb_context().sm_count * 4;
-            k_pf_gather_rows<<<grid, 256, 0, st>>>(*g, max_tiles, wq, ws, (int) cap);
+            LKB_PF_LAUNCH(k_pf_gather_rows, dim3(grid), dim3(256), 0, st, *g, max_tiles, wq, ws, (int) cap);
             r = lkb_check_launch();
             if (r != LKB_OK) return r;
             r = tc_make_map(&ma, wq, qrow, cap, 128u, TC_M, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -855,10 +857,10 @@ int lkb_gemm_tc_launch(const lkb_pf_gemm * g, int epi, int fold, int max_tiles, 
     const int rpe = (int) (g->exp_stride / g->bpr);
     const int grid = lkb_context().sm_count;
     const size_t sm0 = sizeof(TcSmem<0>) + 1024, sm1 = sizeof(TcSmem<1>) + 1024;
-    if (epi && fold)       k_pf_gemm_tc<1, 1><<<grid, TcCfg<1>::THREADS, sm1, st>>>(*g, max_tiles, rpe, tiled, ma, ms, mw[0], mw[1], mw[2], out_rows);
-    else if (epi)          k_pf_gemm_tc<1, 0><<<grid, TcCfg<1>::THREADS, sm1, st>>>(*g, max_tiles, rpe, tiled, ma, ms, mw[0], mw[1], mw[2], out_rows);
-    else if (fold)         k_pf_gemm_tc<0, 1><<<grid, TcCfg<0>::THREADS, sm0, st>>>(*g, max_tiles, rpe, tiled, ma, ms, mw[0], mw[1], mw[2], out_rows);
-    else                   k_pf_gemm_tc<0, 0><<<grid, TcCfg<0>::THREADS, sm0, st>>>(*g, max_tiles, rpe, tiled, ma, ms, mw[0], mw[1], mw[2], out_rows);
+    if (epi && fold)       LKB_PF_LAUNCH((k_pf_gemm_tc<1, 1>), dim3(grid), dim3(TcCfg<1>::THREADS), sm1, st, *g, max_tiles, rpe, tiled, ma, ms, mw[0], mw[1], mw[2], out_rows);
+    else if (epi)          LKB_PF_LAUNCH((k_pf_gemm_tc<1, 0>), dim3(grid), dim3(TcCfg<1>::THREADS), sm1, st, *g, max_tiles, rpe, tiled, ma, ms, mw[0], mw[1], mw[2], out_rows);
+    else if (fold)         LKB_PF_LAUNCH((k_pf_gemm_tc<0, 1>), dim3(grid), dim3(TcCfg<0>::THREADS), sm0, st, *g, max_tiles, rpe, tiled, ma, ms, mw[0], mw[1], mw[2], out_rows);
+    else                   LKB_PF_LAUNCH((k_pf_gemm_tc<0, 0>), dim3(grid), dim3(TcCfg<0>::THREADS), sm0, st, *g, max_tiles, rpe, tiled, ma, ms, mw[0], mw[1], mw[2], out_rows);
     return lkb_check_launch();
 }
 

@@ -12,6 +12,7 @@
 __global__ void __launch_bounds__(256) k_pf_embed(const unsigned char * __restrict__ ql, const unsigned char * __restrict__ qh,
                                                   const int8_t * __restrict__ sc, const __half * __restrict__ d,
                                                   const int * __restrict__ toks, float * __restrict__ x, int n) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int t = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int token = toks[t], sbpr = n / 256;
@@ -37,6 +38,7 @@ __device__ __forceinline__ float4 pf_mul4(const float4 a, const float4 b) {
 }
 __global__ void __launch_bounds__(128) k_pf_conv_run(const float * __restrict__ Y, const float * __restrict__ cw,
                                                      const float * __restrict__ hist, lkb_pf_act a, int m) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int lane = threadIdx.x & 31;
     const int wid = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int cg = wid & 15, t0 = (wid >> 4) * PF_CONV_RUN;
@@ -79,6 +81,7 @@ __global__ void __launch_bounds__(128) k_pf_conv_run(const float * __restrict__ 
 // Runs after the convolution, which reads the old history.  Four channels per thread.
 // ref semantics: src/prefill.cu:960-970
 __global__ void __launch_bounds__(256) k_pf_conv_hist(const float * __restrict__ Y, int m, float * __restrict__ hist) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int ch = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (ch >= LKB_HIDDEN) return;
     const float * yl = Y + (size_t) (m - 1) * (3 * LKB_HIDDEN) + ch;
@@ -102,6 +105,7 @@ __global__ void __launch_bounds__(256) k_pf_conv_hist(const float * __restrict__
 __global__ void __launch_bounds__(256) k_pf_qknr(const float * __restrict__ Y, const float * __restrict__ qn, const float * __restrict__ kn,
                                                  int P, __half * __restrict__ qh, __half * __restrict__ kc, __half * __restrict__ vc,
                                                  float theta) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int t = blockIdx.x, blk = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     const bool is_q = blk < AT_HEADS;
     const int head = is_q ? blk : blk - AT_HEADS;
@@ -142,6 +146,7 @@ __device__ __forceinline__ unsigned fa_pack(float lo, float hi) {
 
 __global__ void __launch_bounds__(256, 2) k_pf_attn(const __half * __restrict__ qh, int m, int P, const __half * __restrict__ kc,
                                                     const __half * __restrict__ vc, float * __restrict__ o) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     __shared__ __align__(16) __half sK[2][FA_BK][FA_ROW];
     __shared__ __align__(16) __half sV[2][FA_BK][FA_ROW];
     const int qt = gridDim.x - 1 - blockIdx.x;              // longest rows first

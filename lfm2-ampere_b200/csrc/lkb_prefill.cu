@@ -32,6 +32,7 @@ __global__ void __launch_bounds__(PF_TOK_WARPS * 32) k_pf_token_norm(float * __r
                                                                       const float * __restrict__ nw, int8_t * __restrict__ aqs,
                                                                       float2 * __restrict__ asc, float * __restrict__ inv_out,
                                                                       float * __restrict__ h32, int m) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     __shared__ float s_sq[PF_TOK_PER_CTA][64];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int tl = warp / PF_TOK_SPLIT, part = warp % PF_TOK_SPLIT;
@@ -88,6 +89,7 @@ __global__ void __launch_bounds__(PF_TOK_WARPS * 32) k_pf_token_norm(float * __r
 __global__ void __launch_bounds__(PF_TOK_WARPS * 32) k_pf_token_norm_plain(const float * __restrict__ X, const float * __restrict__ nw,
                                                                             int8_t * __restrict__ aqs, float2 * __restrict__ asc,
                                                                             float * __restrict__ inv_out, int m) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * PF_TOK_WARPS + (threadIdx.x >> 5);
     if (t >= m) return;
@@ -126,6 +128,7 @@ __global__ void __launch_bounds__(PF_TOK_WARPS * 32) k_pf_token_norm_plain(const
 template <int SWIGLU>
 __global__ void __launch_bounds__(256) k_pf_rows_q8(const float * __restrict__ Y, int ld, int up_off, int kb, int rows,
                                                     int8_t * __restrict__ aqs, float2 * __restrict__ asc) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int lane = threadIdx.x & 31;
     const int gpr = (kb + 3) >> 2;
     const long long wid = (long long) blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -159,6 +162,7 @@ __global__ void __launch_bounds__(256) k_pf_rows_q8(const float * __restrict__ Y
 __global__ void __launch_bounds__(256) k_pf_router_token(const float * __restrict__ H, const float * __restrict__ Wr,
                                                          const float * __restrict__ bias, const float * __restrict__ inv,
                                                          float * __restrict__ sel, float * __restrict__ sig) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float * h = H + (size_t) t * LKB_HIDDEN;
     float hv[LKB_HIDDEN / 32];
@@ -217,6 +221,7 @@ template <int TPT, int NW>
 __global__ void __launch_bounds__(32 * NW) k_pf_router_pipe(const float * __restrict__ H, int m, const float * __restrict__ Wr,
                                                         const float * __restrict__ bias, const float * __restrict__ inv,
                                                         float * __restrict__ sel, float * __restrict__ sig) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     constexpr int TT = 2 * NW * TPT, ROWS = TT + LKB_N_EXPERTS, NTILES = LKB_HIDDEN / RT_KT;
     extern __shared__ __align__(16) float rt_ring[];                   // [RT_STAGES][ROWS][RT_PITCH]
     const int tid = threadIdx.x, te = tid & 15, tg = tid >> 4;
@@ -308,7 +313,7 @@ static int rt_launch(const float * H, int m, const float * Wr, const float * bia
         if (cudaFuncSetAttribute(k_pf_router_pipe<TPT, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess) return -(int) cudaGetLastError();
         ready[dev] = 1;
     }
-    k_pf_router_pipe<TPT, NW><<<(m + TT - 1) / TT, 32 * NW, smem, st>>>(H, m, Wr, bias, inv, sel, sig);
+    LKB_PF_LAUNCH((k_pf_router_pipe<TPT, NW>), dim3((m + TT - 1) / TT), dim3(32 * NW), smem, st, H, m, Wr, bias, inv, sel, sig);
     return lkb_check_launch();
 }
 
@@ -316,6 +321,7 @@ static int rt_launch(const float * H, int m, const float * Wr, const float * bia
 // lkb_router_select shared with the decode router.  ref semantics: src/prefill.cu:1696-1708
 __global__ void __launch_bounds__(256) k_pf_select(const float * __restrict__ sel, const float * __restrict__ sig, int m,
                                                    int4 * __restrict__ idx, float4 * __restrict__ w) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int lane = threadIdx.x & 31;
     const int nw = gridDim.x * (blockDim.x >> 5);
     for (int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < m; t += nw) {
@@ -336,6 +342,7 @@ __global__ void __launch_bounds__(256) k_pf_select(const float * __restrict__ se
 // n is then the launch-time upper bound.
 __global__ void __launch_bounds__(256) k_pf_moe_count(const int * __restrict__ idx, int n, int * __restrict__ cnt,
                                                       const int * __restrict__ n_dev) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     if (n_dev) n = min(n, *n_dev);
     __shared__ int s_c[LKB_N_EXPERTS];
     if (threadIdx.x < LKB_N_EXPERTS) s_c[threadIdx.x] = 0;
@@ -348,6 +355,7 @@ __global__ void __launch_bounds__(256) k_pf_moe_count(const int * __restrict__ i
 // One warp: exclusive scan over the 64 counts, then tiles in expert order.
 __global__ void __launch_bounds__(32) k_pf_moe_plan(const int * __restrict__ cnt, int * __restrict__ off,
                                                     int4 * __restrict__ tiles, int * __restrict__ ntiles) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int lane = threadIdx.x;
     const int c0 = cnt[lane], c1 = cnt[lane + 32];
     const int n0 = (c0 + LKB_MOE_BN - 1) / LKB_MOE_BN, n1 = (c1 + LKB_MOE_BN - 1) / LKB_MOE_BN;
@@ -377,6 +385,7 @@ __global__ void __launch_bounds__(32) k_pf_moe_plan(const int * __restrict__ cnt
 // per-expert compaction (ref: src/prefill.cu:1733-1756) without re-reading idx 64x.
 __global__ void __launch_bounds__(1024) k_pf_moe_scatter(const int * __restrict__ idx, int n, const int * __restrict__ off,
                                                          int * __restrict__ perm, const int * __restrict__ n_dev) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     if (n_dev) n = min(n, *n_dev);
     if ((int) blockIdx.x * 1024 >= n) return;              // CTA-uniform: nothing of this chunk is live
     __shared__ int s_prior[LKB_N_EXPERTS];
@@ -410,6 +419,7 @@ __global__ void __launch_bounds__(1024) k_pf_moe_scatter(const int * __restrict_
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) k_pf_moe_combine(float4 * __restrict__ X, const float4 * __restrict__ D,
                                                         const float * __restrict__ w, int m) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int i = blockIdx.x * blockDim.x + threadIdx.x;          // float4 index into X
     if (i >= m * (LKB_HIDDEN / 4)) return;
     const int t = i / (LKB_HIDDEN / 4), c = i - t * (LKB_HIDDEN / 4);
@@ -429,6 +439,7 @@ __global__ void __launch_bounds__(256) k_pf_moe_combine(float4 * __restrict__ X,
 // ref semantics: src/prefill.cu:1819-1828
 __global__ void __launch_bounds__(512) k_pf_pack_q8_1(const int8_t * __restrict__ aqs, const float2 * __restrict__ asc, int t,
                                                       lkb_q8blk * __restrict__ y) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int b = threadIdx.x >> 3, wd = threadIdx.x & 7;
     reinterpret_cast<int *>(y[b].qs)[wd] = reinterpret_cast<const int *>(aqs + (size_t) t * LKB_HIDDEN + b * 32)[wd];
     if (wd == 0) {
@@ -449,6 +460,7 @@ __global__ void __launch_bounds__(192) k_ep_pack(const int8_t * __restrict__ aqs
                                                  const float * __restrict__ inv, const int * __restrict__ idx,
                                                  const int * __restrict__ send_order, int experts_per_rank,
                                                  unsigned char * __restrict__ out, int * __restrict__ pos) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int p = blockIdx.x, i = threadIdx.x;
     const int slot = send_order[p], t = slot >> 2;
     uint4 * row = reinterpret_cast<uint4 *>(out + (size_t) p * EP_ROW_BYTES);
@@ -464,6 +476,7 @@ __global__ void __launch_bounds__(192) k_ep_pack(const int8_t * __restrict__ aqs
 __global__ void __launch_bounds__(192) k_ep_unpack(const unsigned char * __restrict__ in, int8_t * __restrict__ qs,
                                                    float2 * __restrict__ sc, float * __restrict__ inv, int * __restrict__ le,
                                                    const int * __restrict__ n_dev) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int p = blockIdx.x, i = threadIdx.x;
     if (n_dev && p >= *n_dev) return;
     const uint4 * row = reinterpret_cast<const uint4 *>(in + (size_t) p * EP_ROW_BYTES);
@@ -489,6 +502,7 @@ __global__ void __launch_bounds__(192) k_ep_unpack(const unsigned char * __restr
 
 template <int EPI>
 __global__ void __launch_bounds__(256) k_pf_gemm_simple(const lkb_pf_gemm g, const int fold) {
+    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     __shared__ __align__(16) unsigned char s_w[64 * SG_WP];
     __shared__ __align__(16) __half        s_d[64 * SG_KB];
     __shared__ __align__(16) int8_t        s_a[64 * SG_KB * 32];
@@ -651,8 +665,8 @@ static int gemm_dispatch(const lkb_pf_gemm * g, int epi, int max_tiles, cudaStre
         if (g_gemm_cfg > 0) return t;
     }
     if (out_rows) return LKB_ERR_UNSUPPORTED;              // row targets exist in the tensor-core form only
-    if (epi) k_pf_gemm_simple<1><<<dim3(g->N / 32, ty), 256, 0, st>>>(*g, g_gemm_fold);
-    else     k_pf_gemm_simple<0><<<dim3(g->N / 64, ty), 256, 0, st>>>(*g, g_gemm_fold);
+    if (epi) LKB_PF_LAUNCH((k_pf_gemm_simple<1>), dim3(dim3(g->N / 32, ty)), dim3(256), 0, st, *g, g_gemm_fold);
+    else     LKB_PF_LAUNCH((k_pf_gemm_simple<0>), dim3(dim3(g->N / 64, ty)), dim3(256), 0, st, *g, g_gemm_fold);
     return lkb_check_launch();
 }
 
@@ -666,8 +680,8 @@ int lkb_pf_norm(const float * X, const float * w, int plain, lkb_pf_act a, float
     LKB_REQUIRE_INIT();
     if (!X || !w || !a.qs || !a.sc || !inv_out) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    if (plain) k_pf_token_norm_plain<<<(m + PF_TOK_WARPS - 1) / PF_TOK_WARPS, PF_TOK_WARPS * 32, 0, (cudaStream_t) st>>>(X, w, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out, m);
-    else       k_pf_token_norm<0><<<(m + PF_TOK_PER_CTA - 1) / PF_TOK_PER_CTA, PF_TOK_WARPS * 32, 0, (cudaStream_t) st>>>(const_cast<float *>(X), nullptr, nullptr, nullptr, w, a.qs,
+    if (plain) LKB_PF_LAUNCH(k_pf_token_norm_plain, dim3((m + PF_TOK_WARPS - 1) / PF_TOK_WARPS), dim3(PF_TOK_WARPS * 32), 0, (cudaStream_t) st, X, w, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out, m);
+    else       LKB_PF_LAUNCH((k_pf_token_norm<0>), dim3((m + PF_TOK_PER_CTA - 1) / PF_TOK_PER_CTA), dim3(PF_TOK_WARPS * 32), 0, (cudaStream_t) st, const_cast<float *>(X), nullptr, nullptr, nullptr, w, a.qs,
                                                                                   reinterpret_cast<float2 *>(a.sc), inv_out, h32, m);
     return lkb_check_launch();
 }
@@ -678,7 +692,7 @@ int lkb_pf_quant_rows(const float * X, int ld, int kb, lkb_pf_act a, int rows, l
     if (rows <= 0 || kb <= 0) return (rows == 0) ? LKB_OK : LKB_ERR_SHAPE;
     if ((ld & 3) || (reinterpret_cast<uintptr_t>(X) & 15)) return LKB_ERR_SHAPE;      // 128-bit loads
     const long long warps = (long long) rows * ((kb + 3) / 4);
-    k_pf_rows_q8<0><<<(unsigned) ((warps + 7) / 8), 256, 0, (cudaStream_t) st>>>(X, ld, 0, kb, rows, a.qs, reinterpret_cast<float2 *>(a.sc));
+    LKB_PF_LAUNCH((k_pf_rows_q8<0>), dim3((unsigned) ((warps + 7) / 8)), dim3(256), 0, (cudaStream_t) st, X, ld, 0, kb, rows, a.qs, reinterpret_cast<float2 *>(a.sc));
     return lkb_check_launch();
 }
 
@@ -688,7 +702,7 @@ int lkb_pf_swiglu(const float * Y, int ld, int up_off, int kb, lkb_pf_act a, int
     if (rows <= 0 || kb <= 0) return (rows == 0) ? LKB_OK : LKB_ERR_SHAPE;
     if ((ld & 3) || (up_off & 3) || (reinterpret_cast<uintptr_t>(Y) & 15)) return LKB_ERR_SHAPE;
     const long long warps = (long long) rows * ((kb + 3) / 4);
-    k_pf_rows_q8<1><<<(unsigned) ((warps + 7) / 8), 256, 0, (cudaStream_t) st>>>(Y, ld, up_off, kb, rows, a.qs, reinterpret_cast<float2 *>(a.sc));
+    LKB_PF_LAUNCH((k_pf_rows_q8<1>), dim3((unsigned) ((warps + 7) / 8)), dim3(256), 0, (cudaStream_t) st, Y, ld, up_off, kb, rows, a.qs, reinterpret_cast<float2 *>(a.sc));
     return lkb_check_launch();
 }
 
@@ -698,7 +712,7 @@ int lkb_pf_router_small(const float * H, int m, const float * Wr, const float * 
     if (!H || !Wr || !bias || !inv || !sel || !sig) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
     if (m > 65535) return LKB_ERR_SHAPE;
-    k_pf_router_token<<<m, 256, 0, (cudaStream_t) st>>>(H, Wr, bias, inv, sel, sig);
+    LKB_PF_LAUNCH(k_pf_router_token, dim3(m), dim3(256), 0, (cudaStream_t) st, H, Wr, bias, inv, sel, sig);
     return lkb_check_launch();
 }
 
@@ -723,7 +737,7 @@ int lkb_pf_select(const float * sel, const float * sig, int m, int * idx, float 
     LKB_REQUIRE_INIT();
     if (!sel || !sig || !idx || !w) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    k_pf_select<<<min((m + 7) / 8, 148 * 8), 256, 0, (cudaStream_t) st>>>(sel, sig, m, reinterpret_cast<int4 *>(idx), reinterpret_cast<float4 *>(w));
+    LKB_PF_LAUNCH(k_pf_select, dim3(min((m + 7) / 8, 148 * 8)), dim3(256), 0, (cudaStream_t) st, sel, sig, m, reinterpret_cast<int4 *>(idx), reinterpret_cast<float4 *>(w));
     return lkb_check_launch();
 }
 
@@ -732,7 +746,7 @@ int lkb_pf_moe_count(const int * idx, int n, int * cnt, lkb_stream_t st) {
     if (!idx || !cnt) return LKB_ERR_NULL;
     if (n <= 0) return n == 0 ? LKB_OK : LKB_ERR_SHAPE;
     int grid = (n + 255) / 256; if (grid > 64) grid = 64;
-    k_pf_moe_count<<<grid, 256, 0, (cudaStream_t) st>>>(idx, n, cnt, nullptr);
+    LKB_PF_LAUNCH(k_pf_moe_count, dim3(grid), dim3(256), 0, (cudaStream_t) st, idx, n, cnt, nullptr);
     return lkb_check_launch();
 }
 
@@ -746,7 +760,7 @@ int lkb_zero_i32(int * p, int n, lkb_stream_t st) {
 int lkb_pf_moe_plan(const int * cnt, int * off, int * tiles, int * ntiles, lkb_stream_t st) {
     LKB_REQUIRE_INIT();
     if (!cnt || !off || !tiles || !ntiles) return LKB_ERR_NULL;
-    k_pf_moe_plan<<<1, 32, 0, (cudaStream_t) st>>>(cnt, off, reinterpret_cast<int4 *>(tiles), ntiles);
+    LKB_PF_LAUNCH(k_pf_moe_plan, dim3(1), dim3(32), 0, (cudaStream_t) st, cnt, off, reinterpret_cast<int4 *>(tiles), ntiles);
     return lkb_check_launch();
 }
 
@@ -754,7 +768,7 @@ int lkb_pf_moe_scatter(const int * idx, int n, const int * off, int * perm, lkb_
     LKB_REQUIRE_INIT();
     if (!idx || !off || !perm) return LKB_ERR_NULL;
     if (n <= 0) return n == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    k_pf_moe_scatter<<<(n + 1023) / 1024, 1024, 0, (cudaStream_t) st>>>(idx, n, off, perm, nullptr);
+    LKB_PF_LAUNCH(k_pf_moe_scatter, dim3((n + 1023) / 1024), dim3(1024), 0, (cudaStream_t) st, idx, n, off, perm, nullptr);
     return lkb_check_launch();
 }
 
@@ -778,7 +792,7 @@ int lkb_pf_moe_combine(float * X, const float * D, const float * w, int m, lkb_s
     LKB_REQUIRE_INIT();
     if (!X || !D || !w) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    k_pf_moe_combine<<<m * (LKB_HIDDEN / 4 / 256), 256, 0, (cudaStream_t) st>>>(reinterpret_cast<float4 *>(X), reinterpret_cast<const float4 *>(D), w, m);
+    LKB_PF_LAUNCH(k_pf_moe_combine, dim3(m * (LKB_HIDDEN / 4 / 256)), dim3(256), 0, (cudaStream_t) st, reinterpret_cast<float4 *>(X), reinterpret_cast<const float4 *>(D), w, m);
     return lkb_check_launch();
 }
 
@@ -787,8 +801,7 @@ int lkb_pf_moe_combine_norm(float * X, const float * D, const float * w, const f
     LKB_REQUIRE_INIT();
     if (!X || !D || !w || !nw || !a.qs || !a.sc || !inv_out) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    k_pf_token_norm<1><<<(m + PF_TOK_PER_CTA - 1) / PF_TOK_PER_CTA, PF_TOK_WARPS * 32, 0, (cudaStream_t) st>>>(
-        X, D, nullptr, w, nw, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out, nullptr, m);
+    LKB_PF_LAUNCH((k_pf_token_norm<1>), dim3((m + PF_TOK_PER_CTA - 1) / PF_TOK_PER_CTA), dim3(PF_TOK_WARPS * 32), 0, (cudaStream_t) st, X, D, nullptr, w, nw, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out, nullptr, m);
     return lkb_check_launch();
 }
 
@@ -797,7 +810,7 @@ int lkb_ep_pack_rows(lkb_pf_act a, const float * inv, const int * idx, const int
     LKB_REQUIRE_INIT();
     if (!a.qs || !a.sc || !inv || !idx || !send_order || !out || !pos) return LKB_ERR_NULL;
     if (n <= 0 || experts_per_rank <= 0) return n == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    k_ep_pack<<<n, 192, 0, (cudaStream_t) st>>>(a.qs, reinterpret_cast<const float2 *>(a.sc), inv, idx, send_order,
+    LKB_PF_LAUNCH(k_ep_pack, dim3(n), dim3(192), 0, (cudaStream_t) st, a.qs, reinterpret_cast<const float2 *>(a.sc), inv, idx, send_order,
                                                 experts_per_rank, static_cast<unsigned char *>(out), pos);
     return lkb_check_launch();
 }
@@ -806,7 +819,7 @@ int lkb_ep_unpack_rows(const void * in, int n, lkb_pf_act a, float * inv, int * 
     LKB_REQUIRE_INIT();
     if (!in || !a.qs || !a.sc || !inv || !local_expert) return LKB_ERR_NULL;
     if (n <= 0) return n == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    k_ep_unpack<<<n, 192, 0, (cudaStream_t) st>>>(static_cast<const unsigned char *>(in), a.qs,
+    LKB_PF_LAUNCH(k_ep_unpack, dim3(n), dim3(192), 0, (cudaStream_t) st, static_cast<const unsigned char *>(in), a.qs,
                                                   reinterpret_cast<float2 *>(a.sc), inv, local_expert, nullptr);
     return lkb_check_launch();
 }
@@ -816,7 +829,7 @@ int lkb_ep_unpack_rows_dev(const void * in, int n, const int * n_dev, lkb_pf_act
     LKB_REQUIRE_INIT();
     if (!in || !n_dev || !a.qs || !a.sc || !inv || !local_expert) return LKB_ERR_NULL;
     if (n <= 0) return n == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    k_ep_unpack<<<n, 192, 0, (cudaStream_t) st>>>(static_cast<const unsigned char *>(in), a.qs,
+    LKB_PF_LAUNCH(k_ep_unpack, dim3(n), dim3(192), 0, (cudaStream_t) st, static_cast<const unsigned char *>(in), a.qs,
                                                   reinterpret_cast<float2 *>(a.sc), inv, local_expert, n_dev);
     return lkb_check_launch();
 }
@@ -825,14 +838,14 @@ int lkb_pf_moe_count_dev(const int * idx, int n, const int * n_dev, int * cnt, l
     if (!idx || !cnt || !n_dev) return LKB_ERR_NULL;
     if (n <= 0) return n == 0 ? LKB_OK : LKB_ERR_SHAPE;
     int grid = (n + 255) / 256; if (grid > 64) grid = 64;
-    k_pf_moe_count<<<grid, 256, 0, (cudaStream_t) st>>>(idx, n, cnt, n_dev);
+    LKB_PF_LAUNCH(k_pf_moe_count, dim3(grid), dim3(256), 0, (cudaStream_t) st, idx, n, cnt, n_dev);
     return lkb_check_launch();
 }
 int lkb_pf_moe_scatter_dev(const int * idx, int n, const int * n_dev, const int * off, int * perm, lkb_stream_t st) {
     LKB_REQUIRE_INIT();
     if (!idx || !off || !perm || !n_dev) return LKB_ERR_NULL;
     if (n <= 0) return n == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    k_pf_moe_scatter<<<(n + 1023) / 1024, 1024, 0, (cudaStream_t) st>>>(idx, n, off, perm, n_dev);
+    LKB_PF_LAUNCH(k_pf_moe_scatter, dim3((n + 1023) / 1024), dim3(1024), 0, (cudaStream_t) st, idx, n, off, perm, n_dev);
     return lkb_check_launch();
 }
 
@@ -841,8 +854,7 @@ int lkb_pf_moe_combine_norm_gather(float * X, const float * D, const int * pos, 
     LKB_REQUIRE_INIT();
     if (!X || !D || !pos || !w || !nw || !a.qs || !a.sc || !inv_out) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    k_pf_token_norm<2><<<(m + PF_TOK_PER_CTA - 1) / PF_TOK_PER_CTA, PF_TOK_WARPS * 32, 0, (cudaStream_t) st>>>(
-        X, D, pos, w, nw, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out, nullptr, m);
+    LKB_PF_LAUNCH((k_pf_token_norm<2>), dim3((m + PF_TOK_PER_CTA - 1) / PF_TOK_PER_CTA), dim3(PF_TOK_WARPS * 32), 0, (cudaStream_t) st, X, D, pos, w, nw, a.qs, reinterpret_cast<float2 *>(a.sc), inv_out, nullptr, m);
     return lkb_check_launch();
 }
 
@@ -850,7 +862,7 @@ int lkb_pf_pack_q8_1(lkb_pf_act a, int t, lkb_block_q8_1 * y, lkb_stream_t st) {
     LKB_REQUIRE_INIT();
     if (!a.qs || !a.sc || !y) return LKB_ERR_NULL;
     if (t < 0) return LKB_ERR_SHAPE;
-    k_pf_pack_q8_1<<<1, 512, 0, (cudaStream_t) st>>>(a.qs, reinterpret_cast<const float2 *>(a.sc), t, reinterpret_cast<lkb_q8blk *>(y));
+    LKB_PF_LAUNCH(k_pf_pack_q8_1, dim3(1), dim3(512), 0, (cudaStream_t) st, a.qs, reinterpret_cast<const float2 *>(a.sc), t, reinterpret_cast<lkb_q8blk *>(y));
     return lkb_check_launch();
 }
 
