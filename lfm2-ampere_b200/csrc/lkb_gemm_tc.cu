@@ -17,12 +17,14 @@
 //
 // One MMA per 32-element block: K = 32 int8 is exactly one Q4_0/Q8_1 block, and the per-block scales forbid
 // accumulating across blocks inside the tensor core, so every block's 128x128 int32 result is read back from
-// TMEM and folded into fp32 register accumulators by the CUDA cores: two FMAs per value, no conversion -- the
-// TMEM buffer is PRESET to 0x4B400000 by the epilogue warp that drained it and the MMA accumulates onto it,
-// so what comes back already is F_b.  That epilogue (256 FMA-pipe cycles per block and SM) bounds the kernel,
-// not the MMA (64); measured costs on B200 that shaped it: a TMEM load occupies a scheduler's TMEM port ~26
-// cycles whether it moves 8 or 32 columns, a TMEM store ~1.2 cycles per column; an integer-to-float conversion
-// runs at a quarter of the FMA rate; a warp-uniform 16-byte shared-memory load costs two wavefronts.
+// TMEM and folded into fp32 register accumulators by the CUDA cores: two FMAs per value and no conversion --
+// F_b is the loaded int32 plus 0x4B400000 as an INTEGER add, which rides on the move that pairs two columns for
+// the packed FMA (no extra instruction).  That epilogue (256 FMA-pipe cycles per block and SM) bounds the
+// kernel, not the MMA (64); measured costs on B200 that shaped it: a TMEM load occupies a scheduler's TMEM port
+// ~26 cycles whether it moves 8 or 32 columns, a TMEM store ~1.2 cycles per column (presetting the buffers to
+// the offset and letting the MMA accumulate onto it cost 789 / 402 us per layer against 721 / 383 us with the
+// integer add); an integer-to-float conversion runs at a quarter of the FMA rate; a warp-uniform 16-byte
+// shared-memory load costs two wavefronts.
 //   * M (TMEM lanes) = 128 tokens, N (TMEM columns) = 128 weight rows.  A thread owns one token and 64 columns:
 //     d8 / c are per-thread scalars, and in the SwiGLU form its columns are the gate AND up rows of one 32-row
 //     Q8_1 output block, which it quantises alone, in the standard butterfly order (bit-identical to the
@@ -150,9 +152,9 @@ __device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_commit(unsigned long long * b) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(tc_smem_u32(b)) : "memory");
 }
-// D += A*B (the accumulator holds the preset offset)
+// D = A*B (the TMEM buffer is overwritten: enable-input-d predicate false)
 __device__ __forceinline__ void tc_mma_i8(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned idesc) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, 1, 0;\n"
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, 0, 0;\n"
                  " tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}"
                  :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc) : "memory");
 }
@@ -175,16 +177,7 @@ __device__ __forceinline__ void tc_ld32(unsigned taddr, unsigned (&r)[32]) {
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr) : "memory");
 }
-// 32 columns of this warp's 32 lanes <- v, as two stores of 16 (a store's source is a run of distinct registers:
-// one 32-column store would pin 32 registers on the constant)
-__device__ __forceinline__ void tc_st32(unsigned taddr, unsigned v) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
-                 :: "r"(taddr), "r"(v) : "memory");
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
-                 :: "r"(taddr + 16u), "r"(v) : "memory");
-}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // Two independent IEEE fused multiply-adds in one instruction (half the issue slots of the epilogue).
 __device__ __forceinline__ unsigned long long tc_pack(float x, float y) {
     unsigned long long r;
@@ -230,8 +223,8 @@ __device__ __forceinline__ void tc_fold32(unsigned long long (&acc)[32], const u
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const float4 dd = *reinterpret_cast<const float4 *>(d4c + 4 * i);
-        unsigned long long f0 = tc_pack_u(sv[4 * i], sv[4 * i + 1]);         // (F, F) of two columns
-        unsigned long long f1 = tc_pack_u(sv[4 * i + 2], sv[4 * i + 3]);
+        unsigned long long f0 = tc_pack_u(sv[4 * i] + TC_MAGIC_I, sv[4 * i + 1] + TC_MAGIC_I);   // (F, F) of two columns
+        unsigned long long f1 = tc_pack_u(sv[4 * i + 2] + TC_MAGIC_I, sv[4 * i + 3] + TC_MAGIC_I);
         if (!FOLD) { f0 = tc_fadd2(f0, nmag); f1 = tc_fadd2(f1, nmag); }       // float(S), exact
         f0 = tc_ffma2(d8p, f0, ncp);
         f1 = tc_ffma2(d8p, f1, ncp);
@@ -569,7 +562,7 @@ __global__ void __launch_bounds__(TcCfg<EPI>::THREADS, 1) k_pf_gemm_tc(const lkb
 #pragma unroll
                     for (int j = 0; j < TC_KB; ++j, ++blk) {
                         const int tb = blk % TC_TBUF;
-                        // use k of a buffer waits for phase k: the epilogue presets and releases it once up front,
+                        // use k of a buffer waits for phase k: the epilogue releases every buffer once up front,
                         // then after every read
                         TC_TL(3, blk, 0);
                         if (!tc_wait<TC_HINT_MMA>(S, &S.tempty[tb], (blk / TC_TBUF) & 1u, 21u)) { ok = false; break; }
@@ -599,10 +592,7 @@ __global__ void __launch_bounds__(TcCfg<EPI>::THREADS, 1) k_pf_gemm_tc(const lkb
         // EPI 1: the expansion warps place gate rows [32 half, +32) of the item in columns [c0, +32) and the same up rows
         // in [c0 + 32, +32): acc[0..15] are gate pairs and acc[16..31] the matching up pairs.
         const unsigned tbase = tmem + ((unsigned) (quad * 32) << 16) + c0;
-        // preset this warp's part of every buffer, then hand them to the MMA issuer
-#pragma unroll
-        for (int tb = 0; tb < TC_TBUF; ++tb) { tc_st32(tbase + tb * TC_N, TC_MAGIC_I); tc_st32(tbase + tb * TC_N + 32, TC_MAGIC_I); }
-        tc_wait_st();
+        // all four buffers start out free for the MMA issuer
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
@@ -639,12 +629,9 @@ __global__ void __launch_bounds__(TcCfg<EPI>::THREADS, 1) k_pf_gemm_tc(const lkb
                     if (ptid == 0) TC_TL(4, it * TC_KB + j, 0);
                     tc_wait_ld();                                   // first half of this block is in svA
                     if (ptid == 0) TC_TL(4, it * TC_KB + j, 1);
-                    tc_st32(ta, TC_MAGIC_I);                        // its columns start the buffer's next block from the offset
                     tc_ld32(ta + 32, svB);                          // second half in flight ...
                     tc_fold32<FOLD, 0>(acc, svA, &T.d4[j][c0], d8p, ncp);        // ... while the first is folded
                     tc_wait_ld();
-                    tc_st32(ta + 32, TC_MAGIC_I);
-                    tc_wait_st();
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) tc_mbar_arrive(&S.tempty[j]);    // TMEM buffer is free again
