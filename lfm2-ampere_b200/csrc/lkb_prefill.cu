@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(256) k_pf_router_token(const float * __restric
 #define RT_L_NW  4          // 8 warps x 4 tokens 94 us, 4 warps x 2 tokens 76 us; the k loop of one CTA is the critical path)
 #endif
 #ifndef RT_S_TPT
-#define RT_S_TPT 2          // short form (a chunk share of expert-parallel prefill): 4 warps, 16 tokens per CTA (55 us up to 2048 tokens)
+#define RT_S_TPT 2          // middle form: 4 warps, 16 tokens per CTA
 #define RT_S_NW  4
 #endif
 __device__ __forceinline__ void rt_cp16(float * dst, const float * src, bool live) {
@@ -721,9 +721,14 @@ int lkb_pf_router_tiled(const float * H, int m, const float * Wr, const float * 
     LKB_REQUIRE_INIT();
     if (!H || !Wr || !bias || !inv || !sel || !sig) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    // short token ranges (a chunk share of expert-parallel prefill) run 16 tokens per CTA so that more SMs take part
-    static const int form = [] { const char * e = getenv("LKB_ROUTER_FORM"); return e ? atoi(e) : 0; }();   // 16 / 32 force a form (tuning)
-    if (form == 16 || (form != 32 && m <= 16 * lkb_context().sm_count)) return rt_launch<RT_S_TPT, RT_S_NW>(H, m, Wr, bias, inv, sel, sig, (cudaStream_t) st);
+    // The k loop of one CTA is the critical path and its length grows with the tokens per thread, so a token range takes
+    // the smallest CTA shape that still fits one wave (measured on B200, us: 8-token CTAs 36 up to 1184 tokens, 66 at 2048;
+    // 16-token CTAs 43 up to 2368, 68-78 at 4096; 32-token CTAs 55 at any size up to 4736).  A rank's share of an
+    // expert-parallel chunk lands in the first two.  LKB_ROUTER_FORM = 8 / 16 / 32 forces a shape (tuning).
+    static const int form = [] { const char * e = getenv("LKB_ROUTER_FORM"); return e ? atoi(e) : 0; }();
+    const int sms = lkb_context().sm_count;
+    if (form == 8 || (form == 0 && m <= 8 * sms)) return rt_launch<1, 4>(H, m, Wr, bias, inv, sel, sig, (cudaStream_t) st);
+    if (form == 16 || (form == 0 && m <= 16 * sms)) return rt_launch<RT_S_TPT, RT_S_NW>(H, m, Wr, bias, inv, sel, sig, (cudaStream_t) st);
     return rt_launch<RT_L_TPT, RT_L_NW>(H, m, Wr, bias, inv, sel, sig, (cudaStream_t) st);
 }
 
