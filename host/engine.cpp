@@ -250,8 +250,7 @@ void prefill_chunk(Engine & e, lk::stream_t st, const int * toks_host, int m, in
         // MoE FFN.  ref: src/engine.cu:1170-1241
         const lkb_moe_layer & l = e.moe[i];
         lk::k_pf_norm(st, m, e.X, l.norm_w, 0, a, e.inv, e.h32);
-        lk::check(lkb_pf_router(e.h32, m, l.router, l.rbias, e.inv, e.sel, e.sig, st), "k_pf_router");
-        lk::k_pf_select(st, e.sel, e.sig, m, e.idx, e.w);
+        lk::check(lkb_pf_router_select(e.h32, m, m <= 256, l.router, l.rbias, e.inv, e.sel, e.sig, e.idx, e.w, st), "k_pf_router + k_pf_select");
         lk::check(lkb_zero_i32(e.cnt, E, st), "lkb_zero_i32");
         lk::k_pf_moe_count(st, e.idx, ns, e.cnt);
         lk::k_pf_moe_plan(st, e.cnt, e.off, e.tiles, e.ntiles);

@@ -301,6 +301,11 @@ int lkb_pf_router_small(const float * H, int m, const float * Wr, const float * 
                         float * sel, float * sig, lkb_stream_t st);
 /* ref: src/prefill.cuh:115-116  k_pf_select */
 int lkb_pf_select(const float * sel, const float * sig, int m, int * idx, float * w, lkb_stream_t st);
+/* lkb_pf_router_small (small_form != 0) or lkb_pf_router_tiled followed by lkb_pf_select, in ONE launch: the CTA that
+ * produced a token's 64 sel / sig values selects its top-4 from shared memory (sel / sig are still written).  Same
+ * results as the two calls.  No counterpart in the reference (its engine launches the two kernels, src/engine.cu:1170-1180). */
+int lkb_pf_router_select(const float * H, int m, int small_form, const float * Wr, const float * bias, const float * inv,
+                         float * sel, float * sig, int * idx, float * w, lkb_stream_t st);
 /* ref: src/prefill.cuh:117-122  k_pf_moe_count / _plan / _scatter.  cnt must be
  * zero on entry to count (the engine memsets it, ref: src/engine.cu:1182). */
 int lkb_pf_moe_count(const int * idx, int n, int * cnt, lkb_stream_t st);
@@ -475,6 +480,9 @@ int lkb_ep_route_experts(const void * recv, int cap, const int * flags, int G, c
  * store at the end of lkb_ep_push_back, which this pair replaces). */
 int lkb_pf_gemm_moe_rows(const lkb_pf_gemm * g, int max_tiles, float * const * out_rows, lkb_stream_t st);
 int lkb_ep_publish(const lkb_ep_peers * peers, int me, int G, int phase, const int * epoch, lkb_stream_t st);
+/* lkb_ep_publish followed by lkb_ep_wait(flags, phase, ...) in one launch.  No counterpart in the reference. */
+int lkb_ep_publish_wait(const lkb_ep_peers * peers, int me, int G, int phase, const int * epoch, const int * flags, int * status,
+                        lkb_stream_t st);
 int lkb_ep_push_back(const float * D, const int * offs, int max_rows, const lkb_ep_peers * peers, int me, int G,
                      const int * epoch, unsigned * done, lkb_stream_t st);
 /* No counterpart in the reference: the unpack / count / scatter kernels with the live row count on the device. */

@@ -17,7 +17,7 @@ __all__ = [
     "k_quantize_q8_1", "k_rmsnorm_q8_1", "norm_produce", "k_gemv_q4_0", "k_gemv_q4_0_prod", "k_gemv_q4_0_3",
     "k_gemv_q4_0_exp2", "k_gemv_q4_0_exp", "k_swiglu", "k_moe_accum4", "k_moe_down_accum", "k_router_dot",
     "k_router_top4", "router_top4_softmax", "block_sumi", "k_pf_norm", "k_pf_quant_rows", "k_pf_swiglu",
-    "k_pf_router", "k_pf_router_small", "k_pf_router_tiled", "k_pf_select", "k_pf_moe_count", "k_pf_moe_plan", "k_pf_moe_scatter",
+    "k_pf_router", "k_pf_router_small", "k_pf_router_tiled", "k_pf_router_select", "k_pf_select", "k_pf_moe_count", "k_pf_moe_plan", "k_pf_moe_scatter",
     "pf_gemm_dense", "pf_gemm_moe", "pf_gemm_swiglu", "k_pf_moe_combine", "k_pf_moe_combine_norm",
     "k_pf_pack_q8_1", "zero_i32", "moe_layer_desc", "moe_scratch", "moe_ffn_decode", "moe_ffn_decode_stack",
     "layer_descs_to_device", "ep_pack_rows", "ep_unpack_rows", "k_pf_moe_combine_norm_gather", "moe_ffn_decode_stack_static", "set_pdl", "pf_gemm_config", "pf_gemm_arith", "pf_gemm_workspace_bytes", "pf_gemm_set_workspace", "sm_count",
@@ -25,7 +25,7 @@ __all__ = [
     "k_attn_split", "k_attn_combine", "k_qk_norm_rope", "k_shortconv", "ATTN_SPLIT", "ATTN_PARTW",
     "mixer_layer_desc", "step_scratch", "decode_layers",
     "k_pf_embed", "k_pf_conv", "k_pf_conv_hist", "k_pf_qknr", "k_pf_attn",
-    "ep_peers", "EP_ROW_BYTES", "ep_set_wait_limit_ms", "ep_counts_exchange", "ep_route_exchange", "ep_route_experts", "pf_gemm_moe_rows", "ep_publish", "ep_pack_push", "ep_wait", "ep_push_back", "ep_unpack_rows_dev", "k_pf_moe_count_dev",
+    "ep_peers", "EP_ROW_BYTES", "ep_set_wait_limit_ms", "ep_counts_exchange", "ep_route_exchange", "ep_route_experts", "pf_gemm_moe_rows", "ep_publish", "ep_publish_wait", "ep_pack_push", "ep_wait", "ep_push_back", "ep_unpack_rows_dev", "k_pf_moe_count_dev",
     "k_pf_moe_scatter_dev",
 ]
 
@@ -172,6 +172,11 @@ def k_pf_swiglu(Y, ld, up_off, kb, a, rows):
 
 def k_pf_router(H, m, Wr, bias, inv, sel, sig):
     check(lib.lkb_pf_router(ptr(H), m, ptr(Wr), ptr(bias), ptr(inv), ptr(sel), ptr(sig), stream()), "k_pf_router")
+
+
+def k_pf_router_select(H, m, small_form, Wr, bias, inv, sel, sig, idx, w):
+    check(lib.lkb_pf_router_select(ptr(H), m, int(bool(small_form)), ptr(Wr), ptr(bias), ptr(inv), ptr(sel), ptr(sig), ptr(idx), ptr(w),
+                                   stream()), "k_pf_router_select")
 
 
 def k_pf_router_tiled(H, m, Wr, bias, inv, sel, sig):
@@ -410,6 +415,10 @@ def ep_route_experts(recv, cap, flags, G, epoch, offs, cnt, off, tiles, ntiles, 
 
 def pf_gemm_moe_rows(g, max_tiles, out_rows):
     check(lib.lkb_pf_gemm_moe_rows(C.byref(g), max_tiles, ptr(out_rows), stream()), "pf_gemm_moe_rows")
+
+
+def ep_publish_wait(peers, me, G, phase, epoch, flags, status):
+    check(lib.lkb_ep_publish_wait(C.byref(peers), me, G, phase, ptr(epoch), ptr(flags), ptr(status), stream()), "ep_publish_wait")
 
 
 def ep_publish(peers, me, G, phase, epoch):

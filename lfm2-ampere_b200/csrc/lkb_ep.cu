@@ -290,10 +290,14 @@ __global__ void __launch_bounds__(1024) k_ep_route_experts(const unsigned char *
 
 // Publish `phase` of this epoch to every rank: the stores of the kernels before this one on the stream (the grouped
 // GEMM writing result rows straight into their home ranks' buffers) are complete when this kernel starts.
-__global__ void __launch_bounds__(32) k_ep_publish(EpPeers P, int me, int G, int phase, const int * __restrict__ epoch_dev) {
+__global__ void __launch_bounds__(32) k_ep_publish(EpPeers P, int me, int G, int phase, const int * __restrict__ epoch_dev,
+                                                   const int * __restrict__ wait_flags, int * __restrict__ status, unsigned long long limit_ns) {
     lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     __threadfence_system();
-    if ((int) threadIdx.x < G) ep_st_release(P.flags[threadIdx.x] + phase * EP_MAX_RANKS + me, *epoch_dev);
+    const int epoch = *epoch_dev;
+    if ((int) threadIdx.x < G) ep_st_release(P.flags[threadIdx.x] + phase * EP_MAX_RANKS + me, epoch);
+    // optionally the wait for the same phase of every source in the same launch (lkb_ep_wait's job)
+    if (wait_flags && (int) threadIdx.x < G) ep_wait_flag(wait_flags, phase, threadIdx.x, epoch, status, 2 + phase, limit_ns);
 }
 
 static int ep_peers(EpPeers & P, const void * const * cmat, const void * const * flags, const void * const * recv,
@@ -366,7 +370,19 @@ int lkb_ep_publish(const lkb_ep_peers * peers, int me, int G, int phase, const i
     const int r = ep_peers(P, peers->cmat, peers->flags, peers->recv, peers->dback, G);
     if (r != LKB_OK) return r;
     if (me < 0 || me >= G || phase < 0 || phase > 2) return LKB_ERR_SHAPE;
-    LKB_PF_LAUNCH(k_ep_publish, dim3(1), dim3(32), 0, (cudaStream_t) st, P, me, G, phase, epoch);
+    LKB_PF_LAUNCH(k_ep_publish, dim3(1), dim3(32), 0, (cudaStream_t) st, P, me, G, phase, epoch, (const int *) nullptr, (int *) nullptr, 0ull);
+    return lkb_check_launch();
+}
+
+int lkb_ep_publish_wait(const lkb_ep_peers * peers, int me, int G, int phase, const int * epoch, const int * flags, int * status,
+                        lkb_stream_t st) {
+    if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
+    if (!peers || !epoch || !flags || !status) return LKB_ERR_NULL;
+    EpPeers P = {};
+    const int r = ep_peers(P, peers->cmat, peers->flags, peers->recv, peers->dback, G);
+    if (r != LKB_OK) return r;
+    if (me < 0 || me >= G || phase < 0 || phase > 2) return LKB_ERR_SHAPE;
+    LKB_PF_LAUNCH(k_ep_publish, dim3(1), dim3(32), 0, (cudaStream_t) st, P, me, G, phase, epoch, flags, status, g_ep_limit_ns);
     return lkb_check_launch();
 }
 

@@ -161,8 +161,10 @@ __global__ void __launch_bounds__(256) k_pf_rows_q8(const float * __restrict__ Y
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) k_pf_router_token(const float * __restrict__ H, const float * __restrict__ Wr,
                                                          const float * __restrict__ bias, const float * __restrict__ inv,
-                                                         float * __restrict__ sel, float * __restrict__ sig) {
+                                                         float * __restrict__ sel, float * __restrict__ sig,
+                                                         int4 * __restrict__ idx, float4 * __restrict__ wout) {
     lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
+    __shared__ float s_sel[LKB_N_EXPERTS], s_sig[LKB_N_EXPERTS];
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float * h = H + (size_t) t * LKB_HIDDEN;
     float hv[LKB_HIDDEN / 32];
@@ -181,8 +183,18 @@ __global__ void __launch_bounds__(256) k_pf_router_token(const float * __restric
         const int e = warp * 8 + lane;
         const float l = __fmul_rn(mine, inv[t]);
         const float gv = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-l)));
+        const float sv = __fadd_rn(gv, bias[e]);
         sig[(size_t) t * 64 + e] = gv;
-        sel[(size_t) t * 64 + e] = __fadd_rn(gv, bias[e]);
+        sel[(size_t) t * 64 + e] = sv;
+        s_sig[e] = gv; s_sel[e] = sv;
+    }
+    if (idx) {                                             // the selection in the same launch (lkb_pf_select's result)
+        __syncthreads();
+        if (warp == 0) {
+            int ord[LKB_TOP_K]; float wv[LKB_TOP_K];
+            lkb_router_select(s_sel, s_sig, lane, ord, wv);
+            if (lane == 0) { idx[t] = make_int4(ord[0], ord[1], ord[2], ord[3]); wout[t] = make_float4(wv[0], wv[1], wv[2], wv[3]); }
+        }
     }
 }
 
@@ -220,7 +232,8 @@ __device__ __forceinline__ void rt_cp16(float * dst, const float * src, bool liv
 template <int TPT, int NW>
 __global__ void __launch_bounds__(32 * NW) k_pf_router_pipe(const float * __restrict__ H, int m, const float * __restrict__ Wr,
                                                         const float * __restrict__ bias, const float * __restrict__ inv,
-                                                        float * __restrict__ sel, float * __restrict__ sig) {
+                                                        float * __restrict__ sel, float * __restrict__ sig,
+                                                        int4 * __restrict__ idx, float4 * __restrict__ wout) {
     lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     constexpr int TT = 2 * NW * TPT, ROWS = TT + LKB_N_EXPERTS, NTILES = LKB_HIDDEN / RT_KT;
     extern __shared__ __align__(16) float rt_ring[];                   // [RT_STAGES][ROWS][RT_PITCH]
@@ -286,9 +299,12 @@ __global__ void __launch_bounds__(32 * NW) k_pf_router_pipe(const float * __rest
                 for (int q = 0; q < 4; ++q) acc[i][q] = fmaf(h[i].w, w[q].w, acc[i][q]);
         }
     }
+    // the ring is free after the last tile: the CTA's sel / sig rows pass through it to the selection warps
+    float * s_sel = rt_ring, * s_sig = rt_ring + TT * LKB_N_EXPERTS;
+    if (idx) __syncthreads();
 #pragma unroll
     for (int i = 0; i < TPT; ++i) {
-        const int tk = t0 + tg * TPT + i;
+        const int tl = tg * TPT + i, tk = t0 + tl;
         if (tk >= m) continue;
         const float iv = inv[tk];
 #pragma unroll
@@ -296,14 +312,27 @@ __global__ void __launch_bounds__(32 * NW) k_pf_router_pipe(const float * __rest
             const int e = te + 16 * q;
             const float l = __fmul_rn(acc[i][q], iv);
             const float gv = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-l)));
+            const float sv = __fadd_rn(gv, bias[e]);
             sig[(size_t) tk * 64 + e] = gv;
-            sel[(size_t) tk * 64 + e] = __fadd_rn(gv, bias[e]);
+            sel[(size_t) tk * 64 + e] = sv;
+            if (idx) { s_sig[tl * LKB_N_EXPERTS + e] = gv; s_sel[tl * LKB_N_EXPERTS + e] = sv; }
+        }
+    }
+    if (idx) {                                             // the selection in the same launch (lkb_pf_select's result)
+        __syncthreads();
+        const int warp = tid >> 5, lane = tid & 31;
+        for (int tl = warp; tl < TT; tl += NW) {
+            const int tk = t0 + tl;
+            if (tk >= m) break;
+            int ord[LKB_TOP_K]; float wv[LKB_TOP_K];
+            lkb_router_select(s_sel + tl * LKB_N_EXPERTS, s_sig + tl * LKB_N_EXPERTS, lane, ord, wv);
+            if (lane == 0) { idx[tk] = make_int4(ord[0], ord[1], ord[2], ord[3]); wout[tk] = make_float4(wv[0], wv[1], wv[2], wv[3]); }
         }
     }
 }
 template <int TPT, int NW>
 static int rt_launch(const float * H, int m, const float * Wr, const float * bias, const float * inv, float * sel, float * sig,
-                     cudaStream_t st) {
+                     int * idx, float * w, cudaStream_t st) {
     constexpr int TT = 2 * NW * TPT;
     constexpr size_t smem = (size_t) RT_STAGES * (TT + LKB_N_EXPERTS) * RT_PITCH * sizeof(float);
     static int ready[LKB_STATIC_MAX_DEVICES] = {0};
@@ -313,7 +342,8 @@ static int rt_launch(const float * H, int m, const float * Wr, const float * bia
         if (cudaFuncSetAttribute(k_pf_router_pipe<TPT, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess) return -(int) cudaGetLastError();
         ready[dev] = 1;
     }
-    LKB_PF_LAUNCH((k_pf_router_pipe<TPT, NW>), dim3((m + TT - 1) / TT), dim3(32 * NW), smem, st, H, m, Wr, bias, inv, sel, sig);
+    LKB_PF_LAUNCH((k_pf_router_pipe<TPT, NW>), dim3((m + TT - 1) / TT), dim3(32 * NW), smem, st, H, m, Wr, bias, inv, sel, sig,
+                  reinterpret_cast<int4 *>(idx), reinterpret_cast<float4 *>(w));
     return lkb_check_launch();
 }
 
@@ -706,18 +736,19 @@ int lkb_pf_swiglu(const float * Y, int ld, int up_off, int kb, lkb_pf_act a, int
     return lkb_check_launch();
 }
 
-int lkb_pf_router_small(const float * H, int m, const float * Wr, const float * bias, const float * inv,
-                        float * sel, float * sig, lkb_stream_t st) {
+static int router_small(const float * H, int m, const float * Wr, const float * bias, const float * inv,
+                        float * sel, float * sig, int * idx, float * w, lkb_stream_t st) {
     LKB_REQUIRE_INIT();
     if (!H || !Wr || !bias || !inv || !sel || !sig) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
     if (m > 65535) return LKB_ERR_SHAPE;
-    LKB_PF_LAUNCH(k_pf_router_token, dim3(m), dim3(256), 0, (cudaStream_t) st, H, Wr, bias, inv, sel, sig);
+    LKB_PF_LAUNCH(k_pf_router_token, dim3(m), dim3(256), 0, (cudaStream_t) st, H, Wr, bias, inv, sel, sig,
+                  reinterpret_cast<int4 *>(idx), reinterpret_cast<float4 *>(w));
     return lkb_check_launch();
 }
 
-int lkb_pf_router_tiled(const float * H, int m, const float * Wr, const float * bias, const float * inv,
-                        float * sel, float * sig, lkb_stream_t st) {
+static int router_tiled(const float * H, int m, const float * Wr, const float * bias, const float * inv,
+                        float * sel, float * sig, int * idx, float * w, lkb_stream_t st) {
     LKB_REQUIRE_INIT();
     if (!H || !Wr || !bias || !inv || !sel || !sig) return LKB_ERR_NULL;
     if (m <= 0) return m == 0 ? LKB_OK : LKB_ERR_SHAPE;
@@ -727,15 +758,28 @@ int lkb_pf_router_tiled(const float * H, int m, const float * Wr, const float * 
     // expert-parallel chunk lands in the first two.  LKB_ROUTER_FORM = 8 / 16 / 32 forces a shape (tuning).
     static const int form = [] { const char * e = getenv("LKB_ROUTER_FORM"); return e ? atoi(e) : 0; }();
     const int sms = lkb_context().sm_count;
-    if (form == 8 || (form == 0 && m <= 8 * sms)) return rt_launch<1, 4>(H, m, Wr, bias, inv, sel, sig, (cudaStream_t) st);
-    if (form == 16 || (form == 0 && m <= 16 * sms)) return rt_launch<RT_S_TPT, RT_S_NW>(H, m, Wr, bias, inv, sel, sig, (cudaStream_t) st);
-    return rt_launch<RT_L_TPT, RT_L_NW>(H, m, Wr, bias, inv, sel, sig, (cudaStream_t) st);
+    if (form == 8 || (form == 0 && m <= 8 * sms)) return rt_launch<1, 4>(H, m, Wr, bias, inv, sel, sig, idx, w, (cudaStream_t) st);
+    if (form == 16 || (form == 0 && m <= 16 * sms)) return rt_launch<RT_S_TPT, RT_S_NW>(H, m, Wr, bias, inv, sel, sig, idx, w, (cudaStream_t) st);
+    return rt_launch<RT_L_TPT, RT_L_NW>(H, m, Wr, bias, inv, sel, sig, idx, w, (cudaStream_t) st);
 }
 
+int lkb_pf_router_small(const float * H, int m, const float * Wr, const float * bias, const float * inv,
+                        float * sel, float * sig, lkb_stream_t st) {
+    return router_small(H, m, Wr, bias, inv, sel, sig, nullptr, nullptr, st);
+}
+int lkb_pf_router_tiled(const float * H, int m, const float * Wr, const float * bias, const float * inv,
+                        float * sel, float * sig, lkb_stream_t st) {
+    return router_tiled(H, m, Wr, bias, inv, sel, sig, nullptr, nullptr, st);
+}
 int lkb_pf_router(const float * H, int m, const float * Wr, const float * bias, const float * inv,
                   float * sel, float * sig, lkb_stream_t st) {
     if (m > 0 && m <= 256) return lkb_pf_router_small(H, m, Wr, bias, inv, sel, sig, st);
     return lkb_pf_router_tiled(H, m, Wr, bias, inv, sel, sig, st);
+}
+int lkb_pf_router_select(const float * H, int m, int small_form, const float * Wr, const float * bias, const float * inv,
+                         float * sel, float * sig, int * idx, float * w, lkb_stream_t st) {
+    if (!idx || !w) return LKB_ERR_NULL;
+    return small_form ? router_small(H, m, Wr, bias, inv, sel, sig, idx, w, st) : router_tiled(H, m, Wr, bias, inv, sel, sig, idx, w, st);
 }
 
 int lkb_pf_select(const float * sel, const float * sig, int m, int * idx, float * w, lkb_stream_t st) {

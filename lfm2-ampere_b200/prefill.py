@@ -1,7 +1,7 @@
 """Batched prefill of the MoE FFN stack on one GPU: the host-side call sequence of the
 reference's pf_chunk() for this path (ref: src/engine.cu:1170-1241), one C-ABI call per
 reference kernel / launcher:
-  k_pf_norm(ffn_norm) -> k_pf_router -> k_pf_select -> memset(cnt) -> k_pf_moe_count ->
+  k_pf_norm(ffn_norm) -> k_pf_router + k_pf_select (one launch) -> memset(cnt) -> k_pf_moe_count ->
   k_pf_moe_plan -> k_pf_moe_scatter -> pf_gemm_swiglu (gate|up, a_shift 2, scale inv) ->
   pf_gemm_moe (down, a_shift 0) -> k_pf_moe_combine_norm (next layer's first norm)."""
 from __future__ import annotations
@@ -59,7 +59,7 @@ class PrefillStack:
         self.an = api.pf_act(self.n_qs, self.n_sc)
         # caller-owned workspace of the grouped GEMM: activation rows in token-tile order (widest: the gate|up input)
         self.gemm_ws = torch.zeros(api.pf_gemm_workspace_bytes(self.max_tiles, H), dtype=torch.uint8, device=device)
-        self.launches_per_step = 11 * len(layers)       # kernels per layer (the memset is not a kernel)
+        self.launches_per_step = 10 * len(layers)       # kernels per layer (the memset is not a kernel)
 
     def layer(self, i, next_norm_w=None, next_act=None):
         """One MoE FFN layer over the chunk.  next_norm_w / next_act = (PfAct, inv): where the fused combine + norm
@@ -68,8 +68,8 @@ class PrefillStack:
         l, m = self.layers[i], self.m
         api.pf_gemm_set_workspace(self.gemm_ws)
         api.k_pf_norm(self.X, l.norm_w, 0, self.a, self.inv, self.h32, m)
-        api.k_pf_router(self.h32, m, l.router, l.rbias, self.inv, self.sel, self.sig)
-        api.k_pf_select(self.sel, self.sig, m, self.idx, self.w)
+        # router + top-4 selection in one launch (the form follows the chunk size: src/engine.cu:1170-1176)
+        api.k_pf_router_select(self.h32, m, m <= 256, l.router, l.rbias, self.inv, self.sel, self.sig, self.idx, self.w)
         api.zero_i32(self.cnt, E)
         api.k_pf_moe_count(self.idx, self.ns, self.cnt)
         api.k_pf_moe_plan(self.cnt, self.off, self.tiles, self.ntiles)
@@ -132,7 +132,7 @@ class PrefillStackEP:
         self.dispatch = dispatch
         self.rank, self.world, self.group = rank, world, group
         # this library's kernels per layer (memsets, the torch division and NCCL's own kernels not counted)
-        self.launches_per_step = (14 if dispatch == "peer" else 16) * len(layers)
+        self.launches_per_step = (12 if dispatch == "peer" else 15) * len(layers)
         self.layers = layers
         self.shards = [shard_layer(l, rank, world) for l in layers]
         self.m = m_total // world
@@ -251,7 +251,7 @@ class PrefillStackEP:
         _timed(self, api.pf_gemm_moe_rows, dn, self.max_tiles, self.home_rows)
 
     def _exchange_peer(self, i):
-        """route + counts -> rows to their owners -> plan + experts -> D rows home, all on the stream: 9 launches."""
+        """route + counts -> rows to their owners -> plan + experts -> D rows home, all on the stream."""
         G, ns, per, me = self.world, self.m * TOPK, E // self.world, self.rank
         ep = self.ep_epoch
         api.ep_route_exchange(self.idx, ns, per, self.peers, me, G, ep, self.send_order, self.doff, self.ep_offs, self.ep_status)
@@ -261,8 +261,7 @@ class PrefillStackEP:
                              self.perm, self.nrecv[i:i + 1], self.ep_status, self.peers, self.home_rows)
         api.ep_unpack_rows_dev(self.recv_buf, self.cap, self.ep_offs[3 * G:], self.r_act, self.r_inv, self.r_le)
         self._experts_dev(i)
-        api.ep_publish(self.peers, me, G, 2, ep)
-        api.ep_wait(self.flags, 2, G, ep, self.ep_status)
+        api.ep_publish_wait(self.peers, me, G, 2, ep, self.flags, self.ep_status)
 
     def _experts(self, li, n):
         """count / plan / scatter + the two grouped GEMMs over the n slots received for this rank's experts."""
@@ -292,9 +291,7 @@ class PrefillStackEP:
         api.pf_gemm_set_workspace(self.gemm_ws)
         api.k_pf_norm(self.X, l.norm_w, 0, self.a, self.inv, self.h32, m)
         # the router form follows the CHUNK size, as on one GPU (ref: src/engine.cu:1170-1176)
-        router = api.k_pf_router_small if self.m_total <= 256 else api.k_pf_router_tiled
-        router(self.h32, m, l.router, l.rbias, self.inv, self.sel, self.sig)
-        api.k_pf_select(self.sel, self.sig, m, self.idx, self.w)
+        api.k_pf_router_select(self.h32, m, self.m_total <= 256, l.router, l.rbias, self.inv, self.sel, self.sig, self.idx, self.w)
         nxt = self.layers[(i + 1) % len(self.layers)]
         if self.dispatch == "peer":
             self._exchange_peer(i)

@@ -501,3 +501,23 @@ def test_gemm_moe_full_size_4096_tokens_zipf(L, orc):
     assert np.array_equal(gotD[sperm], oD[sperm])                        # down rows, bit for bit
     L.pf_gemm_set_workspace(None)
     L.pf_gemm_config(-1)
+
+
+@pytest.mark.parametrize("m", [1, 70, 256, 300, 1500, 2500, 4096])
+def test_router_and_selection_in_one_launch(L, m):
+    """lkb_pf_router_select == lkb_pf_router followed by lkb_pf_select, every CTA shape of the tiled form and the short form."""
+    rng = np.random.default_rng(900 + m)
+    H = dev(rng.standard_normal((m, 2048)).astype(np.float32))
+    W = dev((0.02 * rng.standard_normal((64, 2048))).astype(np.float32))
+    bias = dev(zipf_bias(rng, 64, 1.1, 0.05))
+    inv = dev(rng.uniform(0.5, 2.0, size=m).astype(np.float32))
+    for small in ((True, False) if m <= 256 else (False,)):
+        sel, sig = nan_f32(m, 64), nan_f32(m, 64)
+        idx, w = torch.full((m, 4), -1, dtype=torch.int32, device="cuda"), nan_f32(m, 4)
+        (L.k_pf_router_small if small else L.k_pf_router_tiled)(H, m, W, bias, inv, sel, sig)
+        L.k_pf_select(sel, sig, m, idx, w)
+        sel2, sig2 = nan_f32(m, 64), nan_f32(m, 64)
+        idx2, w2 = torch.full((m, 4), -1, dtype=torch.int32, device="cuda"), nan_f32(m, 4)
+        L.k_pf_router_select(H, m, small, W, bias, inv, sel2, sig2, idx2, w2)
+        torch.cuda.synchronize()
+        assert torch.equal(sel, sel2) and torch.equal(sig, sig2) and torch.equal(idx, idx2) and torch.equal(w, w2)
