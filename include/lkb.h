@@ -471,7 +471,7 @@ int lkb_ep_route_exchange(const int * idx, int n, int experts_per_rank, const lk
  * the row count.  When the wait gives up, *ntiles = 0 and the status word holds the code. */
 int lkb_ep_route_experts(const void * recv, int cap, const int * flags, int G, const int * epoch, const int * offs, int * cnt, int * off,
                          int * tiles, int * ntiles, int * perm, int * nrecv_out, const lkb_ep_peers * peers, float ** home_rows,
-                         int * status, lkb_stream_t st);
+                         float * inv_out, int * status, lkb_stream_t st);
 /* No counterpart in the reference.  home_rows (optional, with peers) of lkb_ep_route_experts receives, per received
  * row, the address its result row has in its home rank's return buffer; lkb_pf_gemm_moe_rows is lkb_pf_gemm_moe
  * writing the output row of slot s to out_rows[s] instead of out + s * out_ld (plain stores, peer memory included;
@@ -479,6 +479,12 @@ int lkb_ep_route_experts(const void * recv, int cap, const int * flags, int G, c
  * the GEMM still computes; lkb_ep_publish then announces `phase` of the epoch to every rank (the role of the flag
  * store at the end of lkb_ep_push_back, which this pair replaces). */
 int lkb_pf_gemm_moe_rows(const lkb_pf_gemm * g, int max_tiles, float * const * out_rows, lkb_stream_t st);
+/* No counterpart in the reference.  inv_out (optional) of lkb_ep_route_experts receives the received rows' 1/rms as a
+ * plane; lkb_pf_gemm_swiglu_packed is lkb_pf_gemm_swiglu reading its activations from PACKED rows of row_pitch bytes
+ * (bpr*32 quants, then bpr (d8, 8sum) pairs; g->aqs = the first row, g->asc unused) -- the dispatch rows as they
+ * arrived, so no unpack pass is needed.  Needs the registered workspace (the row gather reads the packed rows);
+ * tensor-core form only. */
+int lkb_pf_gemm_swiglu_packed(const lkb_pf_gemm * g, int max_tiles, int row_pitch, lkb_stream_t st);
 int lkb_ep_publish(const lkb_ep_peers * peers, int me, int G, int phase, const int * epoch, lkb_stream_t st);
 /* lkb_ep_publish followed by lkb_ep_wait(flags, phase, ...) in one launch.  No counterpart in the reference. */
 int lkb_ep_publish_wait(const lkb_ep_peers * peers, int me, int G, int phase, const int * epoch, const int * flags, int * status,

@@ -25,7 +25,7 @@ __all__ = [
     "k_attn_split", "k_attn_combine", "k_qk_norm_rope", "k_shortconv", "ATTN_SPLIT", "ATTN_PARTW",
     "mixer_layer_desc", "step_scratch", "decode_layers",
     "k_pf_embed", "k_pf_conv", "k_pf_conv_hist", "k_pf_qknr", "k_pf_attn",
-    "ep_peers", "EP_ROW_BYTES", "ep_set_wait_limit_ms", "ep_counts_exchange", "ep_route_exchange", "ep_route_experts", "pf_gemm_moe_rows", "ep_publish", "ep_publish_wait", "ep_pack_push", "ep_wait", "ep_push_back", "ep_unpack_rows_dev", "k_pf_moe_count_dev",
+    "ep_peers", "EP_ROW_BYTES", "ep_set_wait_limit_ms", "ep_counts_exchange", "ep_route_exchange", "ep_route_experts", "pf_gemm_moe_rows", "pf_gemm_swiglu_packed", "ep_publish", "ep_publish_wait", "ep_pack_push", "ep_wait", "ep_push_back", "ep_unpack_rows_dev", "k_pf_moe_count_dev",
     "k_pf_moe_scatter_dev",
 ]
 
@@ -407,10 +407,15 @@ def ep_route_exchange(idx, n, experts_per_rank, peers, me, G, epoch, send_order,
                                     ptr(offs), ptr(status), stream()), "ep_route_exchange")
 
 
-def ep_route_experts(recv, cap, flags, G, epoch, offs, cnt, off, tiles, ntiles, perm, nrecv_out, status, peers=None, home_rows=None):
+def ep_route_experts(recv, cap, flags, G, epoch, offs, cnt, off, tiles, ntiles, perm, nrecv_out, status, peers=None, home_rows=None,
+                     inv_out=None):
     check(lib.lkb_ep_route_experts(ptr(recv), cap, ptr(flags), G, ptr(epoch), ptr(offs), ptr(cnt), ptr(off), ptr(tiles), ptr(ntiles),
-                                   ptr(perm), ptr(nrecv_out), None if peers is None else C.byref(peers), ptr(home_rows), ptr(status),
-                                   stream()), "ep_route_experts")
+                                   ptr(perm), ptr(nrecv_out), None if peers is None else C.byref(peers), ptr(home_rows), ptr(inv_out),
+                                   ptr(status), stream()), "ep_route_experts")
+
+
+def pf_gemm_swiglu_packed(g, max_tiles, row_pitch):
+    check(lib.lkb_pf_gemm_swiglu_packed(C.byref(g), max_tiles, row_pitch, stream()), "pf_gemm_swiglu_packed")
 
 
 def pf_gemm_moe_rows(g, max_tiles, out_rows):

@@ -264,7 +264,7 @@ __global__ void __launch_bounds__(1024) k_ep_route_experts(const unsigned char *
                                                            const int * __restrict__ epoch_dev, const int * __restrict__ offs,
                                                            int * __restrict__ cnt, int * __restrict__ off, int4 * __restrict__ tiles,
                                                            int * __restrict__ ntiles, int * __restrict__ perm, int * __restrict__ nrecv_out,
-                                                           EpPeers P, float ** __restrict__ home_rows,
+                                                           EpPeers P, float ** __restrict__ home_rows, float * __restrict__ inv_out,
                                                            int * __restrict__ status, unsigned long long limit_ns) {
     lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     __shared__ EpRouteSmem R;
@@ -278,6 +278,9 @@ __global__ void __launch_bounds__(1024) k_ep_route_experts(const unsigned char *
     ep_route_cta(R, [&](int s) { return (int) __ldcg(reinterpret_cast<const unsigned *>(recv + (size_t) s * EP_ROW_BYTES) + 641); },
                  n, cnt, off, tiles, ntiles, perm);
     if (t == 0 && nrecv_out) *nrecv_out = n;
+    // the rows' 1/rms as a plane of its own (the grouped GEMM's per-row scale), for callers that feed the GEMM the packed rows
+    if (inv_out)
+        for (int r = t; r < n; r += 1024) inv_out[r] = __uint_as_float(__ldcg(reinterpret_cast<const unsigned *>(recv + (size_t) r * EP_ROW_BYTES) + 640));
     // where each received row's result goes home to: row (back_base[s] + j) of source s's return buffer (its send order)
     if (home_rows) {
         for (int r = t; r < n; r += 1024) {
@@ -347,7 +350,7 @@ int lkb_ep_route_exchange(const int * idx, int n, int experts_per_rank, const lk
 
 int lkb_ep_route_experts(const void * recv, int cap, const int * flags, int G, const int * epoch, const int * offs, int * cnt, int * off,
                          int * tiles, int * ntiles, int * perm, int * nrecv_out, const lkb_ep_peers * peers, float ** home_rows,
-                         int * status, lkb_stream_t st) {
+                         float * inv_out, int * status, lkb_stream_t st) {
     if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
     if (!recv || !flags || !epoch || !offs || !cnt || !off || !tiles || !ntiles || !perm || !status) return LKB_ERR_NULL;
     if (cap <= 0 || G < 1 || G > EP_MAX_RANKS) return LKB_ERR_SHAPE;
@@ -358,7 +361,7 @@ int lkb_ep_route_experts(const void * recv, int cap, const int * flags, int G, c
         if (r != LKB_OK) return r;
     }
     LKB_PF_LAUNCH(k_ep_route_experts, dim3(1), dim3(1024), 0, (cudaStream_t) st, reinterpret_cast<const unsigned char *>(recv), cap, flags, G, epoch, offs, cnt, off,
-                                                          reinterpret_cast<int4 *>(tiles), ntiles, perm, nrecv_out, P, home_rows, status,
+                                                          reinterpret_cast<int4 *>(tiles), ntiles, perm, nrecv_out, P, home_rows, inv_out, status,
                                                           g_ep_limit_ns);
     return lkb_check_launch();
 }

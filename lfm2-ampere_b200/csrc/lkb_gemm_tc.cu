@@ -238,8 +238,10 @@ __device__ __forceinline__ void tc_fold32(unsigned long long (&acc)[32], const u
 // of slot perm[p] (p < number of planned slots), so that the GEMM fetches a 128-token tile with one tile copy.
 // One warp per row.
 // ---------------------------------------------------------------------------
+// a_pitch > 0: the activation rows are PACKED rows of a_pitch bytes (quants, then the (d8, 8sum) pairs), as the
+// expert-parallel dispatch delivers them; g.aqs points at the first one and g.asc is not read.
 __global__ void __launch_bounds__(256) k_pf_gather_rows(const lkb_pf_gemm g, const int max_tiles, int8_t * __restrict__ wq,
-                                                        float2 * __restrict__ ws, const int cap_rows) {
+                                                        float2 * __restrict__ ws, const int cap_rows, const int a_pitch) {
     lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int nt = *g.ntiles; if (nt > max_tiles) nt = max_tiles;
@@ -249,10 +251,11 @@ __global__ void __launch_bounds__(256) k_pf_gather_rows(const lkb_pf_gemm g, con
     const int row_bytes = g.bpr * 32;
     for (int p = blockIdx.x * 8 + warp; p < n_live; p += gridDim.x * 8) {
         const int ar = g.perm[p] >> g.a_shift;
-        const uint4 * src = reinterpret_cast<const uint4 *>(g.aqs + (size_t) ar * row_bytes);
+        const uint4 * src = reinterpret_cast<const uint4 *>(g.aqs + (size_t) ar * (a_pitch ? a_pitch : row_bytes));
         uint4 * dst = reinterpret_cast<uint4 *>(wq + (size_t) p * row_bytes);
         for (int i = lane; i < row_bytes / 16; i += 32) dst[i] = __ldg(src + i);
-        const float4 * ss = reinterpret_cast<const float4 *>(reinterpret_cast<const float2 *>(g.asc) + (size_t) ar * g.bpr);
+        const float4 * ss = a_pitch ? reinterpret_cast<const float4 *>(g.aqs + (size_t) ar * a_pitch + row_bytes)
+                                    : reinterpret_cast<const float4 *>(reinterpret_cast<const float2 *>(g.asc) + (size_t) ar * g.bpr);
         float4 * sd = reinterpret_cast<float4 *>(ws + (size_t) p * g.bpr);
         for (int i = lane; i < g.bpr / 2; i += 32) sd[i] = __ldg(ss + i);
     }
@@ -796,7 +799,8 @@ static int tc_make_map(CUtensorMap * m, const void * base, unsigned row_bytes, u
 // Shapes the tensor-core form covers; otherwise LKB_ERR_UNSUPPORTED (the caller falls back
 // to the CUDA-core form): out_ld / okb rows must allow 16-byte vector stores, the planes the
 // alignment the copy engine asks for.
-int lkb_gemm_tc_launch(const lkb_pf_gemm * g, int epi, int fold, int max_tiles, cudaStream_t st, float * const * out_rows) {
+int lkb_gemm_tc_launch(const lkb_pf_gemm * g, int epi, int fold, int max_tiles, cudaStream_t st, float * const * out_rows, int a_pitch) {
+    if (a_pitch && (!g->perm || a_pitch % 16 || a_pitch < g->bpr * 40)) return LKB_ERR_SHAPE;     // packed rows: grouped form, 16-byte aligned
     if (out_rows && (epi || !g->perm || g->add)) return LKB_ERR_SHAPE;          // row targets: the plain grouped form, no residual add
     if (!g_tc_ready) return LKB_ERR_NOT_INIT;
     if (g->bpr % TC_KB) return LKB_ERR_UNSUPPORTED;
@@ -804,7 +808,7 @@ int lkb_gemm_tc_launch(const lkb_pf_gemm * g, int epi, int fold, int max_tiles, 
     else if (g->N % TC_N || g->out_ld % 4 || ((size_t) g->out & 15)) return LKB_ERR_UNSUPPORTED;
     if (g->perm && max_tiles > TC_MAX_TILES) return LKB_ERR_UNSUPPORTED;
     if (!g->perm && (g->ntok + TC_M - 1) / TC_M > TC_MAX_TILES) return LKB_ERR_UNSUPPORTED;
-    if (((size_t) g->aqs & 15) || ((size_t) g->asc & 15)) return LKB_ERR_UNSUPPORTED;
+    if (((size_t) g->aqs & 15) || (!a_pitch && ((size_t) g->asc & 15))) return LKB_ERR_UNSUPPORTED;
     if (g->exp_stride % g->bpr) return LKB_ERR_UNSUPPORTED;
     const int nseg = epi ? 2 : (g->seg_end[0] >= g->N ? 1 : g->seg_end[1] >= g->N ? 2 : 3);
     const unsigned qrow = (unsigned) g->bpr * 32u, srow = (unsigned) g->bpr * 8u;
@@ -822,13 +826,14 @@ int lkb_gemm_tc_launch(const lkb_pf_gemm * g, int epi, int fold, int max_tiles, 
             int8_t * wq = (int8_t *) g_tc_ws;
             float2 * ws = (float2 *) ((char *) g_tc_ws + cap * qrow);
             const int grid = lkb_context().sm_count * 4;
-            LKB_PF_LAUNCH(k_pf_gather_rows, dim3(grid), dim3(256), 0, st, *g, max_tiles, wq, ws, (int) cap);
+            LKB_PF_LAUNCH(k_pf_gather_rows, dim3(grid), dim3(256), 0, st, *g, max_tiles, wq, ws, (int) cap, a_pitch);
             r = lkb_check_launch();
             if (r != LKB_OK) return r;
             r = tc_make_map(&ma, wq, qrow, cap, 128u, TC_M, CU_TENSOR_MAP_SWIZZLE_128B);
             if (r == LKB_OK) r = tc_make_map(&ms, ws, srow, cap, 32u, TC_M, CU_TENSOR_MAP_SWIZZLE_NONE);
         } else {
             // grouped, no workspace: rows gathered through perm inside the kernel, four per copy
+            if (a_pitch) return LKB_ERR_UNSUPPORTED;                        // packed rows need the gather pass
             tiled = 0;
             r = tc_make_map(&ma, g->aqs, qrow, TC_ANY_ROWS, 128u, 1u, CU_TENSOR_MAP_SWIZZLE_128B);
             if (r == LKB_OK) r = tc_make_map(&ms, g->asc, srow, TC_ANY_ROWS, 32u, 1u, CU_TENSOR_MAP_SWIZZLE_NONE);

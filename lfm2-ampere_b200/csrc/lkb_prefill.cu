@@ -658,7 +658,7 @@ __global__ void __launch_bounds__(256) k_pf_gemm_simple(const lkb_pf_gemm g, con
 // C ABI
 // ---------------------------------------------------------------------------
 int lkb_gemm_tc_init();                                      // lkb_gemm_tc.cu
-int lkb_gemm_tc_launch(const lkb_pf_gemm * g, int epi, int fold, int max_tiles, cudaStream_t st, float * const * out_rows);   // LKB_ERR_UNSUPPORTED if shape not covered
+int lkb_gemm_tc_launch(const lkb_pf_gemm * g, int epi, int fold, int max_tiles, cudaStream_t st, float * const * out_rows, int a_pitch);   // LKB_ERR_UNSUPPORTED if shape not covered
 
 static int g_gemm_cfg = -1;        // -1: tensor-core form when it covers the shape; 0: CUDA-core form
 static int g_gemm_fold = 1;        // 1: the reference's shipped per-block term (folded offset); 0: the exact term
@@ -683,18 +683,18 @@ static int gemm_check(const lkb_pf_gemm * g, int epi) {
     return LKB_OK;
 }
 
-static int gemm_dispatch(const lkb_pf_gemm * g, int epi, int max_tiles, cudaStream_t st, float * const * out_rows = nullptr) {
+static int gemm_dispatch(const lkb_pf_gemm * g, int epi, int max_tiles, cudaStream_t st, float * const * out_rows = nullptr, int a_pitch = 0) {
     LKB_REQUIRE_INIT();
     const int r = gemm_check(g, epi);
     if (r != LKB_OK) return r;
     const int ty = g->perm ? max_tiles : (g->ntok + 63) / 64;
     if (ty <= 0) return g->perm ? LKB_ERR_SHAPE : LKB_OK;
     if (g_gemm_cfg != 0) {
-        const int t = lkb_gemm_tc_launch(g, epi, g_gemm_fold, max_tiles, st, out_rows);
+        const int t = lkb_gemm_tc_launch(g, epi, g_gemm_fold, max_tiles, st, out_rows, a_pitch);
         if (t != LKB_ERR_UNSUPPORTED) return t;
         if (g_gemm_cfg > 0) return t;
     }
-    if (out_rows) return LKB_ERR_UNSUPPORTED;              // row targets exist in the tensor-core form only
+    if (out_rows || a_pitch) return LKB_ERR_UNSUPPORTED;   // row targets and packed rows exist in the tensor-core form only
     if (epi) LKB_PF_LAUNCH((k_pf_gemm_simple<1>), dim3(dim3(g->N / 32, ty)), dim3(256), 0, st, *g, g_gemm_fold);
     else     LKB_PF_LAUNCH((k_pf_gemm_simple<0>), dim3(dim3(g->N / 64, ty)), dim3(256), 0, st, *g, g_gemm_fold);
     return lkb_check_launch();
@@ -832,6 +832,10 @@ int lkb_pf_gemm_moe(const lkb_pf_gemm * g, int max_tiles, lkb_stream_t st) {
 int lkb_pf_gemm_moe_rows(const lkb_pf_gemm * g, int max_tiles, float * const * out_rows, lkb_stream_t st) {
     if (!out_rows) return LKB_ERR_NULL;
     return gemm_dispatch(g, 0, max_tiles, (cudaStream_t) st, out_rows);
+}
+int lkb_pf_gemm_swiglu_packed(const lkb_pf_gemm * g, int max_tiles, int row_pitch, lkb_stream_t st) {
+    if (row_pitch <= 0) return LKB_ERR_SHAPE;
+    return gemm_dispatch(g, 1, max_tiles, (cudaStream_t) st, nullptr, row_pitch);
 }
 int lkb_pf_gemm_swiglu(const lkb_pf_gemm * g, int max_tiles, lkb_stream_t st) {
     return gemm_dispatch(g, 1, max_tiles, (cudaStream_t) st);

@@ -132,7 +132,7 @@ class PrefillStackEP:
         self.dispatch = dispatch
         self.rank, self.world, self.group = rank, world, group
         # this library's kernels per layer (memsets, the torch division and NCCL's own kernels not counted)
-        self.launches_per_step = (12 if dispatch == "peer" else 15) * len(layers)
+        self.launches_per_step = (11 if dispatch == "peer" else 15) * len(layers)
         self.layers = layers
         self.shards = [shard_layer(l, rank, world) for l in layers]
         self.m = m_total // world
@@ -240,10 +240,11 @@ class PrefillStackEP:
     def _experts_dev(self, li):
         """The two grouped GEMMs over the received rows; the plan (tiles, perm) is already on the device."""
         sh = self.shards[li]
-        g = api.make_pf_gemm([(sh.gate_qs, sh.gate_d), (sh.up_qs, sh.up_d)], [I, I, I], I, H // 32, self.r_qs, self.r_sc,
+        # the gate|up GEMM's row gather reads the dispatch rows as they arrived (packed: quants | scale pairs | 1/rms, id)
+        g = api.make_pf_gemm([(sh.gate_qs, sh.gate_d), (sh.up_qs, sh.up_d)], [I, I, I], I, H // 32, self.recv_buf, self.recv_buf,
                              exp_stride=I * (H // 32), perm=self.perm, tiles=self.tiles, ntiles=self.ntiles,
                              a_shift=0, scale=self.r_inv, oqs=self.a2_qs, osc=self.a2_sc, okb=I // 32)
-        _timed(self, api.pf_gemm_swiglu, g, self.max_tiles)
+        _timed(self, api.pf_gemm_swiglu_packed, g, self.max_tiles, api.EP_ROW_BYTES)
         dn = api.make_pf_gemm([(sh.down_qs, sh.down_d)], [H, H, H], H, I // 32, self.a2_qs, self.a2_sc,
                               exp_stride=H * (I // 32), perm=self.perm, tiles=self.tiles, ntiles=self.ntiles,
                               a_shift=0, out=self.D, out_ld=H)
@@ -258,8 +259,7 @@ class PrefillStackEP:
         api.ep_pack_push(self.a, self.inv, self.idx, self.send_order, self.doff, self.ep_offs, ns, per, self.peers, me, G, ep,
                          self.pos, self.ep_done[0:])
         api.ep_route_experts(self.recv_buf, self.cap, self.flags, G, ep, self.ep_offs, self.cnt, self.off, self.tiles, self.ntiles,
-                             self.perm, self.nrecv[i:i + 1], self.ep_status, self.peers, self.home_rows)
-        api.ep_unpack_rows_dev(self.recv_buf, self.cap, self.ep_offs[3 * G:], self.r_act, self.r_inv, self.r_le)
+                             self.perm, self.nrecv[i:i + 1], self.ep_status, self.peers, self.home_rows, self.r_inv)
         self._experts_dev(i)
         api.ep_publish_wait(self.peers, me, G, 2, ep, self.flags, self.ep_status)
 
