@@ -436,14 +436,14 @@ int lkb_pf_attn(const void * qh, int m, int P, const void * kc, const void * vc,
  *   flags  int[3*8]            arrival flags (phase 0 counts, 1 dispatched rows, 2 returned rows) per source rank
  *   recv   byte[cap][2576]     dispatched rows (LKB_EP_ROW_BYTES each), cap = worst case = every slot of the chunk
  *   dback  float[slots][2048]  this rank's D rows, in its send order
- * epoch is a device int the caller zeroes once: lkb_ep_counts_exchange advances it by one per layer and the other
- * kernels read it (flags are never reset, and nothing on the host changes from layer to layer); status (device int, 0 = fine) receives a code when a
- * bounded wait expires: 1 counts, 2 / 3 / 4 = lkb_ep_wait of phase 0 / 1 / 2.  A wait lasts at most the limit set by
- * lkb_ep_set_wait_limit_ms (default 5000 ms; 1..60000); once a code is recorded the later waits return at once.
- * lkb_ep_counts_exchange: dcnt[G] = rows I send to each rank; leaves offs[3*G+1] (send bases, receive offsets, return
- *   bases, rows received).   lkb_ep_pack_push: row p of my send order -> its owner's recv buffer; doff[g] = first
- *   position of destination g in my send order; pos[slot] = p.   lkb_ep_push_back: my received rows' D -> home ranks.
- * The *_dev entries are the plan / unpack kernels with the live row count read from device memory. */
+ * epoch is a device int the caller zeroes once: lkb_ep_route_exchange advances it by one per layer and the other
+ * kernels read it (flags are never reset, and nothing on the host changes from layer to layer); status (device int,
+ * 0 = fine) receives a code when a bounded wait expires: 1 counts, 2 / 3 / 4 = the wait of phase 0 / 1 / 2.  A wait
+ * lasts at most the limit set by lkb_ep_set_wait_limit_ms (default 5000 ms; 1..60000); once a code is recorded the
+ * later waits return at once.
+ * lkb_ep_route_exchange leaves offs[3*G+1] (send bases, receive offsets, return bases, rows received).
+ * lkb_ep_pack_push: row p of my send order -> its owner's recv buffer; doff[g] = first position of destination g in
+ * my send order; pos[slot] = p. */
 typedef struct {
     void * cmat[8];
     void * flags[8];
@@ -452,8 +452,6 @@ typedef struct {
 } lkb_ep_peers;
 /* No counterpart in the reference: the exchange over peer memory described above. */
 int lkb_ep_set_wait_limit_ms(int ms);
-int lkb_ep_counts_exchange(const int * dcnt, const lkb_ep_peers * peers, int me, int G, int * epoch, int * offs, int * status,
-                           lkb_stream_t st);
 /* No counterpart in the reference: dispatch, arrival wait and return of the exchange described above. */
 int lkb_ep_pack_push(lkb_pf_act a, const float * inv, const int * idx, const int * send_order, const int * doff, const int * offs,
                      int n, int experts_per_rank, const lkb_ep_peers * peers, int me, int G, const int * epoch, int * pos, unsigned * done,
@@ -461,13 +459,13 @@ int lkb_ep_pack_push(lkb_pf_act a, const float * inv, const int * idx, const int
 int lkb_ep_wait(const int * flags, int phase, int G, const int * epoch, int * status, lkb_stream_t st);
 /* No counterpart in the reference: the home side's routing and count exchange in ONE launch -- slots grouped by the
  * rank owning their expert (send_order[n], doff[64]: first position of each destination; stable, the order of
- * lkb_pf_moe_count / _plan / _scatter keyed by owner rank), then everything lkb_ep_counts_exchange does with those
- * counts.  One CTA; n is a rank's slots of a chunk (a few thousand). */
+ * lkb_pf_moe_count / _plan / _scatter keyed by owner rank), then the count exchange: my count row into every rank's
+ * matrix, flags, wait for all rows, offsets.  One CTA; n is a rank's slots of a chunk (a few thousand). */
 int lkb_ep_route_exchange(const int * idx, int n, int experts_per_rank, const lkb_ep_peers * peers, int me, int G, int * epoch,
                           int * send_order, int * doff, int * offs, int * status, lkb_stream_t st);
 /* No counterpart in the reference: the owner side's wait for the dispatched rows (lkb_ep_wait phase 1) and the grouped
- * GEMM's plan over them (cnt[64], off[64], tiles, ntiles, perm: the results of lkb_pf_moe_count_dev / _plan /
- * _scatter_dev keyed by the local expert id each received row carries) in ONE launch.  nrecv_out (optional) receives
+ * GEMM's plan over them (cnt[64], off[64], tiles, ntiles, perm: the results of lkb_pf_moe_count / _plan / _scatter
+ * keyed by the local expert id each received row carries, with the row count read from device memory) in ONE launch.  nrecv_out (optional) receives
  * the row count.  When the wait gives up, *ntiles = 0 and the status word holds the code. */
 int lkb_ep_route_experts(const void * recv, int cap, const int * flags, int G, const int * epoch, const int * offs, int * cnt, int * off,
                          int * tiles, int * ntiles, int * perm, int * nrecv_out, const lkb_ep_peers * peers, float ** home_rows,
@@ -476,8 +474,7 @@ int lkb_ep_route_experts(const void * recv, int cap, const int * flags, int G, c
  * row, the address its result row has in its home rank's return buffer; lkb_pf_gemm_moe_rows is lkb_pf_gemm_moe
  * writing the output row of slot s to out_rows[s] instead of out + s * out_ld (plain stores, peer memory included;
  * add must be 0; tensor-core form only, else LKB_ERR_UNSUPPORTED), so the down projection's rows travel home while
- * the GEMM still computes; lkb_ep_publish then announces `phase` of the epoch to every rank (the role of the flag
- * store at the end of lkb_ep_push_back, which this pair replaces). */
+ * the GEMM still computes; lkb_ep_publish_wait then announces phase 2 of the epoch to every rank. */
 int lkb_pf_gemm_moe_rows(const lkb_pf_gemm * g, int max_tiles, float * const * out_rows, lkb_stream_t st);
 /* No counterpart in the reference.  inv_out (optional) of lkb_ep_route_experts receives the received rows' 1/rms as a
  * plane; lkb_pf_gemm_swiglu_packed is lkb_pf_gemm_swiglu reading its activations from PACKED rows of row_pitch bytes
@@ -485,16 +482,10 @@ int lkb_pf_gemm_moe_rows(const lkb_pf_gemm * g, int max_tiles, float * const * o
  * arrived, so no unpack pass is needed.  Needs the registered workspace (the row gather reads the packed rows);
  * tensor-core form only. */
 int lkb_pf_gemm_swiglu_packed(const lkb_pf_gemm * g, int max_tiles, int row_pitch, lkb_stream_t st);
-int lkb_ep_publish(const lkb_ep_peers * peers, int me, int G, int phase, const int * epoch, lkb_stream_t st);
-/* lkb_ep_publish followed by lkb_ep_wait(flags, phase, ...) in one launch.  No counterpart in the reference. */
+/* Publish `phase` of the epoch to every rank, then wait for the same phase of every source (lkb_ep_wait), in one
+ * launch.  No counterpart in the reference. */
 int lkb_ep_publish_wait(const lkb_ep_peers * peers, int me, int G, int phase, const int * epoch, const int * flags, int * status,
                         lkb_stream_t st);
-int lkb_ep_push_back(const float * D, const int * offs, int max_rows, const lkb_ep_peers * peers, int me, int G,
-                     const int * epoch, unsigned * done, lkb_stream_t st);
-/* No counterpart in the reference: the unpack / count / scatter kernels with the live row count on the device. */
-int lkb_ep_unpack_rows_dev(const void * in, int n, const int * n_dev, lkb_pf_act a, float * inv, int * local_expert, lkb_stream_t st);
-int lkb_pf_moe_count_dev(const int * idx, int n, const int * n_dev, int * cnt, lkb_stream_t st);
-int lkb_pf_moe_scatter_dev(const int * idx, int n, const int * n_dev, const int * off, int * perm, lkb_stream_t st);
 
 #if defined(__GNUC__)
 #pragma GCC visibility pop

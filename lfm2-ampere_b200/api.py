@@ -25,8 +25,7 @@ __all__ = [
     "k_attn_split", "k_attn_combine", "k_qk_norm_rope", "k_shortconv", "ATTN_SPLIT", "ATTN_PARTW",
     "mixer_layer_desc", "step_scratch", "decode_layers",
     "k_pf_embed", "k_pf_conv", "k_pf_conv_hist", "k_pf_qknr", "k_pf_attn",
-    "ep_peers", "EP_ROW_BYTES", "ep_set_wait_limit_ms", "ep_counts_exchange", "ep_route_exchange", "ep_route_experts", "pf_gemm_moe_rows", "pf_gemm_swiglu_packed", "ep_publish", "ep_publish_wait", "ep_pack_push", "ep_wait", "ep_push_back", "ep_unpack_rows_dev", "k_pf_moe_count_dev",
-    "k_pf_moe_scatter_dev",
+    "ep_peers", "EP_ROW_BYTES", "ep_set_wait_limit_ms", "ep_route_exchange", "ep_route_experts", "pf_gemm_moe_rows", "pf_gemm_swiglu_packed", "ep_publish_wait", "ep_pack_push", "ep_wait",
 ]
 
 
@@ -398,10 +397,6 @@ def ep_peers(cmat_ptrs, flag_ptrs, recv_ptrs, dback_ptrs):
     return p
 
 
-def ep_counts_exchange(dcnt, peers, me, G, epoch, offs, status):
-    check(lib.lkb_ep_counts_exchange(ptr(dcnt), C.byref(peers), me, G, ptr(epoch), ptr(offs), ptr(status), stream()), "ep_counts_exchange")
-
-
 def ep_route_exchange(idx, n, experts_per_rank, peers, me, G, epoch, send_order, doff, offs, status):
     check(lib.lkb_ep_route_exchange(ptr(idx), n, experts_per_rank, C.byref(peers), me, G, ptr(epoch), ptr(send_order), ptr(doff),
                                     ptr(offs), ptr(status), stream()), "ep_route_exchange")
@@ -426,10 +421,6 @@ def ep_publish_wait(peers, me, G, phase, epoch, flags, status):
     check(lib.lkb_ep_publish_wait(C.byref(peers), me, G, phase, ptr(epoch), ptr(flags), ptr(status), stream()), "ep_publish_wait")
 
 
-def ep_publish(peers, me, G, phase, epoch):
-    check(lib.lkb_ep_publish(C.byref(peers), me, G, phase, ptr(epoch), stream()), "ep_publish")
-
-
 def ep_pack_push(a, inv, idx, send_order, doff, offs, n, experts_per_rank, peers, me, G, epoch, pos, done):
     check(lib.lkb_ep_pack_push(a, ptr(inv), ptr(idx), ptr(send_order), ptr(doff), ptr(offs), n, experts_per_rank, C.byref(peers),
                                me, G, ptr(epoch), ptr(pos), ptr(done), stream()), "ep_pack_push")
@@ -443,17 +434,3 @@ def ep_wait(flags, phase, G, epoch, status):
     check(lib.lkb_ep_wait(ptr(flags), phase, G, ptr(epoch), ptr(status), stream()), "ep_wait")
 
 
-def ep_push_back(D, offs, max_rows, peers, me, G, epoch, done):
-    check(lib.lkb_ep_push_back(ptr(D), ptr(offs), max_rows, C.byref(peers), me, G, ptr(epoch), ptr(done), stream()), "ep_push_back")
-
-
-def ep_unpack_rows_dev(buf, n, n_dev, a, inv, local_expert):
-    check(lib.lkb_ep_unpack_rows_dev(ptr(buf), n, ptr(n_dev), a, ptr(inv), ptr(local_expert), stream()), "ep_unpack_rows_dev")
-
-
-def k_pf_moe_count_dev(idx, n, n_dev, cnt):
-    check(lib.lkb_pf_moe_count_dev(ptr(idx), n, ptr(n_dev), ptr(cnt), stream()), "k_pf_moe_count_dev")
-
-
-def k_pf_moe_scatter_dev(idx, n, n_dev, off, perm):
-    check(lib.lkb_pf_moe_scatter_dev(ptr(idx), n, ptr(n_dev), ptr(off), ptr(perm), stream()), "k_pf_moe_scatter_dev")

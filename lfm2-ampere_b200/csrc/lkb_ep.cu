@@ -8,15 +8,17 @@
 // through the switch's reduction or broadcast units, and no bulk-copy engine touches peer memory.  Every wait is bounded: on expiry the kernel records a code in the caller's status word and returns.
 //
 // Order inside a layer (all on the rank's one stream):
-//   counts_exchange   advance the epoch (a device int, so the whole step can be captured in a CUDA graph);
-//                     my row of the count matrix -> every rank (so every rank knows who sends how much to whom);
-//                     wait for all G rows; derive this rank's offsets
+//   route_exchange    ONE CTA: slots grouped by owner rank (stable), advance the epoch (a device int, so the whole step
+//                     can be captured in a CUDA graph); my row of the count matrix -> every rank (so every rank knows
+//                     who sends how much to whom); wait for all G rows; derive this rank's offsets
 //   pack_push         a dispatched slot's 2576-byte row goes straight into its owner's receive buffer at
 //                     (rows lower ranks send there) + (its index among my rows for that owner): the owner sees
 //                     source-ascending, slot-ascending rows -- the order that makes results bit-identical to 1 GPU
-//   wait(rows)        then unpack / count / plan / scatter / grouped GEMMs with the row count read from device memory
-//   push_back         D rows return to the slot's home rank, into its return buffer in ITS send order
-//   wait(back)        then the rank-order combine
+//   route_experts     ONE CTA: wait(rows), then the grouped GEMMs' plan over the received rows (row count read from
+//                     device memory), each row's home address and its 1/rms
+//   grouped GEMMs     gate|up reads the packed rows; down writes each result row straight to its home rank's return
+//                     buffer in that rank's send order
+//   publish_wait      phase 2 published, then wait for every source's; then the rank-order combine
 // A rank can be at most one phase ahead of its slowest peer, which is what makes buffer reuse across layers safe.
 #include "lkb_device.cuh"
 
@@ -63,38 +65,6 @@ __device__ __forceinline__ bool ep_wait_flag(const int * flags, int phase, int s
 //                     [G, 2G) recv_off[s]: first row of source s inside my receive buffer
 //                     [2G, 3G) back_base[s]: first row of my block inside source s's return buffer (its send order)
 //                     [3G] n_recv
-__global__ void __launch_bounds__(64) k_ep_counts_exchange(const int * __restrict__ dcnt, EpPeers P, int me, int G, int * __restrict__ epoch_dev,
-                                                           int * __restrict__ offs, int * __restrict__ status,
-                                                           unsigned long long limit_ns) {
-    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
-    const int t = threadIdx.x;
-    const int epoch = *epoch_dev + 1;                                    // this layer's epoch; stored back at the end
-    if (t < G * G) P.cmat[t / G][me * G + (t % G)] = dcnt[t % G];       // my row, into every rank's matrix
-    __threadfence_system();
-    __syncthreads();
-    if (t < G) ep_st_release(P.flags[t] + 0 * EP_MAX_RANKS + me, epoch);
-    __shared__ int ok;
-    if (t == 0) ok = 1;
-    __syncthreads();
-    if (t < G && !ep_wait_flag(P.flags[me], 0, t, epoch, status, 1, limit_ns)) ok = 0;
-    __syncthreads();
-    if (!ok) return;
-    const int * C = P.cmat[me];                                          // my copy: C[s*G + g] = rows s sends to g
-    if (t < G) {
-        int sb = 0, ro = 0, bb = 0;
-        for (int s = 0; s < me; ++s) sb += __ldcg(C + s * G + t);        // rows lower ranks send to rank t
-        for (int s = 0; s < t; ++s) ro += __ldcg(C + s * G + me);        // rows lower sources send to me
-        for (int g = 0; g < me; ++g) bb += __ldcg(C + t * G + g);        // rows source t sends to lower ranks
-        offs[t] = sb; offs[G + t] = ro; offs[2 * G + t] = bb;
-    }
-    if (t == 0) {
-        int n = 0;
-        for (int s = 0; s < G; ++s) n += __ldcg(C + s * G + me);
-        offs[3 * G] = n;
-        *epoch_dev = epoch;                                              // every thread read the old value before the first barrier
-    }
-}
-
 // Row p of my send order (slot send_order[p], destination rank = its expert's owner) -> the owner's receive buffer.
 // doff[g] = first position of destination g in my send order.  A warp per row, rows walked with a grid stride by a grid
 // of a few CTAs per SM, ONE system-scope fence per CTA at the end (a fence per row made the kernel wait for the NVLink
@@ -136,32 +106,6 @@ __global__ void __launch_bounds__(32) k_ep_wait(const int * __restrict__ flags, 
     lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int epoch = *epoch_dev;
     if ((int) threadIdx.x < G) ep_wait_flag(flags, phase, threadIdx.x, epoch, status, 2 + phase, limit_ns);
-}
-
-// Received row r (source s = the block it lies in, j = its index inside that block) -> source s's return buffer,
-// row back_base[s] + j of ITS send order.  grid = upper bound of rows; rows >= n_recv exit.  One CTA per row.
-__global__ void __launch_bounds__(256) k_ep_push_back(const float * __restrict__ D, const int * __restrict__ offs, EpPeers P, int me, int G,
-                                                      const int * __restrict__ epoch_dev, unsigned * __restrict__ done) {
-    lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
-    const int n = offs[3 * G];
-    for (int r = blockIdx.x; r < n; r += gridDim.x) {
-        int s = 0;
-        while (s + 1 < G && r >= offs[G + s + 1]) ++s;
-        const int j = r - offs[G + s];
-        const uint4 * src = reinterpret_cast<const uint4 *>(D + (size_t) r * LKB_HIDDEN);
-        uint4 * dst = reinterpret_cast<uint4 *>(P.dback[s] + (size_t) (offs[2 * G + s] + j) * LKB_HIDDEN);
-        dst[threadIdx.x] = src[threadIdx.x];
-        dst[threadIdx.x + 256] = src[threadIdx.x + 256];
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0 && atomicAdd(done, 1u) == gridDim.x - 1) {
-        *done = 0u;
-        __threadfence_system();
-        const int epoch = *epoch_dev;
-        for (int g = 0; g < G; ++g) ep_st_release(P.flags[g] + 2 * EP_MAX_RANKS + me, epoch);
-    }
-    (void) me;
 }
 
 // ---------------------------------------------------------------------------
@@ -225,7 +169,7 @@ __device__ __forceinline__ void ep_route_cta(EpRouteSmem & R, KeyFn key, int n, 
 }
 
 // Home side of a layer's exchange in one launch: slots grouped by the rank that owns their expert (send_order, doff),
-// then the count exchange of k_ep_counts_exchange with the counts taken from shared memory.
+// then the count exchange: my row of the G x G count matrix -> every rank, wait for all rows, derive this rank's offsets.
 __global__ void __launch_bounds__(1024) k_ep_route_exchange(const int * __restrict__ idx, int ns, int experts_per_rank, EpPeers P, int me, int G,
                                                             int * __restrict__ epoch_dev, int * __restrict__ send_order, int * __restrict__ doff,
                                                             int * __restrict__ offs, int * __restrict__ status, unsigned long long limit_ns) {
@@ -324,18 +268,6 @@ int lkb_ep_set_wait_limit_ms(int ms) {
     return LKB_OK;
 }
 
-int lkb_ep_counts_exchange(const int * dcnt, const lkb_ep_peers * peers, int me, int G, int * epoch, int * offs, int * status,
-                           lkb_stream_t st) {
-    if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
-    if (!dcnt || !peers || !epoch || !offs || !status) return LKB_ERR_NULL;
-    EpPeers P = {};
-    const int r = ep_peers(P, peers->cmat, peers->flags, peers->recv, peers->dback, G);
-    if (r != LKB_OK) return r;
-    if (me < 0 || me >= G) return LKB_ERR_SHAPE;
-    LKB_PF_LAUNCH(k_ep_counts_exchange, dim3(1), dim3(64), 0, (cudaStream_t) st, dcnt, P, me, G, epoch, offs, status, g_ep_limit_ns);
-    return lkb_check_launch();
-}
-
 int lkb_ep_route_exchange(const int * idx, int n, int experts_per_rank, const lkb_ep_peers * peers, int me, int G, int * epoch,
                           int * send_order, int * doff, int * offs, int * status, lkb_stream_t st) {
     if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
@@ -363,17 +295,6 @@ int lkb_ep_route_experts(const void * recv, int cap, const int * flags, int G, c
     LKB_PF_LAUNCH(k_ep_route_experts, dim3(1), dim3(1024), 0, (cudaStream_t) st, reinterpret_cast<const unsigned char *>(recv), cap, flags, G, epoch, offs, cnt, off,
                                                           reinterpret_cast<int4 *>(tiles), ntiles, perm, nrecv_out, P, home_rows, inv_out, status,
                                                           g_ep_limit_ns);
-    return lkb_check_launch();
-}
-
-int lkb_ep_publish(const lkb_ep_peers * peers, int me, int G, int phase, const int * epoch, lkb_stream_t st) {
-    if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
-    if (!peers || !epoch) return LKB_ERR_NULL;
-    EpPeers P = {};
-    const int r = ep_peers(P, peers->cmat, peers->flags, peers->recv, peers->dback, G);
-    if (r != LKB_OK) return r;
-    if (me < 0 || me >= G || phase < 0 || phase > 2) return LKB_ERR_SHAPE;
-    LKB_PF_LAUNCH(k_ep_publish, dim3(1), dim3(32), 0, (cudaStream_t) st, P, me, G, phase, epoch, (const int *) nullptr, (int *) nullptr, 0ull);
     return lkb_check_launch();
 }
 
@@ -410,20 +331,6 @@ int lkb_ep_wait(const int * flags, int phase, int G, const int * epoch, int * st
     if (!flags || !epoch || !status) return LKB_ERR_NULL;
     if (phase < 0 || phase > 2 || G < 1 || G > EP_MAX_RANKS) return LKB_ERR_SHAPE;
     LKB_PF_LAUNCH(k_ep_wait, dim3(1), dim3(32), 0, (cudaStream_t) st, flags, phase, G, epoch, status, g_ep_limit_ns);
-    return lkb_check_launch();
-}
-
-int lkb_ep_push_back(const float * D, const int * offs, int max_rows, const lkb_ep_peers * peers, int me, int G,
-                     const int * epoch, unsigned * done, lkb_stream_t st) {
-    if (!lkb_context().inited) return LKB_ERR_NOT_INIT;
-    if (!D || !offs || !peers || !epoch || !done) return LKB_ERR_NULL;
-    EpPeers P = {};
-    const int r = ep_peers(P, peers->cmat, peers->flags, peers->recv, peers->dback, G);
-    if (r != LKB_OK) return r;
-    if (max_rows <= 0 || me < 0 || me >= G) return LKB_ERR_SHAPE;
-    int grid = lkb_context().sm_count * 8;                   // rows are walked with a grid stride: the live count is on the device
-    if (grid > max_rows) grid = max_rows;
-    LKB_PF_LAUNCH(k_ep_push_back, dim3(grid), dim3(256), 0, (cudaStream_t) st, D, offs, P, me, G, epoch, done);
     return lkb_check_launch();
 }
 

@@ -368,12 +368,8 @@ __global__ void __launch_bounds__(256) k_pf_select(const float * __restrict__ se
 // count / plan / scatter.  ref: src/prefill.cu:1710-1756
 // ---------------------------------------------------------------------------
 // Per-CTA shared histogram, then 64 global atomics per CTA (integer: order-free).
-// n_dev (optional): the live element count lives in device memory (expert-parallel prefill without a host sync);
-// n is then the launch-time upper bound.
-__global__ void __launch_bounds__(256) k_pf_moe_count(const int * __restrict__ idx, int n, int * __restrict__ cnt,
-                                                      const int * __restrict__ n_dev) {
+__global__ void __launch_bounds__(256) k_pf_moe_count(const int * __restrict__ idx, int n, int * __restrict__ cnt) {
     lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
-    if (n_dev) n = min(n, *n_dev);
     __shared__ int s_c[LKB_N_EXPERTS];
     if (threadIdx.x < LKB_N_EXPERTS) s_c[threadIdx.x] = 0;
     __syncthreads();
@@ -414,9 +410,8 @@ __global__ void __launch_bounds__(32) k_pf_moe_plan(const int * __restrict__ cnt
 // expert-major, slot-ascending within an expert -- identical to the reference's
 // per-expert compaction (ref: src/prefill.cu:1733-1756) without re-reading idx 64x.
 __global__ void __launch_bounds__(1024) k_pf_moe_scatter(const int * __restrict__ idx, int n, const int * __restrict__ off,
-                                                         int * __restrict__ perm, const int * __restrict__ n_dev) {
+                                                         int * __restrict__ perm) {
     lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
-    if (n_dev) n = min(n, *n_dev);
     if ((int) blockIdx.x * 1024 >= n) return;              // CTA-uniform: nothing of this chunk is live
     __shared__ int s_prior[LKB_N_EXPERTS];
     __shared__ int s_wc[32][LKB_N_EXPERTS];
@@ -504,11 +499,9 @@ __global__ void __launch_bounds__(192) k_ep_pack(const int8_t * __restrict__ aqs
 }
 
 __global__ void __launch_bounds__(192) k_ep_unpack(const unsigned char * __restrict__ in, int8_t * __restrict__ qs,
-                                                   float2 * __restrict__ sc, float * __restrict__ inv, int * __restrict__ le,
-                                                   const int * __restrict__ n_dev) {
+                                                   float2 * __restrict__ sc, float * __restrict__ inv, int * __restrict__ le) {
     lkb_pdl_wait(); lkb_pdl_trigger();           // programmatic dependent launch: inputs complete from here on
     const int p = blockIdx.x, i = threadIdx.x;
-    if (n_dev && p >= *n_dev) return;
     const uint4 * row = reinterpret_cast<const uint4 *>(in + (size_t) p * EP_ROW_BYTES);
     if (i < 128) reinterpret_cast<uint4 *>(qs + (size_t) p * LKB_HIDDEN)[i] = row[i];
     else if (i < 160) reinterpret_cast<uint4 *>(sc + (size_t) p * (LKB_HIDDEN / 32))[i - 128] = row[i];
@@ -795,7 +788,7 @@ int lkb_pf_moe_count(const int * idx, int n, int * cnt, lkb_stream_t st) {
     if (!idx || !cnt) return LKB_ERR_NULL;
     if (n <= 0) return n == 0 ? LKB_OK : LKB_ERR_SHAPE;
     int grid = (n + 255) / 256; if (grid > 64) grid = 64;
-    LKB_PF_LAUNCH(k_pf_moe_count, dim3(grid), dim3(256), 0, (cudaStream_t) st, idx, n, cnt, nullptr);
+    LKB_PF_LAUNCH(k_pf_moe_count, dim3(grid), dim3(256), 0, (cudaStream_t) st, idx, n, cnt);
     return lkb_check_launch();
 }
 
@@ -817,7 +810,7 @@ int lkb_pf_moe_scatter(const int * idx, int n, const int * off, int * perm, lkb_
     LKB_REQUIRE_INIT();
     if (!idx || !off || !perm) return LKB_ERR_NULL;
     if (n <= 0) return n == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    LKB_PF_LAUNCH(k_pf_moe_scatter, dim3((n + 1023) / 1024), dim3(1024), 0, (cudaStream_t) st, idx, n, off, perm, nullptr);
+    LKB_PF_LAUNCH(k_pf_moe_scatter, dim3((n + 1023) / 1024), dim3(1024), 0, (cudaStream_t) st, idx, n, off, perm);
     return lkb_check_launch();
 }
 
@@ -873,32 +866,7 @@ int lkb_ep_unpack_rows(const void * in, int n, lkb_pf_act a, float * inv, int * 
     if (!in || !a.qs || !a.sc || !inv || !local_expert) return LKB_ERR_NULL;
     if (n <= 0) return n == 0 ? LKB_OK : LKB_ERR_SHAPE;
     LKB_PF_LAUNCH(k_ep_unpack, dim3(n), dim3(192), 0, (cudaStream_t) st, static_cast<const unsigned char *>(in), a.qs,
-                                                  reinterpret_cast<float2 *>(a.sc), inv, local_expert, nullptr);
-    return lkb_check_launch();
-}
-
-// The same three with the live count in device memory (n = launch-time upper bound).
-int lkb_ep_unpack_rows_dev(const void * in, int n, const int * n_dev, lkb_pf_act a, float * inv, int * local_expert, lkb_stream_t st) {
-    LKB_REQUIRE_INIT();
-    if (!in || !n_dev || !a.qs || !a.sc || !inv || !local_expert) return LKB_ERR_NULL;
-    if (n <= 0) return n == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    LKB_PF_LAUNCH(k_ep_unpack, dim3(n), dim3(192), 0, (cudaStream_t) st, static_cast<const unsigned char *>(in), a.qs,
-                                                  reinterpret_cast<float2 *>(a.sc), inv, local_expert, n_dev);
-    return lkb_check_launch();
-}
-int lkb_pf_moe_count_dev(const int * idx, int n, const int * n_dev, int * cnt, lkb_stream_t st) {
-    LKB_REQUIRE_INIT();
-    if (!idx || !cnt || !n_dev) return LKB_ERR_NULL;
-    if (n <= 0) return n == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    int grid = (n + 255) / 256; if (grid > 64) grid = 64;
-    LKB_PF_LAUNCH(k_pf_moe_count, dim3(grid), dim3(256), 0, (cudaStream_t) st, idx, n, cnt, n_dev);
-    return lkb_check_launch();
-}
-int lkb_pf_moe_scatter_dev(const int * idx, int n, const int * n_dev, const int * off, int * perm, lkb_stream_t st) {
-    LKB_REQUIRE_INIT();
-    if (!idx || !off || !perm || !n_dev) return LKB_ERR_NULL;
-    if (n <= 0) return n == 0 ? LKB_OK : LKB_ERR_SHAPE;
-    LKB_PF_LAUNCH(k_pf_moe_scatter, dim3((n + 1023) / 1024), dim3(1024), 0, (cudaStream_t) st, idx, n, off, perm, n_dev);
+                                                  reinterpret_cast<float2 *>(a.sc), inv, local_expert);
     return lkb_check_launch();
 }
 

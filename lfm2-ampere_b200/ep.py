@@ -82,7 +82,7 @@ def ep_moe_layer(idx, payloads, expert_fn, world, group=None, n_experts=N_EXPERT
 
 
 def peer_offsets(count_matrix, me):
-    """Offset tables of the peer-memory exchange on rank `me` (the arithmetic of k_ep_counts_exchange in
+    """Offset tables of the peer-memory exchange on rank `me` (the arithmetic of k_ep_route_exchange in
     csrc/lkb_ep.cu, restated on the host for tests and for callers that plan on the CPU).
 
     count_matrix[s][g] = rows rank s sends to rank g.  Returns (send_base, recv_off, back_base, n_recv):
