@@ -628,10 +628,28 @@ def run_ours(args):
         ms_e2e = ev0.elapsed_time(ev1)
         if stack.status() != 0:
             raise SystemExit(f"fused decode kernel reported status {stack.status()} (a bounded wait expired)")
+        # the optional expert prefetch (off by default: measured slower), timed the same way, with its hit count
+        pf_rec = None
+        if args.layers > 1:
+            lkb.decode_set_expert_prefetch(1)
+            try:
+                for i in range(5):
+                    one_step(i)
+                torch.cuda.synchronize()
+                ev0.record()
+                for i in range(dsteps):
+                    one_step(i)
+                ev1.record()
+                torch.cuda.synchronize()
+                hits, guesses = lkb.decode_expert_prefetch_hits(stack._scratch, args.layers)
+                pf_rec = {"default": "off", "ms_per_step_on": ev0.elapsed_time(ev1) / dsteps, "ms_per_step_off": ms / dsteps,
+                          "guesses_chosen": hits, "guesses": guesses, "hit_rate": hits / guesses, "status": stack.status()}
+            finally:
+                lkb.decode_set_expert_prefetch(0)
         k_ms = ms / dsteps
         ach_d = args.layers * LAYER_BYTES / (k_ms * 1e-3) / 1e9
         dec = {"moe_stack": {"metric": "bs1 decode tok/s, 40-layer MoE-FFN stack (configuration 1 x 40)", "value": dsteps / (ms * 1e-3),
-                             "unit": UNIT, "ms_per_step": k_ms, "steps": dsteps, "parity_fused_equals_kernel_sequence": dec_parity,
+                             "unit": UNIT, "ms_per_step": k_ms, "steps": dsteps, "parity_fused_equals_kernel_sequence": dec_parity, "expert_prefetch": pf_rec,
                              "e2e": {"value": dsteps / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": H * 4, "d2h_bytes_per_step": H * 4},
                              "roofline": {"bound": "hbm", "kernel": f"k_moe_ffn_stack (persistent, {args.layers} MoE layers per launch)",
                                           "achieved": ach_d, "peak": hbm_peak, "unit": "GB/s", "frac": ach_d / hbm_peak,

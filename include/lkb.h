@@ -213,6 +213,17 @@ typedef struct {
  * ref: src/engine.cu:739-811 into a persistent cooperative kernel (one CTA per SM). */
 int lkb_moe_ffn_decode(const lkb_moe_layer * layer, float * x, int * idx_out, float * w_out,
                        const lkb_norm_prod_t * next, const lkb_moe_scratch * scratch, lkb_stream_t st);
+/* Expert prefetch of the multi-layer kernels (bit 0: lkb_moe_ffn_decode_stack[_static], bit 1: lkb_decode_layers;
+ * sigmoid gate, at least 128 CTAs).  While layer l runs, 64 CTAs that have no router row of their own evaluate layer
+ * l+1's router on layer l's input, and each CTA, once its rows of layer l have arrived, asks for its slice of the four
+ * guessed experts of layer l+1 to be brought into L2 (cp.async.bulk.prefetch.L2).  Results are unchanged bit for bit:
+ * the exact selection decides what is computed, a wrong guess only costs idle HBM bandwidth.  The guesses and the actual
+ * choices of the last launch are kept in the second half of scratch->gu; lkb_decode_expert_prefetch_hits waits for
+ * `st` and counts how many of the 4*(n_layers-1) guesses were chosen.  The idea of warming L2 with expert rows ahead of
+ * their use is the reference's (ref: src/kernels.cu:499-510, there for the current layer's down rows).
+ * Off by default (mode 0): on B200, with 74-81% of the guesses chosen, a 40-layer step measured 2-4% slower with it. */
+int lkb_decode_set_expert_prefetch(int mode);
+int lkb_decode_expert_prefetch_hits(const lkb_moe_scratch * scratch, int n_layers, int * hits, int * guesses, lkb_stream_t st);
 /* The same for n_layers consecutive layers in ONE launch; layers_dev is a DEVICE array
  * of descriptors; idx_out/w_out (optional) are [n_layers][4].  No counterpart in the
  * reference (its decode step is a 343-node graph, ref: src/engine.cu:1336-1342). */

@@ -25,7 +25,7 @@ __all__ = [
     "k_attn_split", "k_attn_combine", "k_qk_norm_rope", "k_shortconv", "ATTN_SPLIT", "ATTN_PARTW",
     "mixer_layer_desc", "step_scratch", "decode_layers",
     "k_pf_embed", "k_pf_conv", "k_pf_conv_hist", "k_pf_qknr", "k_pf_attn",
-    "ep_peers", "EP_ROW_BYTES", "ep_set_wait_limit_ms", "ep_route_exchange", "ep_route_experts", "pf_gemm_moe_rows", "pf_gemm_swiglu_packed", "ep_publish_wait", "ep_pack_push", "ep_wait",
+    "decode_set_expert_prefetch", "decode_expert_prefetch_hits", "ep_peers", "EP_ROW_BYTES", "ep_set_wait_limit_ms", "ep_route_exchange", "ep_route_experts", "pf_gemm_moe_rows", "pf_gemm_swiglu_packed", "ep_publish_wait", "ep_pack_push", "ep_wait",
 ]
 
 
@@ -284,6 +284,19 @@ def moe_ffn_decode_stack_static(layers_dev, n_layers, x, idx_out, w_out, next_np
     check(lib.lkb_moe_ffn_decode_stack_static(ptr(layers_dev), n_layers, hidden, inter, n_experts, top_k, softmax,
                                               ptr(x), ptr(idx_out), ptr(w_out), _np(next_np), stream()),
           "moe_ffn_decode_stack_static")
+
+
+def decode_set_expert_prefetch(mode):
+    """lkb_decode_set_expert_prefetch: bit 0 the MoE stack kernel, bit 1 the whole-step kernel."""
+    check(lib.lkb_decode_set_expert_prefetch(int(mode)), "decode_set_expert_prefetch")
+
+
+def decode_expert_prefetch_hits(scratch, n_layers):
+    """(hits, guesses) of the last multi-layer launch on this scratch (waits for the stream)."""
+    h, g = C.c_int(0), C.c_int(0)
+    check(lib.lkb_decode_expert_prefetch_hits(C.byref(scratch), n_layers, C.byref(h), C.byref(g), stream()),
+          "decode_expert_prefetch_hits")
+    return h.value, g.value
 
 
 # ------------------------------------------------- expert-parallel helpers --

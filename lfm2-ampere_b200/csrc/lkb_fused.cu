@@ -16,6 +16,11 @@
 //     silu(gate)*up itself and publishes one value per pair; every CTA then quantises the 6144
 //     values it needs for its down rows;
 //   * the next layer's router row is requested while the down projection runs;
+//   * optional (template flag PF, lkb_decode_set_expert_prefetch; off by default): 64 otherwise idle CTAs evaluate the
+//     NEXT layer's router on this layer's input, and every CTA asks for its slice of the four guessed experts to be
+//     brought into L2 while the barrier after gate|up completes.  74-81% of the guesses are chosen (synthetic weights)
+//     and the average CTA's gate|up wait drops by 0.4-1.0 us, but the slowest CTA's does not, and the burst of prefetch
+//     requests delays the polls and loads behind it on every SM: measured 2-4% slower as a whole, hence off;
 //   * whole-step variant (MIX): the mixers' weight rows are static, so they are requested a phase
 //     ahead into staging the MoE phases have finished with; a conv mixer adds two grid barriers
 //     per layer, an attention mixer four (see the M0..M3 phases in the kernel).
@@ -38,6 +43,13 @@
 #define N_GU_CH       (MAX_GU_ROWS / CH_ROWS) // 12
 #define N_DN_CH       (LKB_TOP_K * ((MAX_DN_ROWS + CH_ROWS - 1) / CH_ROWS))   // 8
 #define SPIN_LIMIT    (1u << 22)
+// Expert prefetch (optional, see the kernel): the unused second half of the `gu` scratch holds the 64 guessed logits of
+// the next layer, then the guessed and the actual choices of every layer ([layer][4], integers) for the caller's hit count.
+#define PF_LOGITS_OFF (LKB_TOP_K * LKB_MOE_INTER)
+#define PF_MAXL       512
+#define PF_GUESS_OFF  (PF_LOGITS_OFF + 128)
+#define PF_REAL_OFF   (PF_GUESS_OFF + 4 * PF_MAXL)
+static_assert(PF_REAL_OFF + 4 * PF_MAXL <= 2 * LKB_TOP_K * LKB_MOE_INTER, "prefetch records must fit the gu scratch");
 
 struct FusedSmem {
     alignas(128) unsigned char gu_q[MAX_GU_ROWS * GU_BPR * 16];          // 98304
@@ -55,11 +67,14 @@ struct FusedSmem {
     alignas(16) unsigned key[LKB_N_EXPERTS];      // order-preserving integer image of sel
     float  dot[LKB_TOP_K][MAX_DN_ROWS];
     int    idx[LKB_TOP_K];
+    int    pidx[LKB_TOP_K];               // expert prefetch: the guessed choice of the next layer
+    float  ppart[FUSED_WARPS];            // expert prefetch: per-warp partials of the guessed logit
     float  wk[LKB_TOP_K];
     float  inv;
     int    abort;
     unsigned bar_target;
     alignas(8) lkb_moe_layer ly;          // this layer's descriptor (staged: a global read costs ~1 us of latency)
+    alignas(8) lkb_moe_layer ly_next;     // the next layer's (expert prefetch)
     alignas(8) lkb_mixer_layer mx;        // whole-step kernel: this layer's sequence-mixer descriptor
     alignas(8) unsigned long long mbar_mi, mbar_mo;   // whole-step kernel: mixer input rows / output rows staged
     alignas(8) unsigned long long mbar_gu[N_GU_CH];
@@ -89,6 +104,10 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long * b, unsigned parit
 __device__ __forceinline__ void bulk_g2s(void * dst, const void * src, unsigned bytes, unsigned long long * b) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  :: "r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(b)) : "memory");
+}
+// Bring [src, src+bytes) into L2 without a destination (16-byte aligned address and size).
+__device__ __forceinline__ void bulk_prefetch_l2(const void * src, unsigned bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ unsigned ld_acquire(const unsigned * p) {
@@ -169,6 +188,19 @@ __device__ __forceinline__ void issue_gu_rows(const lkb_moe_layer & ly, const in
     }
 }
 
+// The same rows of the guessed experts of the next layer, into L2 only.
+__device__ __forceinline__ void prefetch_gu_rows(const lkb_moe_layer & ly, const int * idx, int g_begin, int g_end) {
+    int g = g_begin;
+    while (g < g_end) {
+        const int seg = g / LKB_MOE_INTER, r = g - seg * LKB_MOE_INTER;
+        int n = g_end - g; if (n > LKB_MOE_INTER - r) n = LKB_MOE_INTER - r;
+        const size_t blk = ((size_t) idx[seg & 3] * LKB_MOE_INTER + r) * GU_BPR;
+        bulk_prefetch_l2((const uint4 *) (seg < 4 ? ly.gate_qs : ly.up_qs) + blk, (unsigned) n * GU_BPR * 16u);
+        bulk_prefetch_l2((const __half *) (seg < 4 ? ly.gate_d : ly.up_d) + blk, (unsigned) n * GU_BPR * 2u);
+        g += n;
+    }
+}
+
 // One row's lane partial from shared memory (blocks lane, lane+32), reference order.
 template <int NB>
 __device__ __forceinline__ float smem_row_partial(const unsigned char * q, const __half * d, int bpr, int lane,
@@ -212,10 +244,13 @@ static unsigned long long * g_fused_timing = nullptr;
 #endif
 static int g_fused_absent_cta = -1;              // test hook, see lkb_debug_fused_absent_cta
 static unsigned g_fused_spin_limit = 0;          // 0: default
+static int g_fused_prefetch = 0;                 // bit 0: MoE stack, bit 1: whole-step kernel (lkb_decode_set_expert_prefetch)
 #ifdef LKB_TUNING
 #define FUSED_STAMP(slot) do { if (a.timing && tid == 0 && l < 4) a.timing[((size_t) cta * 4 + l) * 32 + (slot)] = clock64(); } while (0)
+#define FUSED_STAMP1(slot) do { if (a.timing && tid == 32 && l < 4) a.timing[((size_t) cta * 4 + l) * 32 + (slot)] = clock64(); } while (0)
 #else
 #define FUSED_STAMP(slot) do { } while (0)
+#define FUSED_STAMP1(slot) do { } while (0)
 #endif
 
 
@@ -265,6 +300,7 @@ struct FusedArgs {
     unsigned long long *  timing;
     int                   absent_cta;  // test hook: this CTA leaves at once and never arrives (-1: none)
     unsigned              spin_limit;  // iterations a grid-barrier wait may spin
+    int                   prefetch;    // expert prefetch on
     // whole-step kernel only
     const lkb_mixer_layer * mixers;    // device array [n_layers]
     const lkb_q8blk *     xq_first;    // layer 0's normalised Q8_1 activation (lkb_rmsnorm_q8_1)
@@ -351,7 +387,7 @@ __device__ __forceinline__ void mix_issue_out(FusedSmem & S, const lkb_mixer_lay
     bulk_g2s(S.dn_d, (const __half *) mx.out_d + (size_t) dn0 * GU_BPR, (unsigned) n_dn * GU_BPR * 2u, &S.mbar_mo);
 }
 
-template <bool MIX>
+template <bool MIX, bool PF>
 __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedArgs a) {
     extern __shared__ __align__(128) unsigned char fused_smem_raw[];
     FusedSmem & S = *reinterpret_cast<FusedSmem *>(fused_smem_raw);
@@ -396,6 +432,28 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
 
     if (tid < (int) (sizeof(lkb_moe_layer) / 8))
         reinterpret_cast<unsigned long long *>(&S.ly)[tid] = reinterpret_cast<const unsigned long long *>(&L[0])[tid];
+    // Expert prefetch.  While layer l runs, CTAs 64..127 evaluate layer l+1's router on layer l's INPUT (the residual
+    // before this layer's FFN is added: the exact input does not exist yet), every CTA ranks the 64 guesses, and once
+    // its own rows of layer l have landed it asks the copy engine to bring its slice of the four guessed experts of
+    // layer l+1 into L2 (no destination, nothing waits on it).  HBM is idle from there to the next selection; a right
+    // guess turns the next layer's stream into L2 hits, a wrong one costs bandwidth nobody was using.  Results do
+    // not depend on it: the exact selection decides what is computed.
+    const bool pf = PF && a.layers != nullptr && !a.softmax && nct >= 2 * LKB_N_EXPERTS;      // PF = false: none of it is compiled in
+    const bool pcta = pf && cta >= LKB_N_EXPERTS && cta < 2 * LKB_N_EXPERTS;
+    float pnw[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (pf && a.n_layers > 1) {
+        if (tid < (int) (sizeof(lkb_moe_layer) / 8))
+            reinterpret_cast<unsigned long long *>(&S.ly_next)[tid] = reinterpret_cast<const unsigned long long *>(&L[1])[tid];
+        if (pcta) {
+            if (tid == 0) {
+                mbar_expect_tx(&S.mbar_rt, LKB_HIDDEN * 4);
+                bulk_g2s(S.router, L[1].router + (size_t) (cta - LKB_N_EXPERTS) * LKB_HIDDEN, LKB_HIDDEN * 4, &S.mbar_rt);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) pnw[j] = L[1].norm_w[(warp + FUSED_WARPS * j) * 32 + lane];
+        }
+    }
+    if (tid < LKB_TOP_K) S.pidx[tid] = tid;
     // whole-step kernel: row ranges of the mixers, layer 0's descriptor and weight rows
     const int qa0 = (int) (((long long) cta * MIX_QKV_ROWS) / nct), qa1 = (int) (((long long) (cta + 1) * MIX_QKV_ROWS) / nct);
     int pos = 0;
@@ -425,6 +483,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
     for (int l = 0; l < a.n_layers; ++l) {
         const lkb_moe_layer & ly = S.ly;
         const unsigned par = (unsigned) (l & 1);
+        const bool pf_next = pf && l + 1 < a.n_layers;              // a next layer to guess for
 
         if constexpr (MIX) {
             const lkb_mixer_layer & mx = S.mx;
@@ -575,19 +634,40 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
                     if (lane == 0) S.sel[0] = acc;                   // multiplied by inv below, once inv exists
                 }
             }
+        } else if (pcta && pf_next) {
+            // the next layer's router row (cta - 64) against this layer's input under the next layer's norm weights
+            if (!mbar_wait(&S.mbar_rt, par)) { if (lane == 0) { atomicCAS(status, 0u, 100u + l); S.abort = 1; } }
+            else {
+                float acc = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    acc = fmaf(S.router[(warp + FUSED_WARPS * j) * 32 + lane], __fmul_rn(xv[j], pnw[j]), acc);
+                acc = lkb_warp_sum(acc);
+                if (lane == 0) S.ppart[warp] = acc;
+            }
         }
         FUSED_STAMP(1);
         // ---- B: Q8_1 of u, ssq, inv (needed for the logit scale and for gate|up) --
         fused_quant_u(S, xv, uv);
         if (cta < LKB_N_EXPERTS && tid == 0) a.logits[cta] = __fmul_rn(S.sel[0], S.inv);
+        if (pcta && pf_next && tid == 0) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int w = 0; w < FUSED_WARPS; ++w) acc += S.ppart[w];
+            a.gu[PF_LOGITS_OFF + cta - LKB_N_EXPERTS] = acc * S.inv;
+        }
         FUSED_STAMP(2);
         grid_arrive(a.bar, S);
         // static data of the selection, fetched while the barrier completes
         float rb0 = 0.0f, rb1 = 0.0f;
         if (warp == 0 && ly.rbias) { rb0 = __ldg(ly.rbias + lane); rb1 = __ldg(ly.rbias + lane + 32); }
+        float prb0 = 0.0f, prb1 = 0.0f, plg0 = 0.0f, plg1 = 0.0f;
+        if (pf_next && warp == 1 && S.ly_next.rbias) { prb0 = __ldg(S.ly_next.rbias + lane); prb1 = __ldg(S.ly_next.rbias + lane + 32); }
         if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 1u, a.spin_limit)) return;
         FUSED_STAMP(3);
 
+        // the guessed logits of the next layer: requested here, used by warp 1 once the gate|up rows are done
+        if (pf_next && warp == 1) { plg0 = __ldcg(a.gu + PF_LOGITS_OFF + lane); plg1 = __ldcg(a.gu + PF_LOGITS_OFF + lane + 32); }
         // ---- C: selection (every CTA, warp 0; the softmax gate takes the 64-thread path) ----
         if (!a.softmax) {
             if (warp == 0) {
@@ -658,6 +738,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
                 for (int k = 0; k < LKB_TOP_K; ++k) {
                     if (a.idx_out) a.idx_out[l * 4 + k] = S.idx[k];
                     if (a.w_out) a.w_out[l * 4 + k] = wv[k];
+                    if (pf && l < PF_MAXL) a.gu[PF_REAL_OFF + l * 4 + k] = __int_as_float(S.idx[k]);
                 }
             }
         }
@@ -729,6 +810,61 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
                 for (int j = 0; j < 4; ++j) anw[j] = an[(warp + FUSED_WARPS * j) * 32 + lane];
             }
         }
+        if (pf_next && warp > 0) {
+            // Warps 1..15, inside this barrier's shadow (warp 0 polls).  First the router row of the layer after next.
+            FUSED_STAMP1(26);
+            if (pcta && l + 2 < a.n_layers && tid == 32) {
+                fence_proxy_async();
+                mbar_expect_tx(&S.mbar_rt, LKB_HIDDEN * 4);
+                bulk_g2s(S.router, L[l + 2].router + (size_t) (cta - LKB_N_EXPERTS) * LKB_HIDDEN, LKB_HIDDEN * 4, &S.mbar_rt);
+            }
+            // rank the 64 guesses by the rule of the selection: warp 1 forms the keys, thread e counts who beats expert e
+            if (warp <= 2) {
+                if (warp == 1) {
+                    S.key[lane] = lkb_orderable(__fadd_rn(__fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-plg0))), prb0));
+                    S.key[lane + 32] = lkb_orderable(__fadd_rn(__fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-plg1))), prb1));
+                }
+                asm volatile("bar.sync 2, 64;" ::: "memory");
+                const int e = tid - 32;
+                const unsigned ke = S.key[e];
+                int cnt = 0;
+#pragma unroll 4
+                for (int j = 0; j < LKB_N_EXPERTS; j += 4) {
+                    const uint4 kk = *reinterpret_cast<const uint4 *>(&S.key[j]);
+                    const unsigned kj[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) cnt += (kj[i] > ke || (kj[i] == ke && j + i < e)) ? 1 : 0;
+                }
+                if (cnt < LKB_TOP_K) S.pidx[cnt] = e;
+            }
+            FUSED_STAMP1(27);
+            asm volatile("bar.sync 1, %0;" :: "r"(FUSED_THREADS - 32) : "memory");
+            // this CTA's gate|up rows of layer l have landed: its slice of the guessed experts of layer l+1 goes to L2,
+            // in the chunks of the real request, one or two per issuing lane
+            if (lane == 0) {
+                const lkb_moe_layer & nx = S.ly_next;
+                for (int c = warp - 1; c < n_gu_ch + LKB_TOP_K * dn_ch_per_k; c += FUSED_WARPS - 1) {
+                    if (c < n_gu_ch) {
+                        const int up = c >= gu_half_ch, ch = up ? c - gu_half_ch : c;
+                        const int j0 = ch * CH_ROWS, j1 = min(n_gu, j0 + CH_ROWS);
+                        prefetch_gu_rows(nx, S.pidx, up * GU_PAIRS + gu0 + j0, up * GU_PAIRS + gu0 + j1);
+                    } else {
+                        const int cc = c - n_gu_ch, k = cc / dn_ch_per_k, ch = cc % dn_ch_per_k;
+                        const int j0 = ch * CH_ROWS, j1 = min(n_dn, j0 + CH_ROWS);
+                        const size_t blk = (size_t) S.pidx[k] * LKB_HIDDEN * DN_BPR + (size_t) (dn0 + j0) * DN_BPR;
+                        bulk_prefetch_l2((const uint4 *) nx.down_qs + blk, (unsigned) (j1 - j0) * DN_BPR * 16u);
+                        bulk_prefetch_l2((const __half *) nx.down_d + blk, (unsigned) (j1 - j0) * DN_BPR * 2u);
+                    }
+                }
+            }
+            if (cta == 0 && warp == 1 && lane < LKB_TOP_K && l + 1 < PF_MAXL)
+                a.gu[PF_GUESS_OFF + (l + 1) * 4 + lane] = __int_as_float(S.pidx[lane]);
+            FUSED_STAMP1(29);
+        }
+        if (pf_next && pcta && l + 2 < a.n_layers) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) pnw[j] = L[l + 2].norm_w[(warp + FUSED_WARPS * j) * 32 + lane];
+        }
         if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 2u, a.spin_limit)) return;
         FUSED_STAMP(6);
 
@@ -798,6 +934,8 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
         grid_arrive(a.bar, S);
         if (l + 1 < a.n_layers && tid < (int) (sizeof(lkb_moe_layer) / 8))
             reinterpret_cast<unsigned long long *>(&S.ly)[tid] = reinterpret_cast<const unsigned long long *>(&L[l + 1])[tid];
+        if (pf && l + 2 < a.n_layers && tid >= 32 && tid < 32 + (int) (sizeof(lkb_moe_layer) / 8))
+            reinterpret_cast<unsigned long long *>(&S.ly_next)[tid - 32] = reinterpret_cast<const unsigned long long *>(&L[l + 2])[tid - 32];
         if constexpr (MIX) {
             if (l + 1 < a.n_layers) {
                 if (tid < (int) (sizeof(lkb_mixer_layer) / 8))
@@ -827,11 +965,12 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
 static int g_fused_ready = 0;
 
 int lkb_fused_init() {
-    cudaError_t e = cudaFuncSetAttribute(k_moe_ffn_stack<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int) sizeof(FusedSmem));
-    if (e != cudaSuccess) return -(int) e;
-    e = cudaFuncSetAttribute(k_moe_ffn_stack<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sizeof(FusedSmem));
-    if (e != cudaSuccess) return -(int) e;
+    const void * kernels[4] = {(const void *) k_moe_ffn_stack<false, false>, (const void *) k_moe_ffn_stack<false, true>,
+                               (const void *) k_moe_ffn_stack<true, false>, (const void *) k_moe_ffn_stack<true, true>};
+    for (const void * k : kernels) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sizeof(FusedSmem));
+        if (e != cudaSuccess) return -(int) e;
+    }
     g_fused_ready = 1;
     return LKB_OK;
 }
@@ -855,13 +994,15 @@ static int fused_launch(FusedArgs & a, cudaStream_t st) {
 #endif
     a.absent_cta = g_fused_absent_cta;
     a.spin_limit = g_fused_spin_limit ? g_fused_spin_limit : SPIN_LIMIT;
+    a.prefetch = (g_fused_prefetch >> (a.mixers ? 1 : 0)) & 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid); cfg.blockDim = dim3(FUSED_THREADS); cfg.dynamicSmemBytes = sizeof(FusedSmem); cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeCooperative;
     attr[0].val.cooperative = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    e = a.mixers ? cudaLaunchKernelEx(&cfg, k_moe_ffn_stack<true>, a) : cudaLaunchKernelEx(&cfg, k_moe_ffn_stack<false>, a);
+    if (a.mixers) e = a.prefetch ? cudaLaunchKernelEx(&cfg, k_moe_ffn_stack<true, true>, a) : cudaLaunchKernelEx(&cfg, k_moe_ffn_stack<true, false>, a);
+    else          e = a.prefetch ? cudaLaunchKernelEx(&cfg, k_moe_ffn_stack<false, true>, a) : cudaLaunchKernelEx(&cfg, k_moe_ffn_stack<false, false>, a);
     if (e != cudaSuccess) { (void) cudaGetLastError(); return -(int) e; }
     return LKB_OK;
 }
@@ -878,6 +1019,29 @@ __attribute__((visibility("default"))) int lkb_debug_fused_timing(unsigned long 
 // instead of hanging.  cta = -1 restores normal operation.  Nothing faults, traps or spins without a bound.
 __attribute__((visibility("default"))) int lkb_debug_fused_absent_cta(int cta, unsigned spin_limit) {
     g_fused_absent_cta = cta; g_fused_spin_limit = spin_limit; return LKB_OK;
+}
+
+int lkb_decode_set_expert_prefetch(int mode) {
+    if (mode < 0 || mode > 3) return LKB_ERR_SHAPE;
+    g_fused_prefetch = mode;
+    return LKB_OK;
+}
+
+int lkb_decode_expert_prefetch_hits(const lkb_moe_scratch * scratch, int n_layers, int * hits, int * guesses, lkb_stream_t st) {
+    if (!scratch || !scratch->gu || !hits || !guesses) return LKB_ERR_NULL;
+    if (n_layers < 2) return LKB_ERR_SHAPE;
+    const int nl = n_layers < PF_MAXL ? n_layers : PF_MAXL;
+    static int rec[2][4 * PF_MAXL];
+    cudaError_t e = cudaStreamSynchronize((cudaStream_t) st);
+    if (e == cudaSuccess) e = cudaMemcpy(rec[0], scratch->gu + PF_GUESS_OFF, sizeof(int) * 4 * nl, cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess) e = cudaMemcpy(rec[1], scratch->gu + PF_REAL_OFF, sizeof(int) * 4 * nl, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return -(int) e;
+    int h = 0;
+    for (int l = 1; l < nl; ++l)
+        for (int i = 0; i < 4; ++i)
+            for (int j = 0; j < 4; ++j) h += rec[0][l * 4 + i] == rec[1][l * 4 + j];
+    *hits = h; *guesses = 4 * (nl - 1);
+    return LKB_OK;
 }
 
 int lkb_moe_ffn_decode(const lkb_moe_layer * layer, float * x, int * idx_out, float * w_out,

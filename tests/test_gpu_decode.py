@@ -406,3 +406,42 @@ def test_bounded_wait_reports_status_and_context_survives(L):
     st.step_fused()
     torch.cuda.synchronize()
     assert st.status() == 0 and torch.equal(st.x, good)
+
+
+def test_expert_prefetch_leaves_results_unchanged(L):
+    """lkb_decode_set_expert_prefetch: the guessed experts of the next layer only warm L2.  The residual, the selection
+    and the weights of every layer are those of the kernel sequence bit for bit, the status word stays 0, and the
+    hit counter reports 4 guesses per layer after the first, each guess a valid expert."""
+    import importlib
+    synth = importlib.import_module("lfm2-ampere_b200.synth")
+    decode = importlib.import_module("lfm2-ampere_b200.decode")
+    n_layers = 6
+    layers = synth.make_model(n_layers, seed=17, zipf_s=0.0)
+    st = decode.DecodeStack(layers)
+    gen = torch.Generator("cuda").manual_seed(8)
+    try:
+        for trial in range(3):
+            x0 = torch.randn(2048, device="cuda", generator=gen) * (1.0 + 3 * trial)
+            st.x.copy_(x0); st.step(); ref = st.x.clone()
+            L.decode_set_expert_prefetch(0)
+            st.x.copy_(x0); st.step_fused(); torch.cuda.synchronize()
+            off_x, off_idx, off_w = st.x.clone(), st.sel_idx.clone(), st.sel_w.clone()
+            L.decode_set_expert_prefetch(1)
+            st.x.copy_(x0); st.step_fused(); torch.cuda.synchronize()
+            assert st.status() == 0
+            assert torch.isfinite(ref).all() and torch.equal(off_x, ref) and torch.equal(st.x, ref)
+            assert torch.equal(st.sel_idx, off_idx) and torch.equal(st.sel_w, off_w)
+            hits, guesses = L.decode_expert_prefetch_hits(st._scratch, n_layers)
+            assert guesses == 4 * (n_layers - 1) and 0 <= hits <= guesses
+            rec = st.gu[4 * 1536 + 128:].view(torch.int32)
+            guess, real = rec[:4 * n_layers].view(n_layers, 4), rec[4 * 512:4 * 512 + 4 * n_layers].view(n_layers, 4)
+            assert torch.equal(real, st.sel_idx)
+            assert int(guess[1:].min()) >= 0 and int(guess[1:].max()) < 64
+            for l in range(1, n_layers):
+                assert len(set(guess[l].tolist())) == 4
+        # a single layer has nothing to guess for
+        L.moe_ffn_decode(st._descs[0], st.x, st.sel_idx[0], st.sel_w[0], None, st._scratch)
+        torch.cuda.synchronize()
+        assert st.status() == 0
+    finally:
+        L.decode_set_expert_prefetch(0)

@@ -118,6 +118,14 @@ def test_step_variants_agree_and_advance(M, lkb):
     finally:
         lkb.set_pdl(False)
     assert t == ref_t and all(np.array_equal(a, b) for a, b in zip(x, ref_x))
+    # expert prefetch in the whole-step kernel: same tokens, same residuals
+    lkb.decode_set_expert_prefetch(3)
+    try:
+        for graph in (False, True):
+            t, x, _ = _run(M, model, "mega", graph, steps, pos0)
+            assert t == ref_t and all(np.array_equal(a, b) for a, b in zip(x, ref_x)), graph
+    finally:
+        lkb.decode_set_expert_prefetch(0)
 
 
 def test_new_entry_points_reject_bad_arguments(M, lkb):
