@@ -108,8 +108,8 @@ __device__ __forceinline__ float lkb_quad_sum(float a0, float a1, float a2, floa
 // integer of t IS roundf of the IEEE quotient; only the rare element inside that band (and any NaN) takes the
 // division (one branch for the lane's four).  The nearest integer comes from the 1.5 * 2^23 trick, whose low mantissa
 // byte is q's two's complement.
-__device__ __forceinline__ unsigned lkb_quad_quant(const float4 v, int lane, float2 & sc_out) {
-    (void) lane;
+// lkb_quad_quant_ds hands back the block's (d, raw sum) as the fp16 pair of block_q8_1 instead.
+__device__ __forceinline__ unsigned lkb_quad_quant_ds(const float4 v, __half2 & ds_out) {
     const unsigned m01 = max(__float_as_uint(fabsf(v.x)), __float_as_uint(fabsf(v.y)));
     const unsigned m23 = max(__float_as_uint(fabsf(v.z)), __float_as_uint(fabsf(v.w)));
     unsigned am = max(m01, m23);
@@ -117,8 +117,7 @@ __device__ __forceinline__ unsigned lkb_quad_quant(const float4 v, int lane, flo
     for (int o = 4; o > 0; o >>= 1) am = max(am, __shfl_xor_sync(LKB_FULL, am, o));      // exact, order-free
     const float sum = lkb_quad_sum(v.x, v.y, v.z, v.w);
     const float d = __fdiv_rn(__uint_as_float(am), 127.0f);
-    const __half2 ds = __floats2half2_rn(d, sum);
-    sc_out = make_float2(__low2float(ds), __fmul_rn(8.0f, __high2float(ds)));
+    ds_out = __floats2half2_rn(d, sum);
     float rd;
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rd) : "f"(d));
     const float MAGIC = 12582912.0f;                     // 1.5 * 2^23: adding it rounds to the nearest (even) integer
@@ -140,6 +139,13 @@ __device__ __forceinline__ unsigned lkb_quad_quant(const float4 v, int lane, flo
     }
     return __byte_perm(__byte_perm(__float_as_uint(sft[0]), __float_as_uint(sft[1]), 0x0040),
                        __byte_perm(__float_as_uint(sft[2]), __float_as_uint(sft[3]), 0x0040), 0x5410);
+}
+__device__ __forceinline__ unsigned lkb_quad_quant(const float4 v, int lane, float2 & sc_out) {
+    (void) lane;
+    __half2 ds;
+    const unsigned pk = lkb_quad_quant_ds(v, ds);
+    sc_out = make_float2(__low2float(ds), __fmul_rn(8.0f, __high2float(ds)));
+    return pk;
 }
 
 // Producer of the scale-carrying norm split: quantise RAW u = x*w, emit the

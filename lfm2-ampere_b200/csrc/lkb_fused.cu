@@ -254,32 +254,21 @@ static int g_fused_prefetch = 0;                 // bit 0: MoE stack, bit 1: who
 #endif
 
 
-// Four independent 32-element blocks quantised together: the same operations per block
-// as lkb_quant_lane, with the four dependency chains interleaved so their latencies
-// overlap (the idea of the reference's quantize_q8_1_warp2, ref: src/quant.cuh:83-104).
-template <int N>
-__device__ __forceinline__ void quantN(const float (&v)[N], int (&q)[N], float (&d)[N], float (&sum)[N]) {
-    unsigned am[N];
-#pragma unroll
-    for (int j = 0; j < N; ++j) { am[j] = __reduce_max_sync(LKB_FULL, __float_as_uint(fabsf(v[j]))); sum[j] = v[j]; }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-        for (int j = 0; j < N; ++j) sum[j] = __fadd_rn(sum[j], __shfl_xor_sync(LKB_FULL, sum[j], o));
-#pragma unroll
-    for (int j = 0; j < N; ++j) {
-        d[j] = __fdiv_rn(__uint_as_float(am[j]), 127.0f);
-        q[j] = (am[j] == 0u) ? 0 : (int) roundf(__fdiv_rn(v[j], d[j]));
-    }
+// Thread t holds elements 4t .. 4t+3 of a 2048-vector (one 128-bit access): a 32-element block lives in 8 adjacent
+// lanes, a warp covers four blocks, the 16 warps the 64 blocks.  Quantisation and sums of squares go through
+// lkb_quad_quant_ds / lkb_quad_sum, whose pairings are those of the one-element-per-lane butterfly (same bits), with
+// 6 shuffles per block instead of 10 plus a redux, and a reciprocal with an exact fallback instead of 32 divisions.
+__device__ __forceinline__ void load4(const float * __restrict__ p, float (&o)[4]) {
+    const float4 t = reinterpret_cast<const float4 *>(p)[threadIdx.x];
+    o[0] = t.x; o[1] = t.y; o[2] = t.z; o[3] = t.w;
 }
-__device__ __forceinline__ void quant4(const float (&v)[4], int (&q)[4], float (&d)[4], float (&sum)[4]) { quantN<4>(v, q, d, sum); }
-__device__ __forceinline__ void sumsq4(const float (&x)[4], float (&sq)[4]) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) sq[j] = __fmul_rn(x[j], x[j]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) sq[j] = __fadd_rn(sq[j], __shfl_xor_sync(LKB_FULL, sq[j], o));
+// Q8_1 of the block this lane's group of 8 holds -> S.xq[tid >> 3]
+__device__ __forceinline__ void quad_quant_to_xq(lkb_q8blk * xq, const float (&v)[4]) {
+    const int b = threadIdx.x >> 3, l8 = threadIdx.x & 7;
+    __half2 ds;
+    const unsigned pk = lkb_quad_quant_ds(make_float4(v[0], v[1], v[2], v[3]), ds);
+    reinterpret_cast<unsigned *>(xq[b].qs)[l8] = pk;
+    if (l8 == 0) xq[b].ds = ds;
 }
 
 struct FusedArgs {
@@ -310,28 +299,21 @@ struct FusedArgs {
     float *               part;        // scratch [32][LKB_ATTN_SPLIT][LKB_ATTN_PARTW]
 };
 
-// Blocks b = warp + 16 j (j = 0..3) of the 2048-vector belong to this warp, element `lane`.
-// Loads x (written by other CTAs -> L2) and forms u = x*w into S.h.
+// Loads x (written by other CTAs -> L2), elements 4*tid .. +3, and forms u = x*w into S.h.
 __device__ __forceinline__ void fused_load_u(FusedSmem & S, const float * __restrict__ x, const float (&nw)[4],
                                              float (&xv)[4], float (&uv)[4]) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float4 t = __ldcg(reinterpret_cast<const float4 *>(x) + threadIdx.x);
+    xv[0] = t.x; xv[1] = t.y; xv[2] = t.z; xv[3] = t.w;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) xv[j] = __ldcg(x + (warp + FUSED_WARPS * j) * 32 + lane);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) { uv[j] = __fmul_rn(xv[j], nw[j]); S.h[(warp + FUSED_WARPS * j) * 32 + lane] = uv[j]; }
+    for (int j = 0; j < 4; ++j) uv[j] = __fmul_rn(xv[j], nw[j]);
+    reinterpret_cast<float4 *>(S.h)[threadIdx.x] = make_float4(uv[0], uv[1], uv[2], uv[3]);
 }
 // Q8_1 of u, ssq of x, inv -> S.xq, S.ssq, S.inv (ends with a CTA barrier).
 __device__ __forceinline__ void fused_quant_u(FusedSmem & S, const float (&xv)[4], const float (&uv)[4]) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int q[4]; float d[4], sm[4], sq[4];
-    quant4(uv, q, d, sm);
-    sumsq4(xv, sq);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const int b = warp + FUSED_WARPS * j;
-        S.xq[b].qs[lane] = (int8_t) q[j];
-        if (lane == 0) { S.xq[b].ds = __floats2half2_rn(d[j], sm[j]); S.ssq[b] = sq[j]; }
-    }
+    quad_quant_to_xq(S.xq, uv);
+    const float sq = lkb_quad_sum(__fmul_rn(xv[0], xv[0]), __fmul_rn(xv[1], xv[1]), __fmul_rn(xv[2], xv[2]), __fmul_rn(xv[3], xv[3]));
+    if ((lane & 7) == 0) S.ssq[threadIdx.x >> 3] = sq;
     __syncthreads();
     if (warp == 0) {
         const float inv = lkb_norm_inv(S.ssq, lane, LKB_EPS);
@@ -427,8 +409,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
         bulk_g2s(S.router, L[0].router + (size_t) cta * LKB_HIDDEN, LKB_HIDDEN * 4, &S.mbar_rt);
     }
     float nw[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) nw[j] = L[0].norm_w[(warp + FUSED_WARPS * j) * 32 + lane];
+    load4(L[0].norm_w, nw);
 
     if (tid < (int) (sizeof(lkb_moe_layer) / 8))
         reinterpret_cast<unsigned long long *>(&S.ly)[tid] = reinterpret_cast<const unsigned long long *>(&L[0])[tid];
@@ -449,8 +430,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
                 mbar_expect_tx(&S.mbar_rt, LKB_HIDDEN * 4);
                 bulk_g2s(S.router, L[1].router + (size_t) (cta - LKB_N_EXPERTS) * LKB_HIDDEN, LKB_HIDDEN * 4, &S.mbar_rt);
             }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) pnw[j] = L[1].norm_w[(warp + FUSED_WARPS * j) * 32 + lane];
+            load4(L[1].norm_w, pnw);
         }
     }
     if (tid < LKB_TOP_K) S.pidx[tid] = tid;
@@ -586,19 +566,9 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
             }
             // ---- M3: the mixer's 2048 outputs, written by their owner CTAs, quantised by every CTA; then this CTA's output-projection rows, added to the residual ----
             {
-                float o[4]; int q[4]; float d[4], sm[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int i = (warp + FUSED_WARPS * j) * 32 + lane;
-                    o[j] = __ldcg(a.mxbuf + i);
-                }
-                quant4(o, q, d, sm);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int b = warp + FUSED_WARPS * j;
-                    S.xq[b].qs[lane] = (int8_t) q[j];
-                    if (lane == 0) S.xq[b].ds = __floats2half2_rn(d[j], sm[j]);
-                }
+                const float4 o4 = __ldcg(reinterpret_cast<const float4 *>(a.mxbuf) + tid);
+                const float o[4] = {o4.x, o4.y, o4.z, o4.w};
+                quad_quant_to_xq(S.xq, o);
                 __syncthreads();
                 FUSED_STAMP(22);
                 int xq[2][8]; float d8[2], s8[2];
@@ -641,7 +611,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
                 float acc = 0.0f;
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                    acc = fmaf(S.router[(warp + FUSED_WARPS * j) * 32 + lane], __fmul_rn(xv[j], pnw[j]), acc);
+                    acc = fmaf(S.router[tid * 4 + j], __fmul_rn(xv[j], pnw[j]), acc);
                 acc = lkb_warp_sum(acc);
                 if (lane == 0) S.ppart[warp] = acc;
             }
@@ -775,7 +745,10 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
             load_xregs<2>(S.xq, GU_BPR, lane, xq, d8, s8);
             const float ninv = S.inv;
             for (int j = warp; j < n_gu; j += FUSED_WARPS) {
-                if (!mbar_wait(&S.mbar_gu[j / CH_ROWS], par) || !mbar_wait(&S.mbar_gu[gu_half_ch + j / CH_ROWS], par)) {
+                // both probes are issued before either answer is used (a probe takes ~0.1 us even when the rows are there)
+                unsigned long long * const mg = &S.mbar_gu[j / CH_ROWS], * const mu = &S.mbar_gu[gu_half_ch + j / CH_ROWS];
+                const bool hg = mbar_try_wait(mg, par), hu = mbar_try_wait(mu, par);
+                if ((!hg && !mbar_wait(mg, par)) || (!hu && !mbar_wait(mu, par))) {
                     if (lane == 0) { atomicCAS(status, 0u, 200u + l); S.abort = 1; }
                     break;
                 }
@@ -800,14 +773,11 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
                 mbar_expect_tx(&S.mbar_rt, LKB_HIDDEN * 4);
                 bulk_g2s(S.router, L[l + 1].router + (size_t) cta * LKB_HIDDEN, LKB_HIDDEN * 4, &S.mbar_rt);
             }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) nw[j] = L[l + 1].norm_w[(warp + FUSED_WARPS * j) * 32 + lane];
+            load4(L[l + 1].norm_w, nw);
             if constexpr (MIX) {
                 // gate|up staging is idle from here to the next layer's selection: the next mixer's input rows
                 if (tid == 32) mix_issue_in(S, a.mixers[l + 1], dn0, n_dn, qa0, qa1);   // not thread 0: it polls the barrier
-                const float * an = a.mixers[l + 1].attn_norm;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) anw[j] = an[(warp + FUSED_WARPS * j) * 32 + lane];
+                load4(a.mixers[l + 1].attn_norm, anw);
             }
         }
         if (pf_next && warp > 0) {
@@ -862,37 +832,39 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
             FUSED_STAMP1(29);
         }
         if (pf_next && pcta && l + 2 < a.n_layers) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) pnw[j] = L[l + 2].norm_w[(warp + FUSED_WARPS * j) * 32 + lane];
+            load4(L[l + 2].norm_w, pnw);
         }
         if (!grid_wait(a.bar, status, S, 1000u + 10u * l + 2u, a.spin_limit)) return;
         FUSED_STAMP(6);
 
         // ---- F: Q8_1 of the 6144 published values (every CTA), down rows, residual --
         {
-            float v[12], d[12], sm[12]; int q[12];                // 6144 values = 192 blocks, 12 per warp
+            // 192 blocks, four per warp step (lane l holds elements 4(l&7).. of block l>>3): three 128-bit loads per
+            // lane; same quants, scale and raw sum as the one-element-per-lane form (lkb_quad_quant)
+            float4 v[3];
 #pragma unroll
-            for (int j = 0; j < 12; ++j) v[j] = __ldcg(a.gu + (warp + FUSED_WARPS * j) * 32 + lane);
+            for (int j = 0; j < 3; ++j) v[j] = __ldcg(reinterpret_cast<const float4 *>(a.gu) + (warp + FUSED_WARPS * j) * 32 + lane);
             FUSED_STAMP(10);
-            quantN<12>(v, q, d, sm);
 #pragma unroll
-            for (int j = 0; j < 12; ++j) {
-                const int b = warp + FUSED_WARPS * j;
-                S.xq2_q[b * 32 + lane] = (int8_t) q[j];
-                if (lane == 0) {
-                    const __half2 ds = __floats2half2_rn(d[j], sm[j]);
-                    S.xq2_s[b] = make_float2(__low2float(ds), __fmul_rn(8.0f, __high2float(ds)));
-                }
+            for (int j = 0; j < 3; ++j) {
+                float2 sc;
+                const unsigned pk = lkb_quad_quant(v[j], lane, sc);
+                const int b = (warp + FUSED_WARPS * j) * 4 + (lane >> 3);
+                reinterpret_cast<unsigned *>(S.xq2_q)[b * 8 + (lane & 7)] = pk;
+                if ((lane & 7) == 0) S.xq2_s[b] = sc;
             }
         }
         __syncthreads();
         FUSED_STAMP(11);
         // one output row per warp, its four expert dots interleaved
         for (int j = warp; j < n_dn; j += FUSED_WARPS) {
-            bool ok = true;
+            bool here[LKB_TOP_K], ok = true;                        // four probes in flight, then the bounded waits if needed
 #pragma unroll
-            for (int k = 0; k < LKB_TOP_K; ++k) ok = ok && mbar_wait(&S.mbar_dn[k * dn_ch_per_k + j / CH_ROWS], par);
+            for (int k = 0; k < LKB_TOP_K; ++k) here[k] = mbar_try_wait(&S.mbar_dn[k * dn_ch_per_k + j / CH_ROWS], par);
+#pragma unroll
+            for (int k = 0; k < LKB_TOP_K; ++k) ok = ok && (here[k] || mbar_wait(&S.mbar_dn[k * dn_ch_per_k + j / CH_ROWS], par));
             if (!ok) { if (lane == 0) { atomicCAS(status, 0u, 300u + l); S.abort = 1; } break; }
+            FUSED_STAMP(15);
             float acc[LKB_TOP_K];
 #pragma unroll
             for (int k = 0; k < LKB_TOP_K; ++k) {
@@ -913,6 +885,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
                 }
                 acc[k] = acc_k;
             }
+            FUSED_STAMP(14);
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
@@ -949,8 +922,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
 
     // optional: the quantised, un-normalised activation of the final x for the caller's next consumer
     if (a.final_norm_w && cta == 0) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) nw[j] = a.final_norm_w[(warp + FUSED_WARPS * j) * 32 + lane];
+        load4(a.final_norm_w, nw);
         float xv[4], uv[4];
         fused_load_u(S, a.x, nw, xv, uv);
         fused_quant_u(S, xv, uv);
