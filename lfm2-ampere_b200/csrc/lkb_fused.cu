@@ -748,7 +748,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
                 // both probes are issued before either answer is used (a probe takes ~0.1 us even when the rows are there)
                 unsigned long long * const mg = &S.mbar_gu[j / CH_ROWS], * const mu = &S.mbar_gu[gu_half_ch + j / CH_ROWS];
                 const bool hg = mbar_try_wait(mg, par), hu = mbar_try_wait(mu, par);
-                if ((!hg && !mbar_wait(mg, par)) || (!hu && !mbar_wait(mu, par))) {
+                if (__any_sync(LKB_FULL, (!hg && !mbar_wait(mg, par)) || (!hu && !mbar_wait(mu, par)))) {
                     if (lane == 0) { atomicCAS(status, 0u, 200u + l); S.abort = 1; }
                     break;
                 }
@@ -863,6 +863,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) k_moe_ffn_stack(const FusedA
             for (int k = 0; k < LKB_TOP_K; ++k) here[k] = mbar_try_wait(&S.mbar_dn[k * dn_ch_per_k + j / CH_ROWS], par);
 #pragma unroll
             for (int k = 0; k < LKB_TOP_K; ++k) ok = ok && (here[k] || mbar_wait(&S.mbar_dn[k * dn_ch_per_k + j / CH_ROWS], par));
+            ok = __all_sync(LKB_FULL, ok);                          // the shuffles below need the whole warp
             if (!ok) { if (lane == 0) { atomicCAS(status, 0u, 300u + l); S.abort = 1; } break; }
             FUSED_STAMP(15);
             float acc[LKB_TOP_K];
