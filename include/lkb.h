@@ -164,7 +164,9 @@ typedef struct {
     const float * norm_w;                           /* [2048] ffn_norm weights */
     int           softmax;                          /* 0: sigmoid+bias gate (the reference's); 1: softmax gate */
 } lkb_moe_layer;
-/* Caller-owned global scratch of the fused kernels: 64 floats (router logits), 2*4*1536 floats (exchange of the
+/* The fused kernels read x, the norm weights (ffn_norm, attn_norm, the optional final norm) and the scratch vectors 128
+ * bits at a time: those pointers must be 16-byte aligned (LKB_ERR_SHAPE where the launcher can see them).
+ * Caller-owned global scratch of the fused kernels: 64 floats (router logits), 2*4*1536 floats (exchange of the
  * intermediate activations; the current kernels use the first 4*1536) and
  * two 32-bit words (barrier counter, status; status != 0 after the kernel means a
  * bounded wait expired: 1000+10*layer+n = grid barrier n, 100/200/300+layer = a copy). */

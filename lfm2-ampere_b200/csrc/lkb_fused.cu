@@ -953,6 +953,10 @@ static int fused_launch(FusedArgs & a, cudaStream_t st) {
     if (!a.x || !a.logits || !a.gu || !a.bar) return LKB_ERR_NULL;
     if (a.n_layers <= 0) return LKB_ERR_SHAPE;
     if (a.final_norm_w && (!a.out_yq8 || !a.out_ssq)) return LKB_ERR_NULL;
+    // the residual, the norm weights and the scratch vectors are read 128 bits at a time
+    auto misaligned = [](const void * p) { return (reinterpret_cast<unsigned long long>(p) & 15ull) != 0; };
+    if (misaligned(a.x) || misaligned(a.gu) || misaligned(a.final_norm_w) || misaligned(a.mxbuf) ||
+        (!a.layers && misaligned(a.one.norm_w))) return LKB_ERR_SHAPE;
     int grid = lkb_context().sm_count;
     // every CTA's share must fit the shared-memory staging
     const int pairs = (LKB_TOP_K * LKB_MOE_INTER + grid - 1) / grid;          // gate rows, then (chunk-aligned) as many up rows
